@@ -1,0 +1,57 @@
+// Shared helpers of the CUDA sources: element types, loads/stores in float, status reporting.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "hfb200.h"
+
+namespace hfb {
+
+// Records the message `hfb_last_error()` returns; returns `code` so callers can `return fail(...)`.
+int fail(int code, const char *fmt, ...);
+
+inline int check_launch(const char *what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(HFB_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+    return HFB_OK;
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Load element i of an array whose element type is only known at run time (HFB_F32 / HFB_BF16).
+__device__ __forceinline__ float load_any(const void *p, int dt, size_t i)
+{
+    return dt == HFB_F32 ? ((const float *)p)[i] : __bfloat162float(((const __nv_bfloat16 *)p)[i]);
+}
+
+__device__ __forceinline__ void store_any(void *p, int dt, size_t i, float v)
+{
+    if (dt == HFB_F32) ((float *)p)[i] = v;
+    else ((__nv_bfloat16 *)p)[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+inline bool valid_dt(int dt) { return dt == HFB_F32 || dt == HFB_BF16; }
+
+}  // namespace hfb

@@ -1,0 +1,181 @@
+// Embedding gather, RMSNorm, rotary + cache write, SwiGLU, arg-max: the memory-bound steps.
+#include "common.cuh"
+
+namespace hfb {
+int *error_word();
+
+// ---- embedding (src/model.c:566-571) ---------------------------------------------------------
+__global__ void embed_kernel(const int32_t *ids, const void *table, int dt, float *out, int V, int E, int *err)
+{
+    int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicOr(err, HFB_ERR_TOKEN_ID);
+        for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)t * E + i] = 0.f;
+        return;
+    }
+    size_t base = (size_t)id * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)t * E + i] = load_any(table, dt, base + i);
+}
+
+// ---- RMSNorm (src/mathx.c:65-75): products and sum in float32 ---------------------------------
+__global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
+                               const int32_t *rows, int E)
+{
+    int m = blockIdx.x;
+    const float *xr = x + (size_t)(rows ? rows[m] : m) * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+    __shared__ float part[32];
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float v = lane < nw ? part[lane] : 0.f;
+        v = warp_sum(v);
+        if (lane == 0) part[0] = v;
+    }
+    __syncthreads();
+    float r = 1.0f / sqrtf(part[0] / (float)E + eps);
+    for (int i = threadIdx.x; i < E; i += blockDim.x)
+        store_any(out, out_dt, (size_t)m * E + i, (xr[i] * r) * load_any(w, w_dt, i));
+}
+
+// ---- rotary + cache write (src/model.c:587-601, :468-493) -------------------------------------
+// One block per (token, head of the fused q|k|v row).  Pairs (i, i + n_rot/2) rotate; the rest copies.
+template <typename T>
+__global__ void rope_kv_write_kernel(const T *qkv, const float *cos_sin, int n_rot, int n_positions,
+                                     const int32_t *positions, const int32_t *slots, T *q_out, T *k_cache,
+                                     T *v_cache, long long cache_slots, int H, int G, int d, int *err)
+{
+    int t = blockIdx.x, head = blockIdx.y;
+    const T *src = qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d;
+    T *dst;
+    bool rotate;
+    if (head < H) {
+        dst = q_out + (size_t)t * H * d + (size_t)head * d;
+        rotate = true;
+    } else {
+        if (!slots) return;
+        long long slot = slots[t];
+        if (slot < 0) return;
+        if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        if (head < H + G) { dst = k_cache + ((size_t)slot * G + (head - H)) * d; rotate = true; }
+        else { dst = v_cache + ((size_t)slot * G + (head - H - G)) * d; rotate = false; }
+    }
+    int half = n_rot / 2;
+    if (rotate && half > 0) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= n_positions) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+        const float *cs = cos_sin + (size_t)pos * half * 2;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float c = cs[2 * i], s = cs[2 * i + 1];
+            float a = to_f32(src[i]), b = to_f32(src[i + half]);
+            dst[i] = from_f32<T>(a * c - b * s);
+            dst[i + half] = from_f32<T>(a * s + b * c);
+        }
+        for (int i = n_rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// ---- SwiGLU (src/model.c:532-538, src/mathx.c:34) ----------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    size_t t = i / F;
+    int f = (int)(i % F);
+    float g = to_f32(gu[t * 2 * F + f]), u = to_f32(gu[t * 2 * F + F + f]);
+    out[i] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+}
+
+// ---- arg-max, the lowest index wins ties (src/sample.c:72-77) ---------------------------------
+__global__ void argmax_kernel(const float *logits, int32_t *out, int V)
+{
+    const float *row = logits + (size_t)blockIdx.x * V;
+    float best = 0.f;
+    int bi = -1;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        float v = row[i];
+        if (bi < 0 || v > best) { best = v; bi = i; }
+    }
+    __shared__ float sv[1024];
+    __shared__ int si[1024];
+    sv[threadIdx.x] = best; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+            float v2 = sv[threadIdx.x + o], v1 = sv[threadIdx.x];
+            int i2 = si[threadIdx.x + o], i1 = si[threadIdx.x];
+            if (i2 >= 0 && (i1 < 0 || v2 > v1 || (v2 == v1 && i2 < i1))) { sv[threadIdx.x] = v2; si[threadIdx.x] = i2; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = si[0] < 0 ? 0 : si[0];
+}
+
+}  // namespace hfb
+
+using namespace hfb;
+
+extern "C" int hfb_embed(const int32_t *ids, const void *table, int table_dt, float *out, int T, int V, int E, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(table_dt) || V <= 0 || E <= 0) return fail(HFB_EINVAL, "embed: bad arguments");
+    embed_kernel<<<T, 256, 0, (cudaStream_t)s>>>(ids, table, table_dt, out, V, E, error_word());
+    return check_launch("embed");
+}
+
+extern "C" int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
+                           const int32_t *rows, int M, int E, hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (!valid_dt(w_dt) || !valid_dt(out_dt) || E <= 0) return fail(HFB_EINVAL, "rmsnorm: bad arguments");
+    int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
+    rmsnorm_kernel<<<M, threads, 0, (cudaStream_t)s>>>(x, w, w_dt, eps, out, out_dt, rows, E);
+    return check_launch("rmsnorm");
+}
+
+extern "C" int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, int n_rot, int n_positions,
+                                 const int32_t *positions, const int32_t *slots, void *q_out, void *k_cache,
+                                 void *v_cache, int64_t cache_slots, int T, int H, int G, int d, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(dt) || H <= 0 || G <= 0 || d <= 0 || n_rot < 0 || n_rot > d || (n_rot & 1))
+        return fail(HFB_EINVAL, "rope_kv_write: bad arguments (H=%d G=%d d=%d n_rot=%d)", H, G, d, n_rot);
+    if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "rope_kv_write: rotation needs a table and positions");
+    if (H + 2 * G > 65535) return fail(HFB_ENOTSUP, "rope_kv_write: %d heads exceed the grid limit", H + 2 * G);
+    dim3 grid(T, H + 2 * G);
+    int threads = d >= 128 ? 64 : 32;
+    if (dt == HFB_F32)
+        rope_kv_write_kernel<float><<<grid, threads, 0, (cudaStream_t)s>>>((const float *)qkv, cos_sin, n_rot, n_positions,
+            positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, cache_slots, H, G, d, error_word());
+    else
+        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)qkv, cos_sin, n_rot,
+            n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache,
+            cache_slots, H, G, d, error_word());
+    return check_launch("rope_kv_write");
+}
+
+extern "C" int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(dt) || F <= 0) return fail(HFB_EINVAL, "swiglu: bad arguments");
+    size_t total = (size_t)T * F;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dt == HFB_F32) swiglu_kernel<float><<<blocks, 256, 0, (cudaStream_t)s>>>((const float *)gu, (float *)out, F, total);
+    else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, F, total);
+    return check_launch("swiglu");
+}
+
+extern "C" int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (V <= 0) return fail(HFB_EINVAL, "argmax: empty vocabulary");
+    argmax_kernel<<<M, 1024, 0, (cudaStream_t)s>>>(logits, out, V);
+    return check_launch("argmax");
+}

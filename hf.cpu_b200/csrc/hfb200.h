@@ -1,0 +1,68 @@
+/* hfb200.h - C entry points of the CUDA library (sm_100a).
+ *
+ * Every function takes device pointers, sizes and the CUDA stream to launch on, returns HFB_OK or
+ * an error code, and allocates nothing unless its comment says so.  `hfb_last_error()` gives the
+ * message of the last failure on the calling thread.  Element types are passed as HFB_F32 /
+ * HFB_BF16 codes.  Matrices are row-major with the inner dimension contiguous: activations
+ * [rows, features], weights [out, in] (the reference's layout, src/model.h:14-21).
+ */
+#ifndef HFB200_H
+#define HFB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { HFB_F32 = 0, HFB_BF16 = 1 };
+
+/* status codes, named after the reference's (src/hfc.h:12-22) */
+enum { HFB_OK = 0, HFB_EINVAL = 1, HFB_ENOTSUP = 2, HFB_ECUDA = 3, HFB_ERANGE = 4, HFB_EIO = 5 };
+
+typedef void *hfb_stream;     /* a cudaStream_t */
+
+const char *hfb_last_error(void);
+int hfb_version(void);
+
+/* x[t, :] = table[ids[t], :] as float32.  ids outside [0, V) raise the device error word. */
+int hfb_embed(const int32_t *ids, const void *table, int table_dt, float *out, int T, int V, int E, hfb_stream s);
+
+/* out[m, :] = x[rows ? rows[m] : m, :] * rsqrt(mean(x^2) + eps) * w, sums in float32. */
+int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
+                const int32_t *rows, int M, int E, hfb_stream s);
+
+/* out[M,N] (=|+=) a[M,K] . w[N,K]^T (+ bias[N]); plain float32-accumulating kernel for any sizes and
+ * any mix of element types.  accumulate != 0 requires a float32 `out`. */
+int hfb_linear_plain(const void *a, int a_dt, const void *w, int w_dt, const void *bias, int bias_dt,
+                     void *out, int out_dt, int accumulate, int M, int N, int K, hfb_stream s);
+
+/* Splits qkv[T, (H+2G)*d] into rotated queries q_out[T, H*d], rotated keys and plain values written
+ * to the paged cache at slots[t] (page * block_size + offset; < 0 or slots == NULL: not written).
+ * cos_sin is float32 [positions, n_rot/2, 2]; n_rot == 0 means no rotation. */
+int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, int n_rot, int n_positions,
+                      const int32_t *positions, const int32_t *slots, void *q_out, void *k_cache, void *v_cache,
+                      int64_t cache_slots, int T, int H, int G, int d, hfb_stream s);
+
+/* Attention of every token over its request's cached keys lo..pos (lo = max(0, pos - window + 1) when
+ * window > 0, else 0), plain kernel: one block per (token, head), float32 softmax. */
+int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache, int dt,
+                        const int32_t *block_table, int max_blocks, const int32_t *token_seq,
+                        const int32_t *positions, int block_size, int64_t num_pages, int window, float scale,
+                        void *out, int T, int H, int G, int d, hfb_stream s);
+
+/* out[t, f] = silu(gu[t, f]) * gu[t, F + f] */
+int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, hfb_stream s);
+
+/* out[m] = index of the first maximum of logits[m, :] */
+int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s);
+
+/* Device error word: kernels set bits instead of touching memory out of range.  Reading syncs the stream. */
+enum { HFB_ERR_TOKEN_ID = 1, HFB_ERR_PAGE = 2, HFB_ERR_SLOT = 4, HFB_ERR_WAIT = 8, HFB_ERR_POSITION = 16 };
+int hfb_error_word_take(int32_t *word, hfb_stream s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,260 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step takes any mix of prompt portions and single decoded tokens, cut anywhere, runs only the
+tokens it is given as one flat batch, and returns float32 logits at the wanted places.  The
+reference's forward takes either one sequence of n consecutive tokens or n sequences of one
+token, never both (src/model.c:542-545), reserves cache blocks before any compute
+(src/model.c:555-564) and advances the position only after the layers ran (src/model.c:626-627);
+the same order holds here: reserve, run, advance.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache import KVCacheManager, OutOfPages, StateSlots
+from ..models import Model
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them whose logits are wanted."""
+    req: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class GroupMeta:
+    """What kernels need to find one cache group's pages for this step's tokens."""
+    __slots__ = ("group", "slots", "block_table", "block_size", "max_blocks")
+
+    def __init__(self, group, slots, block_table, block_size, max_blocks):
+        self.group, self.slots, self.block_table = group, slots, block_table
+        self.block_size, self.max_blocks = block_size, max_blocks
+
+
+class Workspace:
+    """Named scratch buffers that live across steps (a buffer grows when a larger one is asked for)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[tuple, torch.Tensor] = {}
+
+    def get(self, name, shape, dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        b = self._bufs.get(key)
+        if b is None or b.numel() < n:
+            b = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = b
+        return b[:n].view(*shape)
+
+
+class StepContext:
+    """Per-step batch description handed to every part."""
+
+    def __init__(self, engine: "Engine"):
+        self.engine = engine
+        self.run_dtype = engine.model.run_dtype
+        self.device = engine.device
+        self.num_tokens = self.num_seqs = self.num_logit_rows = 0
+        self.max_q_len = self.max_kv_len = 0
+        self.token_ids = self.positions = self.token_seq = None
+        self.cu_tokens = self.kv_lens = self.seq_slots = self.logit_rows = None
+        self.h_cu_tokens: List[int] = []
+        self.h_kv_lens: List[int] = []
+        self.h_seq_slots: List[int] = []
+        self._groups: List[GroupMeta] = []
+
+    def buf(self, name, shape, dtype) -> torch.Tensor:
+        return self.engine.workspace.get(name, shape, dtype)
+
+    def group_meta(self, group: int) -> GroupMeta:
+        return self._groups[group]
+
+    def entry_cache(self, entry: int):
+        return self.engine.cache.entry_cache(entry)
+
+    def entry_state(self, entry: int):
+        return self.engine.slots.entry_state(entry)
+
+
+class Engine:
+    """Model + cache + slots + the step function.
+
+    ``num_pages`` pages of ``block_size`` tokens are made for every cache group.  ``ctx_max`` bounds
+    one request's length; ``max_requests`` bounds how many are live at once.
+    """
+
+    def __init__(self, model: Model, *, block_size: int = 16, num_pages: int = 0, max_tokens: int = 0,
+                 max_requests: int = 64, ctx_max: int = 0):
+        if not model.bound:
+            raise ValueError("the model has no weights bound")
+        self.model, self.device = model, model.device
+        plan = model.plan
+        self.ctx_max = int(ctx_max) if ctx_max else plan.max_positions
+        if self.ctx_max > plan.max_positions:
+            raise ValueError(f"ctx_max {self.ctx_max} exceeds the model's {plan.max_positions} positions")
+        if not num_pages:
+            if not max_tokens:
+                raise ValueError("give num_pages or max_tokens")
+            num_pages = (int(max_tokens) + block_size - 1) // block_size
+        self.block_size, self.num_pages, self.max_requests = int(block_size), int(num_pages), int(max_requests)
+        self.max_blocks = (self.ctx_max + block_size - 1) // block_size
+        cache_specs, state_specs = {}, {}
+        for i, e in enumerate(plan.schedule):
+            mixer = model.layers[e.layer].mixer
+            if e.cache_of is None and mixer.cache_spec() is not None:
+                cache_specs[i] = mixer.cache_spec()
+            if mixer.state_spec() is not None:
+                state_specs[i] = mixer.state_spec()
+        for i, e in enumerate(plan.schedule):
+            if e.cache_of is not None and e.cache_of not in cache_specs:
+                raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which keeps none")
+        self.cache = KVCacheManager(cache_specs, self.block_size, self.num_pages, model.run_dtype,
+                                    self.device, self.max_blocks)
+        self.slots = StateSlots(state_specs, self.max_requests, self.device)
+        self.workspace = Workspace(self.device)
+        self._pinned = self.device.type == "cuda"
+        self._meta_ring = []            # [host buffer, device buffer, event of its last copy]
+        self._meta_next = 0
+        self.steps_run = 0
+
+    # ---- requests -----------------------------------------------------------------------------
+    def add_request(self, req: Hashable) -> int:
+        slot = self.slots.acquire(req)
+        self.cache.add(req)
+        return slot
+
+    def finish_request(self, req: Hashable) -> None:
+        self.cache.release(req)
+        self.slots.release(req)
+
+    def has_request(self, req) -> bool:
+        return req in self.slots.slot_of
+
+    def length(self, req) -> int:
+        return self.cache.length(req)
+
+    def live_requests(self):
+        return list(self.slots.slot_of)
+
+    # ---- the step -----------------------------------------------------------------------------
+    def _meta_buffers(self, n: int):
+        """A pinned host buffer and its device twin from a small ring: a host buffer is rewritten only
+        after the copy that last read it has finished, and the device twin only after the steps that
+        read it were queued behind it on the same stream."""
+        if len(self._meta_ring) < 4:
+            self._meta_ring.append([None, None, None])
+        slot = self._meta_ring[self._meta_next % len(self._meta_ring)]
+        self._meta_next += 1
+        if slot[2] is not None:
+            slot[2].synchronize()
+        if slot[0] is None or slot[0].numel() < n:
+            cap = max(n, 4096) * 2
+            slot[0] = torch.empty(cap, dtype=torch.int32, pin_memory=self._pinned)
+            slot[1] = torch.empty(cap, dtype=torch.int32, device=self.device)
+        return slot
+
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Check the entries, reserve their pages (all or nothing) and build the step's batch arrays."""
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        V = self.model.plan.vocab_size
+        seen = set()
+        for e in entries:
+            if e.req in seen:
+                raise ValueError(f"request {e.req!r} appears twice in one step")
+            seen.add(e.req)
+            if not self.has_request(e.req):
+                raise KeyError(f"request {e.req!r} is not live")
+            if len(e.tokens) < 1:
+                raise ValueError(f"request {e.req!r} brings no tokens")
+            for t in e.tokens:
+                if not 0 <= int(t) < V:
+                    raise ValueError(f"token id {t} of request {e.req!r} is outside the vocabulary of {V}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise ValueError(f"request {e.req!r} wants logits at place {w} of {len(e.tokens)} tokens")
+            if self.cache.length(e.req) + len(e.tokens) > self.ctx_max:
+                raise OutOfPages(f"request {e.req!r} would exceed the context limit of {self.ctx_max} tokens")
+        wants = [(e.req, self.cache.length(e.req) + len(e.tokens)) for e in entries]
+        if not self.cache.can_reserve(wants):
+            raise OutOfPages(f"the step needs more pages than are free {self.cache.free_pages()}")
+        for req, new_len in wants:
+            self.cache.reserve(req, new_len)
+
+        ctx = StepContext(self)
+        S = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        M = sum(len(e.want) for e in entries)
+        groups = self.cache.groups
+        bs = self.block_size
+        # one flat int32 buffer: a single host-to-device copy per step
+        kv_lens = [w[1] for w in wants]
+        max_blocks_used = max((n + bs - 1) // bs for n in kv_lens)
+        MB = max(1, max_blocks_used)
+        total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB)
+        ring_slot = self._meta_buffers(total)
+        h, d = ring_slot[0], ring_slot[1]
+        hl: List[int] = []
+        tok, pos, seq, cu, rows = [], [], [], [0], []
+        for s, e in enumerate(entries):
+            start = self.cache.length(e.req)
+            n = len(e.tokens)
+            tok += [int(t) for t in e.tokens]
+            pos += range(start, start + n)
+            seq += [s] * n
+            rows += [cu[-1] + int(w) for w in e.want]
+            cu.append(cu[-1] + n)
+        seq_slots = [self.slots.slot_of[e.req] for e in entries]
+        hl += tok + pos + seq + cu + kv_lens + seq_slots + rows
+        for g in groups:
+            slots_g, table_g = [], []
+            for s, e in enumerate(entries):
+                t = g.tables[e.req]
+                start = self.cache.length(e.req)
+                for p in range(start, start + len(e.tokens)):
+                    slots_g.append(t[p // bs] * bs + p % bs)
+                row = t[:MB] + [-1] * (MB - len(t[:MB]))
+                table_g += row
+            hl += slots_g + table_g
+        assert len(hl) == total
+        h[:total] = torch.tensor(hl, dtype=torch.int32)
+        d[:total].copy_(h[:total], non_blocking=True)
+        if self._pinned:
+            ring_slot[2] = torch.cuda.Event()
+            ring_slot[2].record()
+        o = 0
+
+        def take(n, shape=None):
+            nonlocal o
+            v = d[o:o + n]
+            o += n
+            return v if shape is None else v.view(*shape)
+
+        ctx.token_ids, ctx.positions, ctx.token_seq = take(T), take(T), take(T)
+        ctx.cu_tokens, ctx.kv_lens, ctx.seq_slots, ctx.logit_rows = take(S + 1), take(S), take(S), take(M)
+        for g in groups:
+            ctx._groups.append(GroupMeta(g.index, take(T), take(S * MB, (S, MB)), bs, MB))
+        ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, M
+        ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots
+        ctx.max_q_len = max(len(e.tokens) for e in entries)
+        ctx.max_kv_len = max(kv_lens)
+        return ctx
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one step; returns float32 logits ``[wanted, vocab]`` (device), in the order of the entries and
+        of their ``want`` lists, or None when nothing is wanted.  The returned tensor is scratch that the
+        next step overwrites."""
+        entries = list(entries)
+        ctx = self.prepare(entries)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.cache.advance(e.req, self.cache.length(e.req) + len(e.tokens))
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,104 @@
+"""The kernel interface the parts call.  One backend exists in the product: the CUDA library.
+
+The functions here check shapes and types, refuse sizes the kernels do not take with a clear
+error, and forward to the backend.  There is no CPU path: without the library or without a GPU
+the first call raises.  (Tests may install a stand-in backend with :func:`set_backend` to exercise
+the host-side logic on a machine without a GPU.)
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..config.base import UnsupportedError
+
+_backend = None
+
+MAX_HEAD_DIM = 256
+ERROR_BITS = {1: "a token id outside the vocabulary", 2: "a block-table entry that names no page",
+              4: "a cache slot outside the pool", 8: "a device-side wait that ran out",
+              16: "a position outside the rotary table"}
+
+
+def backend():
+    global _backend
+    if _backend is None:
+        from .native import NativeBackend
+        _backend = NativeBackend()
+    return _backend
+
+
+def set_backend(b) -> None:
+    global _backend
+    _backend = b
+
+
+def check_head_dim(d: int) -> None:
+    if d % 16 or not 16 <= d <= MAX_HEAD_DIM:
+        raise UnsupportedError(f"head_dim {d} is not supported: the attention kernels take multiples of 16 "
+                               f"from 16 to {MAX_HEAD_DIM}")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    _need(ids.dtype == torch.int32 and ids.dim() == 1, "embed: ids must be int32 [T]")
+    _need(out.dtype == torch.float32 and out.shape == (ids.shape[0], table.shape[1]), "embed: out must be float32 [T, E]")
+    backend().embed(ids, table, out)
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    _need(x.dtype == torch.float32 and x.dim() == 2, "rmsnorm: x must be float32 [N, E]")
+    _need(w.shape == (x.shape[1],) and out.shape[1] == x.shape[1], "rmsnorm: width mismatch")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.shape[0] == out.shape[0]), "rmsnorm: rows must be int32 [M]")
+    _need(rows is not None or out.shape[0] == x.shape[0], "rmsnorm: row count mismatch")
+    backend().rmsnorm(x, w, float(eps), out, rows)
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, accumulate: bool) -> None:
+    """out (=|+=) a @ w.T (+ bias); ``accumulate`` adds into a float32 ``out`` (the residual stream)."""
+    _need(a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1], "linear: inner sizes differ")
+    _need(out.shape == (a.shape[0], w.shape[0]), "linear: out must be [M, N]")
+    _need(bias is None or bias.shape == (w.shape[0],), "linear: bias must be [N]")
+    _need(not accumulate or out.dtype == torch.float32, "linear: accumulation needs a float32 output")
+    backend().linear(a, w, bias, out, bool(accumulate))
+
+
+def rope_kv_write(qkv, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d) -> None:
+    _need(qkv.shape[1] == (H + 2 * G) * d and q_out.shape == (qkv.shape[0], H * d), "rope_kv_write: shape mismatch")
+    _need(k_cache.shape[2:] == (G, d) and v_cache.shape == k_cache.shape, "rope_kv_write: cache geometry mismatch")
+    _need(k_cache.dtype == qkv.dtype == q_out.dtype, "rope_kv_write: element types differ")
+    _need(n_rot == 0 or (cos_sin is not None and cos_sin.shape[1:] == (n_rot // 2, 2) and cos_sin.dtype == torch.float32),
+          "rope_kv_write: cos/sin table must be float32 [positions, n_rot/2, 2]")
+    backend().rope_kv_write(qkv, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache, H, G, d)
+
+
+def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out) -> None:
+    check_head_dim(d)
+    _need(q.shape[1] == H * d and out.shape == q.shape, "attention: shape mismatch")
+    _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype, "attention: element types differ")
+    backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out)
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
+    _need(gu.shape == (out.shape[0], 2 * out.shape[1]) and gu.dtype == out.dtype, "swiglu: shape mismatch")
+    backend().swiglu(gu, out)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need(logits.dtype == torch.float32 and out.dtype == torch.int32 and out.shape == (logits.shape[0],),
+          "argmax: logits float32 [M, V], out int32 [M]")
+    backend().argmax(logits, out)
+
+
+def check_device_errors() -> None:
+    """Raise if any kernel recorded an error since the last check (synchronises the stream)."""
+    b = backend()
+    word = b.error_word() if hasattr(b, "error_word") else 0
+    if word:
+        what = [v for k, v in ERROR_BITS.items() if word & k]
+        raise RuntimeError("a kernel met " + "; ".join(what))

@@ -1,0 +1,116 @@
+"""ctypes binding of the CUDA library: the only kernel backend of the product.
+
+Every method takes torch tensors on the GPU, checks what the C entry point cannot (devices,
+contiguity), passes raw pointers and the current torch stream, and raises on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from . import build as _build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+F32, BF16 = 0, 1
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _p(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+class NativeBackend:
+    name = "native"
+
+    def __init__(self):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is visible: this engine has no CPU path")
+        path = _build.build()
+        try:
+            self.lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"the CUDA library {path} could not be loaded: {e}") from None
+        self.lib.hfb_last_error.restype = ctypes.c_char_p
+        self.path = path
+
+    def _stream(self):
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _check(self, rc: int, what: str):
+        if rc != 0:
+            raise KernelError(f"{what}: {self.lib.hfb_last_error().decode()} (status {rc})")
+
+    @staticmethod
+    def _on_gpu(*ts):
+        for t in ts:
+            if t is not None and (not t.is_cuda or not t.is_contiguous()):
+                raise KernelError("kernel arguments must be contiguous CUDA tensors")
+
+    # ---- entry points -------------------------------------------------------------------------
+    def embed(self, ids, table, out):
+        self._on_gpu(ids, table, out)
+        T, (V, E) = ids.shape[0], table.shape
+        self._check(self.lib.hfb_embed(_p(ids), _p(table), c_int(_dt(table)), _p(out), c_int(T), c_int(V), c_int(E),
+                                       self._stream()), "embed")
+
+    def rmsnorm(self, x, w, eps, out, rows):
+        self._on_gpu(x, w, out, rows)
+        M, E = out.shape
+        self._check(self.lib.hfb_rmsnorm(_p(x), _p(w), c_int(_dt(w)), c_float(eps), _p(out), c_int(_dt(out)), _p(rows),
+                                         c_int(M), c_int(E), self._stream()), "rmsnorm")
+
+    def linear(self, a, w, bias, out, accumulate):
+        self._on_gpu(a, w, bias, out)
+        M, K = a.shape
+        N = w.shape[0]
+        self._check(self.lib.hfb_linear_plain(_p(a), c_int(_dt(a)), _p(w), c_int(_dt(w)), _p(bias),
+                                              c_int(_dt(bias) if bias is not None else 0), _p(out), c_int(_dt(out)),
+                                              c_int(1 if accumulate else 0), c_int(M), c_int(N), c_int(K),
+                                              self._stream()), "linear")
+
+    def rope_kv_write(self, qkv, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
+        self._on_gpu(qkv, cos_sin, positions, slots, q_out, k_cache, v_cache)
+        T = qkv.shape[0]
+        cache_slots = k_cache.shape[0] * k_cache.shape[1]
+        npos = cos_sin.shape[0] if cos_sin is not None else 0
+        self._check(self.lib.hfb_rope_kv_write(_p(qkv), c_int(_dt(qkv)), _p(cos_sin), c_int(n_rot), c_int(npos),
+                                               _p(positions), _p(slots), _p(q_out), _p(k_cache), _p(v_cache),
+                                               c_int64(cache_slots), c_int(T), c_int(H), c_int(G), c_int(d),
+                                               self._stream()), "rope_kv_write")
+
+    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out):
+        self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out)
+        T = q.shape[0]
+        self._check(self.lib.hfb_attention_plain(_p(q), _p(k_cache), _p(v_cache), c_int(_dt(q)), _p(meta.block_table),
+                                                 c_int(meta.max_blocks), _p(ctx.token_seq), _p(ctx.positions),
+                                                 c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window),
+                                                 c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d),
+                                                 self._stream()), "attention")
+
+    def swiglu(self, gu, out):
+        self._on_gpu(gu, out)
+        T, F = out.shape
+        self._check(self.lib.hfb_swiglu(_p(gu), _p(out), c_int(_dt(gu)), c_int(T), c_int(F), self._stream()), "swiglu")
+
+    def argmax(self, logits, out):
+        self._on_gpu(logits, out)
+        M, V = logits.shape
+        self._check(self.lib.hfb_argmax(_p(logits), _p(out), c_int(M), c_int(V), self._stream()), "argmax")
+
+    def error_word(self) -> int:
+        w = ctypes.c_int32(0)
+        self._check(self.lib.hfb_error_word_take(ctypes.byref(w), self._stream()), "error word")
+        return w.value

@@ -1,0 +1,97 @@
+"""Grouped-query attention over the paged cache.
+
+Per token: ``q, k, v = xn W{q,k,v}^T + b``; rotary on q and k; k (after rotation) and v go into
+the cache at the token's slot; head h attends with the key/value head ``h // (H/G)`` over keys
+``0 .. pos`` (or the last ``window`` of them), scores scaled by ``1/sqrt(head_dim)`` after the
+dot, softmax, weighted values; ``out = att Wo^T`` is added to the residual
+(src/model.c:581-609, :499-528).  q, k and v are one matrix product over concatenated rows
+(src/model.c:581-585 runs the three jobs in one pass).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import kernels
+from ..config.base import UnsupportedError
+from ..weights.loader import TensorSpec
+from .base import CacheSpec, Mixer, register_part
+
+
+class PagedAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, out_bias: bool, window: int, position, prefix: str,
+                 positions=None, names=None, **_):
+        self.E, self.H, self.G, self.d = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
+        if self.H % self.G:
+            raise UnsupportedError(f"unsupported attention geometry: {self.H} heads over {self.G} key/value heads")
+        kernels.check_head_dim(self.d)
+        self.qkv_bias, self.out_bias, self.window = bool(qkv_bias), bool(out_bias), int(window)
+        self.rotary = (positions or {}).get(position) if position else None
+        if position and self.rotary is None:
+            raise UnsupportedError(f"attention names position encoding '{position}', which the plan does not define")
+        n = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
+        n.update(names or {})
+        self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
+        self.scale = 1.0 / math.sqrt(self.d)
+        self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
+
+    @property
+    def QD(self):
+        return self.H * self.d
+
+    @property
+    def KD(self):
+        return self.G * self.d
+
+    def cache_spec(self):
+        return CacheSpec(self.G, self.d, self.window)
+
+    def tensor_specs(self):
+        s = [TensorSpec(self.names["q"] + ".weight", (self.QD, self.E)),
+             TensorSpec(self.names["k"] + ".weight", (self.KD, self.E)),
+             TensorSpec(self.names["v"] + ".weight", (self.KD, self.E)),
+             TensorSpec(self.names["o"] + ".weight", (self.E, self.QD))]
+        if self.qkv_bias:
+            s += [TensorSpec(self.names[x] + ".bias", (n,)) for x, n in
+                  (("q", self.QD), ("k", self.KD), ("v", self.KD))]
+        if self.out_bias:
+            s.append(TensorSpec(self.names["o"] + ".bias", (self.E,)))
+        return s
+
+    @staticmethod
+    def _cat(ts):
+        if len({t.dtype for t in ts}) > 1:
+            ts = [t.float() for t in ts]
+        return torch.cat(ts, dim=0).contiguous()
+
+    def bind(self, tensors, run_dtype, device):
+        self.w_qkv = self._cat([tensors[self.names[x] + ".weight"] for x in "qkv"])
+        if self.qkv_bias:
+            self.b_qkv = self._cat([tensors[self.names[x] + ".bias"] for x in "qkv"])
+        self.w_o = tensors[self.names["o"] + ".weight"].contiguous()
+        if self.out_bias:
+            self.b_o = tensors[self.names["o"] + ".bias"].contiguous()
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
+                   if w is not None)
+
+    def forward(self, ctx, xn, residual, cache, state, write_cache):
+        T = xn.shape[0]
+        qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
+        kernels.linear(xn, self.w_qkv, self.b_qkv, qkv, accumulate=False)
+        q = ctx.buf("attn_q", (T, self.QD), xn.dtype)
+        meta = ctx.group_meta(cache.group)
+        cos_sin = self.rotary.cos_sin if self.rotary is not None else None
+        n_rot = self.rotary.n_rot if self.rotary is not None else 0
+        kernels.rope_kv_write(qkv, cos_sin, n_rot, ctx.positions, meta.slots if write_cache else None,
+                              q, cache.k, cache.v, self.H, self.G, self.d)
+        att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
+        kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
+                                self.window, self.scale, att)
+        kernels.linear(att, self.w_o, self.b_o, residual, accumulate=True)
+
+
+register_part("mixer", "paged_attention", PagedAttention)

@@ -1,0 +1,111 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+Five categories: ``norm``, ``position``, ``mixer``, ``ffn`` and ``block``.  A part
+is chosen by the ``kind`` of a :class:`PartSpec` and receives every size and
+constant through the spec's arguments; no part knows which model it is in.
+
+The reference runs one fixed layer with ``if`` switches for its variants
+(src/model.c:574-624); the same steps are separate parts here so that a layer
+can pick a different mixer or feed-forward than its neighbour.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config.base import ConfigError, PartSpec
+from ..weights.loader import TensorSpec
+
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head")
+_REGISTRY: Dict[str, Dict[str, Callable[..., "Part"]]] = {c: {} for c in CATEGORIES}
+
+
+def register_part(category: str, kind: str, factory: Callable[..., "Part"]) -> None:
+    """Register ``factory(**spec.args, **context)`` under ``kind`` in ``category``."""
+    if category not in _REGISTRY:
+        raise ConfigError(f"unknown part category '{category}' (known: {', '.join(CATEGORIES)})")
+    _REGISTRY[category][kind] = factory
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _REGISTRY[category].pop(kind, None)
+
+
+def make_part(category: str, spec: PartSpec, **context: Any) -> "Part":
+    try:
+        factory = _REGISTRY[category][spec.kind]
+    except KeyError:
+        raise ConfigError(f"no {category} part of kind '{spec.kind}' is registered "
+                          f"(known: {', '.join(sorted(_REGISTRY[category]))})") from None
+    return factory(**spec.args, **context)
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """What a mixer asks of the paged cache: per token ``2 * num_kv_heads * head_dim`` values
+    (keys then values); ``window`` = 0 keeps every key, else only the most recent ``window``."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size: one tensor of ``shape`` per live request."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    def tensor_specs(self) -> List[TensorSpec]:
+        """The checkpoint tensors this part needs."""
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], run_dtype: torch.dtype, device: torch.device) -> None:
+        """Take ownership of the loaded tensors (and fuse or lay them out for the kernels)."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights a step reads from this part (for roofline accounting)."""
+        return 0
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Normalise rows of the float32 residual ``x`` into ``out`` (run dtype).  With ``rows``
+        (int32 indices) only those rows are read, in that order."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def prepare(self, max_positions: int, device: torch.device) -> None:
+        """Build whatever tables are needed for positions ``0 .. max_positions-1``."""
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, ctx, xn: torch.Tensor, residual: torch.Tensor, cache, state, write_cache: bool) -> None:
+        """Mix ``xn`` ([T, hidden], run dtype) across tokens and add the result into the float32
+        ``residual``.  ``cache`` is the entry's :class:`LayerCache` (or None), ``state`` the entry's
+        per-request state tensor ``[max_requests, *shape]`` (or None); ``write_cache`` is False when
+        the entry reads another entry's cache."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, ctx, xn: torch.Tensor, residual: torch.Tensor) -> None:
+        """Token-wise transform of ``xn`` added into the float32 ``residual``."""
+        raise NotImplementedError
+
+
+class Block(Part):
+    def forward(self, ctx, x: torch.Tensor, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward,
+                cache, state, write_cache: bool) -> None:
+        """Run one layer on the float32 residual stream ``x`` in place."""
+        raise NotImplementedError

@@ -1,0 +1,45 @@
+"""Dense SwiGLU feed-forward: ``h = silu(x Wg^T) * (x Wu^T)``; ``out = h Wd^T`` added to the
+residual; no biases (src/model.c:612-623, src/mathx.c:34).  Gate and up are one matrix product
+over the concatenated rows, as the reference serves both with one pass over the activations
+(src/model.c:612-615)."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_part
+
+
+class SwiGlu(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, names=None, **_):
+        self.E, self.F = int(hidden_size), int(intermediate_size)
+        n = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        n.update(names or {})
+        self.names = {k: f"{prefix}.{v}" for k, v in n.items()}
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.names["gate"], (self.F, self.E)), TensorSpec(self.names["up"], (self.F, self.E)),
+                TensorSpec(self.names["down"], (self.E, self.F))]
+
+    def bind(self, tensors, run_dtype, device):
+        g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_down = tensors[self.names["down"]].contiguous()
+
+    def weight_bytes(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
+
+    def forward(self, ctx, xn, residual):
+        T = xn.shape[0]
+        gu = ctx.buf("ffn_gate_up", (T, 2 * self.F), xn.dtype)
+        kernels.linear(xn, self.w_gate_up, None, gu, accumulate=False)
+        h = ctx.buf("ffn_h", (T, self.F), xn.dtype)
+        kernels.swiglu(gu, h)
+        kernels.linear(h, self.w_down, None, residual, accumulate=True)
+
+
+register_part("ffn", "swiglu", SwiGlu)
