@@ -27,17 +27,55 @@ TINY = {"A": TINY_A, "B": TINY_B}
 BLOCK = {"A": 16, "B": 8}
 
 
+def make_folder(cfg_dict, folder, seed, dtype, sharp=4.0, std=0.05):
+    """Write a model folder with random weights whose attention is far from uniform: the query and key
+    projections are scaled up so that single scores stand out and a wrong or missing key shows."""
+    from hfcpu_b200.config import config_from_dict
+    from hfcpu_b200.models import build_model_specs
+    from hfcpu_b200.weights import random_tensors, write_safetensors, weights_path
+    cfg = config_from_dict(cfg_dict)
+    cfg.save(folder)
+    tensors = random_tensors(build_model_specs(cfg), seed, torch.float32, std=std)
+    for name in tensors:
+        if ".q_proj." in name or ".k_proj." in name:
+            tensors[name] = tensors[name] * sharp
+    write_safetensors(weights_path(folder), {k: v.to(dtype) for k, v in tensors.items()})
+    return folder
+
+
 @pytest.fixture(scope="session")
 def tiny_folders(tmp_path_factory):
-    """Model folders (config.json + model.safetensors, float32 random weights) for both tiny configurations."""
-    import hfcpu_b200
-    from hfcpu_b200.config import config_from_dict
+    """Model folders for both tiny configurations, stored in float32 ("A", "B") and bfloat16 ("A16", "B16")."""
     out = {}
-    for name, d in TINY.items():
-        folder = str(tmp_path_factory.mktemp(f"tiny_{name}"))
-        hfcpu_b200.write_random_model(config_from_dict(d), folder, seed=11 + len(out), dtype=torch.float32)
-        out[name] = folder
+    for i, (name, d) in enumerate(TINY.items()):
+        out[name] = make_folder(d, str(tmp_path_factory.mktemp(f"tiny_{name}")), 11 + i, torch.float32)
+        # bfloat16 storage: smaller weights, so that rounding of sharp scores does not swamp the comparison
+        out[name + "16"] = make_folder(d, str(tmp_path_factory.mktemp(f"tiny_{name}16")), 11 + i, torch.bfloat16,
+                                       std=0.02)
     return out
+
+
+_PLAIN_CACHE = {}
+
+
+def plain_logits(folder, ids):
+    """Logits of the plain implementation (float64) for every position of ``ids``, cached per (folder, ids)."""
+    import plain_qwen2 as plain
+    key = (folder, tuple(ids))
+    if key not in _PLAIN_CACHE:
+        cfg, W = plain.read_folder(folder)
+        _PLAIN_CACHE[key] = plain.forward(cfg, W, list(ids))
+    return _PLAIN_CACHE[key]
+
+
+def make_requests(name, lengths, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    V = TINY[name]["vocab_size"]
+    return {f"r{i}": torch.randint(0, V, (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+
+
+# Tolerances: max|a-b| / max|b| per logits row against the float64 plain implementation.
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 
 
 @pytest.fixture

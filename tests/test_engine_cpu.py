@@ -1,84 +1,72 @@
 """Host-side logic of the step function against the plain implementation, on the CPU.
 
 The kernels are replaced by the torch stand-in (tests/emu_backend.py); what is under test is the
-batch building, the block tables, page reuse and the parts' composition.
+batch building, the block tables, page reuse, window release and the parts' composition, under
+every way of cutting the requests into steps.
 """
-import random
-
 import pytest
 import torch
 
-import plain_qwen2 as plain
-from conftest import BLOCK, TINY
+import traces
+from conftest import BLOCK, TOL, make_requests, plain_logits
+
+LENGTHS = {"A": [7, 16, 33, 100, 70], "B": [1, 19, 64, 130, 200]}
 
 
-def _engine(folder, name, max_tokens, dtype=torch.float32):
+def _engine(folder, name, max_tokens, dtype=torch.float32, max_requests=4):
     import hfcpu_b200
     model = hfcpu_b200.load_model(folder, dtype, "cpu")
-    return hfcpu_b200.Engine(model, block_size=BLOCK[name], max_tokens=max_tokens, max_requests=4)
+    return hfcpu_b200.Engine(model, block_size=BLOCK[name], max_tokens=max_tokens, max_requests=max_requests)
 
 
-def _plain_logits(folder, ids):
-    cfg, W = plain.read_folder(folder)
-    return plain.forward(cfg, W, ids).float()
-
-
-def _rel(a, b):
-    return float((a - b).abs().max() / b.abs().max())
-
-
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed", "one_by_one"])
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_whole_prompt_matches_plain(tiny_folders, emu, name):
-    from hfcpu_b200 import StepEntry
-    g = torch.Generator().manual_seed(1)
-    n = 150 if name == "B" else 70
-    ids = torch.randint(0, TINY[name]["vocab_size"], (n,), generator=g).tolist()
-    eng = _engine(tiny_folders[name], name, 256)
-    eng.add_request("a")
-    logits = eng.step([StepEntry("a", ids, list(range(n)))])
-    ref = _plain_logits(tiny_folders[name], ids)
-    assert _rel(logits, ref) < 1e-4
-    eng.finish_request("a")
-    eng.cache.check()
+def test_cuttings_match_plain(tiny_folders, emu, name, family):
+    reqs = make_requests(name, LENGTHS[name], seed=3)
+    steps = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions,
+             "mixed": traces.mixed, "one_by_one": traces.one_by_one}[family](reqs)
+    eng = _engine(tiny_folders[name], name, traces.peak_tokens(steps))
+    got = traces.run_in_process(eng, steps, check=eng.cache.check)
+    ref = {r: plain_logits(tiny_folders[name], ids) for r, ids in reqs.items()}
+    assert len(got) == sum(len(v) for v in reqs.values())
+    bad = traces.first_bad(got, ref, TOL["float32"])
+    assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} (error {bad[2]:.3g})"
+    assert eng.cache.pages_in_use() == 0 and eng.slots.free_count == eng.max_requests
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_portions_and_mixed_with_page_reuse(tiny_folders, emu, name):
-    from hfcpu_b200 import StepEntry
-    rnd = random.Random(5)
-    V = TINY[name]["vocab_size"]
-    reqs = {r: [rnd.randrange(V) for _ in range(n)] for r, n in (("a", 90), ("b", 33), ("c", 140), ("d", 64), ("e", 20))}
-    ref = {r: _plain_logits(tiny_folders[name], ids) for r, ids in reqs.items()}
-    eng = _engine(tiny_folders[name], name, 320)       # too few pages for all five at once
-    order = list(reqs)
-    live, done, fed = [], set(), {r: 0 for r in reqs}
-    sizes = [32, 7, 16, 2, 5, 64, 1, 3]
-    worst, step = 0.0, 0
-    while len(done) < len(reqs):
-        while len(live) < 3 and order:
-            r = order.pop(0)
-            eng.add_request(r)
-            live.append(r)
-        entries = []
-        for r in live:
-            if rnd.random() < 0.25 and len(live) > 1:
-                continue                                 # a request may sit a step out
-            n = min(sizes[(step + len(entries)) % len(sizes)], len(reqs[r]) - fed[r])
-            entries.append(StepEntry(r, reqs[r][fed[r]:fed[r] + n], list(range(n))))
-        step += 1
-        if not entries:
-            continue
-        logits = eng.step(entries)
-        o = 0
-        for e in entries:
-            n = len(e.tokens)
-            worst = max(worst, _rel(logits[o:o + n], ref[e.req][fed[e.req]:fed[e.req] + n]))
-            o += n
-            fed[e.req] += n
-            if fed[e.req] == len(reqs[e.req]):
-                eng.finish_request(e.req)
-                live.remove(e.req)
-                done.add(e.req)
+def test_mixed_reuses_pages(tiny_folders, emu):
+    reqs = make_requests("B", [130, 40, 200, 64, 90, 150], seed=9)
+    steps = traces.mixed(reqs, max_live=3)
+    eng = _engine(tiny_folders["B"], "B", traces.peak_tokens(steps))
+    seen = [set() for _ in eng.cache.groups]
+    handed_out_again = [False] * len(seen)
+
+    def check():
         eng.cache.check()
-    assert worst < 1e-4
-    assert eng.cache.pages_in_use() == 0
+        for g in eng.cache.groups:
+            now = {p for t in g.tables.values() for p in t if p >= 0}
+            handed_out_again[g.index] |= bool((now & seen[g.index]) - getattr(check, f"prev{g.index}", set()))
+            setattr(check, f"prev{g.index}", now)
+            seen[g.index] |= now
+    got = traces.run_in_process(eng, steps, check=check)
+    ref = {r: plain_logits(tiny_folders["B"], ids) for r, ids in reqs.items()}
+    assert traces.first_bad(got, ref, TOL["float32"]) is None
+    assert all(handed_out_again), "the trace was meant to make every group hand pages out again"
+
+
+def test_step_rejects_bad_entries(tiny_folders, emu):
+    from hfcpu_b200 import StepEntry
+    from hfcpu_b200.cache import OutOfPages
+    eng = _engine(tiny_folders["A"], "A", 64)
+    eng.add_request("a")
+    with pytest.raises(ValueError):
+        eng.step([StepEntry("a", [512], [0])])                  # id outside the vocabulary
+    with pytest.raises(ValueError):
+        eng.step([StepEntry("a", [1, 2], [2])])                 # wanted place outside the tokens
+    with pytest.raises(KeyError):
+        eng.step([StepEntry("zz", [1], [0])])
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("a", [1] * 65, [])])                # more than the pool holds
+    assert eng.length("a") == 0 and eng.cache.pages_in_use() == 0
+    eng.step([StepEntry("a", [1] * 64, [])])
+    assert eng.length("a") == 64

@@ -1,0 +1,218 @@
+"""Each CUDA kernel alone against its plain torch reference, at sizes other than the engine tests'.
+
+Inputs are built so that faults show: a far key among hundreds with a score that stands out, a key
+just outside and just inside a window, keys on both sides of a page's edge, scattered pages.
+"""
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from emu_backend import EmuBackend
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+def native():
+    from hfcpu_b200 import kernels
+    return kernels
+
+
+def rel(a, b):
+    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g, device=DEV) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    V, E, T = 777, 200, 45
+    table = rnd(V, E, dtype=DT[dtype])
+    ids = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
+    out = torch.empty(T, E, device=DEV)
+    native().embed(ids, table, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("E", [48, 200, 3584, 5000])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rmsnorm(dtype, E):
+    x = rnd(37, E, scale=3.0)
+    w = rnd(E, dtype=DT[dtype]) + 1
+    rows = torch.tensor([36, 0, 5, 5, 17], device=DEV, dtype=torch.int32)
+    for r in (None, rows):
+        M = 37 if r is None else 5
+        out, ref = torch.empty(M, E, device=DEV, dtype=DT[dtype]), torch.empty(M, E, device=DEV, dtype=DT[dtype])
+        native().rmsnorm(x, w, 1e-5, out, r)
+        EmuBackend().rmsnorm(x, w, 1e-5, ref, r)
+        assert rel(out.float(), ref.float()) < (1e-6 if dtype == "float32" else 1e-2)
+
+
+@pytest.mark.parametrize("shape", [(1, 50, 70), (5, 130, 64), (67, 1000, 192), (130, 96, 333), (300, 257, 1030)])
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_linear(dtype, wdtype, shape):
+    M, N, K = shape
+    a, w = rnd(M, K, dtype=DT[dtype]), rnd(N, K, dtype=DT[wdtype], scale=0.1)
+    bias = rnd(N, dtype=DT[wdtype])
+    ref = a.double() @ w.double().T
+    out = torch.empty(M, N, device=DEV, dtype=DT[dtype])
+    native().linear(a, w, bias, out, False)
+    assert rel(out, ref + bias.double()) < (1e-5 if dtype == "float32" else 1e-2)
+    res = rnd(M, N, seed=5)
+    want = res.double() + ref
+    native().linear(a, w, None, res, True)
+    assert rel(res, want) < 1e-5
+    logits = torch.empty(M, N, device=DEV)
+    native().linear(a, w, None, logits, False)
+    assert rel(logits, ref) < 1e-5
+
+
+@pytest.mark.parametrize("geom", [(5, 1, 48, 48), (6, 3, 32, 16), (8, 8, 128, 128), (2, 2, 256, 64)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rope_kv_write(dtype, geom):
+    H, G, d, n_rot = geom
+    T, pages, bs, P = 23, 9, 4, 100
+    dt = DT[dtype]
+    qkv = rnd(T, (H + 2 * G) * d, dtype=dt)
+    ang = torch.rand(P, n_rot // 2, device=DEV, dtype=torch.float64) * 6
+    cos_sin = torch.stack([ang.cos(), ang.sin()], -1).float().contiguous()
+    positions = torch.randint(0, P, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * bs, device=DEV)[:T].int()
+    slots[3] = -1
+    outs = []
+    for impl in (native(), EmuBackend()):
+        q = torch.zeros(T, H * d, device=DEV, dtype=dt)
+        kc = torch.zeros(pages, bs, G, d, device=DEV, dtype=dt)
+        vc = torch.zeros_like(kc)
+        impl.rope_kv_write(qkv, cos_sin, n_rot, positions, slots, q, kc, vc, H, G, d)
+        outs.append((q, kc, vc))
+    tol = 1e-6 if dtype == "float32" else 1e-2
+    for a, b in zip(*outs):
+        assert rel(a.float(), b.float()) < tol
+    q2 = torch.zeros(T, H * d, device=DEV, dtype=dt)
+    kc2 = torch.zeros(pages, bs, G, d, device=DEV, dtype=dt)
+    native().rope_kv_write(qkv, cos_sin, n_rot, positions, None, q2, kc2, kc2.clone(), H, G, d)
+    assert torch.equal(q2, outs[0][0]) and not kc2.any()
+
+
+def _attention_case(dtype, H, G, d, bs, lens_q, lens_kv, window, spike=None, seed=0):
+    """Builds a paged cache with scattered pages for requests of ``lens_kv`` keys, the last ``lens_q`` of
+    them being this step's queries.  ``spike = (request, key position, query offset)`` scales one key and one
+    query so that their score stands out."""
+    dt = DT[dtype]
+    S = len(lens_q)
+    MB = max((n + bs - 1) // bs for n in lens_kv)
+    pages = sum((n + bs - 1) // bs for n in lens_kv) + 5
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(pages, generator=g).tolist()
+    table = torch.full((S, MB), -1, dtype=torch.int32)
+    kc = rnd(pages, bs, G, d, dtype=dt, seed=seed + 1)
+    vc = rnd(pages, bs, G, d, dtype=dt, seed=seed + 2)
+    token_seq, positions = [], []
+    for s in range(S):
+        lo = max(0, lens_kv[s] - lens_q[s] - window + 1) if window > 0 else 0
+        for b in range((lens_kv[s] + bs - 1) // bs):
+            if b >= lo // bs:                      # blocks a window has passed stay unmapped
+                table[s, b] = perm.pop()
+        token_seq += [s] * lens_q[s]
+        positions += list(range(lens_kv[s] - lens_q[s], lens_kv[s]))
+    T = len(token_seq)
+    q = rnd(T, H * d, dtype=dt, seed=seed + 3)
+    if spike is not None:
+        s, key_pos, q_off = spike
+        t = sum(lens_q[:s]) + q_off
+        page = int(table[s, key_pos // bs])
+        assert page >= 0
+        direction = torch.ones(d, device=DEV)
+        kc[page, key_pos % bs] = (direction * 2).to(dt)
+        q.view(T, H, d)[t] = (direction * 2).to(dt)
+    meta = SimpleNamespace(block_table=table.to(DEV), block_size=bs, max_blocks=MB)
+    ctx = SimpleNamespace(token_seq=torch.tensor(token_seq, dtype=torch.int32, device=DEV),
+                          positions=torch.tensor(positions, dtype=torch.int32, device=DEV))
+    return q, kc, vc, meta, ctx
+
+
+def _run_attention(impl, case, H, G, d, window):
+    q, kc, vc, meta, ctx = case
+    out = torch.empty_like(q)
+    impl.paged_attention(q, kc, vc, meta, ctx, H, G, d, window, 1.0 / math.sqrt(d), out)
+    return out
+
+
+@pytest.mark.parametrize("geom", [(4, 2, 16, 16), (6, 3, 32, 8), (7, 7, 48, 4), (28, 4, 128, 16), (8, 1, 256, 32),
+                                  (5, 5, 80, 16)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_mixed_batch(dtype, geom):
+    H, G, d, bs = geom
+    lens_q, lens_kv = [1, 40, 1, 7, 2], [300, 40, 1, 133, 64]
+    for window in (0, 50):
+        case = _attention_case(dtype, H, G, d, bs, lens_q, lens_kv, window)
+        out, ref = _run_attention(native(), case, H, G, d, window), _run_attention(EmuBackend(), case, H, G, d, window)
+        assert rel(out.float(), ref.float()) < TOL[dtype]
+    from hfcpu_b200 import kernels
+    kernels.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_far_key_and_page_edges(dtype):
+    """One key among hundreds carries nearly all the weight; it sits at a page's first slot, last slot, the
+    very first position and the query's own position in turn."""
+    H, G, d, bs = 4, 2, 64, 16
+    for key_pos in (0, 15, 16, 31, 303, 304, 599):
+        case = _attention_case(dtype, H, G, d, bs, [1, 3], [200, 600], 0, spike=(1, key_pos, 2), seed=key_pos)
+        out, ref = _run_attention(native(), case, H, G, d, 0), _run_attention(EmuBackend(), case, H, G, d, 0)
+        assert rel(out.float(), ref.float()) < TOL[dtype], f"key {key_pos}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_window_edge(dtype):
+    """A key that would take all the weight lies just outside the window (must be ignored), then just inside."""
+    H, G, d, bs, window = 4, 4, 32, 8, 40
+    n = 100                                   # the single query sits at position 99 and sees keys 60..99
+    for key_pos, inside in ((59, False), (60, True), (99, True)):
+        # map the block of key 59 too, so that a kernel that reads one key too many finds the spike
+        case = _attention_case(dtype, H, G, d, bs, [1], [n], 0, spike=(0, key_pos, 0), seed=7)
+        out, ref = _run_attention(native(), case, H, G, d, window), _run_attention(EmuBackend(), case, H, G, d, window)
+        assert rel(out.float(), ref.float()) < TOL[dtype], f"key {key_pos}"
+        q, kc, vc, meta, ctx = case
+        page = int(meta.block_table[0, key_pos // bs])
+        spike_v = vc[page, key_pos % bs, 0].float()
+        close = rel(out.view(1, H, d)[0, 0].float(), spike_v) < 0.05
+        assert close == inside
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    T, F = 33, 999
+    gu = rnd(T, 2 * F, dtype=DT[dtype], scale=3)
+    out, ref = torch.empty(T, F, device=DEV, dtype=DT[dtype]), torch.empty(T, F, device=DEV, dtype=DT[dtype])
+    native().swiglu(gu, out)
+    EmuBackend().swiglu(gu, ref)
+    assert rel(out.float(), ref.float()) < (1e-6 if dtype == "float32" else 1e-2)
+
+
+def test_argmax_lowest_index_wins():
+    logits = rnd(9, 151937)
+    logits[2, 70000] = logits[2, 140000] = 50.0
+    logits[3, 5] = logits[3, 4] = 60.0
+    logits[4] = 1.0
+    out = torch.empty(9, device=DEV, dtype=torch.int32)
+    native().argmax(logits, out)
+    assert out.tolist() == torch.argmax(logits, -1).tolist()
+    assert out[2] == 70000 and out[3] == 4 and out[4] == 0
+
+
+def test_refuses_unsupported_head_dim():
+    from hfcpu_b200.config.base import UnsupportedError
+    with pytest.raises(UnsupportedError):
+        native().check_head_dim(40)
+    with pytest.raises(UnsupportedError):
+        native().check_head_dim(512)
