@@ -162,8 +162,10 @@ class KVCacheManager:
             g.tables[req] = []
 
     def pages_needed(self, req, new_len: int) -> List[int]:
-        old = self.lengths[req]
-        return [len(g.blocks_to_map(g.tables[req], old, new_len)) for g in self.groups]
+        """Pages each group would have to map for ``req`` to hold ``new_len`` tokens; a request that is
+        not live yet counts from nothing."""
+        old = self.lengths.get(req, 0)
+        return [len(g.blocks_to_map(g.tables.get(req, []), old, new_len)) for g in self.groups]
 
     def can_reserve(self, wants: Sequence[Tuple[object, int]]) -> bool:
         """Would reserving ``new_len`` tokens for each ``(request, new_len)`` fit, all together?"""

@@ -58,6 +58,12 @@ int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, hfb_stream s);
 /* out[m] = index of the first maximum of logits[m, :] */
 int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s);
 
+/* One token per row: greedy where temps[m] <= 0, else temperature sampling with top-k (0 = off), min-p
+ * (0 = off) and top-p (1 = off) in the reference's order of operations (src/sample.c:66-116);
+ * uniforms[m] in [0, 1) is the row's draw. */
+int hfb_sample(const float *logits, int M, int V, const float *temps, const int32_t *top_ks,
+               const float *top_ps, const float *min_ps, const float *uniforms, int32_t *out, hfb_stream s);
+
 /* Device error word: kernels set bits instead of touching memory out of range.  Reading syncs the stream. */
 enum { HFB_ERR_TOKEN_ID = 1, HFB_ERR_PAGE = 2, HFB_ERR_SLOT = 4, HFB_ERR_WAIT = 8, HFB_ERR_POSITION = 16 };
 int hfb_error_word_take(int32_t *word, hfb_stream s);

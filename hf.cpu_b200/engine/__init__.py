@@ -1,3 +1,5 @@
 from .step import Engine, GroupMeta, StepContext, StepEntry, Workspace
+from .scheduler import FinishEvent, Request, RequestError, Scheduler, StepPlan, TokenEvent
 
-__all__ = ["Engine", "StepEntry", "StepContext", "GroupMeta", "Workspace"]
+__all__ = ["Engine", "StepEntry", "StepContext", "GroupMeta", "Workspace", "Scheduler", "Request", "RequestError",
+           "TokenEvent", "FinishEvent", "StepPlan"]

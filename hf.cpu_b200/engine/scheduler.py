@@ -1,0 +1,322 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes, finishes.
+
+The reference serves one request at a time (src/main.c:54-153): it prefills in steps of ``--batch``
+tokens asking for logits only at the last portion (src/ops.c:788-795), then samples, checks the stop
+conditions and feeds the token back (src/ops.c:827-893).  The same order of operations holds per
+request here, for many requests at once:
+
+* every running request that is decoding gets its one token first; decodes never wait behind prompts;
+* what is left of the token budget goes to portions of prompts, oldest request first; waiting requests
+  are admitted first come first served while a slot is free and pages for their first portion exist;
+* when pages run out, portions of prompts are dropped from the step first; if the decodes alone do not
+  fit, the most recently admitted running request is preempted: its pages go back, it keeps the tokens
+  it generated and its generator state, and it returns to the head of the waiting queue to be
+  recomputed as prompt + generated tokens, so the tokens it samples do not change;
+* a request that cannot fit even alone fails with ENOMEM, and only that request.
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import OutOfPages
+from ..sampling import Rng, SamplingParams, logprob, sample_host, top_logprobs
+from .step import Engine, StepEntry
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+class RequestError(ValueError):
+    """A request is refused at submission; ``code`` is the reference's status name."""
+
+    def __init__(self, code: str, msg: str):
+        super().__init__(msg)
+        self.code = code
+
+
+@dataclass
+class Request:
+    id: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    eos_ids: Sequence[int] = ()
+    timeout: float = 0.0
+    # state
+    status: str = WAITING
+    generated: List[int] = field(default_factory=list)
+    computed: int = 0                  # tokens of prompt + generated that are in the cache
+    budget: int = 0                    # generation limit after clipping to the context
+    stop: Optional[str] = None         # eos | length | ctx | timeout | cancel | error
+    error: Optional[str] = None
+    limit_reason: str = "length"
+    rng: Optional[Rng] = None
+    arrival: int = 0
+    preemptions: int = 0
+    t_submit: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+    logprobs: List = field(default_factory=list)
+
+    def tokens(self) -> List[int]:
+        return self.prompt + self.generated
+
+    @property
+    def pending(self) -> int:
+        """Tokens that still have to run before the next token can be sampled."""
+        return len(self.prompt) + len(self.generated) - self.computed
+
+
+@dataclass
+class TokenEvent:
+    req: Hashable
+    pos: int                           # index among the request's generated tokens
+    token: int
+    logprob: Optional[float] = None
+    top: Optional[list] = None
+
+
+@dataclass
+class FinishEvent:
+    req: Hashable
+    stop: str
+    error: Optional[str] = None
+
+
+@dataclass
+class StepPlan:
+    entries: List[StepEntry]
+    requests: List[Request]
+    preempted: List[Request]
+    admitted: List[Request]
+    failed: List[Request]
+
+
+class Scheduler:
+    def __init__(self, engine: Engine, max_num_seqs: int = 0, max_num_batched_tokens: int = 2048,
+                 prefill_chunk: int = 0, device_sampling: bool = True):
+        self.engine = engine
+        self.max_num_seqs = min(max_num_seqs or engine.max_requests, engine.max_requests)
+        self.max_num_batched_tokens = int(max_num_batched_tokens)
+        self.prefill_chunk = int(prefill_chunk) if prefill_chunk else self.max_num_batched_tokens
+        self.device_sampling = device_sampling and engine.device.type == "cuda"
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self.requests: Dict[Hashable, Request] = {}
+        self._arrivals = 0
+        self.stats = {"steps": 0, "preemptions": 0, "tokens_in": 0, "tokens_out": 0, "finished": 0, "errors": 0}
+        self.cancelled = set()
+
+    # ---- submission ---------------------------------------------------------------------------
+    def submit(self, req: Request) -> None:
+        """Checks as the reference's: a prompt must be non-empty and shorter than the context limit
+        (src/ops.c:752-756); ``max_tokens`` is clipped to the room left, stop reason ``ctx`` (src/ops.c:757-758)."""
+        if req.id in self.requests and self.requests[req.id].status != FINISHED:
+            raise RequestError("EINVAL", f"request id {req.id!r} is already in use")
+        req.params.validate()
+        V = self.engine.model.plan.vocab_size
+        if len(req.prompt) == 0:
+            raise RequestError("EINVAL", "empty prompt")
+        for t in req.prompt:
+            if not 0 <= int(t) < V:
+                raise RequestError("EINVAL", f"token id {t} is outside the vocabulary of {V}")
+        if len(req.prompt) >= self.engine.ctx_max:
+            raise RequestError("ERANGE", f"prompt has {len(req.prompt)} tokens but --ctx-max is {self.engine.ctx_max}")
+        req.budget = req.params.max_tokens
+        if req.budget > self.engine.ctx_max - len(req.prompt):
+            req.budget, req.limit_reason = self.engine.ctx_max - len(req.prompt), "ctx"
+        req.rng = Rng(req.params.seed)
+        req.status, req.arrival, req.t_submit = WAITING, self._arrivals, time.perf_counter()
+        self._arrivals += 1
+        self.requests[req.id] = req
+        self.waiting.append(req)
+
+    def cancel(self, req_id) -> None:
+        self.cancelled.add(req_id)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---- planning a step ------------------------------------------------------------------------
+    def _preempt(self, req: Request) -> None:
+        self.engine.finish_request(req.id)
+        self.running.remove(req)
+        req.status, req.computed = WAITING, 0
+        req.preemptions += 1
+        self.stats["preemptions"] += 1
+        self.waiting.appendleft(req)
+
+    def plan(self) -> StepPlan:
+        preempted: List[Request] = []
+        failed: List[Request] = []
+        while True:
+            chosen, admitted = self._choose(preempted, failed)
+            if chosen or not self.running:
+                break
+            # running requests exist but nothing can move: every page is held by requests that all need more
+            victim = max(self.running, key=lambda r: r.arrival)
+            if len(self.running) == 1:
+                failed.append(victim)
+                self.running.remove(victim)
+                self.engine.finish_request(victim.id)
+            else:
+                self._preempt(victim)
+                preempted.append(victim)
+        entries, reqs = [], []
+        for r, n in chosen:
+            toks = r.tokens()[r.computed:r.computed + n]
+            last = r.computed + n == len(r.prompt) + len(r.generated)
+            entries.append(StepEntry(r.id, toks, [n - 1] if last else []))
+            reqs.append(r)
+        return StepPlan(entries, reqs, preempted, admitted, failed)
+
+    def _choose(self, preempted: List[Request], failed: List[Request]):
+        cache = self.engine.cache
+        # 1. decodes: one token for every running request with a single pending token
+        decodes = [r for r in self.running if r.pending == 1 and r.computed > 0]
+        while decodes and not cache.can_reserve([(r.id, r.computed + 1) for r in decodes]):
+            victim = max(self.running, key=lambda r: r.arrival)
+            if len(self.running) == 1:
+                # alone and still short of pages: the pool cannot hold this request at all
+                failed.append(victim)
+                self.running.remove(victim)
+                self.engine.finish_request(victim.id)
+                decodes = []
+                break
+            self._preempt(victim)
+            preempted.append(victim)
+            decodes = [r for r in decodes if r is not victim]
+        chosen = [(r, 1) for r in decodes]
+        budget = self.max_num_batched_tokens - len(chosen)
+        wants = [(r.id, r.computed + 1) for r in decodes]
+
+        def fit_portion(r: Request) -> int:
+            """The largest portion of r's pending tokens that the budget and the free pages allow."""
+            hi = min(r.pending, budget, self.prefill_chunk)
+            if hi <= 0 or not cache.can_reserve(wants + [(r.id, r.computed + 1)]):
+                return 0
+            lo = 1                          # lo always fits; more tokens never need fewer pages
+            while lo < hi:
+                mid = (lo + hi + 1) // 2
+                if cache.can_reserve(wants + [(r.id, r.computed + mid)]):
+                    lo = mid
+                else:
+                    hi = mid - 1
+            return lo
+
+        # 2. portions of prompts of running requests, oldest first
+        for r in sorted(self.running, key=lambda r: r.arrival):
+            if budget <= 0:
+                break
+            if r in decodes or r.pending == 0:
+                continue
+            n = fit_portion(r)
+            if n > 0:
+                chosen.append((r, n))
+                wants.append((r.id, r.computed + n))
+                budget -= n
+        # 3. admit waiting requests, first come first served
+        admitted: List[Request] = []
+        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs \
+                and self.engine.slots.free_count > 0:
+            r = self.waiting[0]
+            if r in preempted:
+                break                      # do not bring back in the same step what was just put out
+            n = fit_portion(r)
+            if n == 0:
+                if not self.running and not chosen:
+                    # nothing else holds pages and not even one token fits
+                    failed.append(self.waiting.popleft())
+                    continue
+                break
+            self.waiting.popleft()
+            self.engine.add_request(r.id)
+            r.status = RUNNING
+            self.running.append(r)
+            admitted.append(r)
+            chosen.append((r, n))
+            wants.append((r.id, n))
+            budget -= n
+        return chosen, admitted
+
+    # ---- running a step ---------------------------------------------------------------------------
+    def _finish(self, r: Request, stop: str, events: list, error: Optional[str] = None) -> None:
+        if r in self.running:
+            self.running.remove(r)
+            self.engine.finish_request(r.id)
+        elif r in self.waiting:
+            self.waiting.remove(r)
+        r.status, r.stop, r.error, r.t_done = FINISHED, stop, error, time.perf_counter()
+        self.stats["finished"] += 1
+        if error:
+            self.stats["errors"] += 1
+        events.append(FinishEvent(r.id, stop, error))
+
+    def step(self) -> list:
+        """One scheduling round: plan, run the engine's step, sample, emit events."""
+        events: list = []
+        now = time.perf_counter()
+        for r in list(self.running) + list(self.waiting):
+            if r.id in self.cancelled:
+                self.cancelled.discard(r.id)
+                self._finish(r, "cancel", events)
+            elif r.timeout > 0 and now - r.t_submit > r.timeout:
+                if r.generated or r.computed >= len(r.prompt):
+                    self._finish(r, "timeout", events)
+                else:
+                    self._finish(r, "error", events, "ECANCEL: timed out during prefill")
+        plan = self.plan()
+        for r in plan.failed:
+            r.status = FINISHED
+            self._finish(r, "error", events, "ENOMEM: the page pool cannot hold this request")
+        if not plan.entries:
+            return events
+        logits = self.engine.step(plan.entries)
+        self.stats["steps"] += 1
+        self.stats["tokens_in"] += sum(len(e.tokens) for e in plan.entries)
+        sampled = [r for r, e in zip(plan.requests, plan.entries) if e.want]
+        for r, e in zip(plan.requests, plan.entries):
+            r.computed += len(e.tokens)
+        if not sampled:
+            return events
+        tokens, rows = self._sample(logits, sampled)
+        for i, r in enumerate(sampled):
+            tok = int(tokens[i])
+            if not r.t_first:
+                r.t_first = time.perf_counter()
+            if tok in r.eos_ids:
+                self._finish(r, "eos", events)          # the end token is not emitted (src/ops.c:849)
+                continue
+            ev = TokenEvent(r.id, len(r.generated), tok)
+            if r.params.logprobs > 0:
+                row = rows[i] if rows is not None else logits[i].float().cpu().numpy()
+                ev.logprob, ev.top = logprob(row, tok), top_logprobs(row, r.params.logprobs)
+            r.generated.append(tok)
+            self.stats["tokens_out"] += 1
+            events.append(ev)
+            if len(r.generated) >= r.budget:
+                self._finish(r, r.limit_reason, events)
+        return events
+
+    def _sample(self, logits: torch.Tensor, reqs: List[Request]):
+        """Next token for each row.  On the GPU the sampling kernels run and only token ids come back;
+        the host mirror serves the stand-in backend of the tests."""
+        if self.device_sampling:
+            from .. import sampling
+            return sampling.device.sample_rows(logits, reqs), None
+        rows = logits.float().cpu().numpy()
+        return [sample_host(rows[i], r.params, r.rng) for i, r in enumerate(reqs)], rows
+
+    def run(self, on_event: Optional[Callable] = None) -> list:
+        """Step until every submitted request is finished; returns (and reports) all events."""
+        out = []
+        while self.has_work():
+            for ev in self.step():
+                out.append(ev)
+                if on_event:
+                    on_event(ev)
+        return out

@@ -95,6 +95,16 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     backend().argmax(logits, out)
 
 
+def sample(logits, temps, top_ks, top_ps, min_ps, uniforms, out) -> None:
+    """One token per row; greedy where temps <= 0, else top-k / min-p / top-p sampling with the row's draw."""
+    M = logits.shape[0]
+    _need(logits.dtype == torch.float32 and out.dtype == torch.int32 and out.shape == (M,), "sample: bad logits / out")
+    for t, dt in ((temps, torch.float32), (top_ks, torch.int32), (top_ps, torch.float32), (min_ps, torch.float32),
+                  (uniforms, torch.float32)):
+        _need(t.dtype == dt and t.shape == (M,), "sample: per-row parameters must be [M]")
+    backend().sample(logits, temps, top_ks, top_ps, min_ps, uniforms, out)
+
+
 def check_device_errors() -> None:
     """Raise if any kernel recorded an error since the last check (synchronises the stream)."""
     b = backend()

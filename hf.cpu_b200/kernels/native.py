@@ -110,6 +110,12 @@ class NativeBackend:
         M, V = logits.shape
         self._check(self.lib.hfb_argmax(_p(logits), _p(out), c_int(M), c_int(V), self._stream()), "argmax")
 
+    def sample(self, logits, temps, top_ks, top_ps, min_ps, uniforms, out):
+        self._on_gpu(logits, temps, top_ks, top_ps, min_ps, uniforms, out)
+        M, V = logits.shape
+        self._check(self.lib.hfb_sample(_p(logits), c_int(M), c_int(V), _p(temps), _p(top_ks), _p(top_ps), _p(min_ps),
+                                        _p(uniforms), _p(out), self._stream()), "sample")
+
     def error_word(self) -> int:
         w = ctypes.c_int32(0)
         self._check(self.lib.hfb_error_word_take(ctypes.byref(w), self._stream()), "error word")

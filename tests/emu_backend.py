@@ -82,3 +82,17 @@ class EmuBackend:
 
     def error_word(self):
         return 0
+
+    def sample(self, logits, temps, top_ks, top_ps, min_ps, uniforms, out):
+        import plain_qwen2 as plain
+
+        class Fixed:
+            def __init__(self, u):
+                self.u = u
+
+            def uniform(self):
+                return self.u
+        rows = logits.float().cpu().numpy()
+        for i in range(rows.shape[0]):
+            out[i] = plain.sample(rows[i], float(temps[i]), int(top_ks[i]), float(top_ps[i]), float(min_ps[i]),
+                                  Fixed(uniforms[i].cpu().numpy()))
