@@ -1,0 +1,247 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on Qwen2.5-7B layer sizes with random bf16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+A step is one decode step of a batch of 8 requests that each hold a 2,048-token prompt (maximum
+context 4,096).  Prints ONE JSON line: ``value`` = decoded tokens a second over exactly K steps, timed
+on the device with CUDA events between synchronisations; ``e2e`` = the same through the Python entry
+point (``Session.generate``: host token ids in, host token ids out); ``prefill`` = one 2,048-token prompt;
+``roofline`` = bytes a decode step has to read (every weight once, and the cache of the live requests)
+over its time against the measured copy bandwidth; ``points`` = decoding at batch 1 and 64.
+The engine runs on one GPU only: for N > 1 a line says so and the exit code is 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN25_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=28, hidden_size=3584,
+                 num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944, vocab_size=152064,
+                 max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
+                 use_sliding_window=False, hidden_act="silu")
+PROMPT, CTX_MAX, BLOCK = 2048, 4096, 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
+    except (OSError, KeyError, ValueError, TypeError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def synthetic_prompts(batch, n, vocab, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (batch, n), generator=g).tolist()
+
+
+def prefill_requests(engine, prompts, tag):
+    """Prefill every prompt (one request a step) and return each request's first greedy token."""
+    import torch
+    from hfcpu_b200 import StepEntry
+    first = []
+    for b, ids in enumerate(prompts):
+        engine.add_request((tag, b))
+        logits = engine.step([StepEntry((tag, b), ids, [len(ids) - 1])])
+        first.append(int(torch.argmax(logits[0])))
+    return first
+
+
+def time_decode(engine, batch, steps, warmup, vocab, seed, sampler=None):
+    """(ms per step, bytes of cache read per step at the middle of the run, launches per step)."""
+    import torch
+    from hfcpu_b200 import StepEntry, kernels
+    tag = f"dec{batch}"
+    toks = prefill_requests(engine, synthetic_prompts(batch, PROMPT, vocab, seed), tag)
+    out = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+    def one_step(toks):
+        logits = engine.step([StepEntry((tag, b), [toks[b]], [0]) for b in range(batch)])
+        kernels.argmax(logits, out)
+        return out.tolist()                       # the device-to-host read of the step's result
+
+    for _ in range(warmup):
+        toks = one_step(toks)
+    torch.cuda.synchronize()
+    launches0 = kernels.backend().launches
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        toks = one_step(toks)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = (kernels.backend().launches - launches0) / steps
+    ctx_mid = PROMPT + warmup + steps // 2
+    for b in range(batch):
+        engine.finish_request((tag, b))
+    return ms, ctx_mid, launches
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the 28 of the configuration (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pip cannot install ebowh/hf.cpu offline: it has neither setup.py nor pyproject.toml "
+                          "(a C99 CPU program built by make; no GPU path, no bf16 safetensors input)"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    import hfcpu_b200
+    from hfcpu_b200 import StepEntry, kernels
+    from hfcpu_b200.config import config_from_dict
+
+    cfg_d = dict(QWEN25_7B)
+    layers_full = cfg_d["num_hidden_layers"]
+    if args.layers:
+        cfg_d["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(cfg_d)
+    V = cfg.vocab_size
+    torch.cuda.set_device(0)
+    kernels.backend()
+    model = hfcpu_b200.random_model(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
+    max_b = max(64, args.batch)
+    pages = max_b * ((PROMPT + warmup + args.steps + 64 + BLOCK - 1) // BLOCK + 1)
+    engine = hfcpu_b200.Engine(model, block_size=BLOCK, num_pages=pages, max_requests=max_b, ctx_max=CTX_MAX)
+    pk, pk_src = peaks()
+    weight_bytes = model.weight_bytes_per_step()
+    kv_per_token = sum(g.page_bytes for g in engine.cache.groups) // BLOCK
+
+    # ---- prefill: one prompt of 2,048 tokens -------------------------------------------------------
+    pre_ms = []
+    for i, ids in enumerate(synthetic_prompts(4, PROMPT, V, seed=100)):
+        engine.add_request(("pre", i))
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        engine.step([StepEntry(("pre", i), ids, [PROMPT - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        pre_ms.append(e0.elapsed_time(e1))
+        engine.finish_request(("pre", i))
+    pre = min(pre_ms[1:])
+    L, E, F = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size
+    QD, KD = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    per_token = 2 * L * (E * (QD + 2 * KD) + QD * E + 3 * E * F)
+    flops = PROMPT * per_token + L * 2 * QD * PROMPT * PROMPT + 2 * E * V      # causal attention: 4*QD*T^2/2
+    prefill = {"value": round(PROMPT / pre * 1e3, 1), "tokens": PROMPT, "ms": round(pre, 3),
+               "frac": round(flops / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflop": round(flops / 1e12, 2),
+               "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src}
+
+    # ---- decode: the default batch, timed with clocks sampled ------------------------------------------
+    sampler = ClockSampler()
+    ms, ctx_mid, launches = time_decode(engine, args.batch, args.steps, warmup, V, seed=1, sampler=sampler)
+    clocks = sampler.stop()
+    value = args.batch / ms * 1e3
+    step_bytes = weight_bytes + args.batch * ctx_mid * kv_per_token
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk_src,
+                "bytes_per_step": step_bytes}
+
+    points, e2e = {}, None
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _ = time_decode(engine, b, args.steps, warmup, V, seed=2 + b)
+            points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        # ---- end to end through the Python entry point: host ids in, host ids out -----------------------
+        del engine
+        torch.cuda.empty_cache()
+        sess = hfcpu_b200.Session(model, kv_block=BLOCK, kv_pages=pages, max_seqs=max_b, ctx_max=CTX_MAX,
+                                  max_batched_tokens=PROMPT)
+        prompts = synthetic_prompts(args.batch, PROMPT, V, seed=7)
+        stamps = []
+        sess.generate(prompts, temp=0, max_tokens=warmup + args.steps + 1,
+                      on_event=lambda ev: stamps.append(time.perf_counter()) if hasattr(ev, "token") else None)
+        # token events arrive batch by batch; time the last K decode steps
+        t_first = stamps[args.batch * (warmup + 1) - 1]
+        t_last = stamps[-1]
+        e2e_value = args.batch * args.steps / (t_last - t_first)
+        meta_ints = 3 * args.batch + (args.batch + 1) + 3 * args.batch + args.batch * (1 + (CTX_MAX // BLOCK // 2))
+        e2e = {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * meta_ints + 20 * args.batch,
+               "d2h_bytes_per_step": 4 * args.batch}
+
+    line = {
+        "metric": "Qwen2.5-7B bf16: decode tok/s @ batch 8 (2,048-token prompts, 4,096 max context)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random-init weights)",
+        "impl": "engine",
+        "config": {"model": "Qwen2.5-7B layer sizes", "layers": cfg.num_hidden_layers, "layers_full": layers_full,
+                   "hidden": E, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "ffn": F, "vocab": V, "global_batch": args.batch, "seq_len": PROMPT,
+                   "ctx_max": CTX_MAX, "kv_block": BLOCK, "kv_dtype": "bf16", "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (weights read every step)"},
+        "prefill": prefill, "roofline": roofline, "points": points, "clocks": clocks,
+        "gpu_launches": int(round(launches * args.steps)), "launches_per_step": round(launches, 1),
+    }
+    if e2e:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,409 @@
+"""The command line: one resident process, requests on stdin, events on stdout, logs on stderr.
+
+Modes of stdin, controls, events and exit codes follow the reference (src/main.c:54-199,
+docs/PROTOCOL.md): ``prompts`` = records separated by a byte, each with an optional option line ended by
+0x1f; ``args`` = one request per line written as options, with ``!quit``, ``!stats``, ``!cancel``; ``none``
+= one request from the command line.  Every request answers ``@begin id= op=`` ... ``@done status=ok|error
+[code= msg=] ms=`` (src/ops.c:1042-1073).  Exit codes: 0, 1 (failed request in mode none, or stdout
+closed), 2 (startup option error), 130 (interrupted).
+"""
+from __future__ import annotations
+
+import os
+import signal
+import sys
+import time
+from typing import Any, Dict, List, Optional
+
+from . import opts as O
+from .proto import EventWriter, RecordReader
+
+LEVELS = {"error": 0, "warn": 1, "info": 2, "debug": 3}
+
+
+class Failure(Exception):
+    def __init__(self, code: str, msg: str):
+        super().__init__(msg)
+        self.code, self.msg = code, msg
+
+
+class App:
+    def __init__(self, session_opts: Dict[str, Any], out: EventWriter):
+        self.o, self.out = session_opts, out
+        self.n_requests = self.n_errors = 0
+        self.session = None             # resident model + engine, reloaded when the model path or its file changes
+        self.session_key = None
+        self.interrupted = False
+        self.cancel_requested = False
+        self._serial = 0
+
+    def log(self, level: str, **kv) -> None:
+        if LEVELS[level] <= LEVELS[self.o["log_level"]]:
+            from .proto import quote
+            print(level + " " + " ".join(f"{k}={quote(str(v))}" for k, v in kv.items()), file=sys.stderr, flush=True)
+
+    # ---- requests -----------------------------------------------------------------------------
+    def run_request(self, eff: Dict[str, Any], body: Optional[bytes]) -> bool:
+        self.n_requests += 1
+        self._serial += 1
+        rid = eff["id"] if eff["id"] is not None else str(self._serial)
+        op = eff["op"] or "generate"
+        self.out.event("begin", id=rid, op=op)
+        t0 = time.perf_counter()
+        try:
+            handler = {"echo": self.op_echo, "generate": self.op_generate, "bench": self.op_bench}.get(op)
+            if handler is None:
+                raise Failure("ENOTSUP" if op in ("inspect", "doctor", "tokenize") else "EINVAL",
+                              f"operation '{op}' is not supported (generate | bench | echo)")
+            handler(eff, body)
+        except Failure as f:
+            self.n_errors += 1
+            self.out.event("done", status="error", code=f.code, msg=f.msg, ms=f"{(time.perf_counter() - t0) * 1e3:.1f}")
+            return False
+        self.out.event("done", status="ok", ms=f"{(time.perf_counter() - t0) * 1e3:.1f}")
+        return True
+
+    def failed_request(self, code: str, msg: str) -> None:
+        self.n_requests += 1
+        self.n_errors += 1
+        self._serial += 1
+        self.out.event("begin", id=str(self._serial), op="none")
+        self.out.event("done", status="error", code=code, msg=msg, ms="0.0")
+
+    def op_echo(self, eff, body):
+        # every option as "@opt key= value=" (src/ops.c:146-159, src/opts.c:446-463), then the texts as payloads
+        for o in O.OPTIONS:
+            v = eff[o.key]
+            if v is None:
+                v = ""
+            elif isinstance(v, bool):
+                v = int(v)
+            elif isinstance(v, float):
+                v = f"{v:g}"
+            self.out.event("opt", key=o.name, value=v)
+        self.out.payload("system", (eff["system"] or "").encode())
+        self.out.payload("prompt", body if body is not None else (eff["prompt"] or "").encode())
+
+    def _reject_text(self, eff, body):
+        for o in O.OPTIONS:
+            if o.note == "text" and o.kind != O.BOOL and eff[o.key] is not None:
+                raise Failure("ENOTSUP", f"--{o.name} needs a tokenizer, which this engine does not have; use --prompt-ids")
+        if body:
+            raise Failure("ENOTSUP", "a text prompt needs a tokenizer, which this engine does not have; use --prompt-ids")
+
+    def _resident(self, eff):
+        path = eff["model"]
+        if not path:
+            raise Failure("EINVAL", f"{eff['op'] or 'generate'} needs --model PATH")
+        import hfcpu_b200
+        from hfcpu_b200.config import ConfigError, UnsupportedError
+        from hfcpu_b200.weights import WeightError, WeightFormatError
+        wfile = os.path.join(path, "model.safetensors")
+        try:
+            st = os.stat(wfile)
+            key = (os.path.abspath(path), st.st_size, st.st_mtime_ns)
+        except OSError:
+            key = (os.path.abspath(path), -1, -1)
+        if self.session is not None and self.session_key == key:
+            return self.session
+        self.session = None
+        eos = None
+        if self.o["eos_ids"]:
+            eos = parse_ids(self.o["eos_ids"], 1 << 31)
+        try:
+            self.session = hfcpu_b200.Session(
+                path, dtype=self.o["dtype"], ctx_max=int(self.o["ctx_max"]), batch=int(self.o["batch"]),
+                kv_block=self.o["kv_block"], kv_pages=int(self.o["kv_pages"]), kv_mem=int(self.o["kv_mem"]),
+                max_seqs=self.o["max_seqs"], max_batched_tokens=self.o["max_batched_tokens"], eos_ids=eos)
+        except UnsupportedError as e:
+            raise Failure("ENOTSUP", str(e)) from None
+        except (ConfigError, WeightError, WeightFormatError) as e:
+            raise Failure("EFORMAT", str(e)) from None
+        except (OSError, RuntimeError) as e:
+            raise Failure("EIO", str(e)) from None
+        self.session_key = key
+        self.log("info", msg="model loaded", path=path, dtype=self.o["dtype"],
+                 pages=self.session.engine.num_pages, ctx_max=self.session.engine.ctx_max)
+        return self.session
+
+    def op_generate(self, eff, body):
+        from hfcpu_b200.engine import FinishEvent, Request, RequestError, TokenEvent
+        from hfcpu_b200.sampling import SamplingParams
+        self._reject_text(eff, body)
+        sess = self._resident(eff)
+        if eff["prompt_ids"] is None:
+            raise Failure("EINVAL", "generate needs --prompt-ids (this engine has no tokenizer)")
+        ids = parse_ids(eff["prompt_ids"], sess.model.plan.vocab_size)
+        nseq = eff["n"]
+        sch = sess.scheduler
+        serial = self._serial
+        reqs = []
+        try:
+            for i in range(nseq):
+                p = SamplingParams(temp=eff["temp"], top_k=eff["top_k"], top_p=eff["top_p"], min_p=eff["min_p"],
+                                   seed=(eff["seed"] + i) & ((1 << 64) - 1), max_tokens=eff["max_tokens"],
+                                   logprobs=eff["logprobs"])
+                r = Request((serial, i), ids, p, eos_ids=sess.eos_ids, timeout=eff["timeout"])
+                sch.submit(r)
+                reqs.append(r)
+        except RequestError as e:
+            for r in reqs:
+                sch.cancel(r.id)
+            sch.run()
+            raise Failure(e.code, str(e)) from None
+        except ValueError as e:
+            raise Failure("EINVAL", str(e)) from None
+        self.out.event("prompt", tokens=len(ids), threads=0)
+        t0 = time.perf_counter()
+        t_prefill = None
+        steps0 = sch.stats["steps"]
+        prof = Profiler() if eff["profile"] else None
+        self.cancel_requested = False
+        errors = []
+        while sch.has_work():
+            if self.cancel_requested:
+                for r in reqs:
+                    sch.cancel(r.id)
+                self.cancel_requested = False
+            with (prof.phase("decode" if t_prefill is not None else "prefill") if prof else _null()):
+                events = sch.step()
+            if t_prefill is None and all(r.computed >= len(r.prompt) or r.status == "finished" for r in reqs):
+                t_prefill = time.perf_counter() - t0
+                self.out.event("prefill", tokens=len(ids), cached=0, ms=f"{t_prefill * 1e3:.1f}",
+                               tok_per_s=f"{len(ids) * nseq / t_prefill if t_prefill > 0 else 0:.2f}",
+                               kv_bytes=sess.engine.cache.bytes_in_use())
+                if prof:
+                    prof.emit(self.out, "prefill")
+                t_dec0 = time.perf_counter()
+            for ev in events:
+                seq = {"seq": ev.req[1]} if nseq > 1 else {}
+                if isinstance(ev, TokenEvent):
+                    extra = {}
+                    if ev.logprob is not None:
+                        extra = {"logprob": f"{ev.logprob:.6f}", "top": " ".join(f"{i}:{lp:.6f}" for i, lp in ev.top)}
+                    self.out.event("token", **seq, pos=ev.pos, id=ev.token, **extra)
+                elif ev.error:
+                    errors.append(ev.error)
+        if errors:
+            code, _, msg = errors[0].partition(": ")
+            raise Failure(code, msg)
+        if prof:
+            prof.emit(self.out, "decode")
+        dt = time.perf_counter() - (t_dec0 if t_prefill is not None else t0)
+        total = 0
+        for r in reqs:
+            seq = {"seq": r.id[1]} if nseq > 1 else {}
+            total += len(r.generated)
+            self.out.event("gen", **seq, tokens=len(r.generated), ms=f"{dt * 1e3:.1f}",
+                           tok_per_s=f"{len(r.generated) / dt if dt > 0 else 0:.2f}", stop=r.stop)
+        if nseq > 1:
+            self.out.event("genall", sequences=nseq, tokens=total, ms=f"{dt * 1e3:.1f}",
+                           tok_per_s=f"{total / dt if dt > 0 else 0:.2f}")
+
+    def op_bench(self, eff, body):
+        """Prefill and decode speed over synthetic ids (src/ops.c:942-1031): ids from xorshift modulo
+        min(V, 2000) (src/ops.c:977-979), median over --probe-reps runs, one @bench line per batch size."""
+        import statistics
+        import torch
+        from hfcpu_b200.engine import StepEntry
+        sess = self._resident(eff)
+        eng = sess.engine
+        V = min(eng.model.plan.vocab_size, 2000)
+        n_prompt, n_gen = eff["bench_prompt"], eff["bench_gen"]
+        if n_prompt + n_gen > eng.ctx_max:
+            raise Failure("ERANGE", f"--bench-prompt + --bench-gen exceed --ctx-max {eng.ctx_max}")
+        try:
+            batches = [int(x) for x in str(eff["bench_batch"]).replace(",", " ").split()]
+        except ValueError:
+            raise Failure("EINVAL", "--bench-batch must be a list of integers") from None
+        x = 0x9E3779B97F4A7C15
+        for B in batches:
+            if B < 1 or B > eng.max_requests:
+                raise Failure("ERANGE", f"--bench-batch {B} exceeds --max-seqs {eng.max_requests}")
+            pre, dec = [], []
+            for _ in range(eff["probe_reps"]):
+                prompts = []
+                for b in range(B):
+                    ids = []
+                    for _ in range(n_prompt):
+                        x ^= (x >> 12); x ^= (x << 25) & ((1 << 64) - 1); x ^= (x >> 27)
+                        ids.append(((x * 0x2545F4914F6CDD1D) & ((1 << 64) - 1)) % V)
+                    prompts.append(ids)
+                    eng.add_request(("bench", b))
+                try:
+                    torch.cuda.synchronize() if eng.device.type == "cuda" else None
+                    t0 = time.perf_counter()
+                    for b in range(B):
+                        for a in range(0, n_prompt, sess.scheduler.prefill_chunk):
+                            chunk = prompts[b][a:a + sess.scheduler.prefill_chunk]
+                            last = a + len(chunk) == n_prompt
+                            logits = eng.step([StepEntry(("bench", b), chunk, [len(chunk) - 1] if last else [])])
+                        prompts[b] = int(torch.argmax(logits[0]))
+                    torch.cuda.synchronize() if eng.device.type == "cuda" else None
+                    pre.append(B * n_prompt / (time.perf_counter() - t0))
+                    t0 = time.perf_counter()
+                    toks = prompts
+                    for _ in range(n_gen):
+                        logits = eng.step([StepEntry(("bench", b), [toks[b]], [0]) for b in range(B)])
+                        toks = torch.argmax(logits, dim=-1).tolist()
+                    dec.append(B * n_gen / (time.perf_counter() - t0))
+                except Exception as e:      # out of pages and the like
+                    raise Failure("ENOMEM", str(e)) from None
+                finally:
+                    for b in range(B):
+                        eng.finish_request(("bench", b))
+            self.out.event("bench", batch=B, prefill_tok_s=f"{statistics.median(pre):.2f}",
+                           decode_tok_s=f"{statistics.median(dec):.2f}", prompt_tokens=n_prompt, gen_tokens=n_gen)
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+class Profiler:
+    """Wall-clock per stage for ``--profile`` (the reference reports per-phase accumulators, src/ops.c:593-604)."""
+
+    def __init__(self):
+        self.acc: Dict[str, float] = {}
+        self.steps: Dict[str, int] = {}
+
+    def phase(self, name):
+        prof = self
+
+        class P:
+            def __enter__(self):
+                self.t = time.perf_counter()
+
+            def __exit__(self, *a):
+                prof.acc[name] = prof.acc.get(name, 0.0) + time.perf_counter() - self.t
+                prof.steps[name] = prof.steps.get(name, 0) + 1
+                return False
+        return P()
+
+    def emit(self, out, stage):
+        out.event("profile", stage=stage, steps=self.steps.get(stage, 0), step_ms=f"{self.acc.get(stage, 0.0) * 1e3:.1f}")
+
+
+def parse_ids(text: str, vocab: int) -> List[int]:
+    """Token ids separated by spaces or commas, each below the vocabulary size (src/ops.c:563-589)."""
+    out = []
+    for w in text.replace(",", " ").split():
+        try:
+            v = int(w)
+        except ValueError:
+            raise Failure("EINVAL", f"'{w}' in the id list is not a token id") from None
+        if not 0 <= v < vocab:
+            raise Failure("EINVAL", f"token id {v} is outside the vocabulary of {vocab}")
+        out.append(v)
+    if not out:
+        raise Failure("EINVAL", "empty prompt")
+    return out
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if "--help" in argv or "-h" in argv:
+        print(O.usage())
+        return 0
+    if "--version" in argv:
+        import hfcpu_b200
+        print(f"hfb200 {hfcpu_b200.__version__}")
+        return 0
+    try:
+        cli = O.apply(O.defaults(), argv)
+        base = O.load_settings(O.defaults(), cli["settings"]) if cli["settings"] else O.defaults()
+        o = O.apply(base, argv)
+    except O.OptionError as e:
+        print(f"hfb200: {e}", file=sys.stderr)
+        return 2
+    out = EventWriter(sys.stdout.buffer)
+    app = App(o, out)
+
+    def on_int(sig, frame):
+        if sig == signal.SIGINT and app.session is not None and app.session.scheduler.has_work():
+            app.cancel_requested = True          # ends the running request with stop=cancel; the process stays
+        else:
+            app.interrupted = True
+    signal.signal(signal.SIGINT, on_int)
+    signal.signal(signal.SIGTERM, on_int)
+    try:
+        signal.signal(signal.SIGPIPE, signal.SIG_IGN)
+    except (AttributeError, ValueError):
+        pass
+    for opt in O.OPTIONS:
+        if opt.note == "ignored" and o[opt.key] != opt.default:
+            app.log("info", msg="option accepted but has no effect in this engine", option=opt.name)
+
+    mode = o["stdin_mode"]
+    ok = True
+    if mode == "none":
+        ok = app.run_request(o, None)
+    elif mode == "args":
+        rd = RecordReader(0)
+        while not app.interrupted and not out.err:
+            got = rd.next(0x0A, int(o["max_record"]))
+            if got is None:
+                break
+            status, rec = got
+            if status:
+                app.failed_request(status, f"request line rejected: line too long (limit --max-record {o['max_record']} bytes)")
+                continue
+            line = rec.decode("utf-8", "surrogateescape").rstrip("\r")
+            if not line.strip() or line.startswith("#"):
+                continue
+            if line.startswith("!"):
+                if line.startswith("!quit"):
+                    break
+                if line.startswith("!stats"):
+                    extra = {}
+                    if app.session is not None:
+                        c = app.session.engine.cache
+                        extra = {"pages_used": c.pages_in_use(), "pages_free": sum(c.free_pages()),
+                                 "preemptions": app.session.scheduler.stats["preemptions"]}
+                    out.event("stats", requests=app.n_requests, errors=app.n_errors, live_allocs=0, **extra)
+                elif line.startswith("!cancel"):
+                    out.event("info", msg="no request is running")
+                else:
+                    out.event("error", msg="unknown control line")
+                continue
+            try:
+                eff = O.apply(o, O.shell_split(line), request_context=True)
+            except O.OptionError as e:
+                app.failed_request("EINVAL", str(e))
+                continue
+            app.run_request(eff, None)
+    else:
+        rd = RecordReader(0)
+        sep = o["record_sep"]
+        while not app.interrupted and not out.err:
+            got = rd.next(sep, int(o["max_record"]))
+            if got is None:
+                break
+            status, rec = got
+            if status:
+                app.failed_request(status, f"request rejected: record too large (limit --max-record {o['max_record']} bytes)")
+            else:
+                header, us, body = rec.partition(b"\x1f")
+                if not us:
+                    header, body = b"", rec
+                try:
+                    eff = O.apply(o, O.shell_split(header.decode("utf-8", "surrogateescape")), request_context=True)
+                except O.OptionError as e:
+                    app.failed_request("EINVAL", str(e))
+                else:
+                    app.run_request(eff, body)
+            out.raw_byte(sep)
+            out.flush()
+    if app.interrupted:
+        return 130
+    if out.err:
+        return 1
+    return 0 if ok or mode != "none" else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -45,6 +45,7 @@ class NativeBackend:
             raise KernelError(f"the CUDA library {path} could not be loaded: {e}") from None
         self.lib.hfb_last_error.restype = ctypes.c_char_p
         self.path = path
+        self.launches = 0          # kernels launched through this binding (one per successful call)
 
     def _stream(self):
         return c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -52,6 +53,7 @@ class NativeBackend:
     def _check(self, rc: int, what: str):
         if rc != 0:
             raise KernelError(f"{what}: {self.lib.hfb_last_error().decode()} (status {rc})")
+        self.launches += 1
 
     @staticmethod
     def _on_gpu(*ts):

@@ -1,0 +1,122 @@
+"""Options, protocol and the command line (what the reference covers in tests/test_opts.c and tests/e2e.pl)."""
+import io
+import os
+import subprocess
+import sys
+
+import pytest
+
+import plain_qwen2 as plain
+from conftest import ROOT, make_requests
+
+
+def test_option_forms_and_ranges():
+    from hfcpu_b200.cli import opts as O
+    d = O.defaults()
+    assert d["temp"] == 0.8 and d["top_k"] == 40 and d["top_p"] == 0.95 and d["min_p"] == 0.05
+    assert d["max_tokens"] == 512 and d["batch"] == 64 and d["ctx_max"] == 32768 and d["record_sep"] == 0x1E
+    o = O.apply(d, ["--temp", "0.5", "--top-k=7", "--no-profile", "--profile", "--ctx-max", "4K", "--record-sep", "US"])
+    assert o["temp"] == 0.5 and o["top_k"] == 7 and o["profile"] is True and o["ctx_max"] == 4096 and o["record_sep"] == 0x1F
+    assert O.apply(d, ["--profile=false"])["profile"] is False
+    assert d["temp"] == 0.8                                   # the input is not modified
+    for bad in (["--temp", "9"], ["--top-k", "-1"], ["--nope"], ["--temp"], ["stray"], ["--stdin-mode", "x"],
+                ["--no-temp"], ["--n", "65"]):
+        with pytest.raises(O.OptionError):
+            O.apply(d, bad)
+    with pytest.raises(O.OptionError):                        # session-only options are refused per request
+        O.apply(d, ["--ctx-max", "100"], request_context=True)
+    assert O.parse_size("2M") == 2 << 20 and O.parse_size("0x10") == 16
+
+
+def test_shell_split():
+    from hfcpu_b200.cli.opts import OptionError, shell_split
+    assert shell_split("--id 'a b' --x \"q\\\"r\\n\" c\\ d") == ["--id", "a b", "--x", 'q"r\n', "c d"]
+    assert shell_split("  ") == [] and shell_split("''") == [""]
+    for bad in ("'open", '"open', "trail\\"):
+        with pytest.raises(OptionError):
+            shell_split(bad)
+
+
+def test_settings_file(tmp_path):
+    from hfcpu_b200.cli import opts as O
+    p = tmp_path / "s.conf"
+    p.write_text("# comment\ntemp = 0.25\nbatch=128\n")
+    o = O.load_settings(O.defaults(), str(p))
+    assert o["temp"] == 0.25 and o["batch"] == 128
+    p.write_text("bogus = 1\n")
+    with pytest.raises(O.OptionError):
+        O.load_settings(O.defaults(), str(p))
+
+
+def test_event_quoting():
+    from hfcpu_b200.cli.proto import EventWriter, quote
+    assert quote("abc") == "abc" and quote("") == '""' and quote("a b") == '"a b"' and quote("a=b") == '"a=b"'
+    assert quote('q"\\\n\t\x01') == '"q\\"\\\\\\n\\t\\x01"'
+    f = io.BytesIO()
+    w = EventWriter(f)
+    w.event("token", pos=3, id=17)
+    w.payload("prompt", b"hi there")
+    assert f.getvalue() == b"@token pos=3 id=17\n@prompt len=8\nhi there\n"
+
+
+def test_record_reader_resyncs_after_an_oversize_record():
+    from hfcpu_b200.cli.proto import RecordReader
+    r, w = os.pipe()
+    os.write(w, b"one\x1e" + b"x" * 5000 + b"\x1etwo\x1etail")
+    os.close(w)
+    rd = RecordReader(r)
+    got = []
+    while True:
+        x = rd.next(0x1E, 100)
+        if x is None:
+            break
+        got.append(x)
+    assert got == [(None, b"one"), ("ERANGE", b""), (None, b"two"), (None, b"tail")]
+
+
+def _run_cli(args, stdin=b""):
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([ROOT, os.path.join(ROOT, "tests")]))
+    code = ("import sys; from hfcpu_b200 import kernels; from emu_backend import EmuBackend; "
+            "kernels.set_backend(EmuBackend()); import hfcpu_b200.api as api; "
+            "orig = api.Session.__init__\n"
+            "def init(self, model, **kw):\n    kw['device'] = 'cpu'; orig(self, model, **kw)\n"
+            "api.Session.__init__ = init\n"
+            "from hfcpu_b200.cli.main import main; sys.exit(main(sys.argv[1:]))")
+    return subprocess.run([sys.executable, "-c", code, *args], input=stdin, capture_output=True, env=env, timeout=120)
+
+
+def test_generate_events_and_errors(tiny_folders):
+    folder = tiny_folders["A"]
+    prompt = make_requests("A", [12], seed=3)["r0"]
+    ids = " ".join(map(str, prompt))
+    common = ["--dtype", "fp32", "--kv-pages", "32", "--ctx-max", "256", "--model", folder]
+    r = _run_cli(["--stdin-mode", "none", "--op", "generate", "--prompt-ids", ids, "--temp", "0", "--max-tokens", "5",
+                  "--logprobs", "3", *common])
+    assert r.returncode == 0, r.stderr.decode()
+    lines = r.stdout.decode().splitlines()
+    assert lines[0].startswith("@begin id=1 op=generate") and lines[-1].startswith("@done status=ok")
+    assert lines[1] == "@prompt tokens=12 threads=0" and lines[2].startswith("@prefill tokens=12 cached=0 ")
+    toks = [l for l in lines if l.startswith("@token")]
+    cfg, W = plain.read_folder(folder)
+    want = plain.greedy(cfg, W, prompt, 5)
+    assert [int(l.split("id=")[1].split()[0]) for l in toks] == want
+    assert all("logprob=" in l and "top=" in l for l in toks)
+    assert [l for l in lines if l.startswith("@gen ")][0].endswith("stop=length")
+    # args mode: several requests to one resident model, errors answered per request, controls
+    script = (f"--op generate --prompt-ids '{ids}' --temp 0 --max-tokens 2 --id a\n"
+              f"--op generate --prompt 'some text' --id b\n"
+              f"--op generate --prompt-ids '1 2 9999' --id c\n"
+              f"--op generate --prompt-ids '{ids}' --n 2 --temp 0.7 --seed 4 --max-tokens 3 --id d\n"
+              f"--ctx-max 5\n!stats\n!quit\n--op echo\n").encode()
+    r = _run_cli(["--stdin-mode", "args", *common], script)
+    out = r.stdout.decode()
+    assert r.returncode == 0, r.stderr.decode()
+    assert "@done status=error code=ENOTSUP" in out and "@done status=error code=EINVAL" in out
+    assert out.count("@begin") == 5 and "@genall sequences=2 tokens=6" in out and "seq=1" in out
+    assert "@stats requests=5 errors=3" in out and "op=echo" not in out
+    assert r.stderr.decode().count("model loaded") == 1          # the model stays resident between requests
+
+
+def test_startup_errors_exit_2():
+    r = _run_cli(["--temp", "77"])
+    assert r.returncode == 2 and b"--temp" in r.stderr

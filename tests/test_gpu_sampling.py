@@ -1,0 +1,69 @@
+"""The sampling kernel against the host mirror (which equals the plain sampler, tests/test_sampling.py)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rows(V, seed):
+    rs = np.random.RandomState(seed)
+    rows = []
+    for kind in range(8):
+        l = (rs.randn(V) * [0.3, 1, 3, 8][kind % 4]).astype(np.float32)
+        if kind >= 4:
+            l[rs.randint(V, size=12)] = l[rs.randint(V)]          # exact ties
+        if kind == 7:
+            l[:] = 0.25                                             # everything ties
+        rows.append(l)
+    return np.stack(rows)
+
+
+@pytest.mark.parametrize("V", [17, 1000, 152064])
+def test_device_sampler_equals_host_mirror(V):
+    from hfcpu_b200 import kernels
+    from hfcpu_b200.sampling import Rng, SamplingParams, sample_host
+    logits = _rows(V, seed=V)
+    dev = torch.from_numpy(logits).cuda()
+    M = logits.shape[0]
+    combos = [(0.0, 40, 0.95, 0.05), (0.8, 40, 0.95, 0.05), (1.0, 0, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.5, 0, 1.0, 0.1),
+              (1.0, 5, 1.0, 0.0), (0.5, 1, 0.5, 0.5), (2.0, 2000, 0.8, 0.01), (1.0, 1024, 1.0, 0.0), (0.3, 0, 0.3, 0.3)]
+    mismatches = 0
+    for ci, (temp, k, tp, mp) in enumerate(combos):
+        for draw in range(6):
+            us = np.array([Rng(1000 * ci + 10 * draw + m).uniform() for m in range(M)], dtype=np.float32)
+            if draw == 5:
+                us[:] = np.float32(1.0 - 2 ** -24)                  # the largest draw there is
+            out = torch.empty(M, dtype=torch.int32, device="cuda")
+            f = lambda v, dt: torch.full((M,), v, dtype=dt, device="cuda")
+            kernels.sample(dev, f(temp, torch.float32), f(k, torch.int32), f(tp, torch.float32), f(mp, torch.float32),
+                           torch.from_numpy(us).cuda(), out)
+            got = out.tolist()
+
+            class Fixed:
+                def __init__(self, u):
+                    self.u = u
+
+                def uniform(self):
+                    return self.u
+            for m in range(M):
+                want = sample_host(logits[m], SamplingParams(temp=temp, top_k=k, top_p=tp, min_p=mp), Fixed(us[m]))
+                if got[m] != want:
+                    # sums in another order may move a cut by one candidate at an exact boundary, never further
+                    order = sorted(range(V), key=lambda i: (-logits[m][i], i))
+                    assert abs(order.index(got[m]) - order.index(want)) <= 1, (temp, k, tp, mp, m)
+                    assert temp > 0 and not 0 < k <= 1024, "the sorted path must agree exactly"
+                    mismatches += 1
+    assert mismatches <= 3
+
+
+def test_greedy_rows_beside_sampled_rows():
+    from hfcpu_b200 import kernels
+    logits = torch.randn(5, 4096, device="cuda")
+    temps = torch.tensor([0, 1.0, 0, 0.5, 0], dtype=torch.float32, device="cuda")
+    z = lambda v, dt: torch.full((5,), v, dtype=dt, device="cuda")
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    kernels.sample(logits, temps, z(0, torch.int32), z(1.0, torch.float32), z(0.0, torch.float32),
+                   torch.rand(5, device="cuda"), out)
+    am = torch.argmax(logits, -1)
+    assert out[0] == am[0] and out[2] == am[2] and out[4] == am[4]
