@@ -1,0 +1,520 @@
+// out[M,N] (=|+=) a[M,K] . w[N,K]^T (+ bias) for bfloat16 operands on the 5th-generation tensor cores.
+//
+// Both operands are K-major (rows of K contiguous elements), which is what tcgen05.mma wants of
+// shared-memory operands, so one kernel serves prefill and decode by choosing which operand
+// supplies the 128 accumulator rows ("X", rows -> TMEM lanes) and which the columns ("Y", rows ->
+// TMEM columns, 16..256 of them):
+//   * many tokens: X = activations, Y = weights (tile 128 tokens x BN features);
+//   * few tokens (decode): X = weights, Y = activations (tile 128 features x BN tokens, "swapped"),
+//     so that the tensor core's 128 rows are filled by the weight matrix that has to be streamed
+//     from HBM anyway, with split-K when there are fewer weight tiles than SMs.
+// Pipeline per CTA (persistent over work items): warp 0 issues TMA loads of 128-byte-swizzled K
+// blocks into a ring of shared-memory stages; warp 1 issues tcgen05.mma from shared memory into one
+// of two TMEM accumulators and commits to the stage's "empty" barrier; warps 2..5 read a finished
+// accumulator with tcgen05.ld, apply the epilogue and store, while the next tile's products run.
+// Every barrier wait has a time limit: on expiry the kernel raises HFB_ERR_WAIT in the device error
+// word, lets its copies land, frees its TMEM and returns.
+//
+// The reference computes the same products with one dot per (row, token) after widening the weight
+// row to float (src/model.c:369-440, src/kern_avx2.c:79-95); accumulation here is float32 too.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace hfb {
+int *error_word();
+
+constexpr int BK = 64;                 // bf16 elements per K block: 128 bytes, one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int TILE_X = 128;            // accumulator rows (TMEM lanes)
+constexpr uint32_t X_BYTES = TILE_X * BK * 2;
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2 };
+
+struct GemmParams {
+    int M, N, K;                       // logical sizes: tokens, output features, inner
+    int swapped;                       // X = weights, Y = activations
+    int tiles_x, tiles_y, splits, kb_total, kb_per_split;
+    void *out; int out_dt;             // [M, N]
+    const void *bias; int bias_dt;     // [N] or null
+    int mode;
+    float *partial;                    // [splits, M, N] when mode == EPI_PARTIAL
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long global_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for the phase of `parity` to complete; gives up after WAIT_LIMIT_NS or when another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err)
+{
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if (*abort_flag) return false;
+        if ((spin & 63) == 63) {
+            unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicOr(err, HFB_ERR_WAIT);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
+{
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t instr_desc(int n)
+{
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_X >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *v)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN> constexpr int tmem_cols()
+{
+    int need = 2 * BN, c = 32;
+    while (c < need) c <<= 1;
+    return c;
+}
+
+template <int BN, int STAGES> constexpr uint32_t gemm_smem_bytes()
+{
+    return 1024 + STAGES * (X_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, GemmParams p, int *err)
+{
+    constexpr uint32_t Y_BYTES = BN * BK * 2;
+    constexpr int TCOLS = tmem_cols<BN>();
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sx = base, sy = base + STAGES * X_BYTES;
+    const uint32_t bars = sy + STAGES * Y_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + STAGES * 8, tfull0 = bars + 2 * STAGES * 8, tempty0 = tfull0 + 16;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen_base + STAGES * (X_BYTES + Y_BYTES) + (2 * STAGES + 4) * 8);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void *)tmem_slot)), "r"(TCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int total_items = p.tiles_x * p.tiles_y * p.splits;
+    const int per_split = p.tiles_x * p.tiles_y;
+
+    if (warp == 0) {
+        // ---- producer: TMA loads --------------------------------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                int split = item / per_split, t = item % per_split;
+                int tx = t % p.tiles_x, ty = t / p.tiles_x;
+                int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    int s = it % STAGES;
+                    uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
+                    mbar_arrive_expect_tx(full0 + 8 * s, X_BYTES + Y_BYTES);
+                    tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
+                    tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor-core issue ------------------------------------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            int last_s = -1;
+            uint32_t last_ph = 0;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, tile_it++) {
+                int split = item / per_split;
+                int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+                int a = tile_it & 1;
+                uint32_t aph = (tile_it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * a, aph ^ 1, abort_flag, err)) { ok = false; break; }
+                tc_fence_after();
+                uint32_t d = tmem_base + a * BN;
+                for (int kb = kb0; kb < kb1; kb++, it++) {
+                    int s = it % STAGES;
+                    uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, err)) { ok = false; break; }
+                    tc_fence_after();
+                    uint64_t dx = smem_desc(sx + s * X_BYTES), dy = smem_desc(sy + s * Y_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        tc_mma_bf16(d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);
+                    last_s = s;
+                    last_ph = ph;
+                }
+                if (ok) tc_commit(tfull0 + 8 * a);
+            }
+            // all commits have landed once the last one has: nothing of this CTA's is in flight afterwards
+            if (ok && last_s >= 0) mbar_wait(empty0 + 8 * last_s, last_ph, abort_flag, err);
+        }
+    } else {
+        // ---- epilogue: TMEM -> registers -> global ------------------------------------------------
+        const int q = warp & 3;                       // the TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, tile_it++) {
+            int split = item / per_split, t = item % per_split;
+            int tx = t % p.tiles_x, ty = t / p.tiles_x;
+            int a = tile_it & 1;
+            uint32_t aph = (tile_it >> 1) & 1;
+            if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag, err)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
+            const int xr = tx * TILE_X + row;         // row of X this thread holds
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(taddr + c0, v);
+                tmem_wait_ld();
+                const int y0 = ty * BN + c0;          // first row of Y in this chunk
+                if (p.swapped) {
+                    // xr = output feature, y = token
+                    if (xr < p.N) {
+                        float b = (p.bias && p.mode != EPI_PARTIAL) ? load_any(p.bias, p.bias_dt, xr) : 0.f;
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            int tok = y0 + i;
+                            if (tok >= p.M) break;
+                            float val = __uint_as_float(v[i]) + b;
+                            size_t o = (size_t)tok * p.N + xr;
+                            if (p.mode == EPI_PARTIAL) p.partial[(size_t)split * p.M * p.N + o] = val;
+                            else if (p.mode == EPI_ADD) ((float *)p.out)[o] += val;
+                            else store_any(p.out, p.out_dt, o, val);
+                        }
+                    }
+                } else if (xr < p.M && y0 < p.N) {
+                    // xr = token, y = output feature: 16 consecutive features of one row
+                    size_t o = (size_t)xr * p.N + y0;
+                    bool full = y0 + 16 <= p.N && (p.N & 7) == 0;
+                    float f[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        f[i] = __uint_as_float(v[i]);
+                        if (p.bias && p.mode != EPI_PARTIAL && (full || y0 + i < p.N)) f[i] += load_any(p.bias, p.bias_dt, y0 + i);
+                    }
+                    if (p.mode == EPI_PARTIAL) {
+                        float *dst = p.partial + (size_t)split * p.M * p.N + o;
+                        if (full) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4) *(float4 *)(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+                        } else {
+                            for (int i = 0; i < 16 && y0 + i < p.N; i++) dst[i] = f[i];
+                        }
+                    } else if (p.mode == EPI_ADD) {
+                        float *dst = (float *)p.out + o;
+                        if (full) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4) {
+                                float4 r = *(float4 *)(dst + i);
+                                *(float4 *)(dst + i) = make_float4(r.x + f[i], r.y + f[i + 1], r.z + f[i + 2], r.w + f[i + 3]);
+                            }
+                        } else {
+                            for (int i = 0; i < 16 && y0 + i < p.N; i++) dst[i] += f[i];
+                        }
+                    } else if (p.out_dt == HFB_BF16 && full) {
+                        __nv_bfloat162 h[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                        uint4 *dst = (uint4 *)((__nv_bfloat16 *)p.out + o);
+                        dst[0] = *(uint4 *)&h[0];
+                        dst[1] = *(uint4 *)&h[4];
+                    } else if (p.out_dt == HFB_F32 && full) {
+                        float *dst = (float *)p.out + o;
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4) *(float4 *)(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+                    } else {
+                        for (int i = 0; i < 16 && y0 + i < p.N; i++) store_any(p.out, p.out_dt, o + i, f[i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * a);
+        }
+    }
+
+    // ---- teardown --------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        // a wait ran out: give loads that are still in flight time to land before the shared memory goes away
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TCOLS) : "memory");
+    }
+}
+
+// Sums split-K partials in split order and applies the epilogue.
+__global__ void splitk_reduce_kernel(const float *partial, int splits, size_t MN, int N, const void *bias, int bias_dt,
+                                     void *out, int out_dt, int mode)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= MN) return;
+    float v = 0.f;
+    for (int s = 0; s < splits; s++) v += partial[(size_t)s * MN + i];
+    if (bias) v += load_any(bias, bias_dt, i % N);
+    if (mode == EPI_ADD) ((float *)out)[i] += v;
+    else store_any(out, out_dt, i, v);
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+struct MapKey {
+    const void *ptr; int rows, cols, box_rows;
+    bool operator==(const MapKey &o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const
+    {
+        size_t h = (size_t)k.ptr;
+        h = h * 1000003u ^ (size_t)k.rows;
+        h = h * 1000003u ^ (size_t)k.cols;
+        return h * 1000003u ^ (size_t)k.box_rows;
+    }
+};
+
+// A 2-D map over a row-major bf16 matrix [rows, cols] with boxes of [box_rows, 64] and 128-byte swizzle.
+static int tensor_map(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *out)
+{
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    MapKey key{ptr, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return HFB_OK; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(HFB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(HFB_ECUDA, "cuTensorMapEncodeTiled failed with %d (rows=%d cols=%d box=%d)", (int)r, rows, cols, box_rows);
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = *out;
+    return HFB_OK;
+}
+
+static int sm_count()
+{
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 1;
+    }
+    return n;
+}
+
+template <int BN, int STAGES>
+static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams &p, cudaStream_t st)
+{
+    constexpr uint32_t smem = gemm_smem_bytes<BN, STAGES>();
+    static_assert(smem > 116 * 1024, "one CTA per SM is assumed (two could not both allocate their TMEM columns)");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail(HFB_ECUDA, "gemm_tc: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    int items = p.tiles_x * p.tiles_y * p.splits;
+    int grid = items < sm_count() ? items : sm_count();
+    gemm_tc_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, st>>>(mx, my, p, error_word());
+    return check_launch("gemm_tc");
+}
+
+}  // namespace hfb
+
+using namespace hfb;
+
+// Bytes of float32 workspace hfb_linear_tc may use for split-K partials with these sizes (0: none needed).
+extern "C" size_t hfb_linear_tc_workspace(int M, int N, int K)
+{
+    if (M > 128) return 0;
+    int tiles = (N + TILE_X - 1) / TILE_X, kb = (K + BK - 1) / BK;
+    int splits = tiles >= sm_count() ? 1 : sm_count() / tiles;      // at most one work item per SM
+    if (splits > kb / 4) splits = kb / 4 > 0 ? kb / 4 : 1;
+    if (splits > 16) splits = 16;
+    return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
+}
+
+extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
+                             int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) return HFB_OK;
+    if (K <= 0 || (K & 7)) return fail(HFB_ENOTSUP, "linear_tc: K = %d must be a positive multiple of 8", K);
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
+        return fail(HFB_ENOTSUP, "linear_tc: operands must be 16-byte aligned");
+    if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "linear_tc: bad element types");
+    if (accumulate && out_dt != HFB_F32) return fail(HFB_EINVAL, "linear_tc: accumulation needs a float32 output");
+    cudaStream_t st = (cudaStream_t)s;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K;
+    p.out = out; p.out_dt = out_dt; p.bias = bias; p.bias_dt = bias_dt;
+    p.mode = accumulate ? EPI_ADD : EPI_STORE;
+    p.kb_total = (K + BK - 1) / BK;
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    p.partial = nullptr;
+    p.swapped = M <= 128;
+    int bn;
+    if (p.swapped) {
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+        p.tiles_x = (N + TILE_X - 1) / TILE_X;
+        p.tiles_y = 1;
+        size_t need = hfb_linear_tc_workspace(M, N, K);
+        if (need && workspace && workspace_bytes >= need) {
+            int splits = (int)(need / ((size_t)M * N * sizeof(float)));
+            p.kb_per_split = (p.kb_total + splits - 1) / splits;
+            p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+            if (p.splits > 1) { p.partial = (float *)workspace; p.mode = EPI_PARTIAL; }
+            else p.kb_per_split = p.kb_total;
+        }
+    } else {
+        bn = 256;
+        p.tiles_x = (M + TILE_X - 1) / TILE_X;
+        p.tiles_y = (N + bn - 1) / bn;
+    }
+    CUtensorMap mx, my;
+    int rc;
+    if (p.swapped) {
+        if ((rc = tensor_map(w, N, K, TILE_X, &mx)) != HFB_OK) return rc;
+        if ((rc = tensor_map(a, M, K, bn, &my)) != HFB_OK) return rc;
+    } else {
+        if ((rc = tensor_map(a, M, K, TILE_X, &mx)) != HFB_OK) return rc;
+        if ((rc = tensor_map(w, N, K, bn, &my)) != HFB_OK) return rc;
+    }
+    switch (bn) {
+    case 16: rc = launch<16, 10>(mx, my, p, st); break;
+    case 32: rc = launch<32, 9>(mx, my, p, st); break;
+    case 64: rc = launch<64, 8>(mx, my, p, st); break;
+    case 128: rc = launch<128, 6>(mx, my, p, st); break;
+    default: rc = launch<256, 4>(mx, my, p, st); break;
+    }
+    if (rc != HFB_OK) return rc;
+    if (p.mode == EPI_PARTIAL) {
+        size_t MN = (size_t)M * N;
+        splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
+                                                                          accumulate ? EPI_ADD : EPI_STORE);
+        return check_launch("splitk_reduce");
+    }
+    return HFB_OK;
+}

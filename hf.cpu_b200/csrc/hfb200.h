@@ -38,6 +38,14 @@ int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, void *out, i
 int hfb_linear_plain(const void *a, int a_dt, const void *w, int w_dt, const void *bias, int bias_dt,
                      void *out, int out_dt, int accumulate, int M, int N, int K, hfb_stream s);
 
+/* The same product for bfloat16 a and w on the tensor cores (tcgen05, TMA, TMEM).  K must be a multiple of 8
+ * and the operands 16-byte aligned, else HFB_ENOTSUP.  With few rows (M <= 128) the kernel may split K over
+ * more CTAs and sum float32 partials kept in `workspace`; hfb_linear_tc_workspace gives the bytes that takes
+ * (0 = none); with a smaller or null workspace it runs unsplit. */
+size_t hfb_linear_tc_workspace(int M, int N, int K);
+int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
+                  int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s);
+
 /* Splits qkv[T, (H+2G)*d] into rotated queries q_out[T, H*d], rotated keys and plain values written
  * to the paged cache at slots[t] (page * block_size + offset; < 0 or slots == NULL: not written).
  * cos_sin is float32 [positions, n_rot/2, 2]; n_rot == 0 means no rotation. */

@@ -85,14 +85,18 @@ __device__ unsigned long long descend(const Row &r, unsigned long long cut, floa
         __syncthreads();
         if (threadIdx.x == 0) {
             float acc = before;
-            int pick = -1;
+            int pick = -1, lowest = -1;
             for (int bin = 255; bin >= 0; bin--) {
                 float h = hist[bin];
                 if (h == 0.f) continue;
                 bool hit = MODE == BY_MASS_GT ? (acc + h > target) : (acc + h >= target);
                 if (hit) { pick = bin; break; }
                 acc += h;
+                lowest = bin;
             }
+            // Below the first byte the target is known to lie inside the chosen bucket; if re-summing its
+            // mass in finer bins falls short by rounding, the bucket's last candidate is the one.
+            if (pick < 0 && b < 7 && lowest >= 0) { pick = lowest; acc -= hist[lowest]; }
             result[0] = pick < 0 ? ~0ull : (unsigned long long)pick;
             ((float *)(result + 1))[0] = acc;
         }

@@ -6,6 +6,7 @@ contiguity), passes raw pointers and the current torch stream, and raises on a n
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
@@ -44,6 +45,10 @@ class NativeBackend:
         except OSError as e:
             raise KernelError(f"the CUDA library {path} could not be loaded: {e}") from None
         self.lib.hfb_last_error.restype = ctypes.c_char_p
+        self.lib.hfb_linear_tc_workspace.restype = ctypes.c_size_t
+        # "tc": tensor-core products where the operands allow; "plain": the float32-accumulating SIMT kernel always
+        self.gemm = os.environ.get("HFB_GEMM", "tc")
+        self._ws = None
         self.path = path
         self.launches = 0          # kernels launched through this binding (one per successful call)
 
@@ -78,6 +83,17 @@ class NativeBackend:
         self._on_gpu(a, w, bias, out)
         M, K = a.shape
         N = w.shape[0]
+        if (self.gemm == "tc" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+            need = self.lib.hfb_linear_tc_workspace(c_int(M), c_int(N), c_int(K))
+            if need and (self._ws is None or self._ws.numel() < need or self._ws.device != a.device):
+                self._ws = torch.empty(max(need, 16 << 20), dtype=torch.uint8, device=a.device)
+            self._check(self.lib.hfb_linear_tc(_p(a), _p(w), _p(bias), c_int(_dt(bias) if bias is not None else 0),
+                                               _p(out), c_int(_dt(out)), c_int(1 if accumulate else 0), c_int(M),
+                                               c_int(N), c_int(K), _p(self._ws if need else None),
+                                               ctypes.c_size_t(self._ws.numel() if need else 0), self._stream()),
+                        "linear_tc")
+            return
         self._check(self.lib.hfb_linear_plain(_p(a), c_int(_dt(a)), _p(w), c_int(_dt(w)), _p(bias),
                                               c_int(_dt(bias) if bias is not None else 0), _p(out), c_int(_dt(out)),
                                               c_int(1 if accumulate else 0), c_int(M), c_int(N), c_int(K),

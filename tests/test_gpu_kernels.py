@@ -216,3 +216,44 @@ def test_refuses_unsupported_head_dim():
         native().check_head_dim(40)
     with pytest.raises(UnsupportedError):
         native().check_head_dim(512)
+
+
+TC_SHAPES = [(1, 128, 64), (1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (16, 1000, 192), (17, 320, 72),
+             (64, 3584, 2048), (100, 1000, 200), (128, 512, 512), (129, 256, 64), (130, 1000, 192), (300, 777 * 8, 136),
+             (2048, 1024, 512), (1000, 4608, 3584), (5, 152064, 256)]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_linear_tensor_core(shape):
+    """bfloat16 x bfloat16 products on the tcgen05 kernel (both operand orders, split-K, ragged edges) against
+    float64, and bit-for-bit stable from call to call."""
+    from hfcpu_b200 import kernels
+    assert kernels.backend().gemm == "tc"
+    M, N, K = shape
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05)
+    bias = rnd(N, dtype=torch.bfloat16)
+    ref = a.double() @ w.double().T
+    scale = float(ref.abs().max())
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    native().linear(a, w, bias, out, False)
+    err = float((out.double() - (ref + bias.double())).abs().max()) / float((ref + bias.double()).abs().max())
+    assert err < 1e-2, f"bf16 store: {err}"
+    logits = torch.empty(M, N, device=DEV)
+    native().linear(a, w, None, logits, False)
+    assert float((logits.double() - ref).abs().max()) / scale < 2e-5, "float32 store"
+    again = torch.empty(M, N, device=DEV)
+    native().linear(a, w, None, again, False)
+    assert torch.equal(logits, again), "two calls differ"
+    res = rnd(M, N, seed=5)
+    want = res.double() + ref + bias.double()
+    native().linear(a, w, bias, res, True)
+    assert float((res.double() - want).abs().max()) / float(want.abs().max()) < 2e-5, "accumulate"
+    plain_out = torch.empty(M, N, device=DEV)
+    b = kernels.backend()
+    b.gemm = "plain"
+    try:
+        native().linear(a, w, None, plain_out, False)
+    finally:
+        b.gemm = "tc"
+    assert float((logits - plain_out).abs().max()) / scale < 2e-5, "differs from the plain kernel"
+    kernels.check_device_errors()

@@ -49,9 +49,12 @@ def test_device_sampler_equals_host_mirror(V):
             for m in range(M):
                 want = sample_host(logits[m], SamplingParams(temp=temp, top_k=k, top_p=tp, min_p=mp), Fixed(us[m]))
                 if got[m] != want:
-                    # sums in another order may move a cut by one candidate at an exact boundary, never further
+                    # sums taken in another order may move a cut across an exact boundary: the two choices
+                    # are then neighbours in the order, or separated only by candidates of negligible mass
                     order = sorted(range(V), key=lambda i: (-logits[m][i], i))
-                    assert abs(order.index(got[m]) - order.index(want)) <= 1, (temp, k, tp, mp, m)
+                    a, b = sorted((order.index(got[m]), order.index(want)))
+                    pr = np.exp((logits[m][order] - logits[m][order[0]]).astype(np.float64) / temp)
+                    assert b - a <= 1 or pr[a + 1:b + 1].sum() / pr.sum() < 1e-5, (temp, k, tp, mp, m)
                     assert temp > 0 and not 0 < k <= 1024, "the sorted path must agree exactly"
                     mismatches += 1
     assert mismatches <= 3
