@@ -33,9 +33,8 @@ class LinearHead(Part):
         self.weight = None
 
     def tensor_specs(self):
-        if self.tied_to:
-            return []
-        return [TensorSpec(self.tensor, (self.vocab_size, self.hidden_size))]
+        # a tied head reads the embedding; a checkpoint that carries a copy of the head anyway is accepted
+        return [TensorSpec(self.tensor, (self.vocab_size, self.hidden_size), optional=bool(self.tied_to))]
 
     def bind(self, tensors, run_dtype, device):
         self.weight = tensors[self.tied_to if self.tied_to else self.tensor].contiguous()

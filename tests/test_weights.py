@@ -1,0 +1,117 @@
+"""Weights by tensor name: dtype policy, the one error that lists everything, hostile files, random weights."""
+import json
+import os
+import struct
+
+import pytest
+import torch
+
+from conftest import TINY_A, TINY_B
+
+
+def _specs(d):
+    from hfcpu_b200.config import config_from_dict
+    from hfcpu_b200.models import build_model_specs
+    return config_from_dict(d), build_model_specs(config_from_dict(d))
+
+
+def test_names_and_shapes_of_the_checkpoint():
+    _, specs = _specs(TINY_B)
+    by = {s.name: s.shape for s in specs}
+    assert by["model.embed_tokens.weight"] == (1000, 192) and by["lm_head.weight"] == (1000, 192)
+    assert by["model.layers.2.self_attn.q_proj.weight"] == (192, 192) and by["model.layers.2.self_attn.k_proj.bias"] == (96,)
+    assert by["model.layers.0.mlp.gate_proj.weight"] == (320, 192) and by["model.layers.0.mlp.down_proj.weight"] == (192, 320)
+    assert by["model.norm.weight"] == (192,) and len(by) == 3 + 3 * 12
+    _, tied = _specs(TINY_A)
+    head = [s for s in tied if s.name == "lm_head.weight"]
+    assert head and head[0].optional                           # a tied head reads the embedding (src/model.c:156-158)
+
+
+def test_random_model_round_trip_and_dtype_policy(tmp_path):
+    import hfcpu_b200
+    from hfcpu_b200.weights import load_tensors
+    cfg, specs = _specs(TINY_A)
+    hfcpu_b200.write_random_model(cfg, str(tmp_path / "bf"), seed=1, dtype=torch.bfloat16)
+    hfcpu_b200.write_random_model(cfg, str(tmp_path / "f32"), seed=1, dtype=torch.float32)
+    again = str(tmp_path / "again")
+    hfcpu_b200.write_random_model(cfg, again, seed=1, dtype=torch.float32)
+    cpu = torch.device("cpu")
+    bf_bf = load_tensors(str(tmp_path / "bf"), specs, torch.bfloat16, cpu)
+    bf_32 = load_tensors(str(tmp_path / "bf"), specs, torch.float32, cpu)
+    f32_bf = load_tensors(str(tmp_path / "f32"), specs, torch.bfloat16, cpu)
+    f32_again = load_tensors(again, specs, torch.float32, cpu)
+    name = "model.layers.1.mlp.up_proj.weight"
+    assert bf_bf[name].dtype == torch.bfloat16                 # 16-bit stays 16-bit in a bfloat16 run
+    assert bf_32[name].dtype == torch.float32 and torch.equal(bf_32[name], bf_bf[name].float())   # widening is exact
+    assert f32_bf[name].dtype == torch.float32                 # a tensor stored in 32-bit stays so
+    assert torch.equal(f32_bf[name], f32_again[name])          # same seed, same values, whatever the order
+    w = f32_again["model.layers.0.input_layernorm.weight"]
+    assert abs(float(w.mean()) - 1) < 0.02 and 0.001 < float(f32_again[name].std()) < 0.05
+    other = str(tmp_path / "other")
+    hfcpu_b200.write_random_model(cfg, other, seed=2, dtype=torch.float32)
+    assert not torch.equal(load_tensors(other, specs, torch.float32, cpu)[name], f32_again[name])
+
+
+def test_one_error_lists_missing_unexpected_and_misshapen(tmp_path):
+    from hfcpu_b200.weights import WeightError, load_tensors, random_tensors, weights_path, write_safetensors
+    cfg, specs = _specs(TINY_A)
+    t = random_tensors(specs, 0, torch.float32)
+    del t["model.norm.weight"], t["model.layers.1.self_attn.v_proj.bias"]
+    t["model.layers.0.mlp.up_proj.weight"] = torch.zeros(176, 63)
+    t["model.layers.9.extra"] = torch.zeros(3)
+    t["lm_head.weight"] = torch.zeros(512, 64)                 # a copy of the tied head is tolerated
+    cfg.save(str(tmp_path))
+    write_safetensors(weights_path(str(tmp_path)), t)
+    with pytest.raises(WeightError) as e:
+        load_tensors(str(tmp_path), specs, torch.float32, torch.device("cpu"))
+    msg = str(e.value)
+    assert "missing (2): " in msg and "model.norm.weight" in msg and "model.layers.1.self_attn.v_proj.bias" in msg
+    assert "unexpected (1): model.layers.9.extra" in msg
+    assert "tensor 'model.layers.0.mlp.up_proj.weight' has shape 176x63, expected 176x64" in msg
+    assert e.value.missing and e.value.unexpected and e.value.misshapen
+
+
+def test_integer_tables_become_int32(tmp_path):
+    from hfcpu_b200.weights import TensorSpec, load_tensors, weights_path, write_safetensors
+    write_safetensors(weights_path(str(tmp_path)), {"table": torch.arange(6, dtype=torch.int64).view(2, 3),
+                                                    "w": torch.ones(2, dtype=torch.float16)})
+    t = load_tensors(str(tmp_path), [TensorSpec("table", (2, 3), init="int"), TensorSpec("w", (2,))], torch.bfloat16,
+                     torch.device("cpu"))
+    assert t["table"].dtype == torch.int32 and t["table"].tolist() == [[0, 1, 2], [3, 4, 5]] and t["w"].dtype == torch.bfloat16
+
+
+def test_hostile_files_are_refused(tmp_path):
+    from hfcpu_b200.weights import SafetensorsFile, WeightFormatError
+    p = str(tmp_path / "model.safetensors")
+
+    def expect(data, what):
+        open(p, "wb").write(data)
+        with pytest.raises(WeightFormatError, match=what):
+            SafetensorsFile(p)
+    expect(b"abc", "too short")
+    expect(struct.pack("<Q", 1 << 40) + b"{}", "header length")
+    expect(struct.pack("<Q", 4) + b"nope", "not valid JSON")
+    expect(struct.pack("<Q", 2) + b"[]", "JSON object")
+    h = json.dumps({"t": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}).encode()
+    expect(struct.pack("<Q", len(h)) + h + b"\0" * 8, "does not match")           # data runs past the file
+    h = json.dumps({"t": {"dtype": "F32", "shape": [5], "data_offsets": [0, 16]}}).encode()
+    expect(struct.pack("<Q", len(h)) + h + b"\0" * 16, "does not match")          # shape and extent disagree
+    h = json.dumps({"t": {"dtype": "Q4_K", "shape": [4], "data_offsets": [0, 16]}}).encode()
+    expect(struct.pack("<Q", len(h)) + h + b"\0" * 16, "unsupported dtype")
+    h = json.dumps({"t": {"dtype": "F32"}}).encode()
+    expect(struct.pack("<Q", len(h)) + h, "malformed entry")
+    with pytest.raises(WeightFormatError, match="no such file"):
+        SafetensorsFile(str(tmp_path / "absent"))
+    # truncation at every length of a good file is refused or leaves every tensor inside the file
+    from hfcpu_b200.weights import write_safetensors
+    write_safetensors(p, {"a": torch.ones(3, 5), "b": torch.zeros(7, dtype=torch.bfloat16)})
+    good = open(p, "rb").read()
+    for n in range(len(good)):
+        open(p, "wb").write(good[:n])
+        try:
+            f = SafetensorsFile(p)
+        except WeightFormatError:
+            continue
+        for name in f.names():
+            f.tensor(name)
+        f.close()
