@@ -6,6 +6,7 @@ entries in order, then the final norm and the head on the rows whose logits are 
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
@@ -111,10 +112,29 @@ def build_model_specs(config: ModelConfig) -> List[TensorSpec]:
 
 def load_model(folder: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0") -> Model:
     """Read ``config.json`` and ``model.safetensors`` from ``folder``; the model class follows config.json."""
+    if os.path.isfile(folder) and folder.endswith(".gguf"):
+        return load_gguf_model(folder, dtype, device)
     config = load_config(folder)
     model = Model(config, dtype, torch.device(device))
     tensors = load_tensors(folder, model.tensor_specs(), dtype, model.device)
     return model.bind(tensors)
+
+
+def load_gguf_model(path: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0") -> Model:
+    """The same from one of the reference's own GGUF files (float tensor types only)."""
+    from ..config import config_from_dict
+    from ..weights.gguf import read_gguf
+    from ..weights.loader import WeightError, storage_dtype
+    cfg_dict, tensors = read_gguf(path)
+    model = Model(config_from_dict(cfg_dict), dtype, torch.device(device))
+    specs = {s.name: s for s in model.tensor_specs()}
+    missing = [n for n, s in specs.items() if n not in tensors and not s.optional]
+    unexpected = sorted(set(tensors) - set(specs))
+    misshapen = [(n, tuple(tensors[n].shape), tuple(specs[n].shape)) for n in sorted(set(tensors) & set(specs))
+                 if tuple(tensors[n].shape) != tuple(specs[n].shape)]
+    if missing or unexpected or misshapen:
+        raise WeightError(path, missing, unexpected, misshapen)
+    return model.bind({n: t.to(storage_dtype(t.dtype, dtype)).to(model.device) for n, t in tensors.items()})
 
 
 def random_model(config: ModelConfig, seed: int = 0, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
