@@ -60,6 +60,20 @@ int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache,
                         const int32_t *positions, int block_size, int64_t num_pages, int window, float scale,
                         void *out, int T, int H, int G, int d, hfb_stream s);
 
+/* The same for bfloat16 with head_dim 64 or 128 and a block size that divides 64, tiled, on tensor cores.
+ * Tiles (tile_seq, tile_t0 = first token index, tile_nt = tokens) cover the step's tokens; a tile holds at
+ * most hfb_attention_fast_tile_tokens(H, G, warps) tokens of one request.  warps = 4 for prompt portions and
+ * mixed batches (splits must be 1), warps = 1 for decode, where `splits` > 1 cuts each request's keys into
+ * that many ranges whose partial results are merged in order; they live in `scratch`
+ * (hfb_attention_fast_scratch bytes). */
+int hfb_attention_fast_tile_tokens(int H, int G, int warps);
+size_t hfb_attention_fast_scratch(int T, int H, int d, int splits);
+int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+                       int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
+                       const int32_t *tile_nt, int n_tiles, int warps, int splits, int block_size,
+                       int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
+                       int T, int H, int G, int d, hfb_stream s);
+
 /* out[t, f] = silu(gu[t, f]) * gu[t, F + f] */
 int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, hfb_stream s);
 

@@ -69,6 +69,7 @@ class StepContext:
         self.h_kv_lens: List[int] = []
         self.h_seq_slots: List[int] = []
         self._groups: List[GroupMeta] = []
+        self._tiles: Dict[tuple, tuple] = {}
 
     def buf(self, name, shape, dtype) -> torch.Tensor:
         return self.engine.workspace.get(name, shape, dtype)
@@ -81,6 +82,11 @@ class StepContext:
 
     def entry_state(self, entry: int):
         return self.engine.slots.entry_state(entry)
+
+    def attn_tiles(self, heads_per_group: int, warps: int):
+        """Tiles of the step's tokens for the tiled attention kernel: (tile_seq, tile_t0, tile_nt, count), or
+        None when that many heads per group do not fit a tile of 16 * warps rows."""
+        return self._tiles.get((heads_per_group, warps))
 
 
 class Engine:
@@ -115,6 +121,9 @@ class Engine:
         for i, e in enumerate(plan.schedule):
             if e.cache_of is not None and e.cache_of not in cache_specs:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which keeps none")
+        # attention tilings the mixers will ask for: heads per key/value head of every paged-attention mixer
+        self._tile_ratios = sorted({m.H // m.G for m in (l.mixer for l in model.layers)
+                                    if hasattr(m, "H") and hasattr(m, "G") and m.G and m.H % m.G == 0})
         self.cache = KVCacheManager(cache_specs, self.block_size, self.num_pages, model.run_dtype,
                                     self.device, self.max_blocks)
         self.slots = StateSlots(state_specs, self.max_requests, self.device)
@@ -198,7 +207,22 @@ class Engine:
         kv_lens = [w[1] for w in wants]
         max_blocks_used = max((n + bs - 1) // bs for n in kv_lens)
         MB = max(1, max_blocks_used)
-        total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB)
+        q_lens = [len(e.tokens) for e in entries]
+        warps = 1 if max(q_lens) == 1 else 4
+        tilings = []
+        for ratio in self._tile_ratios:
+            per = (16 * warps) // ratio
+            if per < 1:
+                continue
+            t_seq, t_t0, t_nt, t0 = [], [], [], 0
+            for s_i, n in enumerate(q_lens):
+                for a in range(0, n, per):
+                    t_seq.append(s_i)
+                    t_t0.append(t0 + a)
+                    t_nt.append(min(per, n - a))
+                t0 += n
+            tilings.append((ratio, t_seq, t_t0, t_nt))
+        total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB) + sum(3 * len(t[1]) for t in tilings)
         ring_slot = self._meta_buffers(total)
         h, d = ring_slot[0], ring_slot[1]
         hl: List[int] = []
@@ -223,6 +247,8 @@ class Engine:
                 row = t[:MB] + [-1] * (MB - len(t[:MB]))
                 table_g += row
             hl += slots_g + table_g
+        for _, t_seq, t_t0, t_nt in tilings:
+            hl += t_seq + t_t0 + t_nt
         assert len(hl) == total
         h[:total] = torch.tensor(hl, dtype=torch.int32)
         d[:total].copy_(h[:total], non_blocking=True)
@@ -241,6 +267,9 @@ class Engine:
         ctx.cu_tokens, ctx.kv_lens, ctx.seq_slots, ctx.logit_rows = take(S + 1), take(S), take(S), take(M)
         for g in groups:
             ctx._groups.append(GroupMeta(g.index, take(T), take(S * MB, (S, MB)), bs, MB))
+        for ratio, t_seq, _, _ in tilings:
+            n = len(t_seq)
+            ctx._tiles[(ratio, warps)] = (take(n), take(n), take(n), n)
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, M
         ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots
         ctx.max_q_len = max(len(e.tokens) for e in entries)

@@ -46,6 +46,10 @@ class NativeBackend:
             raise KernelError(f"the CUDA library {path} could not be loaded: {e}") from None
         self.lib.hfb_last_error.restype = ctypes.c_char_p
         self.lib.hfb_linear_tc_workspace.restype = ctypes.c_size_t
+        self.lib.hfb_attention_fast_scratch.restype = ctypes.c_size_t
+        # "fast": tiled tensor-core attention where the sizes allow; "plain": one block per (token, head) always
+        self.attention = os.environ.get("HFB_ATTENTION", "fast")
+        self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         # "tc": tensor-core products where the operands allow; "plain": the float32-accumulating SIMT kernel always
         self.gemm = os.environ.get("HFB_GEMM", "tc")
         self._ws = None
@@ -112,6 +116,29 @@ class NativeBackend:
     def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out):
         self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out)
         T = q.shape[0]
+        tiles = getattr(ctx, "attn_tiles", None)
+        if (self.attention == "fast" and tiles is not None and q.dtype == torch.bfloat16 and d in (64, 128)
+                and 64 % meta.block_size == 0):
+            decode = ctx.max_q_len == 1
+            warps = 1 if decode else 4
+            tiling = tiles(H // G, warps)
+            if tiling is not None:
+                tile_seq, tile_t0, tile_nt, n_tiles = tiling
+                splits = 1
+                if decode:
+                    key_tiles = (ctx.max_kv_len + 63) // 64
+                    splits = max(1, min(4 * self.sm_count // max(1, n_tiles * G), max(1, key_tiles // 2)))
+                need = self.lib.hfb_attention_fast_scratch(c_int(T), c_int(H), c_int(d), c_int(splits))
+                scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
+                self._check(self.lib.hfb_attention_fast(
+                    _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
+                    _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(warps), c_int(splits),
+                    c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out),
+                    _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), self._stream()),
+                    "attention_fast")
+                if splits > 1:
+                    self.launches += 1
+                return
         self._check(self.lib.hfb_attention_plain(_p(q), _p(k_cache), _p(v_cache), c_int(_dt(q)), _p(meta.block_table),
                                                  c_int(meta.max_blocks), _p(ctx.token_seq), _p(ctx.positions),
                                                  c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window),

@@ -257,3 +257,66 @@ def test_linear_tensor_core(shape):
         b.gemm = "tc"
     assert float((logits - plain_out).abs().max()) / scale < 2e-5, "differs from the plain kernel"
     kernels.check_device_errors()
+
+
+def _with_tiles(case, lens_q, lens_kv, H, G):
+    """Adds what the tiled kernel needs to a case's context: the tile lists and the step's extents."""
+    q, kc, vc, meta, ctx = case
+    warps = 1 if max(lens_q) == 1 else 4
+    per = (16 * warps) // (H // G)
+    t_seq, t_t0, t_nt, t0 = [], [], [], 0
+    for s, n in enumerate(lens_q):
+        for a in range(0, n, per):
+            t_seq.append(s); t_t0.append(t0 + a); t_nt.append(min(per, n - a))
+        t0 += n
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tiles = (dev(t_seq), dev(t_t0), dev(t_nt), len(t_seq))
+    ws = {}
+
+    def buf(name, shape, dtype):
+        return ws.setdefault((name, shape, dtype), torch.empty(shape, dtype=dtype, device=DEV))
+    ctx.attn_tiles = lambda ratio, w: tiles if (ratio, w) == (H // G, warps) else None
+    ctx.max_q_len, ctx.max_kv_len, ctx.buf = max(lens_q), max(lens_kv), buf
+    return case
+
+
+FAST_GEOMS = [(28, 4, 128, 16), (14, 2, 64, 16), (6, 3, 64, 8), (4, 4, 128, 64), (16, 1, 64, 4), (8, 2, 128, 32)]
+
+
+@pytest.mark.parametrize("geom", FAST_GEOMS)
+@pytest.mark.parametrize("window", [0, 50, 300])
+def test_attention_tiled_mixed_and_decode(geom, window):
+    """The tiled tensor-core kernel in both forms: portions beside decode tokens (4 warps), and pure decode
+    with the keys split over CTAs (1 warp), against the torch reference and against the plain kernel."""
+    from hfcpu_b200 import kernels
+    H, G, d, bs = geom
+    b = kernels.backend()
+    for lens_q, lens_kv in (([1, 70, 1, 7, 2, 130], [300, 70, 1, 133, 64, 700]), ([1, 1, 1, 1, 1], [1, 64, 65, 1000, 2311])):
+        case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window), lens_q, lens_kv, H, G)
+        b.launches = 0
+        out = _run_attention(native(), case, H, G, d, window)
+        ref = _run_attention(EmuBackend(), case, H, G, d, window)
+        assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, window)
+        b.attention = "plain"
+        try:
+            plain_out = _run_attention(native(), case, H, G, d, window)
+        finally:
+            b.attention = "fast"
+        assert rel(out.float(), plain_out.float()) < TOL["bfloat16"]
+        again = _run_attention(native(), case, H, G, d, window)
+        assert torch.equal(out, again), "two calls differ"
+    kernels.check_device_errors()
+
+
+def test_attention_tiled_far_key_window_edge_and_page_edges():
+    H, G, d, bs = 28, 4, 128, 16
+    for lens_q, lens_kv, spike_req in (([1, 1], [200, 600], 1), ([5, 40], [200, 600], 1)):
+        for key_pos in (0, 15, 16, 63, 64, 303, 304, 559, 560, 599):
+            q_off = lens_q[spike_req] - 1
+            if key_pos > lens_kv[spike_req] - lens_q[spike_req] + q_off:
+                continue
+            for window in (0, 40):
+                case = _attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, 0, spike=(spike_req, key_pos, q_off), seed=key_pos)
+                case = _with_tiles(case, lens_q, lens_kv, H, G)
+                out, ref = _run_attention(native(), case, H, G, d, window), _run_attention(EmuBackend(), case, H, G, d, window)
+                assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, key_pos, window)
