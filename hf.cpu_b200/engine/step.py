@@ -9,6 +9,7 @@ the same order holds here: reserve, run, advance.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -41,6 +42,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[tuple, torch.Tensor] = {}
+        self._retired: List[torch.Tensor] = []      # outgrown buffers stay alive: captured graphs may point at them
 
     def get(self, name, shape, dtype) -> torch.Tensor:
         n = 1
@@ -49,6 +51,8 @@ class Workspace:
         key = (name, dtype)
         b = self._bufs.get(key)
         if b is None or b.numel() < n:
+            if b is not None:
+                self._retired.append(b)
             b = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = b
         return b[:n].view(*shape)
@@ -129,6 +133,11 @@ class Engine:
         self.slots = StateSlots(state_specs, self.max_requests, self.device)
         self.workspace = Workspace(self.device)
         self._pinned = self.device.type == "cuda"
+        # pure decode steps are captured once per (batch size, key-split bucket) as a CUDA graph and replayed
+        self.use_graphs = (self._pinned and os.environ.get("HFB_GRAPHS", "1") != "0"
+                           and all(getattr(p, "graph_safe", False) for p in model.all_parts()))
+        self._graphs: Dict[tuple, tuple] = {}
+        self._static_meta: Dict[int, torch.Tensor] = {}
         self._meta_ring = []            # [host buffer, device buffer, event of its last copy]
         self._meta_next = 0
         self.steps_run = 0
@@ -169,8 +178,10 @@ class Engine:
             slot[1] = torch.empty(cap, dtype=torch.int32, device=self.device)
         return slot
 
-    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Check the entries, reserve their pages (all or nothing) and build the step's batch arrays."""
+    def prepare(self, entries: Sequence[StepEntry], static: bool = False) -> StepContext:
+        """Check the entries, reserve their pages (all or nothing) and build the step's batch arrays.  With
+        ``static`` the arrays have a layout and device addresses that depend on the number of entries only
+        (block tables at full width, one device buffer per entry count), as graph replay needs."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         V = self.model.plan.vocab_size
@@ -206,7 +217,7 @@ class Engine:
         # one flat int32 buffer: a single host-to-device copy per step
         kv_lens = [w[1] for w in wants]
         max_blocks_used = max((n + bs - 1) // bs for n in kv_lens)
-        MB = max(1, max_blocks_used)
+        MB = self.max_blocks if static else max(1, max_blocks_used)
         q_lens = [len(e.tokens) for e in entries]
         warps = 1 if max(q_lens) == 1 else 4
         tilings = []
@@ -225,6 +236,10 @@ class Engine:
         total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB) + sum(3 * len(t[1]) for t in tilings)
         ring_slot = self._meta_buffers(total)
         h, d = ring_slot[0], ring_slot[1]
+        if static:
+            d = self._static_meta.get(S)
+            if d is None or d.numel() < total:
+                d = self._static_meta[S] = torch.empty(total, dtype=torch.int32, device=self.device)
         hl: List[int] = []
         tok, pos, seq, cu, rows = [], [], [], [0], []
         for s, e in enumerate(entries):
@@ -274,15 +289,41 @@ class Engine:
         ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots
         ctx.max_q_len = max(len(e.tokens) for e in entries)
         ctx.max_kv_len = max(kv_lens)
+        # how finely decode attention may split a request's keys: a power of two, so that few graphs exist
+        hint = max(1, ((ctx.max_kv_len + 63) // 64) // 2)
+        ctx.decode_split_hint = 1 << (min(hint, 64).bit_length() - 1)
         return ctx
+
+    def _replay(self, ctx: StepContext) -> torch.Tensor:
+        """A decode step through its CUDA graph: the first step of a kind runs eagerly (it sizes the scratch
+        buffers), the second is captured, later ones are replayed on the arrays ``prepare`` has just refreshed."""
+        key = (ctx.num_seqs, ctx.decode_split_hint)
+        state = self._graphs.get(key)
+        if state is None:
+            self._graphs[key] = ("warm", None, None)
+            return self.model.forward(ctx)
+        if state[0] == "warm":
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                logits = self.model.forward(ctx)
+            self._graphs[key] = ("ready", graph, logits)
+            graph.replay()
+            return logits
+        state[1].replay()
+        return state[2]
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run one step; returns float32 logits ``[wanted, vocab]`` (device), in the order of the entries and
         of their ``want`` lists, or None when nothing is wanted.  The returned tensor is scratch that the
         next step overwrites."""
         entries = list(entries)
-        ctx = self.prepare(entries)
-        logits = self.model.forward(ctx)
+        graphable = self.use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+        ctx = self.prepare(entries, static=graphable)
+        if graphable:
+            logits = self._replay(ctx)
+        else:
+            logits = self.model.forward(ctx)
         for e in entries:
             self.cache.advance(e.req, self.cache.length(e.req) + len(e.tokens))
         self.steps_run += 1

@@ -126,8 +126,8 @@ class NativeBackend:
                 tile_seq, tile_t0, tile_nt, n_tiles = tiling
                 splits = 1
                 if decode:
-                    key_tiles = (ctx.max_kv_len + 63) // 64
-                    splits = max(1, min(4 * self.sm_count // max(1, n_tiles * G), max(1, key_tiles // 2)))
+                    hint = getattr(ctx, "decode_split_hint", max(1, ((ctx.max_kv_len + 63) // 64) // 2))
+                    splits = max(1, min(4 * self.sm_count // max(1, n_tiles * G), hint))
                 need = self.lib.hfb_attention_fast_scratch(c_int(T), c_int(H), c_int(d), c_int(splits))
                 scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
                 self._check(self.lib.hfb_attention_fast(

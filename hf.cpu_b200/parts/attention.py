@@ -20,6 +20,8 @@ from .base import CacheSpec, Mixer, register_part
 
 
 class PagedAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, out_bias: bool, window: int, position, prefix: str,
                  positions=None, names=None, **_):

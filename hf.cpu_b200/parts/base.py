@@ -59,6 +59,10 @@ class StateSpec:
 
 
 class Part:
+    # True when forward() only launches kernels on tensors at stable addresses and reads nothing of the step
+    # on the host, so that a decode step may be captured once as a CUDA graph and replayed
+    graph_safe = False
+
     def tensor_specs(self) -> List[TensorSpec]:
         """The checkpoint tensors this part needs."""
         return []

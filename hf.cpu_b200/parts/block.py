@@ -5,6 +5,8 @@ from .base import Block, register_part
 
 
 class PreNormResidual(Block):
+    graph_safe = True
+
     def __init__(self, **_):
         pass
 

@@ -11,6 +11,8 @@ from .base import Part, register_part
 
 
 class Embedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tensor: str, **_):
         self.vocab_size, self.hidden_size, self.tensor = int(vocab_size), int(hidden_size), tensor
         self.table = None
@@ -27,6 +29,8 @@ class Embedding(Part):
 
 
 class LinearHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tensor: str, tied_to=None, **_):
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.tensor, self.tied_to = tensor, tied_to

@@ -12,6 +12,8 @@ from .base import FeedForward, register_part
 
 
 class SwiGlu(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, names=None, **_):
         self.E, self.F = int(hidden_size), int(intermediate_size)
         n = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}

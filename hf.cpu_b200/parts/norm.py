@@ -9,6 +9,8 @@ from .base import Norm, register_part
 
 
 class RmsNorm(Norm):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float, tensor: str, **_):
         self.size, self.eps, self.tensor = int(size), float(eps), tensor
         self.weight = None

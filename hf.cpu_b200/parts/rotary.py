@@ -15,6 +15,8 @@ from .base import PositionEncoding, register_part
 
 
 class Rotary(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, n_rot: int, theta: float, pairing: str = "half", **_):
         if pairing != "half":
             raise UnsupportedError(f"rotary pairing '{pairing}' is not supported (only 'half')")

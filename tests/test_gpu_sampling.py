@@ -54,7 +54,8 @@ def test_device_sampler_equals_host_mirror(V):
                     order = sorted(range(V), key=lambda i: (-logits[m][i], i))
                     a, b = sorted((order.index(got[m]), order.index(want)))
                     pr = np.exp((logits[m][order] - logits[m][order[0]]).astype(np.float64) / temp)
-                    assert b - a <= 1 or pr[a + 1:b + 1].sum() / pr.sum() < 1e-5, (temp, k, tp, mp, m)
+                    # (float32 running sums over n candidates are themselves only good to about n * 2^-24)
+                    assert b - a <= 1 or pr[a + 1:b + 1].sum() / pr.sum() < max(1e-5, V * 6e-8), (temp, k, tp, mp, m)
                     assert temp > 0 and not (0 < k <= 1024 and k < V), "the sorted path must agree exactly"
                     mismatches += draw != 5          # at the largest draw the tail's rounding decides
     assert mismatches <= 3

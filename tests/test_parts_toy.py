@@ -1,0 +1,215 @@
+"""Generality of the parts: a toy mixer with state of its own, a layer that runs twice, a layer that reads
+another layer's cache — all registered from here, without a change to the framework's files.
+
+Each case runs on the CPU with the torch stand-in for the kernels and, marked gpu, on the CUDA library.
+"""
+import dataclasses
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import traces
+from conftest import TINY_A, TINY_B, make_folder, make_requests
+
+DEVICES = [pytest.param("cpu", id="cpu"), pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu)]
+
+
+@pytest.fixture
+def backend(request):
+    from hfcpu_b200 import kernels
+    from emu_backend import EmuBackend
+    dev = request.param
+    old = kernels._backend
+    if dev == "cpu":
+        kernels.set_backend(EmuBackend())
+    yield dev
+    kernels.set_backend(old)
+
+
+# ---- a toy mixer with per-request state: a decaying sum of projected tokens ---------------------------
+def _toy_parts():
+    from hfcpu_b200.parts import Mixer, StateSpec
+    from hfcpu_b200.weights import TensorSpec
+
+    class DecayingSum(Mixer):
+        """state_t = decay * state_{t-1} + x_t W^T;  out_t = state_t.  The state lives in the request's slot."""
+
+        def __init__(self, hidden_size, decay, prefix, **_):
+            self.E, self.decay, self.name = hidden_size, decay, f"{prefix}.w"
+            self.w = None
+
+        def state_spec(self):
+            return StateSpec((self.E,), torch.float32)
+
+        def tensor_specs(self):
+            return [TensorSpec(self.name, (self.E, self.E))]
+
+        def bind(self, tensors, run_dtype, device):
+            self.w = tensors[self.name].float()
+
+        def forward(self, ctx, xn, residual, cache, state, write_cache):
+            assert cache is None and state is not None
+            proj = xn.float() @ self.w.T
+            for s in range(ctx.num_seqs):
+                a, b, slot = ctx.h_cu_tokens[s], ctx.h_cu_tokens[s + 1], ctx.h_seq_slots[s]
+                st = state[slot].clone()
+                for t in range(a, b):                     # tokens of a request in order, from the slot's state
+                    st = self.decay * st + proj[t]
+                    residual[t] += st
+                state[slot] = st
+    return DecayingSum
+
+
+@dataclass
+class ToyConfig:
+    """Alternates the toy mixer and paged attention; sizes unlike either tiny Qwen2 configuration."""
+    architecture: str = "ToyForCausalLM"
+    layers: int = 4
+    hidden: int = 48
+    heads: int = 3
+    head_dim: int = 16
+    ffn: int = 80
+    vocab: int = 130
+    positions: int = 256
+    decay: float = 0.75
+
+    @classmethod
+    def from_dict(cls, d):
+        return cls(**{k: v for k, v in d.items() if k in {f.name for f in dataclasses.fields(cls)}})
+
+    def to_dict(self):
+        d = dataclasses.asdict(self)
+        d["architectures"] = [d.pop("architecture")]
+        return d
+
+    def save(self, folder):
+        import json, os
+        os.makedirs(folder, exist_ok=True)
+        json.dump(self.to_dict(), open(os.path.join(folder, "config.json"), "w"))
+
+    def plan(self):
+        from hfcpu_b200.config import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+        E = self.hidden
+        norm = lambda n: PartSpec("rmsnorm", {"size": E, "eps": 1e-5, "tensor": n})
+        layers = []
+        for l in range(self.layers):
+            p = f"toy.{l}"
+            if l % 2 == 0:
+                mixer = PartSpec("toy_decaying_sum", {"hidden_size": E, "decay": self.decay, "prefix": f"{p}.mix"})
+            else:
+                mixer = PartSpec("paged_attention", {"hidden_size": E, "num_heads": self.heads, "num_kv_heads": self.heads,
+                                                     "head_dim": self.head_dim, "qkv_bias": False, "out_bias": False,
+                                                     "window": 0, "position": "rope", "prefix": f"{p}.attn"})
+            layers.append(LayerSpec(p, PartSpec("prenorm_residual"), norm(f"{p}.n1"), mixer, norm(f"{p}.n2"),
+                                    PartSpec("swiglu", {"hidden_size": E, "intermediate_size": self.ffn, "prefix": f"{p}.ffn"})))
+        return ModelPlan(E, self.vocab, self.positions,
+                         PartSpec("embedding", {"vocab_size": self.vocab, "hidden_size": E, "tensor": "toy.embed"}),
+                         {"rope": PartSpec("rotary", {"head_dim": self.head_dim, "n_rot": self.head_dim, "theta": 500.0})},
+                         layers, [ScheduleEntry(l) for l in range(self.layers)], norm("toy.norm"),
+                         PartSpec("linear_head", {"vocab_size": self.vocab, "hidden_size": E, "tensor": "toy.head"}))
+
+
+def _toy_reference(cfg, W, ids):
+    """The toy model on one whole sequence, with the plain implementation's parts."""
+    x = plain.embed(ids, W["toy.embed"])
+    T = len(ids)
+    cos, sin = plain.rope_angles(range(T), cfg.head_dim, 500.0, torch.float64)
+    for l in range(cfg.layers):
+        p = f"toy.{l}"
+        xn = plain.rmsnorm(x, W[f"{p}.n1"], 1e-5)
+        if l % 2 == 0:
+            proj, st, outs = xn @ W[f"{p}.mix.w"].T, torch.zeros(cfg.hidden, dtype=torch.float64), []
+            for t in range(T):
+                st = cfg.decay * st + proj[t]
+                outs.append(st)
+            x = x + torch.stack(outs)
+        else:
+            H, d = cfg.heads, cfg.head_dim
+            q = plain.rope((xn @ W[f"{p}.attn.q_proj.weight"].T).view(T, H, d), cos, sin, d)
+            k = plain.rope((xn @ W[f"{p}.attn.k_proj.weight"].T).view(T, H, d), cos, sin, d)
+            v = (xn @ W[f"{p}.attn.v_proj.weight"].T).view(T, H, d)
+            x = x + plain.attention(q, k, v, H, H, 0).reshape(T, H * d) @ W[f"{p}.attn.o_proj.weight"].T
+        xn = plain.rmsnorm(x, W[f"{p}.n2"], 1e-5)
+        x = x + plain.swiglu_ffn(xn, W[f"{p}.ffn.gate_proj.weight"], W[f"{p}.ffn.up_proj.weight"], W[f"{p}.ffn.down_proj.weight"])
+    return plain.rmsnorm(x, W["toy.norm"], 1e-5) @ W["toy.head"].T
+
+
+@pytest.mark.parametrize("backend", DEVICES, indirect=True)
+def test_toy_mixer_with_state_is_registered_built_and_stepped(backend, tmp_path):
+    import hfcpu_b200
+    from hfcpu_b200.config import unregister_architecture
+    from hfcpu_b200.parts import unregister_part
+    hfcpu_b200.register_part("mixer", "toy_decaying_sum", _toy_parts())
+    hfcpu_b200.register_architecture("ToyForCausalLM", ToyConfig)
+    try:
+        cfg = ToyConfig()
+        folder = hfcpu_b200.write_random_model(cfg, str(tmp_path / "toy"), seed=4, dtype=torch.float32, std=0.3)
+        model = hfcpu_b200.load_model(folder, torch.float32, backend)       # the class follows config.json
+        assert type(model.config).__name__ == "ToyConfig"
+        g = torch.Generator().manual_seed(0)
+        reqs = {f"r{i}": torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for i, n in enumerate([40, 9, 77, 23])}
+        _, W = plain.read_folder(folder)
+        ref = {r: _toy_reference(cfg, W, ids) for r, ids in reqs.items()}
+        for steps in (traces.whole(reqs), traces.portions(reqs), traces.mixed(reqs, max_live=3)):
+            eng = hfcpu_b200.Engine(model, block_size=8, max_tokens=traces.peak_tokens(steps), max_requests=3)
+            assert sorted(eng.slots.tensors) == [0, 2] and eng.slots.bytes_per_request() == 2 * 48 * 4
+            assert [g_.entries for g_ in eng.cache.groups] == [[1, 3]]
+            got = traces.run_in_process(eng, steps, check=eng.cache.check)
+            bad = traces.first_bad(got, ref, 1e-4)
+            assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
+            eng.slots.check()
+    finally:
+        unregister_part("mixer", "toy_decaying_sum")
+        unregister_architecture("ToyForCausalLM")
+
+
+# ---- the run order is data: a layer named twice, a layer reading another entry's cache --------------------
+def _scheduled_reference(cfg, W, ids, schedule):
+    """schedule: list of (layer, cache_of); an entry with cache_of = j attends over the keys and values that
+    entry j computed, with queries of its own."""
+    H, G = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = cfg.get("head_dim") or cfg["hidden_size"] // H
+    eps, T = cfg["rms_norm_eps"], len(ids)
+    W = {k: v.double() for k, v in W.items()}
+    x = plain.embed(ids, W["model.embed_tokens.weight"])
+    cos, sin = plain.rope_angles(range(T), d, cfg["rope_theta"], torch.float64)
+    kv = {}
+    for i, (l, cache_of) in enumerate(schedule):
+        p = f"model.layers.{l}."
+        xn = plain.rmsnorm(x, W[p + "input_layernorm.weight"], eps)
+        q = plain.rope((xn @ W[p + "self_attn.q_proj.weight"].T + W[p + "self_attn.q_proj.bias"]).view(T, H, d), cos, sin, d)
+        if cache_of is None:
+            k = plain.rope((xn @ W[p + "self_attn.k_proj.weight"].T + W[p + "self_attn.k_proj.bias"]).view(T, G, d), cos, sin, d)
+            v = (xn @ W[p + "self_attn.v_proj.weight"].T + W[p + "self_attn.v_proj.bias"]).view(T, G, d)
+            kv[i] = (k, v)
+        else:
+            k, v = kv[cache_of]
+        x = x + plain.attention(q, k, v, H, G, plain.window_of_layer(cfg, l)).reshape(T, H * d) @ W[p + "self_attn.o_proj.weight"].T
+        xn = plain.rmsnorm(x, W[p + "post_attention_layernorm.weight"], eps)
+        x = x + plain.swiglu_ffn(xn, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"], W[p + "mlp.down_proj.weight"])
+    head = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else W["lm_head.weight"]
+    return plain.rmsnorm(x, W["model.norm.weight"], eps) @ head.T
+
+
+@pytest.mark.parametrize("backend", DEVICES, indirect=True)
+def test_schedule_names_a_layer_twice_and_shares_a_cache(backend, tmp_path):
+    import hfcpu_b200
+    from hfcpu_b200.config import ScheduleEntry, config_from_dict
+    folder = make_folder(dict(TINY_B, use_sliding_window=False), str(tmp_path / "m"), 5, torch.float32)
+    cfg = config_from_dict(dict(TINY_B, use_sliding_window=False))
+    order = [(0, None), (1, None), (1, None), (2, 1), (0, None)]
+    plan = dataclasses.replace(cfg.plan(), schedule=[ScheduleEntry(l, c) for l, c in order])
+    model = hfcpu_b200.Model(cfg, torch.float32, torch.device(backend), plan=plan)
+    from hfcpu_b200.weights import load_tensors
+    model.bind(load_tensors(folder, model.tensor_specs(), torch.float32, model.device))
+    reqs = make_requests("B", [50, 21, 90], seed=12)
+    pcfg, W = plain.read_folder(folder)
+    ref = {r: _scheduled_reference(pcfg, W, ids, order) for r, ids in reqs.items()}
+    for steps in (traces.whole(reqs), traces.mixed(reqs, max_live=2)):
+        eng = hfcpu_b200.Engine(model, block_size=8, max_tokens=traces.peak_tokens(steps), max_requests=2)
+        assert [g.entries for g in eng.cache.groups] == [[0, 1, 2, 4]]           # entry 3 keeps no cache of its own
+        got = traces.run_in_process(eng, steps, check=eng.cache.check)
+        bad = traces.first_bad(got, ref, 1e-4)
+        assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
