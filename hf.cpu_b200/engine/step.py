@@ -304,13 +304,21 @@ class Engine:
             return self.model.forward(ctx)
         if state[0] == "warm":
             torch.cuda.synchronize(self.device)
+            from .. import kernels
+            backend = kernels.backend()
+            before = getattr(backend, "launches", 0)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 logits = self.model.forward(ctx)
-            self._graphs[key] = ("ready", graph, logits)
-            graph.replay()
-            return logits
+            captured = getattr(backend, "launches", 0) - before        # kernels one replay launches
+            self._graphs[key] = ("ready", graph, logits, captured)
+            backend.launches = before
+        state = self._graphs[key]
         state[1].replay()
+        from .. import kernels
+        backend = kernels.backend()
+        if hasattr(backend, "launches"):
+            backend.launches += state[3]
         return state[2]
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
