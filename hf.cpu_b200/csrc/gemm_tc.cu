@@ -518,3 +518,114 @@ extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int
     }
     return HFB_OK;
 }
+
+// ---- the entry point that allocates nothing (see hfb200_noalloc.h) ----------------------------------------
+#include "hfb200_noalloc.h"
+
+namespace hfb {
+
+// Split-K partial sums of hfb_linear_tc_noalloc.  In host code this name is only a handle for
+// cudaGetSymbolAddress; the kernels get the device address that call returns.
+static __device__ __align__(256) float g_noalloc_scratch[HFB_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+// Device address of the array on the current device, looked up at the first call on that device.
+static int noalloc_scratch(float **out)
+{
+    static float *ptr[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(HFB_ECUDA, "linear_tc_noalloc: no current device");
+    if (!ptr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return fail(HFB_ECUDA, "linear_tc_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        ptr[dev] = (float *)p;
+    }
+    *out = ptr[dev];
+    return HFB_OK;
+}
+
+// The same map as tensor_map() builds, written into the caller's storage without touching the cache.
+static int tensor_map_uncached(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *out)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(HFB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(HFB_ECUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return HFB_OK;
+}
+
+}  // namespace hfb
+
+extern "C" int hfb_linear_tc_noalloc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
+                                     int accumulate, int M, int N, int K, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) return HFB_OK;
+    if (K <= 0 || (K & 7)) return fail(HFB_ENOTSUP, "linear_tc_noalloc: K = %d must be a positive multiple of 8", K);
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
+        return fail(HFB_ENOTSUP, "linear_tc_noalloc: operands must be 16-byte aligned");
+    if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "linear_tc_noalloc: bad element types");
+    if (accumulate && out_dt != HFB_F32) return fail(HFB_EINVAL, "linear_tc_noalloc: accumulation needs a float32 output");
+    size_t need = hfb_linear_tc_workspace(M, N, K);
+    if (need > HFB_NOALLOC_SCRATCH_BYTES)
+        return fail(HFB_ERANGE, "linear_tc_noalloc: split-K partial sums for M=%d N=%d K=%d take %zu bytes, the built-in "
+                                "array holds %u; use hfb_linear_tc with a workspace of your own", M, N, K, need,
+                    (unsigned)HFB_NOALLOC_SCRATCH_BYTES);
+    float *scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc != HFB_OK) return rc;
+    cudaStream_t st = (cudaStream_t)s;
+    GemmParams p{};
+    p.M = M; p.N = N; p.K = K;
+    p.out = out; p.out_dt = out_dt; p.bias = bias; p.bias_dt = bias_dt;
+    p.mode = accumulate ? EPI_ADD : EPI_STORE;
+    p.kb_total = (K + BK - 1) / BK;
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    p.swapped = M <= 128;
+    int bn = 256;
+    if (p.swapped) {
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+        p.tiles_x = (N + TILE_X - 1) / TILE_X;
+        p.tiles_y = 1;
+        if (need) {
+            int splits = (int)(need / ((size_t)M * N * sizeof(float)));
+            p.kb_per_split = (p.kb_total + splits - 1) / splits;
+            p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+            if (p.splits > 1) { p.partial = scratch; p.mode = EPI_PARTIAL; }
+            else p.kb_per_split = p.kb_total;
+        }
+    } else {
+        p.tiles_x = (M + TILE_X - 1) / TILE_X;
+        p.tiles_y = (N + bn - 1) / bn;
+    }
+    CUtensorMap mx, my;
+    if (p.swapped) {
+        if ((rc = tensor_map_uncached(w, N, K, TILE_X, &mx)) != HFB_OK) return rc;
+        if ((rc = tensor_map_uncached(a, M, K, bn, &my)) != HFB_OK) return rc;
+    } else {
+        if ((rc = tensor_map_uncached(a, M, K, TILE_X, &mx)) != HFB_OK) return rc;
+        if ((rc = tensor_map_uncached(w, N, K, bn, &my)) != HFB_OK) return rc;
+    }
+    switch (bn) {
+    case 16: rc = launch<16, 10>(mx, my, p, st); break;
+    case 32: rc = launch<32, 9>(mx, my, p, st); break;
+    case 64: rc = launch<64, 8>(mx, my, p, st); break;
+    case 128: rc = launch<128, 6>(mx, my, p, st); break;
+    default: rc = launch<256, 4>(mx, my, p, st); break;
+    }
+    if (rc != HFB_OK) return rc;
+    if (p.mode == EPI_PARTIAL) {
+        size_t MN = (size_t)M * N;
+        splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
+                                                                          accumulate ? EPI_ADD : EPI_STORE);
+        return check_launch("splitk_reduce");
+    }
+    return HFB_OK;
+}
