@@ -83,13 +83,14 @@ __global__ void rope_kv_write_kernel(const T *qkv, const float *cos_sin, int n_r
 
 // ---- SwiGLU (src/model.c:532-538, src/mathx.c:34) ----------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total)
+__global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total, int interleaved)
 {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t t = i / F;
     int f = (int)(i % F);
-    float g = to_f32(gu[t * 2 * F + f]), u = to_f32(gu[t * 2 * F + F + f]);
+    // gate and up either fill the two halves of a row or alternate along it
+    float g = to_f32(gu[t * 2 * F + (interleaved ? 2 * f : f)]), u = to_f32(gu[t * 2 * F + (interleaved ? 2 * f + 1 : F + f)]);
     out[i] = from_f32<T>((g / (1.0f + expf(-g))) * u);
 }
 
@@ -161,14 +162,14 @@ extern "C" int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, 
     return check_launch("rope_kv_write");
 }
 
-extern "C" int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, hfb_stream s)
+extern "C" int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved, hfb_stream s)
 {
     if (T <= 0) return HFB_OK;
     if (!valid_dt(dt) || F <= 0) return fail(HFB_EINVAL, "swiglu: bad arguments");
     size_t total = (size_t)T * F;
     unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dt == HFB_F32) swiglu_kernel<float><<<blocks, 256, 0, (cudaStream_t)s>>>((const float *)gu, (float *)out, F, total);
-    else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, F, total);
+    if (dt == HFB_F32) swiglu_kernel<float><<<blocks, 256, 0, (cudaStream_t)s>>>((const float *)gu, (float *)out, F, total, interleaved);
+    else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, F, total, interleaved);
     return check_launch("swiglu");
 }
 

@@ -1,0 +1,196 @@
+// Kernels that finish a split-K product and do the next memory-bound step in the same pass (decode path).
+//
+// With few tokens the tensor-core product leaves float32 partial sums [splits, M, N].  Summing them (in split
+// order), adding bias and residual, and normalising the row for the next product are one pass over a row here
+// instead of three kernels; likewise the sum, bias, rotary encoding and cache write of the q|k|v product.
+// Arithmetic as in the separate kernels: src/model.c:606-611 (residual, then RMSNorm, src/mathx.c:65-75) and
+// src/model.c:581-601 (bias after the dot, rotation, cache write).
+#include "common.cuh"
+
+namespace hfb {
+int *error_word();
+
+// residual[m, :] += sum_s partial[s, m, :] (+ bias);  xn[m, :] = residual[m, :] * rsqrt(mean(residual^2) + eps) * w
+__global__ void reduce_residual_norm_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
+                                            float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt)
+{
+    const int m = blockIdx.x;
+    const size_t MN = (size_t)M * N;
+    float *res = residual + (size_t)m * N;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += partial[(size_t)s * MN + (size_t)m * N + i];
+        if (bias) v += load_any(bias, bias_dt, i);
+        v += res[i];
+        res[i] = v;
+        ss += v * v;
+    }
+    __shared__ float part[32];
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nw ? part[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) part[0] = t;
+    }
+    __syncthreads();
+    if (!xn) return;
+    const float r = 1.0f / sqrtf(part[0] / (float)N + eps);
+    for (int i = threadIdx.x; i < N; i += blockDim.x)       // each thread re-reads what it wrote itself
+        store_any(xn, xn_dt, (size_t)m * N + i, (res[i] * r) * load_any(w, w_dt, i));
+}
+
+// q|k|v row = sum_s partial[s, t, :] + bias; rotate q and k; q -> q_out, k and v -> the paged cache.
+template <typename T>
+__global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, const void *bias, int bias_dt,
+                                      const float *cos_sin, int n_rot, int n_positions, const int32_t *positions,
+                                      const int32_t *slots, T *q_out, T *k_cache, T *v_cache, long long cache_slots,
+                                      int H, int G, int d, int *err)
+{
+    const int t = blockIdx.x, head = blockIdx.y;
+    const int N = (H + 2 * G) * d;
+    const size_t TN = (size_t)Tn * N, row = (size_t)t * N + (size_t)head * d;
+    T *dst;
+    bool rotate;
+    if (head < H) {
+        dst = q_out + (size_t)t * H * d + (size_t)head * d;
+        rotate = true;
+    } else {
+        if (!slots) return;
+        long long slot = slots[t];
+        if (slot < 0) return;
+        if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        if (head < H + G) { dst = k_cache + ((size_t)slot * G + (head - H)) * d; rotate = true; }
+        else { dst = v_cache + ((size_t)slot * G + (head - H - G)) * d; rotate = false; }
+    }
+    auto value = [&](int i) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += partial[(size_t)s * TN + row + i];
+        if (bias) v += load_any(bias, bias_dt, (size_t)head * d + i);
+        return v;
+    };
+    const int half = n_rot / 2;
+    if (rotate && half > 0) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= n_positions) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+        const float *cs = cos_sin + (size_t)pos * half * 2;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float c = cs[2 * i], s = cs[2 * i + 1];
+            float a = value(i), b = value(i + half);
+            // the separate kernels round q|k|v to the run type before rotating; keep the same values
+            a = to_f32(from_f32<T>(a)); b = to_f32(from_f32<T>(b));
+            dst[i] = from_f32<T>(a * c - b * s);
+            dst[i + half] = from_f32<T>(a * s + b * c);
+        }
+        for (int i = n_rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(value(i));
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(value(i));
+    }
+}
+
+// arg-max in two passes so that many blocks share a row: (value, index) per chunk, then the best chunk.
+__global__ void argmax_chunks_kernel(const float *logits, int V, int chunk, float *best_v, int32_t *best_i)
+{
+    const int row = blockIdx.y, c = blockIdx.x;
+    const float *p = logits + (size_t)row * V;
+    const int lo = c * chunk, hi = min(V, lo + chunk);
+    float best = 0.f;
+    int bi = -1;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float v = p[i];
+        if (bi < 0 || v > best) { best = v; bi = i; }
+    }
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    sv[threadIdx.x] = best; si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+            float v2 = sv[threadIdx.x + o], v1 = sv[threadIdx.x];
+            int i2 = si[threadIdx.x + o], i1 = si[threadIdx.x];
+            if (i2 >= 0 && (i1 < 0 || v2 > v1 || (v2 == v1 && i2 < i1))) { sv[threadIdx.x] = v2; si[threadIdx.x] = i2; }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { best_v[(size_t)row * gridDim.x + c] = sv[0]; best_i[(size_t)row * gridDim.x + c] = si[0]; }
+}
+
+__global__ void argmax_final_kernel(const float *best_v, const int32_t *best_i, int chunks, int32_t *out)
+{
+    const int row = blockIdx.x;
+    float best = 0.f;
+    int bi = -1;
+    for (int c = threadIdx.x; c < chunks; c += 32) {
+        float v = best_v[(size_t)row * chunks + c];
+        int i = best_i[(size_t)row * chunks + c];
+        if (i >= 0 && (bi < 0 || v > best || (v == best && i < bi))) { best = v; bi = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        float v2 = __shfl_xor_sync(0xffffffffu, best, o);
+        int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (i2 >= 0 && (bi < 0 || v2 > best || (v2 == best && i2 < bi))) { best = v2; bi = i2; }
+    }
+    if (threadIdx.x == 0) out[row] = bi < 0 ? 0 : bi;
+}
+
+}  // namespace hfb
+
+using namespace hfb;
+
+extern "C" int hfb_reduce_residual_norm(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
+                                        float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt,
+                                        hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (splits < 1 || N <= 0 || (bias && !valid_dt(bias_dt)) || (xn && (!valid_dt(w_dt) || !valid_dt(xn_dt))))
+        return fail(HFB_EINVAL, "reduce_residual_norm: bad arguments");
+    int threads = N >= 2048 ? 512 : (N >= 512 ? 256 : 128);
+    reduce_residual_norm_kernel<<<M, threads, 0, (cudaStream_t)s>>>(partial, splits, M, N, bias, bias_dt, residual, w, w_dt, eps, xn, xn_dt);
+    return check_launch("reduce_residual_norm");
+}
+
+extern "C" int hfb_reduce_rope_kv(const float *partial, int splits, int dt, const void *bias, int bias_dt,
+                                  const float *cos_sin, int n_rot, int n_positions, const int32_t *positions,
+                                  const int32_t *slots, void *q_out, void *k_cache, void *v_cache, int64_t cache_slots,
+                                  int T, int H, int G, int d, hfb_stream s)
+{
+    if (T <= 0) return HFB_OK;
+    if (!valid_dt(dt) || splits < 1 || H <= 0 || G <= 0 || d <= 0 || n_rot < 0 || n_rot > d || (n_rot & 1) || (bias && !valid_dt(bias_dt)))
+        return fail(HFB_EINVAL, "reduce_rope_kv: bad arguments");
+    if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "reduce_rope_kv: rotation needs a table and positions");
+    if (H + 2 * G > 65535) return fail(HFB_ENOTSUP, "reduce_rope_kv: %d heads exceed the grid limit", H + 2 * G);
+    dim3 grid(T, H + 2 * G);
+    int threads = d >= 128 ? 64 : 32;
+    cudaStream_t st = (cudaStream_t)s;
+    if (dt == HFB_F32)
+        reduce_rope_kv_kernel<float><<<grid, threads, 0, st>>>(partial, splits, T, bias, bias_dt, cos_sin, n_rot, n_positions, positions,
+            slots, (float *)q_out, (float *)k_cache, (float *)v_cache, cache_slots, H, G, d, error_word());
+    else
+        reduce_rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(partial, splits, T, bias, bias_dt, cos_sin, n_rot, n_positions,
+            positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, cache_slots, H, G, d, error_word());
+    return check_launch("reduce_rope_kv");
+}
+
+// Floats + ints of scratch hfb_argmax2 needs for M rows of V logits.
+extern "C" size_t hfb_argmax2_scratch(int M, int V)
+{
+    int chunks = (V + 4095) / 4096;
+    return (size_t)M * chunks * 8;
+}
+
+extern "C" int hfb_argmax2(const float *logits, int32_t *out, int M, int V, void *scratch, size_t scratch_bytes, hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (V <= 0) return fail(HFB_EINVAL, "argmax: empty vocabulary");
+    int chunks = (V + 4095) / 4096;
+    if (!scratch || scratch_bytes < hfb_argmax2_scratch(M, V)) return fail(HFB_EINVAL, "argmax: scratch too small");
+    if (M > 65535) return fail(HFB_ENOTSUP, "argmax: %d rows exceed the grid limit", M);
+    float *bv = (float *)scratch;
+    int32_t *bi = (int32_t *)(bv + (size_t)M * chunks);
+    argmax_chunks_kernel<<<dim3(chunks, M), 256, 0, (cudaStream_t)s>>>(logits, V, 4096, bv, bi);
+    argmax_final_kernel<<<M, 32, 0, (cudaStream_t)s>>>(bv, bi, chunks, out);
+    return check_launch("argmax2");
+}

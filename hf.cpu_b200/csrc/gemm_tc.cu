@@ -34,7 +34,7 @@ constexpr uint32_t X_BYTES = TILE_X * BK * 2;
 constexpr int GEMM_THREADS = 192;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
 
 struct GemmParams {
     int M, N, K;                       // logical sizes: tokens, output features, inner
@@ -261,7 +261,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tmem_ld16(taddr + c0, v);
                 tmem_wait_ld();
                 const int y0 = ty * BN + c0;          // first row of Y in this chunk
-                if (p.swapped) {
+                if (p.swapped && p.mode == EPI_SWIGLU) {
+                    // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2]
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        float mine = __uint_as_float(v[i]);
+                        float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+                        int tok = y0 + i;
+                        if (!(lane & 1) && xr + 1 < p.N && tok < p.M)
+                            store_any(p.out, p.out_dt, (size_t)tok * (p.N >> 1) + (xr >> 1), (mine / (1.0f + expf(-mine))) * other);
+                    }
+                } else if (p.swapped) {
                     // xr = output feature, y = token
                     if (xr < p.N) {
                         float b = (p.bias && p.mode != EPI_PARTIAL) ? load_any(p.bias, p.bias_dt, xr) : 0.f;
@@ -274,6 +284,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             if (p.mode == EPI_PARTIAL) p.partial[(size_t)split * p.M * p.N + o] = val;
                             else if (p.mode == EPI_ADD) ((float *)p.out)[o] += val;
                             else store_any(p.out, p.out_dt, o, val);
+                        }
+                    }
+                } else if (p.mode == EPI_SWIGLU) {
+                    // columns alternate gate, up: 8 pairs -> 8 outputs of row xr, out is [M, N/2]
+                    if (xr < p.M && y0 < p.N) {
+                        float h[8];
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            float g = __uint_as_float(v[2 * i]), u = __uint_as_float(v[2 * i + 1]);
+                            h[i] = (g / (1.0f + expf(-g))) * u;
+                        }
+                        size_t o = (size_t)xr * (p.N >> 1) + (y0 >> 1);
+                        if (y0 + 16 <= p.N && (p.N & 15) == 0 && p.out_dt == HFB_BF16) {
+                            __nv_bfloat162 hh[4];
+#pragma unroll
+                            for (int i = 0; i < 4; i++) hh[i] = __floats2bfloat162_rn(h[2 * i], h[2 * i + 1]);
+                            *(uint4 *)((__nv_bfloat16 *)p.out + o) = *(uint4 *)&hh[0];
+                        } else {
+                            for (int i = 0; i < 8 && y0 + 2 * i + 1 < p.N; i++) store_any(p.out, p.out_dt, o + i, h[i]);
                         }
                     }
                 } else if (xr < p.M && y0 < p.N) {
@@ -517,6 +546,100 @@ extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int
         return check_launch("splitk_reduce");
     }
     return HFB_OK;
+}
+
+// Common set-up of the product's tiling: fills p (sizes, tiles, maps) for `bn`; no split.
+static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb::GemmParams &p, int &bn, CUtensorMap &mx, CUtensorMap &my)
+{
+    using namespace hfb;
+    p.M = M; p.N = N; p.K = K;
+    p.kb_total = (K + BK - 1) / BK;
+    p.splits = 1;
+    p.kb_per_split = p.kb_total;
+    p.partial = nullptr;
+    p.swapped = M <= 128;
+    int rc;
+    if (p.swapped) {
+        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+        p.tiles_x = (N + TILE_X - 1) / TILE_X;
+        p.tiles_y = 1;
+        if ((rc = tensor_map(w, N, K, TILE_X, &mx)) != HFB_OK) return rc;
+        if ((rc = tensor_map(a, M, K, bn, &my)) != HFB_OK) return rc;
+    } else {
+        bn = 256;
+        p.tiles_x = (M + TILE_X - 1) / TILE_X;
+        p.tiles_y = (N + bn - 1) / bn;
+        if ((rc = tensor_map(a, M, K, TILE_X, &mx)) != HFB_OK) return rc;
+        if ((rc = tensor_map(w, N, K, bn, &my)) != HFB_OK) return rc;
+    }
+    return HFB_OK;
+}
+
+static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const hfb::GemmParams &p, cudaStream_t st)
+{
+    using namespace hfb;
+    switch (bn) {
+    case 16: return launch<16, 10>(mx, my, p, st);
+    case 32: return launch<32, 9>(mx, my, p, st);
+    case 64: return launch<64, 8>(mx, my, p, st);
+    case 128: return launch<128, 6>(mx, my, p, st);
+    default: return launch<256, 4>(mx, my, p, st);
+    }
+}
+
+static int check_tc_args(const char *who, const void *a, const void *w, const void *out, int M, int N, int K)
+{
+    if (K <= 0 || (K & 7)) return fail(HFB_ENOTSUP, "%s: K = %d must be a positive multiple of 8", who, K);
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
+        return fail(HFB_ENOTSUP, "%s: operands must be 16-byte aligned", who);
+    (void)M; (void)N;
+    return HFB_OK;
+}
+
+// h[M, N/2] = silu(g) * u where row 2i of w holds gate feature i and row 2i+1 up feature i: the activation runs in
+// the product's epilogue, from the float32 accumulators.
+extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) return HFB_OK;
+    int rc = check_tc_args("linear_tc_swiglu", a, w, out, M, N, K);
+    if (rc != HFB_OK) return rc;
+    if ((N & 1) || !valid_dt(out_dt)) return fail(HFB_EINVAL, "linear_tc_swiglu: N must be even (gate and up rows alternate)");
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn;
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
+    p.out = out; p.out_dt = out_dt; p.bias = nullptr; p.mode = EPI_SWIGLU;
+    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
+}
+
+// Only the split-K partial sums: partial[s, M, N] float32 for s < *splits, in `workspace`
+// (hfb_linear_tc_partials_workspace bytes).  M <= 128.  A fused reduction kernel finishes the product.
+extern "C" size_t hfb_linear_tc_partials_workspace(int M, int N, int K)
+{
+    size_t need = hfb_linear_tc_workspace(M, N, K);
+    return need ? need : (size_t)M * N * sizeof(float);
+}
+
+extern "C" int hfb_linear_tc_partials(const void *a, const void *w, int M, int N, int K, void *workspace,
+                                      size_t workspace_bytes, int *splits, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) { *splits = 0; return HFB_OK; }
+    if (M > 128) return fail(HFB_ENOTSUP, "linear_tc_partials: at most 128 rows");
+    int rc = check_tc_args("linear_tc_partials", a, w, workspace, M, N, K);
+    if (rc != HFB_OK) return rc;
+    size_t need = hfb_linear_tc_partials_workspace(M, N, K);
+    if (!workspace || workspace_bytes < need) return fail(HFB_EINVAL, "linear_tc_partials: workspace of %zu bytes, %zu needed", workspace_bytes, need);
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn;
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
+    int want = (int)(need / ((size_t)M * N * sizeof(float)));
+    p.kb_per_split = (p.kb_total + want - 1) / want;
+    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    p.partial = (float *)workspace;
+    p.mode = EPI_PARTIAL;
+    *splits = p.splits;
+    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
 }
 
 // ---- the entry point that allocates nothing (see hfb200_noalloc.h) ----------------------------------------

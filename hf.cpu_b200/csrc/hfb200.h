@@ -46,6 +46,28 @@ size_t hfb_linear_tc_workspace(int M, int N, int K);
 int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
                   int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s);
 
+/* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
+int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
+
+/* Only the split-K partial sums partial[*splits, M, N] (float32) of a product with M <= 128 rows, for a fused
+ * reduction to finish; `workspace` must hold hfb_linear_tc_partials_workspace bytes. */
+size_t hfb_linear_tc_partials_workspace(int M, int N, int K);
+int hfb_linear_tc_partials(const void *a, const void *w, int M, int N, int K, void *workspace, size_t workspace_bytes,
+                           int *splits, hfb_stream s);
+
+/* residual[M,N] += sum_s partial[s] (+ bias); if xn: xn = rmsnorm(residual) * w (the next product's input). */
+int hfb_reduce_residual_norm(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
+                             float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt, hfb_stream s);
+
+/* hfb_rope_kv_write reading sum_s partial[s] + bias instead of a finished q|k|v row. */
+int hfb_reduce_rope_kv(const float *partial, int splits, int dt, const void *bias, int bias_dt, const float *cos_sin,
+                       int n_rot, int n_positions, const int32_t *positions, const int32_t *slots, void *q_out,
+                       void *k_cache, void *v_cache, int64_t cache_slots, int T, int H, int G, int d, hfb_stream s);
+
+/* arg-max with many blocks per row (two passes; scratch of hfb_argmax2_scratch bytes). */
+size_t hfb_argmax2_scratch(int M, int V);
+int hfb_argmax2(const float *logits, int32_t *out, int M, int V, void *scratch, size_t scratch_bytes, hfb_stream s);
+
 /* Splits qkv[T, (H+2G)*d] into rotated queries q_out[T, H*d], rotated keys and plain values written
  * to the paged cache at slots[t] (page * block_size + offset; < 0 or slots == NULL: not written).
  * cos_sin is float32 [positions, n_rot/2, 2]; n_rot == 0 means no rotation. */
@@ -74,8 +96,8 @@ int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, 
                        int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
                        int T, int H, int G, int d, hfb_stream s);
 
-/* out[t, f] = silu(gu[t, f]) * gu[t, F + f] */
-int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, hfb_stream s);
+/* out[t, f] = silu(g) * u with g = gu[t, f], u = gu[t, F + f], or, interleaved, g = gu[t, 2f], u = gu[t, 2f + 1] */
+int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved, hfb_stream s);
 
 /* out[m] = index of the first maximum of logits[m, :] */
 int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s);

@@ -84,9 +84,36 @@ def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out)
     backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out)
 
 
-def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
+def swiglu(gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out = silu(gate) * up; gate and up are the two halves of a row of ``gu``, or alternate along it."""
     _need(gu.shape == (out.shape[0], 2 * out.shape[1]) and gu.dtype == out.dtype, "swiglu: shape mismatch")
-    backend().swiglu(gu, out)
+    backend().swiglu(gu, out, bool(interleaved))
+
+
+def linear_swiglu(a: torch.Tensor, w: torch.Tensor, gu_buf: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(g) * u where [g0, u0, g1, u1, ...] = a @ w.T (rows of ``w`` alternate gate, up).  ``gu_buf``
+    [M, 2F] is scratch for the unfused form."""
+    _need(a.shape[1] == w.shape[1] and w.shape[0] == 2 * out.shape[1] and out.shape[0] == a.shape[0],
+          "linear_swiglu: shape mismatch")
+    _need(gu_buf.shape == (a.shape[0], w.shape[0]), "linear_swiglu: scratch must be [M, 2F]")
+    backend().linear_swiglu(a, w, gu_buf, out)
+
+
+def linear_residual_norm(a, w, bias, residual, norm_w, eps, xn_out) -> None:
+    """residual += a @ w.T (+ bias); then, if ``xn_out`` is given, xn_out = rmsnorm(residual) * norm_w."""
+    _need(a.shape[1] == w.shape[1] and residual.shape == (a.shape[0], w.shape[0]) and residual.dtype == torch.float32,
+          "linear_residual_norm: shape mismatch")
+    _need(xn_out is None or (xn_out.shape == residual.shape and norm_w.shape == (w.shape[0],)),
+          "linear_residual_norm: norm shape mismatch")
+    backend().linear_residual_norm(a, w, bias, residual, norm_w, float(eps), xn_out)
+
+
+def linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d) -> None:
+    """q|k|v = a @ w.T + bias, then :func:`rope_kv_write`; ``qkv_buf`` [T, (H+2G)d] is scratch for the unfused form."""
+    _need(w.shape[0] == (H + 2 * G) * d and q_out.shape == (a.shape[0], H * d), "linear_rope_kv: shape mismatch")
+    _need(k_cache.shape[2:] == (G, d) and v_cache.shape == k_cache.shape and k_cache.dtype == q_out.dtype,
+          "linear_rope_kv: cache geometry mismatch")
+    backend().linear_rope_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache, H, G, d)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -53,6 +53,9 @@ class NativeBackend:
         # "tc": tensor-core products where the operands allow; "plain": the float32-accumulating SIMT kernel always
         self.gemm = os.environ.get("HFB_GEMM", "tc")
         self._ws = None
+        self._argmax_ws = None
+        self.lib.hfb_linear_tc_partials_workspace.restype = ctypes.c_size_t
+        self.lib.hfb_argmax2_scratch.restype = ctypes.c_size_t
         self.path = path
         self.launches = 0          # kernels launched through this binding (one per successful call)
 
@@ -90,8 +93,10 @@ class NativeBackend:
         if (self.gemm == "tc" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
             need = self.lib.hfb_linear_tc_workspace(c_int(M), c_int(N), c_int(K))
-            if need and (self._ws is None or self._ws.numel() < need or self._ws.device != a.device):
-                self._ws = torch.empty(max(need, 16 << 20), dtype=torch.uint8, device=a.device)
+            if need:
+                self._workspace(a.device)
+                if need > self._ws.numel():
+                    need = 0                                        # runs unsplit
             self._check(self.lib.hfb_linear_tc(_p(a), _p(w), _p(bias), c_int(_dt(bias) if bias is not None else 0),
                                                _p(out), c_int(_dt(out)), c_int(1 if accumulate else 0), c_int(M),
                                                c_int(N), c_int(K), _p(self._ws if need else None),
@@ -145,15 +150,88 @@ class NativeBackend:
                                                  c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d),
                                                  self._stream()), "attention")
 
-    def swiglu(self, gu, out):
+    def swiglu(self, gu, out, interleaved):
         self._on_gpu(gu, out)
         T, F = out.shape
-        self._check(self.lib.hfb_swiglu(_p(gu), _p(out), c_int(_dt(gu)), c_int(T), c_int(F), self._stream()), "swiglu")
+        self._check(self.lib.hfb_swiglu(_p(gu), _p(out), c_int(_dt(gu)), c_int(T), c_int(F), c_int(1 if interleaved else 0),
+                                        self._stream()), "swiglu")
 
     def argmax(self, logits, out):
         self._on_gpu(logits, out)
         M, V = logits.shape
-        self._check(self.lib.hfb_argmax(_p(logits), _p(out), c_int(M), c_int(V), self._stream()), "argmax")
+        need = self.lib.hfb_argmax2_scratch(c_int(M), c_int(V))
+        if self._argmax_ws is None or self._argmax_ws.numel() < need:
+            self._argmax_ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=logits.device)
+        self._check(self.lib.hfb_argmax2(_p(logits), _p(out), c_int(M), c_int(V), _p(self._argmax_ws),
+                                         ctypes.c_size_t(self._argmax_ws.numel()), self._stream()), "argmax")
+        self.launches += 1
+
+    # ---- fused forms: the tensor-core product with the next memory-bound step in its tail ------------------
+    def _tc_ok(self, a, w, out=None):
+        return (self.gemm == "tc" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (out is None or out.data_ptr() % 16 == 0))
+
+    def _workspace(self, device):
+        if self._ws is None or self._ws.device != device:
+            self._ws = torch.empty(16 << 20, dtype=torch.uint8, device=device)     # split-K partials never need more
+        return self._ws
+
+    def _partials(self, a, w):
+        """Split-K partial sums of a @ w.T in the workspace; returns (workspace, splits)."""
+        M, K = a.shape
+        N = w.shape[0]
+        ws = self._workspace(a.device)
+        need = self.lib.hfb_linear_tc_partials_workspace(c_int(M), c_int(N), c_int(K))
+        if need > ws.numel():
+            return None
+        splits = c_int(0)
+        self._check(self.lib.hfb_linear_tc_partials(_p(a), _p(w), c_int(M), c_int(N), c_int(K), _p(ws),
+                                                    ctypes.c_size_t(ws.numel()), ctypes.byref(splits), self._stream()),
+                    "linear_tc_partials")
+        return ws, splits.value
+
+    def linear_swiglu(self, a, w, gu_buf, out):
+        self._on_gpu(a, w, out)
+        M, K = a.shape
+        N = w.shape[0]
+        if self._tc_ok(a, w, out):
+            self._check(self.lib.hfb_linear_tc_swiglu(_p(a), _p(w), _p(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),
+                                                      self._stream()), "linear_tc_swiglu")
+            return
+        self.linear(a, w, None, gu_buf, False)
+        self.swiglu(gu_buf, out, True)
+
+    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out):
+        self._on_gpu(a, w, bias, residual, norm_w, xn_out)
+        M, K = a.shape
+        N = w.shape[0]
+        part = self._partials(a, w) if (M <= 128 and self._tc_ok(a, w)) else None
+        if part is None:
+            self.linear(a, w, bias, residual, True)
+            if xn_out is not None:
+                self.rmsnorm(residual, norm_w, eps, xn_out, None)
+            return
+        ws, splits = part
+        self._check(self.lib.hfb_reduce_residual_norm(
+            _p(ws), c_int(splits), c_int(M), c_int(N), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(residual),
+            _p(norm_w), c_int(_dt(norm_w) if norm_w is not None else 0), c_float(eps), _p(xn_out),
+            c_int(_dt(xn_out) if xn_out is not None else 0), self._stream()), "reduce_residual_norm")
+
+    def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
+        self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
+        M, K = a.shape
+        part = self._partials(a, w) if (M <= 128 and self._tc_ok(a, w)) else None
+        if part is None:
+            self.linear(a, w, bias, qkv_buf, False)
+            self.rope_kv_write(qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d)
+            return
+        ws, splits = part
+        cache_slots = k_cache.shape[0] * k_cache.shape[1]
+        npos = cos_sin.shape[0] if cos_sin is not None else 0
+        self._check(self.lib.hfb_reduce_rope_kv(
+            _p(ws), c_int(splits), c_int(_dt(q_out)), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(cos_sin),
+            c_int(n_rot), c_int(npos), _p(positions), _p(slots), _p(q_out), _p(k_cache), _p(v_cache), c_int64(cache_slots),
+            c_int(M), c_int(H), c_int(G), c_int(d), self._stream()), "reduce_rope_kv")
 
     def sample(self, logits, temps, top_ks, top_ps, min_ps, uniforms, out):
         self._on_gpu(logits, temps, top_ks, top_ps, min_ps, uniforms, out)

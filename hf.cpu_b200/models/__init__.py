@@ -91,11 +91,15 @@ class Model:
         T = ctx.token_ids.shape[0]
         x = ctx.buf("residual", (T, self.plan.hidden_size), torch.float32)
         self.embedding.forward(ctx.token_ids, x)
-        for i, e in enumerate(self.plan.schedule):
+        schedule = self.plan.schedule
+        xn = None                                # norm1 of the coming block, when the previous block computed it
+        for i, e in enumerate(schedule):
             layer = self.layers[e.layer]
             owner = i if e.cache_of is None else e.cache_of
-            layer.block.forward(ctx, x, layer.norm1, layer.mixer, layer.norm2, layer.ffn,
-                                ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None)
+            next_norm = self.layers[schedule[i + 1].layer].norm1 if i + 1 < len(schedule) else None
+            xn = layer.block.forward(ctx, x, layer.norm1, layer.mixer, layer.norm2, layer.ffn,
+                                     ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None,
+                                     xn_ready=xn, next_norm=next_norm)
         M = ctx.num_logit_rows
         if M == 0:
             return None

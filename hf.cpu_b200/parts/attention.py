@@ -80,20 +80,31 @@ class PagedAttention(Mixer):
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
                    if w is not None)
 
-    def forward(self, ctx, xn, residual, cache, state, write_cache):
+    def _attend(self, ctx, xn, cache, write_cache):
         T = xn.shape[0]
         qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
-        kernels.linear(xn, self.w_qkv, self.b_qkv, qkv, accumulate=False)
         q = ctx.buf("attn_q", (T, self.QD), xn.dtype)
         meta = ctx.group_meta(cache.group)
         cos_sin = self.rotary.cos_sin if self.rotary is not None else None
         n_rot = self.rotary.n_rot if self.rotary is not None else 0
-        kernels.rope_kv_write(qkv, cos_sin, n_rot, ctx.positions, meta.slots if write_cache else None,
-                              q, cache.k, cache.v, self.H, self.G, self.d)
+        kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
+                               meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
         att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
         kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
                                 self.window, self.scale, att)
-        kernels.linear(att, self.w_o, self.b_o, residual, accumulate=True)
+        return att
+
+    def forward(self, ctx, xn, residual, cache, state, write_cache):
+        kernels.linear(self._attend(ctx, xn, cache, write_cache), self.w_o, self.b_o, residual, accumulate=True)
+
+    def forward_then_norm(self, ctx, xn, residual, cache, state, write_cache, norm, out):
+        args = norm.fused_args()
+        if args is None:
+            self.forward(ctx, xn, residual, cache, state, write_cache)
+            return False
+        kernels.linear_residual_norm(self._attend(ctx, xn, cache, write_cache), self.w_o, self.b_o, residual,
+                                     args[0], args[1], out)
+        return True
 
 
 register_part("mixer", "paged_attention", PagedAttention)

@@ -76,6 +76,10 @@ class Part:
 
 
 class Norm(Part):
+    def fused_args(self):
+        """(weight, eps) when this norm is an RMSNorm that a product's tail may apply itself, else None."""
+        return None
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Normalise rows of the float32 residual ``x`` into ``out`` (run dtype).  With ``rows``
         (int32 indices) only those rows are read, in that order."""
@@ -101,15 +105,23 @@ class Mixer(Part):
         the entry reads another entry's cache."""
         raise NotImplementedError
 
+    # Optional: ``forward_then_norm(ctx, xn, residual, cache, state, write_cache, norm, out) -> bool`` does the same
+    # and, if it returns True, has also written ``out = norm(residual)`` (the block then skips that norm).
+
 
 class FeedForward(Part):
     def forward(self, ctx, xn: torch.Tensor, residual: torch.Tensor) -> None:
         """Token-wise transform of ``xn`` added into the float32 ``residual``."""
         raise NotImplementedError
 
+    # Optional: ``forward_then_norm(ctx, xn, residual, norm, out) -> bool``, as for mixers.
+
 
 class Block(Part):
     def forward(self, ctx, x: torch.Tensor, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward,
-                cache, state, write_cache: bool) -> None:
-        """Run one layer on the float32 residual stream ``x`` in place."""
+                cache, state, write_cache: bool, xn_ready: Optional[torch.Tensor] = None,
+                next_norm: Optional[Norm] = None) -> Optional[torch.Tensor]:
+        """Run one layer on the float32 residual stream ``x`` in place.  ``xn_ready`` is ``norm1(x)`` if the
+        previous block already computed it.  If ``next_norm`` is given the block may return ``next_norm(x)`` of
+        its result (computed in the tail of its last product); returning None leaves that norm to the next block."""
         raise NotImplementedError

@@ -29,19 +29,30 @@ class SwiGlu(FeedForward):
         g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        # rows alternate gate_i, up_i, so that a product's epilogue finds both of a pair side by side
+        self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.F, self.E).contiguous()
         self.w_down = tensors[self.names["down"]].contiguous()
 
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
 
-    def forward(self, ctx, xn, residual):
+    def _hidden(self, ctx, xn):
         T = xn.shape[0]
         gu = ctx.buf("ffn_gate_up", (T, 2 * self.F), xn.dtype)
-        kernels.linear(xn, self.w_gate_up, None, gu, accumulate=False)
         h = ctx.buf("ffn_h", (T, self.F), xn.dtype)
-        kernels.swiglu(gu, h)
-        kernels.linear(h, self.w_down, None, residual, accumulate=True)
+        kernels.linear_swiglu(xn, self.w_gate_up, gu, h)
+        return h
+
+    def forward(self, ctx, xn, residual):
+        kernels.linear(self._hidden(ctx, xn), self.w_down, None, residual, accumulate=True)
+
+    def forward_then_norm(self, ctx, xn, residual, norm, out):
+        args = norm.fused_args()
+        if args is None:
+            self.forward(ctx, xn, residual)
+            return False
+        kernels.linear_residual_norm(self._hidden(ctx, xn), self.w_down, None, residual, args[0], args[1], out)
+        return True
 
 
 register_part("ffn", "swiglu", SwiGlu)

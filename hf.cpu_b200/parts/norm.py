@@ -21,6 +21,9 @@ class RmsNorm(Norm):
     def bind(self, tensors, run_dtype, device):
         self.weight = tensors[self.tensor].contiguous()
 
+    def fused_args(self):
+        return self.weight, self.eps
+
     def forward(self, x, out, rows=None):
         kernels.rmsnorm(x, self.weight, self.eps, out, rows)
         return out

@@ -72,10 +72,26 @@ class EmuBackend:
                 res[t, h] = p @ v[:, g]
         out.copy_(res.view(T, H * d).to(out.dtype))
 
-    def swiglu(self, gu, out):
+    def swiglu(self, gu, out, interleaved):
         F = out.shape[1]
-        g, u = gu[:, :F].float(), gu[:, F:].float()
+        if interleaved:
+            g, u = gu[:, 0::2].float(), gu[:, 1::2].float()
+        else:
+            g, u = gu[:, :F].float(), gu[:, F:].float()
         out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
+
+    def linear_swiglu(self, a, w, gu_buf, out):
+        self.linear(a, w, None, gu_buf, False)
+        self.swiglu(gu_buf, out, True)
+
+    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out):
+        self.linear(a, w, bias, residual, True)
+        if xn_out is not None:
+            self.rmsnorm(residual, norm_w, eps, xn_out, None)
+
+    def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
+        self.linear(a, w, bias, qkv_buf, False)
+        self.rope_kv_write(qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d)
 
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).int())

@@ -194,9 +194,10 @@ def test_swiglu(dtype):
     T, F = 33, 999
     gu = rnd(T, 2 * F, dtype=DT[dtype], scale=3)
     out, ref = torch.empty(T, F, device=DEV, dtype=DT[dtype]), torch.empty(T, F, device=DEV, dtype=DT[dtype])
-    native().swiglu(gu, out)
-    EmuBackend().swiglu(gu, ref)
-    assert rel(out.float(), ref.float()) < (1e-6 if dtype == "float32" else 1e-2)
+    for inter in (False, True):
+        native().swiglu(gu, out, inter)
+        EmuBackend().swiglu(gu, ref, inter)
+        assert rel(out.float(), ref.float()) < (1e-6 if dtype == "float32" else 1e-2)
 
 
 def test_argmax_lowest_index_wins():
@@ -320,3 +321,57 @@ def test_attention_tiled_far_key_window_edge_and_page_edges():
                 case = _with_tiles(case, lens_q, lens_kv, H, G)
                 out, ref = _run_attention(native(), case, H, G, d, window), _run_attention(EmuBackend(), case, H, G, d, window)
                 assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, key_pos, window)
+
+
+@pytest.mark.parametrize("shape", [(1, 352, 64), (8, 37888, 3584), (5, 640, 192), (64, 2048, 512), (130, 640, 192),
+                                   (300, 2048, 256), (2048, 4096, 512), (7, 352, 70)])
+def test_linear_swiglu_fused(shape):
+    """The product with the SwiGLU epilogue (both operand orders; odd K falls back to two kernels) against torch."""
+    M, N, K = shape
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1)
+    gu = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
+    native().linear_swiglu(a, w, gu, out)
+    y = a.double() @ w.double().T
+    g, u = y[:, 0::2], y[:, 1::2]
+    ref = (g / (1 + torch.exp(-g))) * u
+    assert rel(out, ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("shape", [(1, 3584, 3584), (8, 3584, 18944), (8, 192, 320), (64, 3584, 512), (128, 1000, 64),
+                                   (200, 512, 256), (5, 64, 44)])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_linear_residual_norm_fused(shape, with_norm):
+    M, N, K = shape
+    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1)
+    bias, nw = rnd(N, dtype=torch.bfloat16), rnd(N, dtype=torch.bfloat16) + 1
+    res = rnd(M, N, seed=3)
+    res_ref = res.double() + a.double() @ w.double().T + bias.double()
+    xn = torch.empty(M, N, device=DEV, dtype=torch.bfloat16) if with_norm else None
+    native().linear_residual_norm(a, w, bias, res, nw if with_norm else None, 1e-6, xn)
+    assert rel(res, res_ref) < 2e-5
+    if with_norm:
+        r = 1 / torch.sqrt((res_ref ** 2).mean(-1, keepdim=True) + 1e-6)
+        assert rel(xn, res_ref * r * nw.double()) < 1e-2
+
+
+@pytest.mark.parametrize("geom", [(28, 4, 128, 3584, 8), (6, 3, 32, 192, 5), (4, 2, 16, 64, 1), (8, 8, 64, 512, 130), (5, 1, 48, 100, 3)])
+def test_linear_rope_kv_fused(geom):
+    H, G, d, K, T = geom
+    N = (H + 2 * G) * d
+    a, w, bias = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N, dtype=torch.bfloat16)
+    pages, bs, P = 40, 4, 64
+    ang = torch.rand(P, d // 2, device=DEV, dtype=torch.float64) * 6
+    cos_sin = torch.stack([ang.cos(), ang.sin()], -1).float().contiguous()
+    positions = torch.randint(0, P, (T,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * bs, device=DEV)[:T].int()
+    outs = []
+    for impl in (native(), EmuBackend()):
+        qkv = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+        q = torch.zeros(T, H * d, device=DEV, dtype=torch.bfloat16)
+        kc = torch.zeros(pages, bs, G, d, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        impl.linear_rope_kv(a, w, bias, qkv, cos_sin, d, positions, slots, q, kc, vc, H, G, d)
+        outs.append((q, kc, vc))
+    for x, y in zip(*outs):
+        assert rel(x.float(), y.float()) < 1.5e-2
