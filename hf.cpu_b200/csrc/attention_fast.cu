@@ -119,6 +119,7 @@ attention_fast_kernel(AttnParams p, int *err)
     const int pos0 = v0 ? p.positions[t0 + tl0] : -1, pos1 = v1 ? p.positions[t0 + tl1] : -1;
     const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, pos1 - p.window + 1) : 0;
 
+    const bool warp_active = warp * 16 < nt * r;      // a warp whose 16 rows are all padding only helps with the loads
     float o[D / 8][4];
 #pragma unroll
     for (int i = 0; i < D / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -131,6 +132,7 @@ attention_fast_kernel(AttnParams p, int *err)
         if (kt + 1 < kt_hi) { load_kv(kt + 1, stage ^ 1); cp_async_wait<1>(); }
         else cp_async_wait<0>();
         __syncthreads();
+        if (!warp_active) { __syncthreads(); continue; }
         if (!q_loaded) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; kk++)
@@ -287,7 +289,7 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_fast: head_dim %d (64 and 128 only; use the plain kernel)", d);
-    if (warps != 1 && warps != 4) return fail(HFB_EINVAL, "attention_fast: 1 or 4 warps");
+    if (warps != 1 && warps != 4 && warps != 8) return fail(HFB_EINVAL, "attention_fast: 1, 4 or 8 warps");
     if (block_size <= 0 || ABN % block_size) return fail(HFB_ENOTSUP, "attention_fast: block size %d does not divide %d", block_size, ABN);
     if (hfb_attention_fast_tile_tokens(H, G, warps) == 0) return fail(HFB_ENOTSUP, "attention_fast: %d heads per key/value head do not fit a tile", G ? H / G : 0);
     if (splits < 1 || G > 65535 || splits > 65535) return fail(HFB_EINVAL, "attention_fast: bad split or group count");
@@ -302,8 +304,8 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
     p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t st = (cudaStream_t)s;
     int rc;
-    if (d == 128) rc = warps == 4 ? launch_attention<128, 4>(p, n_tiles, st) : launch_attention<128, 1>(p, n_tiles, st);
-    else rc = warps == 4 ? launch_attention<64, 4>(p, n_tiles, st) : launch_attention<64, 1>(p, n_tiles, st);
+    if (d == 128) rc = warps == 8 ? launch_attention<128, 8>(p, n_tiles, st) : warps == 4 ? launch_attention<128, 4>(p, n_tiles, st) : launch_attention<128, 1>(p, n_tiles, st);
+    else rc = warps == 8 ? launch_attention<64, 8>(p, n_tiles, st) : warps == 4 ? launch_attention<64, 4>(p, n_tiles, st) : launch_attention<64, 1>(p, n_tiles, st);
     if (rc != HFB_OK || splits == 1) return rc;
     if (d == 128) attention_combine_kernel<128><<<(unsigned)((size_t)T * H), 128, 0, st>>>(p.part_o, p.part_ml, splits, p.out);
     else attention_combine_kernel<64><<<(unsigned)((size_t)T * H), 64, 0, st>>>(p.part_o, p.part_ml, splits, p.out);

@@ -42,6 +42,40 @@ __global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float ep
         store_any(out, out_dt, (size_t)m * E + i, (xr[i] * r) * load_any(w, w_dt, i));
 }
 
+// The same with 16-byte accesses, for widths that are a multiple of 4.
+template <typename TW, typename TO>
+__global__ void rmsnorm_vec_kernel(const float *x, const TW *w, float eps, TO *out, const int32_t *rows, int E)
+{
+    int m = blockIdx.x;
+    const float4 *xr = (const float4 *)(x + (size_t)(rows ? rows[m] : m) * E);
+    const int E4 = E >> 2;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E4; i += blockDim.x) { float4 v = xr[i]; ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w; }
+    __shared__ float part[32];
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float v = lane < nw ? part[lane] : 0.f;
+        v = warp_sum(v);
+        if (lane == 0) part[0] = v;
+    }
+    __syncthreads();
+    float r = 1.0f / sqrtf(part[0] / (float)E + eps);
+    for (int i = threadIdx.x; i < E4; i += blockDim.x) {
+        float4 v = xr[i];
+        float w0 = to_f32(w[4 * i]), w1 = to_f32(w[4 * i + 1]), w2 = to_f32(w[4 * i + 2]), w3 = to_f32(w[4 * i + 3]);
+        float y0 = (v.x * r) * w0, y1 = (v.y * r) * w1, y2 = (v.z * r) * w2, y3 = (v.w * r) * w3;
+        TO *o = out + (size_t)m * E + 4 * i;
+        if (sizeof(TO) == 4) *(float4 *)o = make_float4(y0, y1, y2, y3);
+        else {
+            __nv_bfloat162 a = __floats2bfloat162_rn(y0, y1), b = __floats2bfloat162_rn(y2, y3);
+            *(uint2 *)o = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+        }
+    }
+}
+
 // ---- rotary + cache write (src/model.c:587-601, :468-493) -------------------------------------
 // One block per (token, head of the fused q|k|v row).  Pairs (i, i + n_rot/2) rotate; the rest copies.
 template <typename T>
@@ -78,6 +112,48 @@ __global__ void rope_kv_write_kernel(const T *qkv, const float *cos_sin, int n_r
         for (int i = n_rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
     } else {
         for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// The same with 16-byte accesses: one block per token walks all heads; VEC elements per access.
+template <typename T>
+__global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int n_rot, int n_positions,
+                                         const int32_t *positions, const int32_t *slots, T *q_out, T *k_cache,
+                                         T *v_cache, long long cache_slots, int H, int G, int d, int *err)
+{
+    constexpr int VEC = 16 / sizeof(T);
+    struct alignas(16) Pack { T e[VEC]; };
+    const int t = blockIdx.x;
+    const int half = n_rot / 2, per_head = d / VEC;
+    long long slot = slots ? slots[t] : -1;
+    if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); slot = -1; }
+    int pos = positions ? positions[t] : 0;
+    if (half > 0 && (pos < 0 || pos >= n_positions)) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+    const float *cs = half > 0 ? cos_sin + (size_t)pos * half * 2 : nullptr;
+    const T *row = qkv + (size_t)t * (H + 2 * G) * d;
+    for (int item = threadIdx.x; item < (H + 2 * G) * per_head; item += blockDim.x) {
+        const int head = item / per_head, e0 = (item % per_head) * VEC;
+        T *dst;
+        bool rotate = head < H + G;
+        if (head < H) dst = q_out + (size_t)t * H * d + (size_t)head * d;
+        else if (slot < 0) continue;
+        else if (head < H + G) dst = k_cache + ((size_t)slot * G + (head - H)) * d;
+        else dst = v_cache + ((size_t)slot * G + (head - H - G)) * d;
+        const T *src = row + (size_t)head * d;
+        if (rotate && e0 < half) {
+            Pack a = *(const Pack *)(src + e0), b = *(const Pack *)(src + e0 + half), ra, rb;
+#pragma unroll
+            for (int i = 0; i < VEC; i++) {
+                float c = cs[2 * (e0 + i)], sn = cs[2 * (e0 + i) + 1];
+                float x = to_f32(a.e[i]), y = to_f32(b.e[i]);
+                ra.e[i] = from_f32<T>(x * c - y * sn);
+                rb.e[i] = from_f32<T>(x * sn + y * c);
+            }
+            *(Pack *)(dst + e0) = ra;
+            *(Pack *)(dst + e0 + half) = rb;
+        } else if (!rotate || e0 >= n_rot) {
+            *(Pack *)(dst + e0) = *(const Pack *)(src + e0);
+        }
     }
 }
 
@@ -137,7 +213,15 @@ extern "C" int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, v
     if (M <= 0) return HFB_OK;
     if (!valid_dt(w_dt) || !valid_dt(out_dt) || E <= 0) return fail(HFB_EINVAL, "rmsnorm: bad arguments");
     int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
-    rmsnorm_kernel<<<M, threads, 0, (cudaStream_t)s>>>(x, w, w_dt, eps, out, out_dt, rows, E);
+    cudaStream_t st = (cudaStream_t)s;
+    if ((E & 3) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+        if (w_dt == HFB_F32 && out_dt == HFB_F32) rmsnorm_vec_kernel<float, float><<<M, threads, 0, st>>>(x, (const float *)w, eps, (float *)out, rows, E);
+        else if (w_dt == HFB_F32) rmsnorm_vec_kernel<float, __nv_bfloat16><<<M, threads, 0, st>>>(x, (const float *)w, eps, (__nv_bfloat16 *)out, rows, E);
+        else if (out_dt == HFB_F32) rmsnorm_vec_kernel<__nv_bfloat16, float><<<M, threads, 0, st>>>(x, (const __nv_bfloat16 *)w, eps, (float *)out, rows, E);
+        else rmsnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<M, threads, 0, st>>>(x, (const __nv_bfloat16 *)w, eps, (__nv_bfloat16 *)out, rows, E);
+    } else {
+        rmsnorm_kernel<<<M, threads, 0, st>>>(x, w, w_dt, eps, out, out_dt, rows, E);
+    }
     return check_launch("rmsnorm");
 }
 
@@ -150,6 +234,20 @@ extern "C" int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, 
         return fail(HFB_EINVAL, "rope_kv_write: bad arguments (H=%d G=%d d=%d n_rot=%d)", H, G, d, n_rot);
     if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "rope_kv_write: rotation needs a table and positions");
     if (H + 2 * G > 65535) return fail(HFB_ENOTSUP, "rope_kv_write: %d heads exceed the grid limit", H + 2 * G);
+    const int vec = dt == HFB_F32 ? 4 : 8;
+    if (d % vec == 0 && (n_rot / 2) % vec == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+        ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0) {
+        int items = (H + 2 * G) * (d / vec);
+        int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
+        if (dt == HFB_F32)
+            rope_kv_write_vec_kernel<float><<<T, threads, 0, (cudaStream_t)s>>>((const float *)qkv, cos_sin, n_rot, n_positions,
+                positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, cache_slots, H, G, d, error_word());
+        else
+            rope_kv_write_vec_kernel<__nv_bfloat16><<<T, threads, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)qkv, cos_sin, n_rot,
+                n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache,
+                cache_slots, H, G, d, error_word());
+        return check_launch("rope_kv_write");
+    }
     dim3 grid(T, H + 2 * G);
     int threads = d >= 128 ? 64 : 32;
     if (dt == HFB_F32)

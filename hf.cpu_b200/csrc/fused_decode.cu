@@ -5,6 +5,8 @@
 // instead of three kernels; likewise the sum, bias, rotary encoding and cache write of the q|k|v product.
 // Arithmetic as in the separate kernels: src/model.c:606-611 (residual, then RMSNorm, src/mathx.c:65-75) and
 // src/model.c:581-601 (bias after the dot, rotation, cache write).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace hfb {
@@ -41,6 +43,61 @@ __global__ void reduce_residual_norm_kernel(const float *partial, int splits, in
     const float r = 1.0f / sqrtf(part[0] / (float)N + eps);
     for (int i = threadIdx.x; i < N; i += blockDim.x)       // each thread re-reads what it wrote itself
         store_any(xn, xn_dt, (size_t)m * N + i, (res[i] * r) * load_any(w, w_dt, i));
+}
+
+// The same with a cluster of CTAs per row: each CTA owns a slice of the columns, keeps its sums in registers,
+// and the CTAs exchange their partial sums of squares through distributed shared memory (summed in rank order).
+constexpr int RRN_THREADS = 256, RRN_PER_THREAD = 4;
+
+__global__ void __launch_bounds__(RRN_THREADS)
+reduce_residual_norm_cluster_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
+                                    float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt)
+{
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    const int m = blockIdx.x / C;
+    const int per = (N + C - 1) / C, lo = rank * per, hi = min(N, lo + per);
+    const size_t MN = (size_t)M * N;
+    float *res = residual + (size_t)m * N;
+    float vals[RRN_PER_THREAD];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < RRN_PER_THREAD; j++) {
+        int i = lo + threadIdx.x + j * RRN_THREADS;
+        float v = 0.f;
+        if (i < hi) {
+            for (int s = 0; s < splits; s++) v += partial[(size_t)s * MN + (size_t)m * N + i];
+            if (bias) v += load_any(bias, bias_dt, i);
+            v += res[i];
+            res[i] = v;
+        }
+        vals[j] = v;
+        ss += v * v;
+    }
+    __shared__ float part[32];
+    __shared__ float cta_ss;
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < RRN_THREADS / 32 ? part[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) cta_ss = t;
+    }
+    cluster.sync();
+    if (xn) {
+        float total = 0.f;
+        for (int c = 0; c < C; c++) total += *cluster.map_shared_rank(&cta_ss, c);
+        const float r = 1.0f / sqrtf(total / (float)N + eps);
+#pragma unroll
+        for (int j = 0; j < RRN_PER_THREAD; j++) {
+            int i = lo + threadIdx.x + j * RRN_THREADS;
+            if (i < hi) store_any(xn, xn_dt, (size_t)m * N + i, (vals[j] * r) * load_any(w, w_dt, i));
+        }
+    }
+    cluster.sync();          // no CTA leaves while another may still read its shared memory
 }
 
 // q|k|v row = sum_s partial[s, t, :] + bias; rotate q and k; q -> q_out, k and v -> the paged cache.
@@ -147,6 +204,24 @@ extern "C" int hfb_reduce_residual_norm(const float *partial, int splits, int M,
     if (M <= 0) return HFB_OK;
     if (splits < 1 || N <= 0 || (bias && !valid_dt(bias_dt)) || (xn && (!valid_dt(w_dt) || !valid_dt(xn_dt))))
         return fail(HFB_EINVAL, "reduce_residual_norm: bad arguments");
+    // a cluster of up to 8 CTAs per row when the row is wide enough to share out
+    int C = N >= 2048 ? 8 : N >= 1024 ? 4 : N >= 512 ? 2 : 1;
+    while (C < 8 && (N + C - 1) / C > RRN_THREADS * RRN_PER_THREAD) C *= 2;
+    if (C > 1 && (N + C - 1) / C <= RRN_THREADS * RRN_PER_THREAD) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(M * C));
+        cfg.blockDim = dim3(RRN_THREADS);
+        cfg.stream = (cudaStream_t)s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, reduce_residual_norm_cluster_kernel, partial, splits, M, N, bias, bias_dt,
+                                           residual, w, w_dt, eps, xn, xn_dt);
+        if (e != cudaSuccess) return fail(HFB_ECUDA, "reduce_residual_norm: %s", cudaGetErrorString(e));
+        return HFB_OK;
+    }
     int threads = N >= 2048 ? 512 : (N >= 512 ? 256 : 128);
     reduce_residual_norm_kernel<<<M, threads, 0, (cudaStream_t)s>>>(partial, splits, M, N, bias, bias_dt, residual, w, w_dt, eps, xn, xn_dt);
     return check_launch("reduce_residual_norm");

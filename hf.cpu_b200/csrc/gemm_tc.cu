@@ -150,6 +150,99 @@ template <int BN, int STAGES> constexpr uint32_t gemm_smem_bytes()
     return 1024 + STAGES * (X_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
 }
 
+// One chunk of 16 accumulator columns of one row: v[i] is element (xr, y0 + i) of X . Y^T.
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t *v, int xr, int y0, int split, int lane)
+{
+    if (p.swapped && p.mode == EPI_SWIGLU) {
+        // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2]
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            float mine = __uint_as_float(v[i]);
+            float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            int tok = y0 + i;
+            if (!(lane & 1) && xr + 1 < p.N && tok < p.M)
+                store_any(p.out, p.out_dt, (size_t)tok * (p.N >> 1) + (xr >> 1), (mine / (1.0f + expf(-mine))) * other);
+        }
+    } else if (p.swapped) {
+        // xr = output feature, y = token
+        if (xr < p.N) {
+            float b = (p.bias && p.mode != EPI_PARTIAL) ? load_any(p.bias, p.bias_dt, xr) : 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                int tok = y0 + i;
+                if (tok >= p.M) break;
+                float val = __uint_as_float(v[i]) + b;
+                size_t o = (size_t)tok * p.N + xr;
+                if (p.mode == EPI_PARTIAL) p.partial[(size_t)split * p.M * p.N + o] = val;
+                else if (p.mode == EPI_ADD) ((float *)p.out)[o] += val;
+                else store_any(p.out, p.out_dt, o, val);
+            }
+        }
+    } else if (p.mode == EPI_SWIGLU) {
+        // columns alternate gate, up: 8 pairs -> 8 outputs of row xr, out is [M, N/2]
+        if (xr < p.M && y0 < p.N) {
+            float h[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float g = __uint_as_float(v[2 * i]), u = __uint_as_float(v[2 * i + 1]);
+                h[i] = (g / (1.0f + expf(-g))) * u;
+            }
+            size_t o = (size_t)xr * (p.N >> 1) + (y0 >> 1);
+            if (y0 + 16 <= p.N && (p.N & 15) == 0 && p.out_dt == HFB_BF16) {
+                __nv_bfloat162 hh[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) hh[i] = __floats2bfloat162_rn(h[2 * i], h[2 * i + 1]);
+                *(uint4 *)((__nv_bfloat16 *)p.out + o) = *(uint4 *)&hh[0];
+            } else {
+                for (int i = 0; i < 8 && y0 + 2 * i + 1 < p.N; i++) store_any(p.out, p.out_dt, o + i, h[i]);
+            }
+        }
+    } else if (xr < p.M && y0 < p.N) {
+        // xr = token, y = output feature: 16 consecutive features of one row
+        size_t o = (size_t)xr * p.N + y0;
+        bool full = y0 + 16 <= p.N && (p.N & 7) == 0;
+        float f[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            f[i] = __uint_as_float(v[i]);
+            if (p.bias && p.mode != EPI_PARTIAL && (full || y0 + i < p.N)) f[i] += load_any(p.bias, p.bias_dt, y0 + i);
+        }
+        if (p.mode == EPI_PARTIAL) {
+            float *dst = p.partial + (size_t)split * p.M * p.N + o;
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) *(float4 *)(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+            } else {
+                for (int i = 0; i < 16 && y0 + i < p.N; i++) dst[i] = f[i];
+            }
+        } else if (p.mode == EPI_ADD) {
+            float *dst = (float *)p.out + o;
+            if (full) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    float4 r = *(float4 *)(dst + i);
+                    *(float4 *)(dst + i) = make_float4(r.x + f[i], r.y + f[i + 1], r.z + f[i + 2], r.w + f[i + 3]);
+                }
+            } else {
+                for (int i = 0; i < 16 && y0 + i < p.N; i++) dst[i] += f[i];
+            }
+        } else if (p.out_dt == HFB_BF16 && full) {
+            __nv_bfloat162 h[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            uint4 *dst = (uint4 *)((__nv_bfloat16 *)p.out + o);
+            dst[0] = *(uint4 *)&h[0];
+            dst[1] = *(uint4 *)&h[4];
+        } else if (p.out_dt == HFB_F32 && full) {
+            float *dst = (float *)p.out + o;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) *(float4 *)(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+        } else {
+            for (int i = 0; i < 16 && y0 + i < p.N; i++) store_any(p.out, p.out_dt, o + i, f[i]);
+        }
+    }
+}
+
 // ---- the kernel ---------------------------------------------------------------------------------
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -256,99 +349,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
             const int xr = tx * TILE_X + row;         // row of X this thread holds
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                uint32_t v[16];
+            for (int c0 = 0; c0 < BN; c0 += (BN >= 32 ? 32 : 16)) {
+                uint32_t v[BN >= 32 ? 32 : 16];
                 tmem_ld16(taddr + c0, v);
+                if (BN >= 32) tmem_ld16(taddr + c0 + 16, v + (BN >= 32 ? 16 : 0));
                 tmem_wait_ld();
-                const int y0 = ty * BN + c0;          // first row of Y in this chunk
-                if (p.swapped && p.mode == EPI_SWIGLU) {
-                    // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2]
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        float mine = __uint_as_float(v[i]);
-                        float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-                        int tok = y0 + i;
-                        if (!(lane & 1) && xr + 1 < p.N && tok < p.M)
-                            store_any(p.out, p.out_dt, (size_t)tok * (p.N >> 1) + (xr >> 1), (mine / (1.0f + expf(-mine))) * other);
-                    }
-                } else if (p.swapped) {
-                    // xr = output feature, y = token
-                    if (xr < p.N) {
-                        float b = (p.bias && p.mode != EPI_PARTIAL) ? load_any(p.bias, p.bias_dt, xr) : 0.f;
-#pragma unroll
-                        for (int i = 0; i < 16; i++) {
-                            int tok = y0 + i;
-                            if (tok >= p.M) break;
-                            float val = __uint_as_float(v[i]) + b;
-                            size_t o = (size_t)tok * p.N + xr;
-                            if (p.mode == EPI_PARTIAL) p.partial[(size_t)split * p.M * p.N + o] = val;
-                            else if (p.mode == EPI_ADD) ((float *)p.out)[o] += val;
-                            else store_any(p.out, p.out_dt, o, val);
-                        }
-                    }
-                } else if (p.mode == EPI_SWIGLU) {
-                    // columns alternate gate, up: 8 pairs -> 8 outputs of row xr, out is [M, N/2]
-                    if (xr < p.M && y0 < p.N) {
-                        float h[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            float g = __uint_as_float(v[2 * i]), u = __uint_as_float(v[2 * i + 1]);
-                            h[i] = (g / (1.0f + expf(-g))) * u;
-                        }
-                        size_t o = (size_t)xr * (p.N >> 1) + (y0 >> 1);
-                        if (y0 + 16 <= p.N && (p.N & 15) == 0 && p.out_dt == HFB_BF16) {
-                            __nv_bfloat162 hh[4];
-#pragma unroll
-                            for (int i = 0; i < 4; i++) hh[i] = __floats2bfloat162_rn(h[2 * i], h[2 * i + 1]);
-                            *(uint4 *)((__nv_bfloat16 *)p.out + o) = *(uint4 *)&hh[0];
-                        } else {
-                            for (int i = 0; i < 8 && y0 + 2 * i + 1 < p.N; i++) store_any(p.out, p.out_dt, o + i, h[i]);
-                        }
-                    }
-                } else if (xr < p.M && y0 < p.N) {
-                    // xr = token, y = output feature: 16 consecutive features of one row
-                    size_t o = (size_t)xr * p.N + y0;
-                    bool full = y0 + 16 <= p.N && (p.N & 7) == 0;
-                    float f[16];
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        f[i] = __uint_as_float(v[i]);
-                        if (p.bias && p.mode != EPI_PARTIAL && (full || y0 + i < p.N)) f[i] += load_any(p.bias, p.bias_dt, y0 + i);
-                    }
-                    if (p.mode == EPI_PARTIAL) {
-                        float *dst = p.partial + (size_t)split * p.M * p.N + o;
-                        if (full) {
-#pragma unroll
-                            for (int i = 0; i < 16; i += 4) *(float4 *)(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
-                        } else {
-                            for (int i = 0; i < 16 && y0 + i < p.N; i++) dst[i] = f[i];
-                        }
-                    } else if (p.mode == EPI_ADD) {
-                        float *dst = (float *)p.out + o;
-                        if (full) {
-#pragma unroll
-                            for (int i = 0; i < 16; i += 4) {
-                                float4 r = *(float4 *)(dst + i);
-                                *(float4 *)(dst + i) = make_float4(r.x + f[i], r.y + f[i + 1], r.z + f[i + 2], r.w + f[i + 3]);
-                            }
-                        } else {
-                            for (int i = 0; i < 16 && y0 + i < p.N; i++) dst[i] += f[i];
-                        }
-                    } else if (p.out_dt == HFB_BF16 && full) {
-                        __nv_bfloat162 h[8];
-#pragma unroll
-                        for (int i = 0; i < 8; i++) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                        uint4 *dst = (uint4 *)((__nv_bfloat16 *)p.out + o);
-                        dst[0] = *(uint4 *)&h[0];
-                        dst[1] = *(uint4 *)&h[4];
-                    } else if (p.out_dt == HFB_F32 && full) {
-                        float *dst = (float *)p.out + o;
-#pragma unroll
-                        for (int i = 0; i < 16; i += 4) *(float4 *)(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
-                    } else {
-                        for (int i = 0; i < 16 && y0 + i < p.N; i++) store_any(p.out, p.out_dt, o + i, f[i]);
-                    }
-                }
+                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane);
+                if (BN >= 32) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -474,80 +481,6 @@ static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams
 
 using namespace hfb;
 
-// Bytes of float32 workspace hfb_linear_tc may use for split-K partials with these sizes (0: none needed).
-extern "C" size_t hfb_linear_tc_workspace(int M, int N, int K)
-{
-    if (M > 128) return 0;
-    int tiles = (N + TILE_X - 1) / TILE_X, kb = (K + BK - 1) / BK;
-    int splits = tiles >= sm_count() ? 1 : sm_count() / tiles;      // at most one work item per SM
-    if (splits > kb / 4) splits = kb / 4 > 0 ? kb / 4 : 1;
-    if (splits > 16) splits = 16;
-    return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
-}
-
-extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
-                             int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s)
-{
-    if (M <= 0 || N <= 0) return HFB_OK;
-    if (K <= 0 || (K & 7)) return fail(HFB_ENOTSUP, "linear_tc: K = %d must be a positive multiple of 8", K);
-    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
-        return fail(HFB_ENOTSUP, "linear_tc: operands must be 16-byte aligned");
-    if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "linear_tc: bad element types");
-    if (accumulate && out_dt != HFB_F32) return fail(HFB_EINVAL, "linear_tc: accumulation needs a float32 output");
-    cudaStream_t st = (cudaStream_t)s;
-    GemmParams p{};
-    p.M = M; p.N = N; p.K = K;
-    p.out = out; p.out_dt = out_dt; p.bias = bias; p.bias_dt = bias_dt;
-    p.mode = accumulate ? EPI_ADD : EPI_STORE;
-    p.kb_total = (K + BK - 1) / BK;
-    p.splits = 1;
-    p.kb_per_split = p.kb_total;
-    p.partial = nullptr;
-    p.swapped = M <= 128;
-    int bn;
-    if (p.swapped) {
-        bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-        p.tiles_x = (N + TILE_X - 1) / TILE_X;
-        p.tiles_y = 1;
-        size_t need = hfb_linear_tc_workspace(M, N, K);
-        if (need && workspace && workspace_bytes >= need) {
-            int splits = (int)(need / ((size_t)M * N * sizeof(float)));
-            p.kb_per_split = (p.kb_total + splits - 1) / splits;
-            p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
-            if (p.splits > 1) { p.partial = (float *)workspace; p.mode = EPI_PARTIAL; }
-            else p.kb_per_split = p.kb_total;
-        }
-    } else {
-        bn = 256;
-        p.tiles_x = (M + TILE_X - 1) / TILE_X;
-        p.tiles_y = (N + bn - 1) / bn;
-    }
-    CUtensorMap mx, my;
-    int rc;
-    if (p.swapped) {
-        if ((rc = tensor_map(w, N, K, TILE_X, &mx)) != HFB_OK) return rc;
-        if ((rc = tensor_map(a, M, K, bn, &my)) != HFB_OK) return rc;
-    } else {
-        if ((rc = tensor_map(a, M, K, TILE_X, &mx)) != HFB_OK) return rc;
-        if ((rc = tensor_map(w, N, K, bn, &my)) != HFB_OK) return rc;
-    }
-    switch (bn) {
-    case 16: rc = launch<16, 10>(mx, my, p, st); break;
-    case 32: rc = launch<32, 9>(mx, my, p, st); break;
-    case 64: rc = launch<64, 8>(mx, my, p, st); break;
-    case 128: rc = launch<128, 6>(mx, my, p, st); break;
-    default: rc = launch<256, 4>(mx, my, p, st); break;
-    }
-    if (rc != HFB_OK) return rc;
-    if (p.mode == EPI_PARTIAL) {
-        size_t MN = (size_t)M * N;
-        splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
-                                                                          accumulate ? EPI_ADD : EPI_STORE);
-        return check_launch("splitk_reduce");
-    }
-    return HFB_OK;
-}
-
 // Common set-up of the product's tiling: fills p (sizes, tiles, maps) for `bn`; no split.
 static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb::GemmParams &p, int &bn, CUtensorMap &mx, CUtensorMap &my)
 {
@@ -566,8 +499,16 @@ static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb:
         if ((rc = tensor_map(w, N, K, TILE_X, &mx)) != HFB_OK) return rc;
         if ((rc = tensor_map(a, M, K, bn, &my)) != HFB_OK) return rc;
     } else {
-        bn = 256;
+        // the tile width that needs the fewest column-rounds over the SMs (every CTA walks its tiles in turn)
         p.tiles_x = (M + TILE_X - 1) / TILE_X;
+        const int widths[4] = {256, 224, 192, 128};
+        long best = -1;
+        bn = 256;
+        for (int i = 0; i < 4; i++) {
+            long tiles = (long)p.tiles_x * ((N + widths[i] - 1) / widths[i]);
+            long cost = (tiles + sm_count() - 1) / sm_count() * widths[i];
+            if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
+        }
         p.tiles_y = (N + bn - 1) / bn;
         if ((rc = tensor_map(a, M, K, TILE_X, &mx)) != HFB_OK) return rc;
         if ((rc = tensor_map(w, N, K, bn, &my)) != HFB_OK) return rc;
@@ -583,6 +524,8 @@ static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const
     case 32: return launch<32, 9>(mx, my, p, st);
     case 64: return launch<64, 8>(mx, my, p, st);
     case 128: return launch<128, 6>(mx, my, p, st);
+    case 192: return launch<192, 5>(mx, my, p, st);
+    case 224: return launch<224, 4>(mx, my, p, st);
     default: return launch<256, 4>(mx, my, p, st);
     }
 }
@@ -593,6 +536,52 @@ static int check_tc_args(const char *who, const void *a, const void *w, const vo
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
         return fail(HFB_ENOTSUP, "%s: operands must be 16-byte aligned", who);
     (void)M; (void)N;
+    return HFB_OK;
+}
+
+// Bytes of float32 workspace hfb_linear_tc may use for split-K partials with these sizes (0: none needed).
+extern "C" size_t hfb_linear_tc_workspace(int M, int N, int K)
+{
+    if (M > 128) return 0;
+    int tiles = (N + TILE_X - 1) / TILE_X, kb = (K + BK - 1) / BK;
+    int splits = tiles >= sm_count() ? 1 : sm_count() / tiles;      // at most one work item per SM
+    if (splits > kb / 4) splits = kb / 4 > 0 ? kb / 4 : 1;
+    if (splits > 16) splits = 16;
+    return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
+}
+
+extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
+                             int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) return HFB_OK;
+    int rc = check_tc_args("linear_tc", a, w, out, M, N, K);
+    if (rc != HFB_OK) return rc;
+    if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "linear_tc: bad element types");
+    if (accumulate && out_dt != HFB_F32) return fail(HFB_EINVAL, "linear_tc: accumulation needs a float32 output");
+    cudaStream_t st = (cudaStream_t)s;
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn;
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
+    p.out = out; p.out_dt = out_dt; p.bias = bias; p.bias_dt = bias_dt;
+    p.mode = accumulate ? EPI_ADD : EPI_STORE;
+    if (p.swapped) {
+        size_t need = hfb_linear_tc_workspace(M, N, K);
+        if (need && workspace && workspace_bytes >= need) {
+            int splits = (int)(need / ((size_t)M * N * sizeof(float)));
+            p.kb_per_split = (p.kb_total + splits - 1) / splits;
+            p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+            if (p.splits > 1) { p.partial = (float *)workspace; p.mode = EPI_PARTIAL; }
+            else p.kb_per_split = p.kb_total;
+        }
+    }
+    if ((rc = launch_bn(bn, mx, my, p, st)) != HFB_OK) return rc;
+    if (p.mode == EPI_PARTIAL) {
+        size_t MN = (size_t)M * N;
+        splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
+                                                                          accumulate ? EPI_ADD : EPI_STORE);
+        return check_launch("splitk_reduce");
+    }
     return HFB_OK;
 }
 

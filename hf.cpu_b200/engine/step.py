@@ -136,6 +136,7 @@ class Engine:
         # pure decode steps are captured once per (batch size, key-split bucket) as a CUDA graph and replayed
         self.use_graphs = (self._pinned and os.environ.get("HFB_GRAPHS", "1") != "0"
                            and all(getattr(p, "graph_safe", False) for p in model.all_parts()))
+        self.wide_attention_tiles = os.environ.get("HFB_PREFILL_WARPS", "8") == "8"
         self._graphs: Dict[tuple, tuple] = {}
         self._static_meta: Dict[int, torch.Tensor] = {}
         self._meta_ring = []            # [host buffer, device buffer, event of its last copy]
@@ -219,7 +220,8 @@ class Engine:
         max_blocks_used = max((n + bs - 1) // bs for n in kv_lens)
         MB = self.max_blocks if static else max(1, max_blocks_used)
         q_lens = [len(e.tokens) for e in entries]
-        warps = 1 if max(q_lens) == 1 else 4
+        # rows of an attention tile: 16 per warp; long portions get the wide tile (keys are read half as often)
+        warps = 1 if max(q_lens) == 1 else (8 if max(q_lens) >= 64 and self.wide_attention_tiles else 4)
         tilings = []
         for ratio in self._tile_ratios:
             per = (16 * warps) // ratio
@@ -285,6 +287,8 @@ class Engine:
         for ratio, t_seq, _, _ in tilings:
             n = len(t_seq)
             ctx._tiles[(ratio, warps)] = (take(n), take(n), take(n), n)
+            if warps == 1 and 64 // ratio >= 1:
+                ctx._tiles[(ratio, 4)] = ctx._tiles[(ratio, 1)]        # one token a tile fits the wider kernel too
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, M
         ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots
         ctx.max_q_len = max(len(e.tokens) for e in entries)

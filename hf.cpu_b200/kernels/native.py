@@ -49,6 +49,7 @@ class NativeBackend:
         self.lib.hfb_attention_fast_scratch.restype = ctypes.c_size_t
         # "fast": tiled tensor-core attention where the sizes allow; "plain": one block per (token, head) always
         self.attention = os.environ.get("HFB_ATTENTION", "fast")
+        self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "4"))
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         # "tc": tensor-core products where the operands allow; "plain": the float32-accumulating SIMT kernel always
         self.gemm = os.environ.get("HFB_GEMM", "tc")
@@ -125,8 +126,11 @@ class NativeBackend:
         if (self.attention == "fast" and tiles is not None and q.dtype == torch.bfloat16 and d in (64, 128)
                 and 64 % meta.block_size == 0):
             decode = ctx.max_q_len == 1
-            warps = 1 if decode else 4
+            warps = self.decode_warps if decode else 4
             tiling = tiles(H // G, warps)
+            if tiling is None and not decode:
+                warps = 8
+                tiling = tiles(H // G, 8)
             if tiling is not None:
                 tile_seq, tile_t0, tile_nt, n_tiles = tiling
                 splits = 1

@@ -260,10 +260,10 @@ def test_linear_tensor_core(shape):
     kernels.check_device_errors()
 
 
-def _with_tiles(case, lens_q, lens_kv, H, G):
+def _with_tiles(case, lens_q, lens_kv, H, G, wide=False):
     """Adds what the tiled kernel needs to a case's context: the tile lists and the step's extents."""
     q, kc, vc, meta, ctx = case
-    warps = 1 if max(lens_q) == 1 else 4
+    warps = 1 if max(lens_q) == 1 else (8 if wide else 4)
     per = (16 * warps) // (H // G)
     t_seq, t_t0, t_nt, t0 = [], [], [], 0
     for s, n in enumerate(lens_q):
@@ -276,7 +276,7 @@ def _with_tiles(case, lens_q, lens_kv, H, G):
 
     def buf(name, shape, dtype):
         return ws.setdefault((name, shape, dtype), torch.empty(shape, dtype=dtype, device=DEV))
-    ctx.attn_tiles = lambda ratio, w: tiles if (ratio, w) == (H // G, warps) else None
+    ctx.attn_tiles = lambda ratio, w: tiles if ratio == H // G and (w == warps or (warps == 1 and 64 // ratio >= 1)) else None
     ctx.max_q_len, ctx.max_kv_len, ctx.buf = max(lens_q), max(lens_kv), buf
     return case
 
@@ -292,8 +292,10 @@ def test_attention_tiled_mixed_and_decode(geom, window):
     from hfcpu_b200 import kernels
     H, G, d, bs = geom
     b = kernels.backend()
-    for lens_q, lens_kv in (([1, 70, 1, 7, 2, 130], [300, 70, 1, 133, 64, 700]), ([1, 1, 1, 1, 1], [1, 64, 65, 1000, 2311])):
-        case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window), lens_q, lens_kv, H, G)
+    for lens_q, lens_kv, wide in (([1, 70, 1, 7, 2, 130], [300, 70, 1, 133, 64, 700], False),
+                                  ([1, 70, 1, 7, 2, 130], [300, 70, 1, 133, 64, 700], True),
+                                  ([1, 1, 1, 1, 1], [1, 64, 65, 1000, 2311], False)):
+        case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window), lens_q, lens_kv, H, G, wide)
         b.launches = 0
         out = _run_attention(native(), case, H, G, d, window)
         ref = _run_attention(EmuBackend(), case, H, G, d, window)
