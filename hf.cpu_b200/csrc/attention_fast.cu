@@ -13,6 +13,8 @@
 // swizzled shared memory, double buffered; fragments are read with ldmatrix.
 #include "common.cuh"
 
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
 namespace hfb {
 int *error_word();
 
@@ -68,6 +70,7 @@ template <int D, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_fast_kernel(AttnParams p, int *err)
 {
+    pdl_sync();
     constexpr int BM = 16 * WARPS, CH = D / 8, NT = WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sq = (uint32_t)__cvta_generic_to_shared(smem);
@@ -233,6 +236,7 @@ attention_fast_kernel(AttnParams p, int *err)
 template <int D>
 __global__ void attention_combine_kernel(const float *part_o, const float *part_ml, int splits, __nv_bfloat16 *out)
 {
+    pdl_sync();
     const size_t th = blockIdx.x;
     const float *ml = part_ml + th * splits * 2;
     float m = -INFINITY;
@@ -259,8 +263,8 @@ static int launch_attention(const AttnParams &p, int n_tiles, cudaStream_t st)
         configured = true;
     }
     dim3 grid(n_tiles, p.G, p.splits);
-    attention_fast_kernel<D, WARPS><<<grid, WARPS * 32, smem, st>>>(p, error_word());
-    return check_launch("attention_fast");
+    g_launch_err = launch_pdl(attention_fast_kernel<D, WARPS>, dim3(grid), dim3(WARPS * 32), smem, st, p, error_word());
+    return check_pdl_launch(g_launch_err, "attention_fast");
 }
 
 }  // namespace hfb
@@ -307,7 +311,7 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
     if (d == 128) rc = warps == 8 ? launch_attention<128, 8>(p, n_tiles, st) : warps == 4 ? launch_attention<128, 4>(p, n_tiles, st) : launch_attention<128, 1>(p, n_tiles, st);
     else rc = warps == 8 ? launch_attention<64, 8>(p, n_tiles, st) : warps == 4 ? launch_attention<64, 4>(p, n_tiles, st) : launch_attention<64, 1>(p, n_tiles, st);
     if (rc != HFB_OK || splits == 1) return rc;
-    if (d == 128) attention_combine_kernel<128><<<(unsigned)((size_t)T * H), 128, 0, st>>>(p.part_o, p.part_ml, splits, p.out);
-    else attention_combine_kernel<64><<<(unsigned)((size_t)T * H), 64, 0, st>>>(p.part_o, p.part_ml, splits, p.out);
-    return check_launch("attention_combine");
+    if (d == 128) g_launch_err = launch_pdl(attention_combine_kernel<128>, dim3((unsigned)((size_t)T * H)), dim3(128), 0, st, p.part_o, p.part_ml, splits, p.out);
+    else g_launch_err = launch_pdl(attention_combine_kernel<64>, dim3((unsigned)((size_t)T * H)), dim3(64), 0, st, p.part_o, p.part_ml, splits, p.out);
+    return check_pdl_launch(g_launch_err, "attention_combine");
 }

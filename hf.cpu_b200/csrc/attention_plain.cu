@@ -7,6 +7,8 @@
 // only on (lo, pos) and the values, never on what else is in the batch.
 #include "common.cuh"
 
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
 namespace hfb {
 int *error_word();
 
@@ -19,6 +21,7 @@ attention_plain_kernel(const T *q, const T *k_cache, const T *v_cache, const int
                        const int32_t *token_seq, const int32_t *positions, int block_size, long long num_pages,
                        int window, float scale, T *out, int H, int G, int d, int *err)
 {
+    pdl_sync();
     int t = blockIdx.x, h = blockIdx.y;
     int g = h / (H / G);
     int seq = token_seq[t], pos = positions[t];
@@ -101,12 +104,12 @@ extern "C" int hfb_attention_plain(const void *q, const void *k_cache, const voi
     if (H > 65535) return fail(HFB_ENOTSUP, "attention: %d heads exceed the grid limit", H);
     dim3 grid(T, H);
     if (dt == HFB_F32)
-        attention_plain_kernel<float><<<grid, ATT_WARPS * 32, 0, (cudaStream_t)s>>>((const float *)q, (const float *)k_cache,
+        g_launch_err = launch_pdl(attention_plain_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const float *)q, (const float *)k_cache,
             (const float *)v_cache, block_table, max_blocks, token_seq, positions, block_size, num_pages, window, scale,
             (float *)out, H, G, d, error_word());
     else
-        attention_plain_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)q,
+        g_launch_err = launch_pdl(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(ATT_WARPS * 32), 0, (cudaStream_t)s, (const __nv_bfloat16 *)q,
             (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, block_table, max_blocks, token_seq, positions,
             block_size, num_pages, window, scale, (__nv_bfloat16 *)out, H, G, d, error_word());
-    return check_launch("attention_plain");
+    return check_pdl_launch(g_launch_err, "attention_plain");
 }

@@ -52,6 +52,38 @@ __device__ __forceinline__ float warp_max(float v)
     return v;
 }
 
+// Programmatic dependent launch.  Every kernel of the forward pass is launched so that it may start while the
+// kernel before it is still running; it does what needs none of that kernel's results (set-up, and in the
+// products the first loads of the weights), then waits for the predecessor to finish, then lets its own
+// successor start, so that never more than one kernel runs ahead.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_sync() { pdl_wait(); pdl_trigger(); }
+
+bool pdl_enabled();          // HFB_PDL != 0
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+inline int check_pdl_launch(cudaError_t e, const char *what)
+{
+    if (e != cudaSuccess) return fail(HFB_ECUDA, "%s: %s", what, cudaGetErrorString(e));
+    return check_launch(what);
+}
+
 inline bool valid_dt(int dt) { return dt == HFB_F32 || dt == HFB_BF16; }
 
 }  // namespace hfb

@@ -1,12 +1,15 @@
 // Embedding gather, RMSNorm, rotary + cache write, SwiGLU, arg-max: the memory-bound steps.
 #include "common.cuh"
 
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
 namespace hfb {
 int *error_word();
 
 // ---- embedding (src/model.c:566-571) ---------------------------------------------------------
 __global__ void embed_kernel(const int32_t *ids, const void *table, int dt, float *out, int V, int E, int *err)
 {
+    pdl_sync();
     int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= V) {
@@ -22,6 +25,7 @@ __global__ void embed_kernel(const int32_t *ids, const void *table, int dt, floa
 __global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
                                const int32_t *rows, int E)
 {
+    pdl_sync();
     int m = blockIdx.x;
     const float *xr = x + (size_t)(rows ? rows[m] : m) * E;
     float ss = 0.f;
@@ -46,6 +50,7 @@ __global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float ep
 template <typename TW, typename TO>
 __global__ void rmsnorm_vec_kernel(const float *x, const TW *w, float eps, TO *out, const int32_t *rows, int E)
 {
+    pdl_sync();
     int m = blockIdx.x;
     const float4 *xr = (const float4 *)(x + (size_t)(rows ? rows[m] : m) * E);
     const int E4 = E >> 2;
@@ -83,6 +88,7 @@ __global__ void rope_kv_write_kernel(const T *qkv, const float *cos_sin, int n_r
                                      const int32_t *positions, const int32_t *slots, T *q_out, T *k_cache,
                                      T *v_cache, long long cache_slots, int H, int G, int d, int *err)
 {
+    pdl_sync();
     int t = blockIdx.x, head = blockIdx.y;
     const T *src = qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d;
     T *dst;
@@ -121,6 +127,7 @@ __global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int
                                          const int32_t *positions, const int32_t *slots, T *q_out, T *k_cache,
                                          T *v_cache, long long cache_slots, int H, int G, int d, int *err)
 {
+    pdl_sync();
     constexpr int VEC = 16 / sizeof(T);
     struct alignas(16) Pack { T e[VEC]; };
     const int t = blockIdx.x;
@@ -161,6 +168,7 @@ __global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int
 template <typename T>
 __global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total, int interleaved)
 {
+    pdl_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t t = i / F;
@@ -173,6 +181,7 @@ __global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total, int inte
 // ---- arg-max, the lowest index wins ties (src/sample.c:72-77) ---------------------------------
 __global__ void argmax_kernel(const float *logits, int32_t *out, int V)
 {
+    pdl_sync();
     const float *row = logits + (size_t)blockIdx.x * V;
     float best = 0.f;
     int bi = -1;
@@ -203,8 +212,8 @@ extern "C" int hfb_embed(const int32_t *ids, const void *table, int table_dt, fl
 {
     if (T <= 0) return HFB_OK;
     if (!valid_dt(table_dt) || V <= 0 || E <= 0) return fail(HFB_EINVAL, "embed: bad arguments");
-    embed_kernel<<<T, 256, 0, (cudaStream_t)s>>>(ids, table, table_dt, out, V, E, error_word());
-    return check_launch("embed");
+    g_launch_err = launch_pdl(embed_kernel, dim3(T), dim3(256), 0, (cudaStream_t)s, ids, table, table_dt, out, V, E, error_word());
+    return check_pdl_launch(g_launch_err, "embed");
 }
 
 extern "C" int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
@@ -215,14 +224,14 @@ extern "C" int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, v
     int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
     cudaStream_t st = (cudaStream_t)s;
     if ((E & 3) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w & 15) == 0) {
-        if (w_dt == HFB_F32 && out_dt == HFB_F32) rmsnorm_vec_kernel<float, float><<<M, threads, 0, st>>>(x, (const float *)w, eps, (float *)out, rows, E);
-        else if (w_dt == HFB_F32) rmsnorm_vec_kernel<float, __nv_bfloat16><<<M, threads, 0, st>>>(x, (const float *)w, eps, (__nv_bfloat16 *)out, rows, E);
-        else if (out_dt == HFB_F32) rmsnorm_vec_kernel<__nv_bfloat16, float><<<M, threads, 0, st>>>(x, (const __nv_bfloat16 *)w, eps, (float *)out, rows, E);
-        else rmsnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16><<<M, threads, 0, st>>>(x, (const __nv_bfloat16 *)w, eps, (__nv_bfloat16 *)out, rows, E);
+        if (w_dt == HFB_F32 && out_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<float, float>, dim3(M), dim3(threads), 0, st, x, (const float *)w, eps, (float *)out, rows, E);
+        else if (w_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<float, __nv_bfloat16>, dim3(M), dim3(threads), 0, st, x, (const float *)w, eps, (__nv_bfloat16 *)out, rows, E);
+        else if (out_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<__nv_bfloat16, float>, dim3(M), dim3(threads), 0, st, x, (const __nv_bfloat16 *)w, eps, (float *)out, rows, E);
+        else g_launch_err = launch_pdl(rmsnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(M), dim3(threads), 0, st, x, (const __nv_bfloat16 *)w, eps, (__nv_bfloat16 *)out, rows, E);
     } else {
-        rmsnorm_kernel<<<M, threads, 0, st>>>(x, w, w_dt, eps, out, out_dt, rows, E);
+        g_launch_err = launch_pdl(rmsnorm_kernel, dim3(M), dim3(threads), 0, st, x, w, w_dt, eps, out, out_dt, rows, E);
     }
-    return check_launch("rmsnorm");
+    return check_pdl_launch(g_launch_err, "rmsnorm");
 }
 
 extern "C" int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, int n_rot, int n_positions,
@@ -240,24 +249,24 @@ extern "C" int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, 
         int items = (H + 2 * G) * (d / vec);
         int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
         if (dt == HFB_F32)
-            rope_kv_write_vec_kernel<float><<<T, threads, 0, (cudaStream_t)s>>>((const float *)qkv, cos_sin, n_rot, n_positions,
+            g_launch_err = launch_pdl(rope_kv_write_vec_kernel<float>, dim3(T), dim3(threads), 0, (cudaStream_t)s, (const float *)qkv, cos_sin, n_rot, n_positions,
                 positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, cache_slots, H, G, d, error_word());
         else
-            rope_kv_write_vec_kernel<__nv_bfloat16><<<T, threads, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)qkv, cos_sin, n_rot,
+            g_launch_err = launch_pdl(rope_kv_write_vec_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, (cudaStream_t)s, (const __nv_bfloat16 *)qkv, cos_sin, n_rot,
                 n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache,
                 cache_slots, H, G, d, error_word());
-        return check_launch("rope_kv_write");
+        return check_pdl_launch(g_launch_err, "rope_kv_write");
     }
     dim3 grid(T, H + 2 * G);
     int threads = d >= 128 ? 64 : 32;
     if (dt == HFB_F32)
-        rope_kv_write_kernel<float><<<grid, threads, 0, (cudaStream_t)s>>>((const float *)qkv, cos_sin, n_rot, n_positions,
+        g_launch_err = launch_pdl(rope_kv_write_kernel<float>, dim3(grid), dim3(threads), 0, (cudaStream_t)s, (const float *)qkv, cos_sin, n_rot, n_positions,
             positions, slots, (float *)q_out, (float *)k_cache, (float *)v_cache, cache_slots, H, G, d, error_word());
     else
-        rope_kv_write_kernel<__nv_bfloat16><<<grid, threads, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)qkv, cos_sin, n_rot,
+        g_launch_err = launch_pdl(rope_kv_write_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, (cudaStream_t)s, (const __nv_bfloat16 *)qkv, cos_sin, n_rot,
             n_positions, positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache,
             cache_slots, H, G, d, error_word());
-    return check_launch("rope_kv_write");
+    return check_pdl_launch(g_launch_err, "rope_kv_write");
 }
 
 extern "C" int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved, hfb_stream s)
@@ -266,15 +275,15 @@ extern "C" int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int i
     if (!valid_dt(dt) || F <= 0) return fail(HFB_EINVAL, "swiglu: bad arguments");
     size_t total = (size_t)T * F;
     unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dt == HFB_F32) swiglu_kernel<float><<<blocks, 256, 0, (cudaStream_t)s>>>((const float *)gu, (float *)out, F, total, interleaved);
-    else swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)s>>>((const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, F, total, interleaved);
-    return check_launch("swiglu");
+    if (dt == HFB_F32) g_launch_err = launch_pdl(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const float *)gu, (float *)out, F, total, interleaved);
+    else g_launch_err = launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)s, (const __nv_bfloat16 *)gu, (__nv_bfloat16 *)out, F, total, interleaved);
+    return check_pdl_launch(g_launch_err, "swiglu");
 }
 
 extern "C" int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_stream s)
 {
     if (M <= 0) return HFB_OK;
     if (V <= 0) return fail(HFB_EINVAL, "argmax: empty vocabulary");
-    argmax_kernel<<<M, 1024, 0, (cudaStream_t)s>>>(logits, out, V);
-    return check_launch("argmax");
+    g_launch_err = launch_pdl(argmax_kernel, dim3(M), dim3(1024), 0, (cudaStream_t)s, logits, out, V);
+    return check_pdl_launch(g_launch_err, "argmax");
 }

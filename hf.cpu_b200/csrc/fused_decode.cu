@@ -9,6 +9,8 @@
 
 #include "common.cuh"
 
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
 namespace hfb {
 int *error_word();
 
@@ -16,6 +18,7 @@ int *error_word();
 __global__ void reduce_residual_norm_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
                                             float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt)
 {
+    pdl_sync();
     const int m = blockIdx.x;
     const size_t MN = (size_t)M * N;
     float *res = residual + (size_t)m * N;
@@ -53,6 +56,7 @@ __global__ void __launch_bounds__(RRN_THREADS)
 reduce_residual_norm_cluster_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
                                     float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt)
 {
+    pdl_sync();
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
@@ -107,6 +111,7 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
                                       const int32_t *slots, T *q_out, T *k_cache, T *v_cache, long long cache_slots,
                                       int H, int G, int d, int *err)
 {
+    pdl_sync();
     const int t = blockIdx.x, head = blockIdx.y;
     const int N = (H + 2 * G) * d;
     const size_t TN = (size_t)Tn * N, row = (size_t)t * N + (size_t)head * d;
@@ -151,6 +156,7 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
 // arg-max in two passes so that many blocks share a row: (value, index) per chunk, then the best chunk.
 __global__ void argmax_chunks_kernel(const float *logits, int V, int chunk, float *best_v, int32_t *best_i)
 {
+    pdl_sync();
     const int row = blockIdx.y, c = blockIdx.x;
     const float *p = logits + (size_t)row * V;
     const int lo = c * chunk, hi = min(V, lo + chunk);
@@ -177,6 +183,7 @@ __global__ void argmax_chunks_kernel(const float *logits, int V, int chunk, floa
 
 __global__ void argmax_final_kernel(const float *best_v, const int32_t *best_i, int chunks, int32_t *out)
 {
+    pdl_sync();
     const int row = blockIdx.x;
     float best = 0.f;
     int bi = -1;
@@ -212,19 +219,21 @@ extern "C" int hfb_reduce_residual_norm(const float *partial, int splits, int M,
         cfg.gridDim = dim3((unsigned)(M * C));
         cfg.blockDim = dim3(RRN_THREADS);
         cfg.stream = (cudaStream_t)s;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = pdl_enabled() ? 2 : 1;
         cudaError_t e = cudaLaunchKernelEx(&cfg, reduce_residual_norm_cluster_kernel, partial, splits, M, N, bias, bias_dt,
                                            residual, w, w_dt, eps, xn, xn_dt);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "reduce_residual_norm: %s", cudaGetErrorString(e));
         return HFB_OK;
     }
     int threads = N >= 2048 ? 512 : (N >= 512 ? 256 : 128);
-    reduce_residual_norm_kernel<<<M, threads, 0, (cudaStream_t)s>>>(partial, splits, M, N, bias, bias_dt, residual, w, w_dt, eps, xn, xn_dt);
-    return check_launch("reduce_residual_norm");
+    g_launch_err = launch_pdl(reduce_residual_norm_kernel, dim3(M), dim3(threads), 0, (cudaStream_t)s, partial, splits, M, N, bias, bias_dt, residual, w, w_dt, eps, xn, xn_dt);
+    return check_pdl_launch(g_launch_err, "reduce_residual_norm");
 }
 
 extern "C" int hfb_reduce_rope_kv(const float *partial, int splits, int dt, const void *bias, int bias_dt,
@@ -241,12 +250,12 @@ extern "C" int hfb_reduce_rope_kv(const float *partial, int splits, int dt, cons
     int threads = d >= 128 ? 64 : 32;
     cudaStream_t st = (cudaStream_t)s;
     if (dt == HFB_F32)
-        reduce_rope_kv_kernel<float><<<grid, threads, 0, st>>>(partial, splits, T, bias, bias_dt, cos_sin, n_rot, n_positions, positions,
+        g_launch_err = launch_pdl(reduce_rope_kv_kernel<float>, dim3(grid), dim3(threads), 0, st, partial, splits, T, bias, bias_dt, cos_sin, n_rot, n_positions, positions,
             slots, (float *)q_out, (float *)k_cache, (float *)v_cache, cache_slots, H, G, d, error_word());
     else
-        reduce_rope_kv_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(partial, splits, T, bias, bias_dt, cos_sin, n_rot, n_positions,
+        g_launch_err = launch_pdl(reduce_rope_kv_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, st, partial, splits, T, bias, bias_dt, cos_sin, n_rot, n_positions,
             positions, slots, (__nv_bfloat16 *)q_out, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, cache_slots, H, G, d, error_word());
-    return check_launch("reduce_rope_kv");
+    return check_pdl_launch(g_launch_err, "reduce_rope_kv");
 }
 
 // Floats + ints of scratch hfb_argmax2 needs for M rows of V logits.
@@ -265,7 +274,7 @@ extern "C" int hfb_argmax2(const float *logits, int32_t *out, int M, int V, void
     if (M > 65535) return fail(HFB_ENOTSUP, "argmax: %d rows exceed the grid limit", M);
     float *bv = (float *)scratch;
     int32_t *bi = (int32_t *)(bv + (size_t)M * chunks);
-    argmax_chunks_kernel<<<dim3(chunks, M), 256, 0, (cudaStream_t)s>>>(logits, V, 4096, bv, bi);
-    argmax_final_kernel<<<M, 32, 0, (cudaStream_t)s>>>(bv, bi, chunks, out);
-    return check_launch("argmax2");
+    g_launch_err = launch_pdl(argmax_chunks_kernel, dim3(chunks, M), dim3(256), 0, (cudaStream_t)s, logits, V, 4096, bv, bi);
+    g_launch_err = launch_pdl(argmax_final_kernel, dim3(M), dim3(32), 0, (cudaStream_t)s, bv, bi, chunks, out);
+    return check_pdl_launch(g_launch_err, "argmax2");
 }

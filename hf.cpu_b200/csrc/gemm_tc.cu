@@ -24,6 +24,8 @@
 
 #include "common.cuh"
 
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
 namespace hfb {
 int *error_word();
 
@@ -282,9 +284,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     if (warp == 0) {
         // ---- producer: TMA loads --------------------------------------------------------------
+        // The weights do not depend on the kernel before this one, the activations do.  The first STAGES
+        // weight tiles are requested at once; only then does the producer wait for the predecessor
+        // (and let the successor start), and sends the activation loads it had put off.
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true, dep_ready = false;
+            int pend_n = 0, pend_s[STAGES], pend_kb[STAGES], pend_row[STAGES];
+            auto load_dependent = [&](int s, int kb, int row) {
+                if (p.swapped) tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, row, full0 + 8 * s);
+                else tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, row, full0 + 8 * s);
+            };
+            auto flush = [&]() {
+                pdl_sync();
+                for (int i = 0; i < pend_n; i++) load_dependent(pend_s[i], pend_kb[i], pend_row[i]);
+                pend_n = 0;
+                dep_ready = true;
+            };
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 int split = item / per_split, t = item % per_split;
                 int tx = t % p.tiles_x, ty = t / p.tiles_x;
@@ -292,15 +308,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int kb = kb0; kb < kb1; kb++, it++) {
                     int s = it % STAGES;
                     uint32_t ph = (it / STAGES) & 1;
+                    if (!dep_ready && it >= STAGES) flush();       // the stage to be reused still awaits its activation tile
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
                     mbar_arrive_expect_tx(full0 + 8 * s, X_BYTES + Y_BYTES);
-                    tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
-                    tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * s);
+                    if (p.swapped) tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
+                    else tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * s);
+                    const int dep_row = p.swapped ? ty * BN : tx * TILE_X;
+                    if (dep_ready) load_dependent(s, kb, dep_row);
+                    else { pend_s[pend_n] = s; pend_kb[pend_n] = kb; pend_row[pend_n] = dep_row; pend_n++; }
                 }
             }
+            if (!dep_ready) flush();
+        } else {
+            pdl_sync();
         }
     } else if (warp == 1) {
         // ---- tensor-core issue ------------------------------------------------------------------
+        pdl_sync();
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(BN);
             uint32_t it = 0, tile_it = 0;
@@ -335,6 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else {
         // ---- epilogue: TMEM -> registers -> global ------------------------------------------------
+        pdl_sync();                                   // nothing is written before the kernel in front has finished
         const int q = warp & 3;                       // the TMEM lane quarter this warp may read
         const int row = q * 32 + lane;
         uint32_t tile_it = 0;
@@ -381,6 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 __global__ void splitk_reduce_kernel(const float *partial, int splits, size_t MN, int N, const void *bias, int bias_dt,
                                      void *out, int out_dt, int mode)
 {
+    pdl_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= MN) return;
     float v = 0.f;
@@ -473,8 +499,8 @@ static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams
     }
     int items = p.tiles_x * p.tiles_y * p.splits;
     int grid = items < sm_count() ? items : sm_count();
-    gemm_tc_kernel<BN, STAGES><<<grid, GEMM_THREADS, smem, st>>>(mx, my, p, error_word());
-    return check_launch("gemm_tc");
+    g_launch_err = launch_pdl(gemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), smem, st, mx, my, p, error_word());
+    return check_pdl_launch(g_launch_err, "gemm_tc");
 }
 
 }  // namespace hfb
@@ -578,9 +604,9 @@ extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int
     if ((rc = launch_bn(bn, mx, my, p, st)) != HFB_OK) return rc;
     if (p.mode == EPI_PARTIAL) {
         size_t MN = (size_t)M * N;
-        splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
+        g_launch_err = launch_pdl(splitk_reduce_kernel, dim3((unsigned)((MN + 255) / 256)), dim3(256), 0, st, p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
                                                                           accumulate ? EPI_ADD : EPI_STORE);
-        return check_launch("splitk_reduce");
+        return check_pdl_launch(g_launch_err, "splitk_reduce");
     }
     return HFB_OK;
 }
@@ -735,9 +761,9 @@ extern "C" int hfb_linear_tc_noalloc(const void *a, const void *w, const void *b
     if (rc != HFB_OK) return rc;
     if (p.mode == EPI_PARTIAL) {
         size_t MN = (size_t)M * N;
-        splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, st>>>(p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
+        g_launch_err = launch_pdl(splitk_reduce_kernel, dim3((unsigned)((MN + 255) / 256)), dim3(256), 0, st, p.partial, p.splits, MN, N, bias, bias_dt, out, out_dt,
                                                                           accumulate ? EPI_ADD : EPI_STORE);
-        return check_launch("splitk_reduce");
+        return check_pdl_launch(g_launch_err, "splitk_reduce");
     }
     return HFB_OK;
 }

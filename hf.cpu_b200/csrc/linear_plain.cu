@@ -6,6 +6,8 @@
 // (src/kern_generic.c:84-91 beside src/kern_avx2.c:79-95; call shape src/model.c:419-425).
 #include "common.cuh"
 
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
 namespace hfb {
 
 constexpr int TM = 64, TN = 64, TK = 16;
@@ -15,6 +17,7 @@ __global__ void __launch_bounds__(256)
 linear_plain_kernel(const TA *__restrict__ a, const TW *__restrict__ w, const void *bias, int bias_dt,
                     void *out, int out_dt, int accumulate, int M, int N, int K)
 {
+    pdl_sync();
     __shared__ float sa[TK][TM + 1];
     __shared__ float sw[TK][TN + 1];
     int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
@@ -82,11 +85,11 @@ extern "C" int hfb_linear_plain(const void *a, int a_dt, const void *w, int w_dt
     dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM);
     if (grid.y > 65535) return fail(HFB_ENOTSUP, "linear: %d rows exceed the plain kernel's grid", M);
     cudaStream_t st = (cudaStream_t)s;
-#define LAUNCH(TA, TW) linear_plain_kernel<TA, TW><<<grid, 256, 0, st>>>((const TA *)a, (const TW *)w, bias, bias_dt, out, out_dt, accumulate, M, N, K)
+#define LAUNCH(TA, TW) g_launch_err = launch_pdl(linear_plain_kernel<TA, TW>, dim3(grid), dim3(256), 0, st, (const TA *)a, (const TW *)w, bias, bias_dt, out, out_dt, accumulate, M, N, K)
     if (a_dt == HFB_F32 && w_dt == HFB_F32) LAUNCH(float, float);
     else if (a_dt == HFB_F32) LAUNCH(float, __nv_bfloat16);
     else if (w_dt == HFB_F32) LAUNCH(__nv_bfloat16, float);
     else LAUNCH(__nv_bfloat16, __nv_bfloat16);
 #undef LAUNCH
-    return check_launch("linear_plain");
+    return check_pdl_launch(g_launch_err, "linear_plain");
 }

@@ -1,6 +1,7 @@
 // Status reporting and the device error word.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -15,6 +16,16 @@ int fail(int code, const char *fmt, ...)
     vsnprintf(g_msg, sizeof g_msg, fmt, ap);
     va_end(ap);
     return code;
+}
+
+bool pdl_enabled()
+{
+    static int on = -1;
+    if (on < 0) {
+        const char *v = getenv("HFB_PDL");
+        on = !(v && v[0] == '0');
+    }
+    return on != 0;
 }
 
 __device__ int g_error_word = 0;

@@ -13,6 +13,8 @@
 // summing in the reference's order.
 #include "common.cuh"
 
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
 namespace hfb {
 
 constexpr int SAMPLE_THREADS = 1024;
@@ -114,6 +116,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float *logits, int V, const float *temps, const int32_t *top_ks, const float *top_ps,
               const float *min_ps, const float *uniforms, int32_t *out)
 {
+    pdl_sync();
     __shared__ float red[32];
     __shared__ float hist[256];
     __shared__ unsigned long long result[2];
@@ -267,6 +270,6 @@ extern "C" int hfb_sample(const float *logits, int M, int V, const float *temps,
 {
     if (M <= 0) return HFB_OK;
     if (V <= 0 || V >= (1 << 24)) return fail(HFB_ENOTSUP, "sample: vocabulary of %d is not supported (1..2^24-1)", V);
-    sample_kernel<<<M, SAMPLE_THREADS, 0, (cudaStream_t)s>>>(logits, V, temps, top_ks, top_ps, min_ps, uniforms, out);
-    return check_launch("sample");
+    g_launch_err = launch_pdl(sample_kernel, dim3(M), dim3(SAMPLE_THREADS), 0, (cudaStream_t)s, logits, V, temps, top_ks, top_ps, min_ps, uniforms, out);
+    return check_pdl_launch(g_launch_err, "sample");
 }
