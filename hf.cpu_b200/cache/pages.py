@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import CacheSpec
@@ -90,6 +91,7 @@ class CacheGroup:
         self.storage = torch.zeros((len(self.entries), 2, num_pages, block_size, spec.num_kv_heads, spec.head_dim),
                                    dtype=dtype, device=device)
         self.tables: Dict[object, List[int]] = {}       # request -> page id per block, -1 = not mapped
+        self.np_tables: Dict[object, np.ndarray] = {}   # the same at full width as int32, ready to be copied to the device
 
     @property
     def page_bytes(self) -> int:
@@ -111,7 +113,12 @@ class CacheGroup:
         and every query among them sees its keys."""
         last = (new_len - 1) // self.block_size
         first = self.first_needed_block(old_len)
-        return [b for b in range(first, last + 1) if b >= len(table) or table[b] < 0]
+        # blocks below len(table) are mapped unless a window has passed them, and those lie before `first`
+        # (advance() released them): only the blocks beyond the table are new, and holes made by a failed step
+        start = max(first, len(table))
+        if start > first and any(table[b] < 0 for b in range(first, min(len(table), last + 1))):
+            return [b for b in range(first, last + 1) if b >= len(table) or table[b] < 0]
+        return list(range(start, last + 1))
 
 
 class KVCacheManager:
@@ -160,6 +167,7 @@ class KVCacheManager:
         self.lengths[req] = 0
         for g in self.groups:
             g.tables[req] = []
+            g.np_tables[req] = np.full(self.max_blocks, -1, dtype=np.int32)
 
     def pages_needed(self, req, new_len: int) -> List[int]:
         """Pages each group would have to map for ``req`` to hold ``new_len`` tokens; a request that is
@@ -194,6 +202,7 @@ class KVCacheManager:
                 while len(t) <= b:
                     t.append(-1)
                 t[b] = g.pool.alloc()
+                g.np_tables[req][b] = t[b]
 
     def advance(self, req, new_len: int) -> None:
         """The request now holds ``new_len`` tokens; pages a window has passed go back to the pool."""
@@ -204,6 +213,7 @@ class KVCacheManager:
                 if t[b] >= 0:
                     g.pool.free(t[b])
                     t[b] = -1
+                    g.np_tables[req][b] = -1
 
     def release(self, req) -> None:
         """The request ends: every page it holds in every group goes back."""
@@ -211,6 +221,7 @@ class KVCacheManager:
             for p in g.tables.pop(req):
                 if p >= 0:
                     g.pool.free(p)
+            del g.np_tables[req]
         del self.lengths[req]
 
     def check(self) -> None:
@@ -223,3 +234,5 @@ class KVCacheManager:
                 f"group {g.index}: {g.pool.used_count} pages in use but {len(held)} in block tables"
             for p in held:
                 assert g.pool.refcount(p) == 1
+            for req, t in g.tables.items():
+                assert g.np_tables[req][:len(t)].tolist() == t and (g.np_tables[req][len(t):] == -1).all()

@@ -5,8 +5,6 @@
 // instead of three kernels; likewise the sum, bias, rotary encoding and cache write of the q|k|v product.
 // Arithmetic as in the separate kernels: src/model.c:606-611 (residual, then RMSNorm, src/mathx.c:65-75) and
 // src/model.c:581-601 (bias after the dot, rotation, cache write).
-#include <cooperative_groups.h>
-
 #include "common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
@@ -48,60 +46,69 @@ __global__ void reduce_residual_norm_kernel(const float *partial, int splits, in
         store_any(xn, xn_dt, (size_t)m * N + i, (res[i] * r) * load_any(w, w_dt, i));
 }
 
-// The same with a cluster of CTAs per row: each CTA owns a slice of the columns, keeps its sums in registers,
-// and the CTAs exchange their partial sums of squares through distributed shared memory (summed in rank order).
-constexpr int RRN_THREADS = 256, RRN_PER_THREAD = 4;
+// The same with 16-byte accesses and the row's sums kept in registers between the two passes: one CTA of up to
+// 1024 threads per row, each thread owning up to RRN_VEC float4 columns.
+constexpr int RRN_VEC = 4;
 
-__global__ void __launch_bounds__(RRN_THREADS)
-reduce_residual_norm_cluster_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
-                                    float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt)
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(1024)
+reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
+                                float *residual, const TW *w, float eps, TO *xn)
 {
     pdl_sync();
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
-    const int m = blockIdx.x / C;
-    const int per = (N + C - 1) / C, lo = rank * per, hi = min(N, lo + per);
-    const size_t MN = (size_t)M * N;
-    float *res = residual + (size_t)m * N;
-    float vals[RRN_PER_THREAD];
+    const int m = blockIdx.x, N4 = N >> 2;
+    const size_t MN4 = ((size_t)M * N) >> 2;
+    const float4 *part = (const float4 *)partial + (size_t)m * N4;
+    float4 *res = (float4 *)(residual + (size_t)m * N);
+    float4 vals[RRN_VEC];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < RRN_PER_THREAD; j++) {
-        int i = lo + threadIdx.x + j * RRN_THREADS;
-        float v = 0.f;
-        if (i < hi) {
-            for (int s = 0; s < splits; s++) v += partial[(size_t)s * MN + (size_t)m * N + i];
-            if (bias) v += load_any(bias, bias_dt, i);
-            v += res[i];
+    for (int j = 0; j < RRN_VEC; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < N4) {
+            for (int s = 0; s < splits; s++) {
+                float4 q = part[(size_t)s * MN4 + i];
+                v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+            }
+            if (bias) {
+                v.x += load_any(bias, bias_dt, 4 * i); v.y += load_any(bias, bias_dt, 4 * i + 1);
+                v.z += load_any(bias, bias_dt, 4 * i + 2); v.w += load_any(bias, bias_dt, 4 * i + 3);
+            }
+            float4 r = res[i];
+            v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
             res[i] = v;
         }
         vals[j] = v;
-        ss += v * v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
-    __shared__ float part[32];
-    __shared__ float cta_ss;
+    if (!xn) return;
+    __shared__ float part_ss[32];
     ss = warp_sum(ss);
-    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) part[warp] = ss;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if (lane == 0) part_ss[warp] = ss;
     __syncthreads();
     if (warp == 0) {
-        float t = lane < RRN_THREADS / 32 ? part[lane] : 0.f;
+        float t = lane < nw ? part_ss[lane] : 0.f;
         t = warp_sum(t);
-        if (lane == 0) cta_ss = t;
+        if (lane == 0) part_ss[0] = t;
     }
-    cluster.sync();
-    if (xn) {
-        float total = 0.f;
-        for (int c = 0; c < C; c++) total += *cluster.map_shared_rank(&cta_ss, c);
-        const float r = 1.0f / sqrtf(total / (float)N + eps);
+    __syncthreads();
+    const float r = 1.0f / sqrtf(part_ss[0] / (float)N + eps);
 #pragma unroll
-        for (int j = 0; j < RRN_PER_THREAD; j++) {
-            int i = lo + threadIdx.x + j * RRN_THREADS;
-            if (i < hi) store_any(xn, xn_dt, (size_t)m * N + i, (vals[j] * r) * load_any(w, w_dt, i));
+    for (int j = 0; j < RRN_VEC; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i >= N4) continue;
+        const float4 v = vals[j];
+        float y0 = (v.x * r) * to_f32(w[4 * i]), y1 = (v.y * r) * to_f32(w[4 * i + 1]);
+        float y2 = (v.z * r) * to_f32(w[4 * i + 2]), y3 = (v.w * r) * to_f32(w[4 * i + 3]);
+        TO *o = xn + (size_t)m * N + 4 * i;
+        if (sizeof(TO) == 4) *(float4 *)o = make_float4(y0, y1, y2, y3);
+        else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+            *(uint2 *)o = make_uint2(*(uint32_t *)&lo, *(uint32_t *)&hi);
         }
     }
-    cluster.sync();          // no CTA leaves while another may still read its shared memory
 }
 
 // q|k|v row = sum_s partial[s, t, :] + bias; rotate q and k; q -> q_out, k and v -> the paged cache.
@@ -211,25 +218,19 @@ extern "C" int hfb_reduce_residual_norm(const float *partial, int splits, int M,
     if (M <= 0) return HFB_OK;
     if (splits < 1 || N <= 0 || (bias && !valid_dt(bias_dt)) || (xn && (!valid_dt(w_dt) || !valid_dt(xn_dt))))
         return fail(HFB_EINVAL, "reduce_residual_norm: bad arguments");
-    // a cluster of up to 8 CTAs per row when the row is wide enough to share out
-    int C = N >= 2048 ? 8 : N >= 1024 ? 4 : N >= 512 ? 2 : 1;
-    while (C < 8 && (N + C - 1) / C > RRN_THREADS * RRN_PER_THREAD) C *= 2;
-    if (C > 1 && (N + C - 1) / C <= RRN_THREADS * RRN_PER_THREAD) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(M * C));
-        cfg.blockDim = dim3(RRN_THREADS);
-        cfg.stream = (cudaStream_t)s;
-        cudaLaunchAttribute attr[2];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[1].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = pdl_enabled() ? 2 : 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, reduce_residual_norm_cluster_kernel, partial, splits, M, N, bias, bias_dt,
-                                           residual, w, w_dt, eps, xn, xn_dt);
-        if (e != cudaSuccess) return fail(HFB_ECUDA, "reduce_residual_norm: %s", cudaGetErrorString(e));
-        return HFB_OK;
+    if ((N & 3) == 0 && N <= 4 * RRN_VEC * 1024 && ((uintptr_t)partial & 15) == 0 && ((uintptr_t)residual & 15) == 0 &&
+        (!xn || (((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0))) {
+        int threads = (N / 4 + 31) / 32 * 32;          // one float4 per thread where the row allows, four at most
+        if (threads > 1024) threads = 1024;
+        cudaStream_t st = (cudaStream_t)s;
+        dim3 grid(M), block(threads);
+#define RRN(TW, TO) g_launch_err = launch_pdl(reduce_residual_norm_vec_kernel<TW, TO>, grid, block, 0, st, partial, splits, M, N, bias, bias_dt, residual, (const TW *)w, eps, (TO *)xn)
+        if (w_dt == HFB_F32 && xn_dt == HFB_F32) RRN(float, float);
+        else if (w_dt == HFB_F32) RRN(float, __nv_bfloat16);
+        else if (xn_dt == HFB_F32) RRN(__nv_bfloat16, float);
+        else RRN(__nv_bfloat16, __nv_bfloat16);
+#undef RRN
+        return check_pdl_launch(g_launch_err, "reduce_residual_norm");
     }
     int threads = N >= 2048 ? 512 : (N >= 512 ? 256 : 128);
     g_launch_err = launch_pdl(reduce_residual_norm_kernel, dim3(M), dim3(threads), 0, (cudaStream_t)s, partial, splits, M, N, bias, bias_dt, residual, w, w_dt, eps, xn, xn_dt);

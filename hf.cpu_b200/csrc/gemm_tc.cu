@@ -19,6 +19,8 @@
 // row to float (src/model.c:369-440, src/kern_avx2.c:79-95); accumulation here is float32 too.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -486,11 +488,22 @@ static int sm_count()
     return n;
 }
 
+// Experiment switches (environment): HFB_SHALLOW=1 picks the half-depth pipelines so that two CTAs fit an SM
+// (the next kernel's CTAs can then start beside this kernel's last ones); HFB_CTAS_PER_SM caps the grid.
+static int env_int(const char *name, int dflt)
+{
+    const char *v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+static int ctas_per_sm() { static int v = env_int("HFB_CTAS_PER_SM", 1); return v; }
+static bool shallow() { static int v = env_int("HFB_SHALLOW", 0); return v != 0; }
+
 template <int BN, int STAGES>
 static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams &p, cudaStream_t st)
 {
     constexpr uint32_t smem = gemm_smem_bytes<BN, STAGES>();
-    static_assert(smem > 116 * 1024, "one CTA per SM is assumed (two could not both allocate their TMEM columns)");
+    // CTAs that can share an SM by shared memory must also all find their TMEM columns (512 per SM)
+    static_assert((227 * 1024 / smem) * tmem_cols<BN>() <= 512, "co-resident CTAs would wait for TMEM columns");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -498,7 +511,8 @@ static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams
         configured = true;
     }
     int items = p.tiles_x * p.tiles_y * p.splits;
-    int grid = items < sm_count() ? items : sm_count();
+    int cap = sm_count() * ctas_per_sm();
+    int grid = items < cap ? items : cap;
     g_launch_err = launch_pdl(gemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), smem, st, mx, my, p, error_word());
     return check_pdl_launch(g_launch_err, "gemm_tc");
 }
@@ -546,9 +560,9 @@ static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const
 {
     using namespace hfb;
     switch (bn) {
-    case 16: return launch<16, 10>(mx, my, p, st);
-    case 32: return launch<32, 9>(mx, my, p, st);
-    case 64: return launch<64, 8>(mx, my, p, st);
+    case 16: return shallow() ? launch<16, 5>(mx, my, p, st) : launch<16, 10>(mx, my, p, st);
+    case 32: return shallow() ? launch<32, 5>(mx, my, p, st) : launch<32, 9>(mx, my, p, st);
+    case 64: return shallow() ? launch<64, 4>(mx, my, p, st) : launch<64, 8>(mx, my, p, st);
     case 128: return launch<128, 6>(mx, my, p, st);
     case 192: return launch<192, 5>(mx, my, p, st);
     case 224: return launch<224, 4>(mx, my, p, st);
@@ -570,7 +584,8 @@ extern "C" size_t hfb_linear_tc_workspace(int M, int N, int K)
 {
     if (M > 128) return 0;
     int tiles = (N + TILE_X - 1) / TILE_X, kb = (K + BK - 1) / BK;
-    int splits = tiles >= sm_count() ? 1 : sm_count() / tiles;      // at most one work item per SM
+    int cap = sm_count() * env_int("HFB_CTAS_PER_SM", 1);
+    int splits = tiles >= cap ? 1 : cap / tiles;                    // at most one work item per CTA slot
     if (splits > kb / 4) splits = kb / 4 > 0 ? kb / 4 : 1;
     if (splits > 16) splits = 16;
     return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;

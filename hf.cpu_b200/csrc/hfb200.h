@@ -46,6 +46,12 @@ size_t hfb_linear_tc_workspace(int M, int N, int K);
 int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
                   int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s);
 
+/* The product for at most 16 rows of bfloat16 a (decode): weights stream from global memory straight into
+ * mma.sync fragments, no partial sums leave the CTA.  mode 0: store (+bias); 1: accumulate into a float32 out
+ * (+bias); 2: SwiGLU of alternating gate/up rows of w, out [M, N/2]. */
+int hfb_linear_mma(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
+                   int mode, int M, int N, int K, hfb_stream s);
+
 /* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
 int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
 
@@ -87,12 +93,13 @@ int hfb_attention_plain(const void *q, const void *k_cache, const void *v_cache,
  * most hfb_attention_fast_tile_tokens(H, G, warps) tokens of one request.  warps = 4 for prompt portions and
  * mixed batches (splits must be 1), warps = 1 for decode, where `splits` > 1 cuts each request's keys into
  * that many ranges whose partial results are merged in order; they live in `scratch`
+ * (stages = 4 with warps = 4 selects a deeper load pipeline for CTAs that have an SM to themselves)
  * (hfb_attention_fast_scratch bytes). */
 int hfb_attention_fast_tile_tokens(int H, int G, int warps);
 size_t hfb_attention_fast_scratch(int T, int H, int d, int splits);
 int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                        int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
-                       const int32_t *tile_nt, int n_tiles, int warps, int splits, int block_size,
+                       const int32_t *tile_nt, int n_tiles, int warps, int stages, int splits, int block_size,
                        int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
                        int T, int H, int G, int d, hfb_stream s);
 

@@ -13,6 +13,7 @@ import os
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import KVCacheManager, OutOfPages, StateSlots
@@ -211,67 +212,78 @@ class Engine:
 
         ctx = StepContext(self)
         S = len(entries)
-        T = sum(len(e.tokens) for e in entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
         M = sum(len(e.want) for e in entries)
         groups = self.cache.groups
         bs = self.block_size
-        # one flat int32 buffer: a single host-to-device copy per step
+        starts = [self.cache.length(e.req) for e in entries]
         kv_lens = [w[1] for w in wants]
-        max_blocks_used = max((n + bs - 1) // bs for n in kv_lens)
-        MB = self.max_blocks if static else max(1, max_blocks_used)
-        q_lens = [len(e.tokens) for e in entries]
+        max_q = max(q_lens)
+        MB = self.max_blocks if static else max(1, (max(kv_lens) + bs - 1) // bs)
         # rows of an attention tile: 16 per warp; long portions get the wide tile (keys are read half as often)
-        warps = 1 if max(q_lens) == 1 else (8 if max(q_lens) >= 64 and self.wide_attention_tiles else 4)
+        warps = 1 if max_q == 1 else (8 if max_q >= 64 and self.wide_attention_tiles else 4)
         tilings = []
         for ratio in self._tile_ratios:
             per = (16 * warps) // ratio
             if per < 1:
                 continue
-            t_seq, t_t0, t_nt, t0 = [], [], [], 0
-            for s_i, n in enumerate(q_lens):
-                for a in range(0, n, per):
-                    t_seq.append(s_i)
-                    t_t0.append(t0 + a)
-                    t_nt.append(min(per, n - a))
-                t0 += n
+            if max_q == 1:
+                t_seq = t_t0 = np.arange(S, dtype=np.int32)
+                t_nt = np.ones(S, dtype=np.int32)
+            else:
+                ls, lt, ln, t0 = [], [], [], 0
+                for s_i, n in enumerate(q_lens):
+                    for a in range(0, n, per):
+                        ls.append(s_i)
+                        lt.append(t0 + a)
+                        ln.append(min(per, n - a))
+                    t0 += n
+                t_seq, t_t0, t_nt = (np.asarray(x, dtype=np.int32) for x in (ls, lt, ln))
             tilings.append((ratio, t_seq, t_t0, t_nt))
         total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB) + sum(3 * len(t[1]) for t in tilings)
+        # one flat int32 buffer, filled through its numpy view: a single host-to-device copy per step
         ring_slot = self._meta_buffers(total)
         h, d = ring_slot[0], ring_slot[1]
         if static:
             d = self._static_meta.get(S)
             if d is None or d.numel() < total:
                 d = self._static_meta[S] = torch.empty(total, dtype=torch.int32, device=self.device)
-        hl: List[int] = []
-        tok, pos, seq, cu, rows = [], [], [], [0], []
-        for s, e in enumerate(entries):
-            start = self.cache.length(e.req)
-            n = len(e.tokens)
-            tok += [int(t) for t in e.tokens]
-            pos += range(start, start + n)
-            seq += [s] * n
-            rows += [cu[-1] + int(w) for w in e.want]
-            cu.append(cu[-1] + n)
+        hn = h.numpy()
+        cu = np.zeros(S + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu[1:])
+        if max_q == 1:
+            tok = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=S)
+            pos = np.asarray(starts, dtype=np.int32)
+            seq = np.arange(S, dtype=np.int32)
+        else:
+            tok = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+            pos = np.concatenate([np.arange(st, st + n, dtype=np.int32) for st, n in zip(starts, q_lens)])
+            seq = np.repeat(np.arange(S, dtype=np.int32), q_lens)
+        rows = [int(cu[s]) + int(w) for s, e in enumerate(entries) for w in e.want]
         seq_slots = [self.slots.slot_of[e.req] for e in entries]
-        hl += tok + pos + seq + cu + kv_lens + seq_slots + rows
+        o = 0
+
+        def put(arr):
+            nonlocal o
+            n = len(arr)
+            hn[o:o + n] = arr
+            o += n
+
+        put(tok), put(pos), put(seq), put(cu), put(kv_lens), put(seq_slots), put(rows)
         for g in groups:
-            slots_g, table_g = [], []
-            for s, e in enumerate(entries):
-                t = g.tables[e.req]
-                start = self.cache.length(e.req)
-                for p in range(start, start + len(e.tokens)):
-                    slots_g.append(t[p // bs] * bs + p % bs)
-                row = t[:MB] + [-1] * (MB - len(t[:MB]))
-                table_g += row
-            hl += slots_g + table_g
+            tables = np.stack([g.np_tables[e.req][:MB] for e in entries])          # [S, MB]
+            blk = pos // bs
+            put(tables[seq, blk] * bs + pos % bs)                                  # cache slot of every token
+            put(tables.reshape(-1))
         for _, t_seq, t_t0, t_nt in tilings:
-            hl += t_seq + t_t0 + t_nt
-        assert len(hl) == total
-        h[:total] = torch.tensor(hl, dtype=torch.int32)
+            put(t_seq), put(t_t0), put(t_nt)
+        assert o == total
         d[:total].copy_(h[:total], non_blocking=True)
         if self._pinned:
             ring_slot[2] = torch.cuda.Event()
             ring_slot[2].record()
+        cu = cu.tolist()
         o = 0
 
         def take(n, shape=None):
@@ -291,7 +303,7 @@ class Engine:
                 ctx._tiles[(ratio, 4)] = ctx._tiles[(ratio, 1)]        # one token a tile fits the wider kernel too
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, M
         ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots
-        ctx.max_q_len = max(len(e.tokens) for e in entries)
+        ctx.max_q_len = max_q
         ctx.max_kv_len = max(kv_lens)
         # how finely decode attention may split a request's keys: a power of two, so that few graphs exist
         hint = max(1, ((ctx.max_kv_len + 63) // 64) // 2)

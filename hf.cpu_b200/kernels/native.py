@@ -49,7 +49,11 @@ class NativeBackend:
         self.lib.hfb_attention_fast_scratch.restype = ctypes.c_size_t
         # "fast": tiled tensor-core attention where the sizes allow; "plain": one block per (token, head) always
         self.attention = os.environ.get("HFB_ATTENTION", "fast")
-        self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "4"))
+        # products with at most this many rows take the weight-streaming mma.sync kernel instead of tcgen05
+        self.gemv_max = int(os.environ.get("HFB_GEMV_MAX", "0"))
+        self.decode_ctas_per_sm = int(os.environ.get("HFB_DECODE_CTAS", "2"))
+        self.decode_stages = int(os.environ.get("HFB_DECODE_STAGES", "2"))
+        self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "2"))
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         # "tc": tensor-core products where the operands allow; "plain": the float32-accumulating SIMT kernel always
         self.gemm = os.environ.get("HFB_GEMM", "tc")
@@ -91,6 +95,9 @@ class NativeBackend:
         self._on_gpu(a, w, bias, out)
         M, K = a.shape
         N = w.shape[0]
+        if M <= self.gemv_max and self._tc_ok(a, w):
+            self._mma(a, w, bias, out, 1 if accumulate else 0)
+            return
         if (self.gemm == "tc" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
             need = self.lib.hfb_linear_tc_workspace(c_int(M), c_int(N), c_int(K))
@@ -127,21 +134,23 @@ class NativeBackend:
                 and 64 % meta.block_size == 0):
             decode = ctx.max_q_len == 1
             warps = self.decode_warps if decode else 4
-            tiling = tiles(H // G, warps)
+            tiling = tiles(H // G, 1 if warps == 2 else warps)        # the decode form (2) tiles like the 16-row kernel
             if tiling is None and not decode:
                 warps = 8
                 tiling = tiles(H // G, 8)
             if tiling is not None:
                 tile_seq, tile_t0, tile_nt, n_tiles = tiling
-                splits = 1
+                splits, stages = 1, 2
                 if decode:
+                    # about `decode_ctas_per_sm` CTAs per SM in all; with one per SM the deep pipeline fits
                     hint = getattr(ctx, "decode_split_hint", max(1, ((ctx.max_kv_len + 63) // 64) // 2))
-                    splits = max(1, min(4 * self.sm_count // max(1, n_tiles * G), hint))
+                    splits = max(1, min(self.decode_ctas_per_sm * self.sm_count // max(1, n_tiles * G), hint))
+                    stages = self.decode_stages if warps in (2, 4) else 2
                 need = self.lib.hfb_attention_fast_scratch(c_int(T), c_int(H), c_int(d), c_int(splits))
                 scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
                 self._check(self.lib.hfb_attention_fast(
                     _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
-                    _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(warps), c_int(splits),
+                    _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(warps), c_int(stages), c_int(splits),
                     c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out),
                     _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), self._stream()),
                     "attention_fast")
@@ -194,10 +203,20 @@ class NativeBackend:
                     "linear_tc_partials")
         return ws, splits.value
 
+    def _mma(self, a, w, bias, out, mode):
+        M, K = a.shape
+        N = w.shape[0]
+        self._check(self.lib.hfb_linear_mma(_p(a), _p(w), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(out),
+                                            c_int(_dt(out)), c_int(mode), c_int(M), c_int(N), c_int(K), self._stream()),
+                    "linear_mma")
+
     def linear_swiglu(self, a, w, gu_buf, out):
         self._on_gpu(a, w, out)
         M, K = a.shape
         N = w.shape[0]
+        if M <= self.gemv_max and self._tc_ok(a, w):
+            self._mma(a, w, None, out, 2)
+            return
         if self._tc_ok(a, w, out):
             self._check(self.lib.hfb_linear_tc_swiglu(_p(a), _p(w), _p(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),
                                                       self._stream()), "linear_tc_swiglu")
@@ -209,7 +228,8 @@ class NativeBackend:
         self._on_gpu(a, w, bias, residual, norm_w, xn_out)
         M, K = a.shape
         N = w.shape[0]
-        part = self._partials(a, w) if (M <= 128 and self._tc_ok(a, w)) else None
+        small = M <= self.gemv_max and self._tc_ok(a, w)
+        part = self._partials(a, w) if (M <= 128 and not small and self._tc_ok(a, w)) else None
         if part is None:
             self.linear(a, w, bias, residual, True)
             if xn_out is not None:
@@ -224,7 +244,8 @@ class NativeBackend:
     def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
         self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
         M, K = a.shape
-        part = self._partials(a, w) if (M <= 128 and self._tc_ok(a, w)) else None
+        small = M <= self.gemv_max and self._tc_ok(a, w)
+        part = self._partials(a, w) if (M <= 128 and not small and self._tc_ok(a, w)) else None
         if part is None:
             self.linear(a, w, bias, qkv_buf, False)
             self.rope_kv_write(qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d)

@@ -17,6 +17,10 @@ from .. import kernels
 def sample_rows(logits: torch.Tensor, reqs) -> List[int]:
     """``reqs[i]`` (with ``.params`` and ``.rng``) owns row i of the float32 ``logits`` [M, V]."""
     M = logits.shape[0]
+    if all(r.params.temp <= 0 for r in reqs):
+        out = torch.empty(M, dtype=torch.int32, device=logits.device)
+        kernels.argmax(logits.contiguous(), out)             # greedy rows need no parameters and no draws
+        return out.tolist()
     host = np.zeros((5, M), dtype=np.float32)
     for i, r in enumerate(reqs):
         p = r.params
