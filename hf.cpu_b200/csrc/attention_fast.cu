@@ -44,6 +44,13 @@ __device__ __forceinline__ void mma_bf16(float *c, const uint32_t *a, uint32_t b
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware approximation (relative error about 2^-22, far below bfloat16's own rounding)
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
 {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -75,7 +82,8 @@ attention_fast_kernel(AttnParams p, int *err)
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sq = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t sk = sq + BM * D * 2, sv = sk + STAGES * ABN * D * 2;      // K and V: STAGES tiles each
-    const int tile = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+    // tiles late in a prompt see the most keys: hand them out first, so that the last CTAs to start are short ones
+    const int tile = gridDim.x - 1 - blockIdx.x, g = blockIdx.y, split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = p.H / p.G;
     const int seq = p.tile_seq[tile], t0 = p.tile_t0[tile], nt = p.tile_nt[tile];
@@ -163,32 +171,45 @@ attention_fast_kernel(AttnParams p, int *err)
                 mma_bf16(s[2 * nj + 1], qf[kk], b2, b3);
             }
         }
-        // scale, mask by absolute position, running maximum
+        // scale, mask by absolute position, running maximum.  A tile whose keys every row may see (all below the
+        // tile's first position and inside every window) needs no per-element test.
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        const bool all_visible = v0 && v1 && kt * ABN + ABN - 1 <= pos_first &&
+                                 (p.window == 0 || kt * ABN >= max(0, pos_last - p.window + 1));
+        if (all_visible) {
 #pragma unroll
-        for (int i = 0; i < ABN / 8; i++) {
+            for (int i = 0; i < ABN / 8; i++) {
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
-                int key = kt * ABN + i * 8 + (lane & 3) * 2 + e;
-                float a = s[i][e] * p.scale_log2, b = s[i][2 + e] * p.scale_log2;
-                a = (v0 && key >= lo0 && key <= pos0) ? a : -INFINITY;
-                b = (v1 && key >= lo1 && key <= pos1) ? b : -INFINITY;
-                s[i][e] = a; s[i][2 + e] = b;
-                mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b);
+                for (int e = 0; e < 4; e++) s[i][e] *= p.scale_log2;
+                mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < ABN / 8; i++) {
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    int key = kt * ABN + i * 8 + (lane & 3) * 2 + e;
+                    float a = s[i][e] * p.scale_log2, b = s[i][2 + e] * p.scale_log2;
+                    a = (v0 && key >= lo0 && key <= pos0) ? a : -INFINITY;
+                    b = (v1 && key >= lo1 && key <= pos1) ? b : -INFINITY;
+                    s[i][e] = a; s[i][2 + e] = b;
+                    mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b);
+                }
             }
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;     // rows with no key yet
-        float c0 = exp2f(m0 - base0), c1 = exp2f(m1 - base1);                                   // exp2(-inf) = 0
+        float c0 = fast_exp2(m0 - base0), c1 = fast_exp2(m1 - base1);                                   // exp2(-inf) = 0
         m0 = mn0; m1 = mn1;
         float sum0 = 0.f, sum1 = 0.f;
         uint32_t pf[ABN / 16][4];
 #pragma unroll
         for (int i = 0; i < ABN / 8; i++) {
-            float p00 = exp2f(s[i][0] - base0), p01 = exp2f(s[i][1] - base0);
-            float p10 = exp2f(s[i][2] - base1), p11 = exp2f(s[i][3] - base1);
+            float p00 = fast_exp2(s[i][0] - base0), p01 = fast_exp2(s[i][1] - base0);
+            float p10 = fast_exp2(s[i][2] - base1), p11 = fast_exp2(s[i][3] - base1);
             sum0 += p00 + p01; sum1 += p10 + p11;
             pf[i >> 1][(i & 1) * 2] = pack_bf16(p00, p01);
             pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p10, p11);
@@ -342,11 +363,11 @@ attention_decode_kernel(AttnParams p, int *err)
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
-        float c0 = exp2f(m0 - base0), c1 = exp2f(m1 - base1);
+        float c0 = fast_exp2(m0 - base0), c1 = fast_exp2(m1 - base1);
         m0 = mn0; m1 = mn1;
         uint32_t pf[4];
-        float p00 = exp2f(s[0][0] - base0), p01 = exp2f(s[0][1] - base0), p10 = exp2f(s[0][2] - base1), p11 = exp2f(s[0][3] - base1);
-        float q00 = exp2f(s[1][0] - base0), q01 = exp2f(s[1][1] - base0), q10 = exp2f(s[1][2] - base1), q11 = exp2f(s[1][3] - base1);
+        float p00 = fast_exp2(s[0][0] - base0), p01 = fast_exp2(s[0][1] - base0), p10 = fast_exp2(s[0][2] - base1), p11 = fast_exp2(s[0][3] - base1);
+        float q00 = fast_exp2(s[1][0] - base0), q01 = fast_exp2(s[1][1] - base0), q10 = fast_exp2(s[1][2] - base1), q11 = fast_exp2(s[1][3] - base1);
         pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p10, p11); pf[2] = pack_bf16(q00, q01); pf[3] = pack_bf16(q10, q11);
         l0 = l0 * c0 + (p00 + p01 + q00 + q01);
         l1 = l1 * c1 + (p10 + p11 + q10 + q11);
@@ -391,7 +412,7 @@ attention_decode_kernel(AttnParams p, int *err)
 #pragma unroll
         for (int w = 0; w < 4; w++) {
             float mw = mml[(w * 16 + row) * 2];
-            float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+            float f = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
             denom += mml[(w * 16 + row) * 2 + 1] * f;
             acc += mo[((size_t)w * 16 + row) * D + col] * f;
         }

@@ -207,9 +207,23 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
         bool full = y0 + 16 <= p.N && (p.N & 7) == 0;
         float f[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            f[i] = __uint_as_float(v[i]);
-            if (p.bias && p.mode != EPI_PARTIAL && (full || y0 + i < p.N)) f[i] += load_any(p.bias, p.bias_dt, y0 + i);
+        for (int i = 0; i < 16; i++) f[i] = __uint_as_float(v[i]);
+        if (p.bias && p.mode != EPI_PARTIAL) {
+            if (full && p.bias_dt == HFB_BF16) {
+                // 16 consecutive bias values in two 16-byte loads (N is a multiple of 8 here, so they are aligned)
+                const uint4 *bp = (const uint4 *)((const __nv_bfloat16 *)p.bias + y0);
+                uint4 b0 = bp[0], b1 = bp[1];
+                const __nv_bfloat162 *h0 = (const __nv_bfloat162 *)&b0, *h1 = (const __nv_bfloat162 *)&b1;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float2 x = __bfloat1622float2(h0[i]), y = __bfloat1622float2(h1[i]);
+                    f[2 * i] += x.x; f[2 * i + 1] += x.y; f[8 + 2 * i] += y.x; f[8 + 2 * i + 1] += y.y;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    if (full || y0 + i < p.N) f[i] += load_any(p.bias, p.bias_dt, y0 + i);
+            }
         }
         if (p.mode == EPI_PARTIAL) {
             float *dst = p.partial + (size_t)split * p.M * p.N + o;
@@ -378,11 +392,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += (BN >= 32 ? 32 : 16)) {
                 uint32_t v[BN >= 32 ? 32 : 16];
+                const bool two = BN >= 32 && c0 + 16 < BN;       // widths such as 208 end on a single chunk
                 tmem_ld16(taddr + c0, v);
-                if (BN >= 32) tmem_ld16(taddr + c0 + 16, v + (BN >= 32 ? 16 : 0));
+                if (two) tmem_ld16(taddr + c0 + 16, v + (BN >= 32 ? 16 : 0));
                 tmem_wait_ld();
                 epilogue_chunk(p, v, xr, ty * BN + c0, split, lane);
-                if (BN >= 32) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane);
+                if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -541,10 +556,10 @@ static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb:
     } else {
         // the tile width that needs the fewest column-rounds over the SMs (every CTA walks its tiles in turn)
         p.tiles_x = (M + TILE_X - 1) / TILE_X;
-        const int widths[4] = {256, 224, 192, 128};
+        const int widths[6] = {256, 240, 224, 208, 192, 128};
         long best = -1;
         bn = 256;
-        for (int i = 0; i < 4; i++) {
+        for (int i = 0; i < 6; i++) {
             long tiles = (long)p.tiles_x * ((N + widths[i] - 1) / widths[i]);
             long cost = (tiles + sm_count() - 1) / sm_count() * widths[i];
             if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
@@ -565,7 +580,9 @@ static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const
     case 64: return shallow() ? launch<64, 4>(mx, my, p, st) : launch<64, 8>(mx, my, p, st);
     case 128: return launch<128, 6>(mx, my, p, st);
     case 192: return launch<192, 5>(mx, my, p, st);
+    case 208: return launch<208, 4>(mx, my, p, st);
     case 224: return launch<224, 4>(mx, my, p, st);
+    case 240: return launch<240, 4>(mx, my, p, st);
     default: return launch<256, 4>(mx, my, p, st);
     }
 }
