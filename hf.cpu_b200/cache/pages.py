@@ -113,11 +113,10 @@ class CacheGroup:
         and every query among them sees its keys."""
         last = (new_len - 1) // self.block_size
         first = self.first_needed_block(old_len)
-        # blocks below len(table) are mapped unless a window has passed them, and those lie before `first`
-        # (advance() released them): only the blocks beyond the table are new, and holes made by a failed step
+        # Blocks below len(table) are mapped unless a window has passed them, and those lie before `first`
+        # (advance() released them; a step that failed after its reservation leaves its blocks mapped):
+        # only blocks beyond the table are new.
         start = max(first, len(table))
-        if start > first and any(table[b] < 0 for b in range(first, min(len(table), last + 1))):
-            return [b for b in range(first, last + 1) if b >= len(table) or table[b] < 0]
         return list(range(start, last + 1))
 
 
