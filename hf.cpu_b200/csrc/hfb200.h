@@ -103,6 +103,13 @@ int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, 
                        int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
                        int T, int H, int G, int d, hfb_stream s);
 
+/* Attention of prompt portions on tcgen05 (S and PV accumulators in TMEM, K and V gathered page by page with
+ * TMA): bfloat16, head_dim 128, block sizes 8..128 that divide 128.  Tiles hold at most 128 / (H/G) tokens. */
+int hfb_attention_tc(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+                     int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
+                     const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window,
+                     float scale, void *out, int T, int H, int G, int d, hfb_stream s);
+
 /* out[t, f] = silu(g) * u with g = gu[t, f], u = gu[t, F + f], or, interleaved, g = gu[t, 2f], u = gu[t, 2f + 1] */
 int hfb_swiglu(const void *gu, void *out, int dt, int T, int F, int interleaved, hfb_stream s);
 

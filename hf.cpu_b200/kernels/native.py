@@ -51,6 +51,7 @@ class NativeBackend:
         self.attention = os.environ.get("HFB_ATTENTION", "fast")
         # products with at most this many rows take the weight-streaming mma.sync kernel instead of tcgen05
         self.gemv_max = int(os.environ.get("HFB_GEMV_MAX", "0"))
+        self.attention_tc = os.environ.get("HFB_ATTN_TC", "1") != "0"     # tcgen05 attention for prompt portions
         self.decode_ctas_per_sm = int(os.environ.get("HFB_DECODE_CTAS", "2"))
         self.decode_stages = int(os.environ.get("HFB_DECODE_STAGES", "2"))
         self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "2"))
@@ -133,6 +134,17 @@ class NativeBackend:
         if (self.attention == "fast" and tiles is not None and q.dtype == torch.bfloat16 and d in (64, 128)
                 and 64 % meta.block_size == 0):
             decode = ctx.max_q_len == 1
+            if (not decode and self.attention_tc and d == 128 and meta.block_size >= 8 and 128 % meta.block_size == 0
+                    and H // G <= 128):
+                tiling = tiles(H // G, 8)                    # tiles of 128 rows, as the 8-warp kernel's
+                if tiling is not None:
+                    tile_seq, tile_t0, tile_nt, n_tiles = tiling
+                    self._check(self.lib.hfb_attention_tc(
+                        _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
+                        _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(meta.block_size),
+                        c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out), c_int(T), c_int(H), c_int(G),
+                        c_int(d), self._stream()), "attention_tc")
+                    return
             warps = self.decode_warps if decode else 4
             tiling = tiles(H // G, 1 if warps == 2 else warps)        # the decode form (2) tiles like the 16-row kernel
             if tiling is None and not decode:

@@ -319,10 +319,11 @@ def test_attention_tiled_far_key_window_edge_and_page_edges():
             if key_pos > lens_kv[spike_req] - lens_q[spike_req] + q_off:
                 continue
             for window in (0, 40):
-                case = _attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, 0, spike=(spike_req, key_pos, q_off), seed=key_pos)
-                case = _with_tiles(case, lens_q, lens_kv, H, G)
-                out, ref = _run_attention(native(), case, H, G, d, window), _run_attention(EmuBackend(), case, H, G, d, window)
-                assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, key_pos, window)
+                for wide in (False, True):            # wide: 128-row tiles, the tcgen05 kernel for prompt portions
+                    case = _attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, 0, spike=(spike_req, key_pos, q_off), seed=key_pos)
+                    case = _with_tiles(case, lens_q, lens_kv, H, G, wide)
+                    out, ref = _run_attention(native(), case, H, G, d, window), _run_attention(EmuBackend(), case, H, G, d, window)
+                    assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, key_pos, window, wide)
 
 
 @pytest.mark.parametrize("shape", [(1, 352, 64), (8, 37888, 3584), (5, 640, 192), (64, 2048, 512), (130, 640, 192),
@@ -413,3 +414,28 @@ def test_linear_weight_streaming(shape):
         g_, u_ = ref[:, 0::2], ref[:, 1::2]
         assert rel(h, (g_ / (1 + torch.exp(-g_))) * u_) < 1.5e-2
     b.gemv_max = old_max
+
+
+@pytest.mark.parametrize("geom", [(28, 4, 128, 16), (4, 4, 128, 8), (16, 1, 128, 128), (5, 5, 128, 32)])
+def test_attention_tensor_core_prompt_portions(geom):
+    """The tcgen05 attention kernel (head_dim 128): long portions over long histories, several requests, windows,
+    against the torch reference and against the mma.sync kernel."""
+    from hfcpu_b200 import kernels
+    H, G, d, bs = geom
+    b = kernels.backend()
+    assert b.attention_tc
+    for lens_q, lens_kv in (([300, 1, 40], [300, 900, 417]), ([130, 64], [700, 64]), ([2, 1], [2, 1])):
+        for window in (0, 100):
+            case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window, seed=len(lens_q)), lens_q, lens_kv, H, G, wide=True)
+            out = _run_attention(native(), case, H, G, d, window)
+            ref = _run_attention(EmuBackend(), case, H, G, d, window)
+            assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, window)
+            b.attention_tc = False
+            try:
+                other = _run_attention(native(), case, H, G, d, window)
+            finally:
+                b.attention_tc = True
+            assert rel(out.float(), other.float()) < TOL["bfloat16"]
+            again = _run_attention(native(), case, H, G, d, window)
+            assert torch.equal(out, again)
+    kernels.check_device_errors()
