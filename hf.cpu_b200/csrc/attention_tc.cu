@@ -5,8 +5,9 @@
 // key/value head for up to 128 / (H/G) consecutive tokens, and walks the keys in tiles of 128:
 //   S = Q K^T   tcgen05.mma, M = 128, N = 128 keys, K = head_dim; Q and K from shared memory (K-major, 128-byte
 //               swizzle), S (float32) in TMEM;
-//   softmax     four warps, one thread per row: the row's 128 scores come from TMEM with tcgen05.ld, so maximum
-//               and sum need no exchange between threads; P (bf16) goes to shared memory as the next A operand;
+//   softmax     eight warps, two threads per row (64 keys and 64 output columns each): the scores come from TMEM
+//               with tcgen05.ld and stay in registers; the two halves of a row exchange their maxima through
+//               shared memory; P (bf16) goes to shared memory as the next A operand;
 //   PV = P V    tcgen05.mma, M = 128, N = 2 x 64 of head_dim, K = 128 keys; V is the B operand in MN-major form,
 //               which is how the cache holds it (a key's 64 values are one 128-byte row); the result lands in
 //               TMEM and is added into the row's running output, which lives in the thread's registers.
@@ -28,7 +29,7 @@ int tensor_map(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *o
 constexpr int TQ = 128, TKEYS = 128, TD = 128;
 constexpr uint32_t SUB = 128 * 64 * 2;              // one swizzled sub-tile: 128 rows of 64 bf16
 constexpr uint32_t KV_STAGE = 2 * SUB;              // K (or V) tile: two sub-tiles (the halves of head_dim)
-constexpr int ATC_THREADS = 192;
+constexpr int ATC_THREADS = 320;                   // TMA warp, MMA warp, eight softmax warps
 constexpr int ATC_TMEM_COLS = 256;                  // S: columns 0..127, PV: columns 128..255
 
 struct AttnTcParams {
@@ -63,13 +64,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const uint32_t sQ = base, sP = base + 2 * SUB, sK = base + 4 * SUB, sV = sK + 2 * KV_STAGE;
     const uint32_t bars = sV + 2 * KV_STAGE;
     const uint32_t q_ready = bars, s_full = bars + 8, p_ready = bars + 16, pv_full = bars + 24;
-    const uint32_t kv_full0 = bars + 32, kv_empty0 = bars + 48;
-    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen + 4 * SUB + 4 * KV_STAGE + 64);
+    const uint32_t kv_full0 = bars + 32, kv_empty0 = bars + 48, x_ready = bars + 64;
+    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen + 4 * SUB + 4 * KV_STAGE + 96);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    float *xchg = (float *)(gen + 4 * SUB + 4 * KV_STAGE + 128);       // [2][2][128]: maxima of the row halves, double buffered
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
-        mbar_init(q_ready, 4); mbar_init(s_full, 1); mbar_init(p_ready, 4); mbar_init(pv_full, 1);
+        mbar_init(q_ready, 8); mbar_init(s_full, 1); mbar_init(p_ready, 8); mbar_init(pv_full, 1); mbar_init(x_ready, 8);
         for (int s = 0; s < 2; s++) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -160,17 +162,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             if (ok && n_kt > 0) mbar_wait(kv_empty0 + 8 * ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, abort_flag, err);
         }
     } else {
-        // ---- softmax and output: one thread per row ---------------------------------------------------------
-        const int q4 = warp & 3, row = q4 * 32 + lane;
+        // ---- softmax and output: two threads per row, 64 keys / 64 output columns each ---------------------
+        const int q4 = warp & 3, half = (warp - 2) >> 2, row = q4 * 32 + lane;
         const int tl = row / r, hl = row % r;
         const bool valid = tl < nt;
         const size_t th = ((size_t)(t0 + (valid ? tl : 0)) * p.H + g * r + hl) * TD;
         {
-            const uint4 *src = (const uint4 *)(p.q + th);
+            const uint4 *src = (const uint4 *)(p.q + th) + half * 8;
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
+            for (int c = 0; c < 8; c++) {
                 uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + sw_off(row, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + sw_off(row, half * 8 + c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -178,69 +180,57 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
         const int pos = valid ? p.positions[t0 + tl] : -1;
         const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-        const uint32_t tS = tmem_base + ((uint32_t)(q4 * 32) << 16), tPV = tS + 128;
-        float o[TD];
+        const uint32_t tS = tmem_base + ((uint32_t)(q4 * 32) << 16) + half * 64, tPV = tmem_base + ((uint32_t)(q4 * 32) << 16) + 128 + half * 64;
+        float o[64];
 #pragma unroll
-        for (int i = 0; i < TD; i++) o[i] = 0.f;
+        for (int i = 0; i < 64; i++) o[i] = 0.f;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kt && ok; j++) {
-            const int key0 = (kt_lo + j) * TKEYS;
+            const int key0 = (kt_lo + j) * TKEYS + half * 64;         // first key of this thread's half
             if (!mbar_wait(s_full, j & 1, abort_flag, err)) { ok = false; break; }
             tc_fence_after();
-            const bool all_visible = valid && key0 + TKEYS - 1 <= pos && key0 >= lo;
-            // pass 1: the row's maximum
+            const bool all_visible = valid && key0 + 63 <= pos && key0 >= lo;
+            uint32_t sv[64];
+            tmem_ld16(tS, sv); tmem_ld16(tS + 16, sv + 16); tmem_ld16(tS + 32, sv + 32); tmem_ld16(tS + 48, sv + 48);
+            tmem_wait_ld();
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < TKEYS; c += 32) {
-                uint32_t v[32];
-                tmem_ld16(tS + c, v);
-                tmem_ld16(tS + c + 16, v + 16);
-                tmem_wait_ld();
-                if (all_visible) {
+            if (all_visible) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
+                for (int i = 0; i < 64; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        const int key = key0 + c + i;
-                        if (valid && key >= lo && key <= pos) mx = fmaxf(mx, __uint_as_float(v[i]));
-                    }
+                for (int i = 0; i < 64; i++) {
+                    const int key = key0 + i;
+                    const bool see = valid && key >= lo && key <= pos;
+                    if (!see) sv[i] = 0xff800000u;                  // -inf: contributes neither to the maximum nor to the sum
+                    mx = fmaxf(mx, __uint_as_float(sv[i]));
                 }
             }
-            mx *= p.scale_log2;                                    // scale > 0: the maximum commutes with it
+            float *xm = xchg + (j & 1) * 256;
+            xm[half * 128 + row] = mx;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(x_ready);                   // the eight softmax warps meet here (a bounded wait)
+            if (!mbar_wait(x_ready, j & 1, abort_flag, err)) { ok = false; break; }
+            mx = fmaxf(mx, xm[(half ^ 1) * 128 + row]) * p.scale_log2;   // scale > 0 commutes with the maximum
             const float m_new = fmaxf(m, mx);
             const float bs = m_new == -INFINITY ? 0.f : m_new;
             const float corr = ex2(m - bs);                        // 2^-inf = 0 for the first tile
             m = m_new;
-            // pass 2: probabilities, their sum, and P as the next A operand
             float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < TKEYS; c += 32) {
-                uint32_t v[32];
-                tmem_ld16(tS + c, v);
-                tmem_ld16(tS + c + 16, v + 16);
-                tmem_wait_ld();
-                uint32_t pk[16];
+            uint32_t pk[32];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float a = ex2(__uint_as_float(v[i]) * p.scale_log2 - bs), b = ex2(__uint_as_float(v[i + 1]) * p.scale_log2 - bs);
-                    if (!all_visible) {
-                        const int key = key0 + c + i;
-                        if (!(valid && key >= lo && key <= pos)) a = 0.f;
-                        if (!(valid && key + 1 >= lo && key + 1 <= pos)) b = 0.f;
-                    }
-                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                    // the sum is taken over the rounded values the product will use
-                    float2 back = __bfloat1622float2(h);
-                    sum += back.x + back.y;
-                    pk[i >> 1] = *(uint32_t *)&h;
-                }
-#pragma unroll
-                for (int q = 0; q < 4; q++)
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sP + sw_off(row, (c >> 3) + q)), "r"(pk[4 * q]),
-                                 "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
+            for (int i = 0; i < 64; i += 2) {
+                float a = ex2(__uint_as_float(sv[i]) * p.scale_log2 - bs), b = ex2(__uint_as_float(sv[i + 1]) * p.scale_log2 - bs);
+                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                float2 back = __bfloat1622float2(h);                // the sum runs over the rounded values the product uses
+                sum += back.x + back.y;
+                pk[i >> 1] = *(uint32_t *)&h;
             }
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sP + sw_off(row, half * 8 + q)), "r"(pk[4 * q]),
+                             "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
             l = l * corr + sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
@@ -248,26 +238,29 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             if (lane == 0) mbar_arrive(p_ready);
             if (corr != 1.f) {
 #pragma unroll
-                for (int i = 0; i < TD; i++) o[i] *= corr;
+                for (int i = 0; i < 64; i++) o[i] *= corr;
             }
             if (!mbar_wait(pv_full, j & 1, abort_flag, err)) { ok = false; break; }
             tc_fence_after();
+            uint32_t pv[64];
+            tmem_ld16(tPV, pv); tmem_ld16(tPV + 16, pv + 16); tmem_ld16(tPV + 32, pv + 32); tmem_ld16(tPV + 48, pv + 48);
+            tmem_wait_ld();
 #pragma unroll
-            for (int c = 0; c < TD; c += 32) {
-                uint32_t v[32];
-                tmem_ld16(tPV + c, v);
-                tmem_ld16(tPV + c + 16, v + 16);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i++) o[c + i] += __uint_as_float(v[i]);
-            }
+            for (int i = 0; i < 64; i++) o[i] += __uint_as_float(pv[i]);
             tc_fence_before();
         }
+        // the two halves of a row saw different keys with the same maxima: their sums add up
+        float *xl = xchg + 512;
+        xl[half * 128 + row] = l;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(x_ready);
+        ok = ok && mbar_wait(x_ready, n_kt & 1, abort_flag, err);
+        l += xl[(half ^ 1) * 128 + row];
         if (ok && valid) {
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            uint4 *dst = (uint4 *)(p.out + th);
+            uint4 *dst = (uint4 *)(p.out + th) + half * 8;
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
+            for (int c = 0; c < 8; c++) {
                 __nv_bfloat162 h[4];
 #pragma unroll
                 for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
@@ -319,7 +312,7 @@ extern "C" int hfb_attention_tc(const void *q, const void *k_cache, const void *
     p.block_table = block_table; p.positions = positions; p.tile_seq = tile_seq; p.tile_t0 = tile_t0; p.tile_nt = tile_nt;
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.num_slots = slots;
     p.scale_log2 = scale * 1.4426950408889634f;
-    constexpr uint32_t smem = 1024 + 4 * SUB + 4 * KV_STAGE + 128;
+    constexpr uint32_t smem = 1024 + 4 * SUB + 4 * KV_STAGE + 128 + 768 * 4;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
