@@ -209,8 +209,9 @@ def main():
         # ---- end to end through the Python entry point: host ids in, host ids out -----------------------
         del engine
         torch.cuda.empty_cache()
+        # all prompts are prefilled in the first step, so that every later step decodes exactly `batch` tokens
         sess = hfcpu_b200.Session(model, kv_block=BLOCK, kv_pages=pages, max_seqs=max_b, ctx_max=CTX_MAX,
-                                  max_batched_tokens=PROMPT)
+                                  max_batched_tokens=args.batch * PROMPT)
         prompts = synthetic_prompts(args.batch, PROMPT, V, seed=7)
         stamps = []
         sess.generate(prompts, temp=0, max_tokens=warmup + args.steps + 1,
