@@ -23,8 +23,14 @@ TINY_B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden
               num_attention_heads=6, num_key_value_heads=3, head_dim=32, intermediate_size=320, vocab_size=1000,
               max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=1e6, tie_word_embeddings=False,
               use_sliding_window=True, sliding_window=64, max_window_layers=1, hidden_act="silu")
-TINY = {"A": TINY_A, "B": TINY_B}
-BLOCK = {"A": 16, "B": 8}
+# A third one whose sizes the tensor-core kernels take (head_dim 128, widths that are multiples of 8), so that the
+# replay tests drive those kernels too, with a window on its second layer.
+TINY_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2, hidden_size=256,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=128, intermediate_size=456, vocab_size=1032,
+              max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=50000.0, tie_word_embeddings=False,
+              use_sliding_window=True, sliding_window=96, max_window_layers=1, hidden_act="silu")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+BLOCK = {"A": 16, "B": 8, "C": 16}
 
 
 def make_folder(cfg_dict, folder, seed, dtype, sharp=4.0, std=0.05):

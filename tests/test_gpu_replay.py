@@ -14,7 +14,7 @@ from conftest import BLOCK, TINY, TOL, make_requests, plain_logits
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [7, 16, 33, 100, 70], "B": [1, 19, 64, 130, 200]}
+LENGTHS = {"A": [7, 16, 33, 100, 70], "B": [1, 19, 64, 130, 200], "C": [3, 150, 64, 129, 260]}
 FAMILIES = {"whole": traces.whole, "tail": traces.tail_one_by_one, "portions": traces.portions,
             "mixed": traces.mixed}
 DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
@@ -55,7 +55,7 @@ def whole_rows(tiny_folders, name, dtype, reqs):
 
 @pytest.mark.parametrize("family", list(FAMILIES))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_cuttings_match_plain(tiny_folders, name, dtype, family):
     folder = folder_for(tiny_folders, name, dtype)
     reqs = make_requests(name, LENGTHS[name], seed=3)
@@ -74,13 +74,14 @@ def test_cuttings_match_plain(tiny_folders, name, dtype, family):
         assert bad is None, f"differs from the whole-prompt run at request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_long_decoding_past_the_window(tiny_folders, dtype):
-    """Token by token from the first token, far past configuration B's window of 64 and across many pages."""
-    folder = folder_for(tiny_folders, "B", dtype)
-    reqs = make_requests("B", [300], seed=21)
+def test_long_decoding_past_the_window(tiny_folders, dtype, name):
+    """Token by token from the first token, far past the window (64 in B, 96 in C) and across many pages."""
+    folder = folder_for(tiny_folders, name, dtype)
+    reqs = make_requests(name, [300], seed=21)
     steps = traces.one_by_one(reqs)
-    eng = engine_for(folder, "B", dtype, traces.peak_tokens(steps))
+    eng = engine_for(folder, name, dtype, traces.peak_tokens(steps))
     got = traces.run_in_process(eng, steps, check=eng.cache.check)
     check_clean(eng)
     ref = {r: plain_logits(folder, ids) for r, ids in reqs.items()}
