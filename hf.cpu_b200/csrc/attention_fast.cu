@@ -65,14 +65,6 @@ struct AttnParams {
     int max_blocks, block_size, window, H, G, splits;
     long long num_pages;
     float scale_log2;                   // scale * log2(e)
-    // decode form only.  With qkv_part the kernel finishes the q|k|v product itself: row = sum of the split-K
-    // partials + bias, rotated; the token's own key and value go to the cache (one CTA writes them) and into the
-    // tile in shared memory.  With counters the last CTA of a (token, kv head) merges the splits in place of
-    // a second kernel.
-    const float *qkv_part; int qkv_splits, T; const void *qkv_bias; int bias_dt;
-    const float *cos_sin; int n_rot, n_positions; const int32_t *slots;
-    __nv_bfloat16 *k_cache_w, *v_cache_w; long long cache_slots;
-    int *counters;
 };
 
 // Byte offset of 16-byte chunk `c` of row `row` in a tile whose rows hold D bf16 (D = 64 or 128).
@@ -292,17 +284,12 @@ attention_decode_kernel(AttnParams p, int *err)
         kt_lo = kt_lo + split * per;
         kt_hi = min(kt_hi, kt_lo + per);
     }
-    __shared__ __align__(16) __nv_bfloat16 cur_kv[2][D];      // fused form: this token's rotated key, and its value
-    const bool fused = p.qkv_part != nullptr;                 // nt == 1 then
-    const bool own_key = fused && p.slots && pos_last / ABN >= kt_lo && pos_last / ABN < kt_hi;   // this CTA's keys include the token's own, and it is to be cached
-    if (!fused) {
-        for (int i = threadIdx.x; i < 16 * CH; i += NT) {
-            int row = i / CH, c = i % CH;
-            int tl = row / r, hl = row % r;
-            bool valid = tl < nt;
-            const __nv_bfloat16 *src = p.q + ((size_t)(t0 + (valid ? tl : 0)) * p.H + g * r + hl) * D + c * 8;
-            cp_async16(sq + swz<D>(row, c), src, valid);
-        }
+    for (int i = threadIdx.x; i < 16 * CH; i += NT) {
+        int row = i / CH, c = i % CH;
+        int tl = row / r, hl = row % r;
+        bool valid = tl < nt;
+        const __nv_bfloat16 *src = p.q + ((size_t)(t0 + (valid ? tl : 0)) * p.H + g * r + hl) * D + c * 8;
+        cp_async16(sq + swz<D>(row, c), src, valid);
     }
     cp_async_commit();
     auto load_kv = [&](int kt, int stage) {
@@ -323,71 +310,6 @@ attention_decode_kernel(AttnParams p, int *err)
         if (kt_lo + st < kt_hi) load_kv(kt_lo + st, st);
         else cp_async_commit();
     }
-    if (fused) {
-        // the q|k|v row of token t0: partial sums in split order, bias, rounding to the run type, rotation
-        const int N = (p.H + 2 * p.G) * D, half = p.n_rot / 2;
-        const size_t TN = (size_t)p.T * N, rowoff = (size_t)t0 * N;
-        int pos = pos_last;
-        if (half > 0 && (pos < 0 || pos >= p.n_positions)) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
-        const float *cs = half > 0 ? p.cos_sin + (size_t)pos * half * 2 : nullptr;
-        auto value = [&](int col) {                      // column of the fused q|k|v row
-            float v = 0.f;
-            for (int sp = 0; sp < p.qkv_splits; sp++) v += p.qkv_part[(size_t)sp * TN + rowoff + col];
-            if (p.qkv_bias) v += load_any(p.qkv_bias, p.bias_dt, col);
-            return __bfloat162float(__float2bfloat16_rn(v));
-        };
-        uint8_t *sq_gen = smem;
-        // heads: r query heads of this group, then (for the CTA that owns the token's position) key and value
-        const int heads = r + (own_key ? 2 : 0);
-        for (int i = threadIdx.x; i < heads * (D / 2); i += NT) {
-            const int hh = i / (D / 2), e = i % (D / 2);          // element pair (e, e + D/2)
-            int col0;
-            bool rotate = true;
-            if (hh < r) col0 = (g * r + hh) * D;
-            else if (hh == r) col0 = (p.H + g) * D;
-            else { col0 = (p.H + p.G + g) * D; rotate = false; }
-            float a = value(col0 + e), b = value(col0 + e + D / 2), ya = a, yb = b;
-            if (rotate && half > 0) {
-                // pairs (i, i + n_rot/2) for i < n_rot/2; with n_rot == D these are (e, e + D/2)
-                if (p.n_rot == D) { float c = cs[2 * e], sn = cs[2 * e + 1]; ya = a * c - b * sn; yb = a * sn + b * c; }
-                else {
-                    // partial rotation: handle the two elements separately
-                    auto rot1 = [&](int idx, float x) {
-                        if (idx >= p.n_rot) return x;
-                        int j = idx < half ? idx : idx - half;
-                        float other = value(col0 + (idx < half ? idx + half : idx - half));
-                        float c = cs[2 * j], sn = cs[2 * j + 1];
-                        return idx < half ? x * c - other * sn : other * sn + x * c;
-                    };
-                    ya = rot1(e, a); yb = rot1(e + D / 2, b);
-                }
-            }
-            const __nv_bfloat16 ha = __float2bfloat16_rn(ya), hb = __float2bfloat16_rn(yb);
-            if (hh < r) {
-                *(__nv_bfloat16 *)(sq_gen + swz<D>(hh, e >> 3) + (e & 7) * 2) = ha;
-                *(__nv_bfloat16 *)(sq_gen + swz<D>(hh, (e + D / 2) >> 3) + ((e + D / 2) & 7) * 2) = hb;
-            } else {
-                cur_kv[hh - r][e] = ha;
-                cur_kv[hh - r][e + D / 2] = hb;
-            }
-        }
-        // rows of padding in the query tile
-        for (int i = threadIdx.x; i < (16 - r) * CH; i += NT) {
-            int row = r + i / CH, c = i % CH;
-            *(uint4 *)(sq_gen + swz<D>(row, c)) = make_uint4(0, 0, 0, 0);
-        }
-        __syncthreads();
-        if (own_key && p.slots) {
-            long long slot = p.slots[t0];
-            if (slot >= p.cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); slot = -1; }
-            if (slot >= 0) {
-                for (int i = threadIdx.x; i < 2 * CH; i += NT) {
-                    __nv_bfloat16 *dst = (i < CH ? p.k_cache_w : p.v_cache_w) + ((size_t)slot * p.G + g) * D + (i % CH) * 8;
-                    *(uint4 *)dst = *(const uint4 *)&cur_kv[i / CH][(i % CH) * 8];
-                }
-            }
-        }
-    }
     const int row0 = lane >> 2, row1 = row0 + 8;
     const int tl0 = row0 / r, tl1 = row1 / r;
     const bool v0 = tl0 < nt, v1 = tl1 < nt;
@@ -406,15 +328,6 @@ attention_decode_kernel(AttnParams p, int *err)
         else cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncthreads();
-        if (own_key && kt == pos_last / ABN) {
-            // the token's own key and value are not in the cache yet for the loads above: put them into the tile
-            const int kr = pos_last % ABN;
-            for (int i = threadIdx.x; i < 2 * CH; i += NT) {
-                uint8_t *dst = smem + ((i < CH ? sk : sv) - sq) + stage * (ABN * D * 2) + swz<D>(kr, i % CH);
-                *(uint4 *)dst = *(const uint4 *)&cur_kv[i / CH][(i % CH) * 8];
-            }
-            __syncthreads();
-        }
         if (!q_loaded) {
 #pragma unroll
             for (int kk = 0; kk < D / 16; kk++)
@@ -512,38 +425,6 @@ attention_decode_kernel(AttnParams p, int *err)
             p.out[th * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
         }
     }
-    if (p.splits > 1 && p.counters) {
-        // the CTA that finishes last for this (tile, kv head) merges all splits, in split order
-        __shared__ int is_last;
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int *cnt = p.counters + (size_t)tile * p.G + g;
-            int old = atomicAdd(cnt, 1);
-            is_last = old == p.splits - 1;
-            if (is_last) *cnt = 0;                      // ready for the next launch
-        }
-        __syncthreads();
-        if (!is_last) return;
-        __threadfence();
-        for (int idx = threadIdx.x; idx < rows * D; idx += NT) {
-            const int row = idx / D, col = idx % D;
-            const int tok = t0 + row / r, head = g * r + row % r;
-            const size_t th = (size_t)tok * p.H + head;
-            const volatile float *ml = p.part_ml + th * p.splits * 2;
-            float m = -INFINITY;
-            for (int sp = 0; sp < p.splits; sp++) m = fmaxf(m, ml[2 * sp]);
-            float denom = 0.f, acc = 0.f;
-            for (int sp = 0; sp < p.splits; sp++) {
-                float ms = ml[2 * sp];
-                if (ms == -INFINITY) continue;
-                float f = exp2f(ms - m);
-                denom += ml[2 * sp + 1] * f;
-                acc += ((const volatile float *)p.part_o)[(th * p.splits + sp) * D + col] * f;
-            }
-            p.out[th * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
-        }
-    }
 }
 
 template <int D, int STAGES>
@@ -615,40 +496,6 @@ extern "C" size_t hfb_attention_fast_scratch(int T, int H, int d, int splits)
     return splits > 1 ? (size_t)T * H * splits * (d + 2) * sizeof(float) : 0;
 }
 
-// Decode attention that finishes the q|k|v product itself and merges its own splits (one launch instead of three):
-// qkv_part[qkv_splits, T, (H+2G)d] are the split-K partial sums of the q|k|v product of T single-token requests.
-extern "C" int hfb_attention_decode_fused(const float *qkv_part, int qkv_splits, const void *qkv_bias, int bias_dt,
-                                          const float *cos_sin, int n_rot, int n_positions, const int32_t *slots,
-                                          void *k_cache, void *v_cache, const int32_t *block_table, int max_blocks,
-                                          const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
-                                          const int32_t *tile_nt, int T, int stages, int splits, int block_size,
-                                          int64_t num_pages, int window, float scale, void *out, void *scratch,
-                                          size_t scratch_bytes, int *counters, int H, int G, int d, hfb_stream s)
-{
-    if (T <= 0) return HFB_OK;
-    if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_decode_fused: head_dim %d (64 and 128 only)", d);
-    if (block_size <= 0 || ABN % block_size) return fail(HFB_ENOTSUP, "attention_decode_fused: block size %d does not divide %d", block_size, ABN);
-    if (G <= 0 || H % G || H / G > 16) return fail(HFB_ENOTSUP, "attention_decode_fused: %d heads per key/value head exceed 16 rows", G ? H / G : 0);
-    if (splits < 1 || G > 65535 || splits > 65535 || qkv_splits < 1) return fail(HFB_EINVAL, "attention_decode_fused: bad split or group count");
-    if (n_rot < 0 || n_rot > d || (n_rot & 1) || (n_rot > 0 && !cos_sin)) return fail(HFB_EINVAL, "attention_decode_fused: bad rotary arguments");
-    if (splits > 1 && (!scratch || scratch_bytes < hfb_attention_fast_scratch(T, H, d, splits) || !counters))
-        return fail(HFB_EINVAL, "attention_decode_fused: scratch too small for %d splits", splits);
-    AttnParams p = {};
-    p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
-    p.out = (__nv_bfloat16 *)out; p.block_table = block_table; p.positions = positions;
-    p.tile_seq = tile_seq; p.tile_t0 = tile_t0; p.tile_nt = tile_nt;
-    p.part_o = (float *)scratch; p.part_ml = splits > 1 ? (float *)scratch + (size_t)T * H * splits * d : nullptr;
-    p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.splits = splits;
-    p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
-    p.qkv_part = qkv_part; p.qkv_splits = qkv_splits; p.T = T; p.qkv_bias = qkv_bias; p.bias_dt = bias_dt;
-    p.cos_sin = cos_sin; p.n_rot = n_rot; p.n_positions = n_positions; p.slots = slots;
-    p.k_cache_w = (__nv_bfloat16 *)k_cache; p.v_cache_w = (__nv_bfloat16 *)v_cache; p.cache_slots = num_pages * block_size;
-    p.counters = counters;
-    cudaStream_t st = (cudaStream_t)s;
-    return d == 128 ? (stages >= 3 ? launch_attention_decode<128, 3>(p, T, st) : launch_attention_decode<128, 2>(p, T, st))
-                    : (stages >= 3 ? launch_attention_decode<64, 3>(p, T, st) : launch_attention_decode<64, 2>(p, T, st));
-}
-
 extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                                   int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                                   const int32_t *tile_nt, int n_tiles, int warps, int stages, int splits, int block_size,
@@ -663,7 +510,7 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
     if (splits < 1 || G > 65535 || splits > 65535) return fail(HFB_EINVAL, "attention_fast: bad split or group count");
     if (splits > 1 && (!scratch || scratch_bytes < hfb_attention_fast_scratch(T, H, d, splits)))
         return fail(HFB_EINVAL, "attention_fast: scratch of %zu bytes is too small for %d splits", scratch_bytes, splits);
-    AttnParams p = {};
+    AttnParams p;
     p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
     p.out = (__nv_bfloat16 *)out; p.block_table = block_table; p.positions = positions;
     p.tile_seq = tile_seq; p.tile_t0 = tile_t0; p.tile_nt = tile_nt;

@@ -103,18 +103,6 @@ int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, 
                        int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
                        int T, int H, int G, int d, hfb_stream s);
 
-/* Decode attention in one launch: finishes the q|k|v product from its split-K partial sums (bias, rotary, the
- * token's own key and value into the cache and into the tile), attends with the keys split over CTAs, and
- * lets the last CTA of every (request, kv head) merge the splits.  `counters` is zeroed int32 [T * G] scratch
- * that the kernel leaves zeroed; `slots` == NULL means the cache is another entry's and is only read. */
-int hfb_attention_decode_fused(const float *qkv_part, int qkv_splits, const void *qkv_bias, int bias_dt,
-                               const float *cos_sin, int n_rot, int n_positions, const int32_t *slots,
-                               void *k_cache, void *v_cache, const int32_t *block_table, int max_blocks,
-                               const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
-                               const int32_t *tile_nt, int T, int stages, int splits, int block_size,
-                               int64_t num_pages, int window, float scale, void *out, void *scratch,
-                               size_t scratch_bytes, int *counters, int H, int G, int d, hfb_stream s);
-
 /* Attention of prompt portions on tcgen05 (S and PV accumulators in TMEM, K and V gathered page by page with
  * TMA): bfloat16, head_dim 128, block sizes 8..128 that divide 128.  Tiles hold at most 128 / (H/G) tokens. */
 int hfb_attention_tc(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,

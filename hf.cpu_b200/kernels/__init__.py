@@ -84,23 +84,6 @@ def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out)
     backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out)
 
 
-def linear_attention_decode(a, w, bias, qkv_buf, q_buf, cos_sin, n_rot, slots, k_cache, v_cache, meta, ctx,
-                            H, G, d, window, scale, out) -> None:
-    """:func:`linear_rope_kv` followed by :func:`paged_attention`; a backend may run a pure decode step's pair as
-    one fused launch.  ``qkv_buf`` and ``q_buf`` are scratch for the separate form."""
-    check_head_dim(d)
-    _need(w.shape[0] == (H + 2 * G) * d and out.shape == (a.shape[0], H * d), "linear_attention_decode: shape mismatch")
-    _need(k_cache.shape[2:] == (G, d) and v_cache.shape == k_cache.shape and k_cache.dtype == out.dtype,
-          "linear_attention_decode: cache geometry mismatch")
-    b = backend()
-    if hasattr(b, "linear_attention_decode"):
-        b.linear_attention_decode(a, w, bias, qkv_buf, q_buf, cos_sin, int(n_rot), slots, k_cache, v_cache, meta, ctx,
-                                  H, G, d, int(window), float(scale), out)
-    else:
-        b.linear_rope_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), ctx.positions, slots, q_buf, k_cache, v_cache, H, G, d)
-        b.paged_attention(q_buf, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out)
-
-
 def swiglu(gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
     """out = silu(gate) * up; gate and up are the two halves of a row of ``gu``, or alternate along it."""
     _need(gu.shape == (out.shape[0], 2 * out.shape[1]) and gu.dtype == out.dtype, "swiglu: shape mismatch")

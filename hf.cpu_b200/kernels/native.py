@@ -60,9 +60,6 @@ class NativeBackend:
         self.gemm = os.environ.get("HFB_GEMM", "tc")
         self._ws = None
         self._argmax_ws = None
-        self._counters = None
-        # pure decode steps: one attention launch that also finishes the q|k|v product and merges its splits
-        self.decode_fused = os.environ.get("HFB_DECODE_FUSED", "1") != "0"
         self.lib.hfb_linear_tc_partials_workspace.restype = ctypes.c_size_t
         self.lib.hfb_argmax2_scratch.restype = ctypes.c_size_t
         self.path = path
@@ -177,36 +174,6 @@ class NativeBackend:
                                                  c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window),
                                                  c_float(scale), _p(out), c_int(T), c_int(H), c_int(G), c_int(d),
                                                  self._stream()), "attention")
-
-    def linear_attention_decode(self, a, w, bias, qkv_buf, q_buf, cos_sin, n_rot, slots, k_cache, v_cache, meta, ctx,
-                                H, G, d, window, scale, out):
-        """q|k|v product, rotary, cache write and attention of a pure decode step."""
-        M, K = a.shape
-        fused = (self.decode_fused and ctx.max_q_len == 1 and M <= 128 and self._tc_ok(a, w) and M > self.gemv_max
-                 and self.attention == "fast" and d in (64, 128) and 64 % meta.block_size == 0 and H // G <= 16
-                 and k_cache.dtype == torch.bfloat16)
-        tiling = ctx.attn_tiles(H // G, 1) if fused else None
-        part = self._partials(a, w) if tiling is not None else None
-        if part is None:
-            self.linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, ctx.positions, slots, q_buf, k_cache, v_cache, H, G, d)
-            self.paged_attention(q_buf, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out)
-            return
-        ws, qkv_splits = part
-        tile_seq, tile_t0, tile_nt, n_tiles = tiling
-        hint = getattr(ctx, "decode_split_hint", max(1, ((ctx.max_kv_len + 63) // 64) // 2))
-        splits = max(1, min(self.decode_ctas_per_sm * self.sm_count // max(1, n_tiles * G), hint))
-        need = self.lib.hfb_attention_fast_scratch(c_int(M), c_int(H), c_int(d), c_int(splits))
-        scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
-        if self._counters is None or self._counters.numel() < M * G:
-            self._counters = torch.zeros(max(M * G, 1 << 16), dtype=torch.int32, device=a.device)
-        npos = cos_sin.shape[0] if cos_sin is not None else 0
-        self._check(self.lib.hfb_attention_decode_fused(
-            _p(ws), c_int(qkv_splits), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(cos_sin), c_int(n_rot),
-            c_int(npos), _p(slots), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks),
-            _p(ctx.positions), _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(M), c_int(self.decode_stages), c_int(splits),
-            c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out), _p(scratch),
-            ctypes.c_size_t(need), _p(self._counters), c_int(H), c_int(G), c_int(d), self._stream()),
-            "attention_decode_fused")
 
     def swiglu(self, gu, out, interleaved):
         self._on_gpu(gu, out)

@@ -84,13 +84,14 @@ class PagedAttention(Mixer):
         T = xn.shape[0]
         qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
         q = ctx.buf("attn_q", (T, self.QD), xn.dtype)
-        att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
         meta = ctx.group_meta(cache.group)
         cos_sin = self.rotary.cos_sin if self.rotary is not None else None
         n_rot = self.rotary.n_rot if self.rotary is not None else 0
-        kernels.linear_attention_decode(xn, self.w_qkv, self.b_qkv, qkv, q, cos_sin, n_rot,
-                                        meta.slots if write_cache else None, cache.k, cache.v, meta, ctx,
-                                        self.H, self.G, self.d, self.window, self.scale, att)
+        kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
+                               meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
+        att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
+        kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
+                                self.window, self.scale, att)
         return att
 
     def forward(self, ctx, xn, residual, cache, state, write_cache):

@@ -439,42 +439,3 @@ def test_attention_tensor_core_prompt_portions(geom):
             again = _run_attention(native(), case, H, G, d, window)
             assert torch.equal(out, again)
     kernels.check_device_errors()
-
-
-@pytest.mark.parametrize("geom", [(28, 4, 128, 16, 3584), (8, 2, 64, 8, 256), (16, 1, 128, 64, 512), (6, 6, 64, 32, 192)])
-@pytest.mark.parametrize("window", [0, 70])
-def test_decode_attention_fused_with_qkv_tail(geom, window):
-    """A pure decode step: q|k|v product, bias, rotary, cache write, attention and the merge of the splits as the
-    fused launch, against the separate kernels of the torch reference, including what lands in the cache."""
-    from hfcpu_b200 import kernels
-    H, G, d, bs, K = geom
-    b = kernels.backend()
-    assert b.decode_fused
-    lens_kv = [1, 64, 65, 700, 2311, 130]
-    lens_q = [1] * len(lens_kv)
-    T, N = len(lens_q), (H + 2 * G) * d
-    xn, w, bias = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05), rnd(N, dtype=torch.bfloat16)
-    P = max(lens_kv) + 1
-    ang = torch.rand(P, d // 2, device=DEV, dtype=torch.float64) * 6
-    cos_sin = torch.stack([ang.cos(), ang.sin()], -1).float().contiguous()
-    outs = []
-    for impl, write in ((native(), True), (EmuBackend(), True), (native(), False), (EmuBackend(), False)):
-        case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window, seed=5), lens_q, lens_kv, H, G)
-        q_, kc, vc, meta, ctx = case
-        ctx.decode_split_hint = 8
-        # the slot of every request's newest position, as the engine computes it
-        table = meta.block_table.cpu()
-        slots = torch.tensor([int(table[s, (n - 1) // bs]) * bs + (n - 1) % bs for s, n in enumerate(lens_kv)], dtype=torch.int32, device=DEV)
-        qkv, qb = torch.empty(T, N, device=DEV, dtype=torch.bfloat16), torch.empty(T, H * d, device=DEV, dtype=torch.bfloat16)
-        out = torch.empty(T, H * d, device=DEV, dtype=torch.bfloat16)
-        args = (xn, w, bias, qkv, qb, cos_sin, d, slots if write else None, kc, vc, meta, ctx, H, G, d, window, 1.0 / math.sqrt(d), out)
-        if isinstance(impl, EmuBackend):
-            impl.linear_rope_kv(xn, w, bias, qkv, cos_sin, d, ctx.positions, slots if write else None, qb, kc, vc, H, G, d)
-            impl.paged_attention(qb, kc, vc, meta, ctx, H, G, d, window, 1.0 / math.sqrt(d), out)
-        else:
-            impl.linear_attention_decode(*args)
-        outs.append((out, kc.clone(), vc.clone()))
-    for a_, b_ in ((0, 1), (2, 3)):
-        for x, y in zip(outs[a_], outs[b_]):
-            assert rel(x.float(), y.float()) < TOL["bfloat16"]
-    kernels.check_device_errors()
