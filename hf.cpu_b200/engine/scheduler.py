@@ -65,6 +65,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.generated
 
+    def token_slice(self, a: int, b: int) -> List[int]:
+        """Tokens a..b-1 of prompt + generated, without building the whole list."""
+        n = len(self.prompt)
+        if a >= n:
+            return self.generated[a - n:b - n]
+        if b <= n:
+            return self.prompt[a:b]
+        return self.prompt[a:] + self.generated[:b - n]
+
     @property
     def pending(self) -> int:
         """Tokens that still have to run before the next token can be sampled."""
@@ -153,6 +162,12 @@ class Scheduler:
     def plan(self) -> StepPlan:
         preempted: List[Request] = []
         failed: List[Request] = []
+        if not self.waiting and self.running and len(self.running) <= self.max_num_batched_tokens \
+                and all(r.pending == 1 and r.computed > 0 for r in self.running) \
+                and self.engine.cache.can_reserve([(r.id, r.computed + 1) for r in self.running]):
+            # the steady state: everyone decodes, nobody waits, the pages are there
+            entries = [StepEntry(r.id, r.token_slice(r.computed, r.computed + 1), [0]) for r in self.running]
+            return StepPlan(entries, list(self.running), preempted, [], failed)
         while True:
             chosen, admitted = self._choose(preempted, failed)
             if chosen or not self.running:
@@ -168,7 +183,7 @@ class Scheduler:
                 preempted.append(victim)
         entries, reqs = [], []
         for r, n in chosen:
-            toks = r.tokens()[r.computed:r.computed + n]
+            toks = r.token_slice(r.computed, r.computed + n)
             last = r.computed + n == len(r.prompt) + len(r.generated)
             entries.append(StepEntry(r.id, toks, [n - 1] if last else []))
             reqs.append(r)

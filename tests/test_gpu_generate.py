@@ -57,3 +57,23 @@ def test_command_line_generate(tiny_folders):
     toks = [int(l.split("id=")[1].split()[0]) for l in r.stdout.decode().splitlines() if l.startswith("@token")]
     cfg, W = plain.read_folder(tiny_folders["A"])
     assert toks == plain.greedy(cfg, W, prompt, 5)
+
+
+def test_many_requests_under_pressure_match_plain(tiny_folders):
+    """Twelve requests of mixed lengths through four slots, a small token budget and a pool too small for all of
+    them: portions beside decodes, pages handed out again, preemption; every request's greedy tokens equal the plain
+    implementation's."""
+    import random
+    import hfcpu_b200
+    folder = tiny_folders["A"]
+    rnd = random.Random(11)
+    prompts = [[rnd.randrange(512) for _ in range(n)] for n in (90, 150, 40, 120, 17, 100, 3, 140, 60, 1, 130, 75)]
+    sess = hfcpu_b200.Session(folder, dtype="float32", kv_block=16, kv_pages=20, max_seqs=4, max_batched_tokens=48, batch=32)
+    out = sess.generate(prompts, temp=0, max_tokens=12)
+    cfg, W = plain.read_folder(folder)
+    for p, comps in zip(prompts, out):
+        assert comps[0].stop == "length" and comps[0].tokens == plain.greedy(cfg, W, p, 12)
+    st = sess.scheduler.stats
+    assert st["preemptions"] > 0 and st["steps"] > 20
+    sess.engine.cache.check()
+    assert sess.engine.cache.pages_in_use() == 0 and sess.engine.slots.free_count == 4
