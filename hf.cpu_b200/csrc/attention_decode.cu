@@ -1,0 +1,326 @@
+// Decode attention over the paged cache for bfloat16: the keys and values arrive by TMA, page by page.
+//
+// With one new token per request the work is a pure read of the request's keys and values, and what costs
+// is every instruction spent on moving them.  A fifth warp owns the copies: for each tile of 64 keys it looks
+// up the tile's pages and asks the TMA unit for them (one box of [block_size keys, 64 elements] per page and
+// 128-byte half of the head, 128-byte swizzle; a page the table does not map is read from beyond the cache and
+// arrives as zeros), several tiles ahead of the four warps that compute.  Those share each tile as the cp.async
+// form does (attention_fast.cu): 16 keys per warp, the query heads of one key/value head on the 16 rows of
+// mma.sync m16n8k16, a running maximum and sum per warp, merged in warp order at the end.  Full and empty
+// mbarriers pair the two sides, so the loop has no CTA-wide barrier.  Tiles that lie wholly inside every row's
+// range skip the masks, and the accumulator is rescaled only when a maximum grew.
+// Rows of a mapped page beyond the request's length hold old (finite) values or the zeros the cache starts
+// with; their scores are masked to -inf, so their weights are exactly zero.
+// Same arithmetic as src/model.c:499-528 of the reference, in flash-attention form.
+#include <cuda.h>
+
+#include "attention_common.cuh"
+#include "tc_ptx.cuh"
+
+static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
+
+namespace hfb {
+int *error_word();
+int tensor_map(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *out);
+
+constexpr int ADT_THREADS = 160;        // four computing warps and the copying warp
+constexpr uint32_t ADT_SUB = ABN * 128; // one 128-byte half of a tile of 64 keys
+
+// Byte offset of 16-byte chunk `c` of key row `row` in a tile the TMA unit wrote with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t tma_off(int row, int c)
+{
+    return (uint32_t)(c >> 3) * ADT_SUB + (uint32_t)row * 128u + (uint32_t)(((c & 7) ^ (row & 7)) << 4);
+}
+
+template <int D, int STAGES>
+__global__ void __launch_bounds__(ADT_THREADS)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p,
+                            int num_slots, int *err)
+{
+    HFB_TRACE_ENTRY(3);
+    constexpr int CH = D / 8, HALVES = D / 64;
+    constexpr uint32_t TILE = HALVES * ADT_SUB;          // bytes of the keys (or the values) of one tile
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t sk = base, sv = base + STAGES * TILE, sq = sv + STAGES * TILE;
+    const uint32_t full0 = sq + 16 * D * 2, empty0 = full0 + 8 * STAGES;
+    volatile int *abort_flag = (volatile int *)(gen + 2 * STAGES * TILE + 16 * D * 2 + 16 * STAGES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // The tiling, the positions and the block table are inputs of the step, and the keys of earlier steps are in
+    // the cache already: none of that waits for the kernel in front.  Only the queries and the tiles that hold
+    // this step's tokens do.
+    const int tile = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+    const int r = p.H / p.G;
+    const int seq = p.tile_seq[tile], t0 = p.tile_t0[tile], nt = p.tile_nt[tile];
+    const int pos_first = p.positions[t0], pos_last = p.positions[t0 + nt - 1];
+    const int lo_first = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int lo_last = p.window > 0 ? max(0, pos_last - p.window + 1) : 0;
+    int kt_lo = lo_first / ABN, kt_hi = pos_last / ABN + 1;
+    if (p.splits > 1) {
+        int per = (kt_hi - kt_lo + p.splits - 1) / p.splits;
+        kt_lo = kt_lo + split * per;
+        kt_hi = min(kt_hi, kt_lo + per);
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const int row0 = lane >> 2, row1 = row0 + 8;
+
+    if (warp == 4) {
+        // ---- the copying warp ------------------------------------------------------------------------
+        // The lanes look up 32 pages at a time (the pages of several tiles, one coalesced read of the block
+        // table); lane 0 then asks for tile after tile without waiting for another table entry.
+        const int32_t *table = p.block_table + (size_t)seq * p.max_blocks;
+        const int bs = p.block_size, pages = ABN / bs, tiles_per_round = 32 / pages;
+        bool waited = false;
+        for (int kt0 = kt_lo; kt0 < kt_hi; kt0 += tiles_per_round) {
+            const int key0 = kt0 * ABN + lane * bs, blk = key0 / bs;
+            const bool mapped = lane < tiles_per_round * pages && kt0 + lane / pages < kt_hi && key0 <= pos_last && blk < p.max_blocks;
+            const long long page = mapped ? table[blk] : -1;
+            const int my_row = (page >= 0 && page < p.num_pages) ? (int)(page * bs) : num_slots;     // beyond the cache: zeros
+            bool ok = true;
+            for (int t = 0; t < tiles_per_round && kt0 + t < kt_hi; t++) {
+                const int j = kt0 + t - kt_lo, s = j % STAGES;
+                if (!waited && (kt0 + t) * ABN + ABN - 1 >= pos_first) {
+                    pdl_wait();                           // this tile holds keys the kernel in front writes
+                    waited = true;
+                }
+                if (lane == 0) {
+                    ok = mbar_wait(empty0 + 8 * s, ((j / STAGES) & 1) ^ 1, abort_flag, err);
+                    if (ok) mbar_arrive_expect_tx(full0 + 8 * s, 2 * TILE);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                for (int pg = 0; pg < pages; pg++) {
+                    const int row = __shfl_sync(0xffffffffu, my_row, t * pages + pg);
+                    if (lane == 0) {
+                        const uint32_t off = (uint32_t)s * TILE + (uint32_t)pg * bs * 128u;
+#pragma unroll
+                        for (int half = 0; half < HALVES; half++) {
+                            tma_load_2d(sk + off + half * ADT_SUB, &map_k, g * D + half * 64, row, full0 + 8 * s);
+                            tma_load_2d(sv + off + half * ADT_SUB, &map_v, g * D + half * 64, row, full0 + 8 * s);
+                        }
+                    }
+                }
+            }
+            if (!ok) break;
+        }
+    } else {
+        // ---- the computing warps: 16 keys of every tile each --------------------------------------------
+        pdl_sync();                                       // the queries come from the kernel in front
+        for (int i = threadIdx.x; i < 16 * CH; i += 128) {
+            int row = i / CH, c = i % CH;
+            int tl = row / r, hl = row % r;
+            bool valid = tl < nt;
+            const __nv_bfloat16 *src = p.q + ((size_t)(t0 + (valid ? tl : 0)) * p.H + g * r + hl) * D + c * 8;
+            cp_async16(sq + swz<D>(row, c), src, valid);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint32_t qf[D / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < D / 16; kk++)
+            ldsm_x4(sq + swz<D>(lane & 15, kk * 2 + (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+
+        const int tl0 = row0 / r, tl1 = row1 / r;
+        const bool v0 = tl0 < nt, v1 = tl1 < nt;
+        const int pos0 = v0 ? p.positions[t0 + tl0] : -1, pos1 = v1 ? p.positions[t0 + tl1] : -1;
+        const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, pos1 - p.window + 1) : 0;
+        const int kbase = warp * 16, mi = lane >> 3;
+
+        for (int kt = kt_lo; kt < kt_hi; kt++) {
+            const int j = kt - kt_lo, s = j % STAGES;
+            if (!mbar_wait(full0 + 8 * s, (j / STAGES) & 1, abort_flag, err)) break;
+            const uint32_t ks = sk + s * TILE, vs = sv + s * TILE;
+            float sc[2][4];
+            sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; kk++) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(ks + tma_off(kbase + (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)), b0, b1, b2, b3);
+                mma_bf16(sc[0], qf[kk], b0, b1);
+                mma_bf16(sc[1], qf[kk], b2, b3);
+            }
+            // a tile wholly inside every row's range needs no mask
+            const bool edge = kt * ABN + ABN - 1 > pos_first || kt * ABN < lo_last;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    float a = sc[i][e] * p.scale_log2, b = sc[i][2 + e] * p.scale_log2;
+                    if (edge) {
+                        const int key = kt * ABN + kbase + i * 8 + (lane & 3) * 2 + e;
+                        a = (v0 && key >= lo0 && key <= pos0) ? a : -INFINITY;
+                        b = (v1 && key >= lo1 && key <= pos1) ? b : -INFINITY;
+                    }
+                    sc[i][e] = a; sc[i][2 + e] = b;
+                    mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b);
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            if (__any_sync(0xffffffffu, mn0 > m0 || mn1 > m1)) {
+                // a maximum grew somewhere in the warp: rescale what has been summed so far
+                const float c0 = fast_exp2(m0 - (mn0 == -INFINITY ? 0.f : mn0)), c1 = fast_exp2(m1 - (mn1 == -INFINITY ? 0.f : mn1));
+                l0 *= c0; l1 *= c1;
+#pragma unroll
+                for (int i = 0; i < D / 8; i++) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+                m0 = mn0; m1 = mn1;
+            }
+            const float base0 = m0 == -INFINITY ? 0.f : m0, base1 = m1 == -INFINITY ? 0.f : m1;
+            uint32_t pf[4];
+            const float p00 = fast_exp2(sc[0][0] - base0), p01 = fast_exp2(sc[0][1] - base0), p10 = fast_exp2(sc[0][2] - base1), p11 = fast_exp2(sc[0][3] - base1);
+            const float q00 = fast_exp2(sc[1][0] - base0), q01 = fast_exp2(sc[1][1] - base0), q10 = fast_exp2(sc[1][2] - base1), q11 = fast_exp2(sc[1][3] - base1);
+            pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p10, p11); pf[2] = pack_bf16(q00, q01); pf[3] = pack_bf16(q10, q11);
+            l0 += p00 + p01 + q00 + q01;
+            l1 += p10 + p11 + q10 + q11;
+#pragma unroll
+            for (int dn = 0; dn < D / 16; dn++) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(vs + tma_off(kbase + (mi & 1) * 8 + (lane & 7), dn * 2 + (mi >> 1)), b0, b1, b2, b3);
+                mma_bf16(o[2 * dn], pf, b0, b1);
+                mma_bf16(o[2 * dn + 1], pf, b2, b3);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * s);
+        }
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
+
+    // ---- merge the four warps (they saw disjoint keys) in warp order -------------------------------------
+    __syncthreads();                                      // every tile has been used: its buffers are free
+    if (*abort_flag) {
+        // a wait ran out: give copies that are still in flight time to land before the shared memory goes away
+        if (threadIdx.x == 0)
+            for (int i = 0; i < 2000; i++) __nanosleep(1000);
+        __syncthreads();
+        return;
+    }
+    float *mo = (float *)gen;                             // [4][16][D]
+    float *mml = mo + 4 * 16 * D;                         // [4][16][2]
+    float *fac = mml + 4 * 16 * 2;                        // [16][4] weights of the warps, then [16] maxima and [16] sums
+    if (warp < 4) {
+#pragma unroll
+        for (int i = 0; i < D / 8; i++) {
+            int col = i * 8 + (lane & 3) * 2;
+            *(float2 *)(mo + ((size_t)warp * 16 + row0) * D + col) = make_float2(o[i][0], o[i][1]);
+            *(float2 *)(mo + ((size_t)warp * 16 + row1) * D + col) = make_float2(o[i][2], o[i][3]);
+        }
+        if ((lane & 3) == 0) {
+            *(float2 *)(mml + (warp * 16 + row0) * 2) = make_float2(m0, l0);
+            *(float2 *)(mml + (warp * 16 + row1) * 2) = make_float2(m1, l1);
+        }
+    }
+    __syncthreads();
+    const int rows = nt * r;
+    if (threadIdx.x < rows) {
+        const int row = threadIdx.x;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) m = fmaxf(m, mml[(w * 16 + row) * 2]);
+        float denom = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float mw = mml[(w * 16 + row) * 2];
+            const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
+            fac[row * 4 + w] = f;
+            denom += mml[(w * 16 + row) * 2 + 1] * f;
+        }
+        fac[64 + row] = m;
+        fac[80 + row] = denom;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rows * D; idx += ADT_THREADS) {
+        const int row = idx / D, col = idx % D;
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) acc += mo[((size_t)w * 16 + row) * D + col] * fac[row * 4 + w];
+        const float denom = fac[80 + row];
+        const int tok = t0 + row / r, head = g * r + row % r;
+        const size_t th = (size_t)tok * p.H + head;
+        if (p.splits > 1) {
+            p.part_o[(th * p.splits + split) * D + col] = acc;
+            if (col == 0) *(float2 *)(p.part_ml + (th * p.splits + split) * 2) = make_float2(fac[64 + row], denom);
+        } else {
+            p.out[th * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+        }
+    }
+}
+
+template <int D, int STAGES>
+static int launch_decode_tma(const CUtensorMap &mk, const CUtensorMap &mv, const AttnParams &p, int num_slots, int n_tiles, cudaStream_t st)
+{
+    constexpr uint32_t TILE = (D / 64) * ADT_SUB;
+    constexpr int smem = 1024 + 2 * STAGES * TILE + 16 * D * 2 + 16 * STAGES + 16;
+    static_assert(2 * STAGES * TILE >= (4 * 16 * (D + 2) + 96) * 4, "the merge reuses the tile buffers");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_decode: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    g_launch_err = launch_pdl(attention_decode_tma_kernel<D, STAGES>, dim3(n_tiles, p.G, p.splits), dim3(ADT_THREADS), smem, st,
+                              mk, mv, p, num_slots, error_word());
+    return check_pdl_launch(g_launch_err, "attention_decode");
+}
+
+}  // namespace hfb
+
+using namespace hfb;
+
+// Decode attention (tiles of one or two tokens of one request each, as hfb_attention_fast's 16-row form makes
+// them): bfloat16, head_dim 64 or 128, block sizes 8..64 that divide 64, at most 16 query rows per tile.
+// `stages` tiles of 64 keys are in flight per CTA (2..4); `splits` > 1 cuts each request's keys over that many
+// CTAs and needs hfb_attention_fast_scratch(T, H, d, splits) bytes of float32 scratch.
+extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
+                                    int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
+                                    const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size,
+                                    int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
+                                    int T, int H, int G, int d, hfb_stream s)
+{
+    if (n_tiles <= 0) return HFB_OK;
+    if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_decode: head_dim %d (64 and 128 only)", d);
+    if (G <= 0 || H % G || H / G > 16) return fail(HFB_ENOTSUP, "attention_decode: %d heads over %d key/value heads do not fit 16 rows", H, G);
+    if (block_size < 8 || block_size > ABN || ABN % block_size) return fail(HFB_ENOTSUP, "attention_decode: block size %d (8..64, dividing 64)", block_size);
+    if (num_pages * block_size >= (1ll << 31) - ABN) return fail(HFB_ENOTSUP, "attention_decode: cache too large for 32-bit coordinates");
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
+        return fail(HFB_ENOTSUP, "attention_decode: operands must be 16-byte aligned");
+    if (splits < 1 || G > 65535 || splits > 65535) return fail(HFB_EINVAL, "attention_decode: bad split or group count");
+    if (splits > 1 && (!scratch || scratch_bytes < (size_t)T * H * splits * (d + 2) * sizeof(float)))
+        return fail(HFB_EINVAL, "attention_decode: scratch of %zu bytes is too small for %d splits", scratch_bytes, splits);
+    CUtensorMap mk, mv;
+    int rc;
+    const int slots = (int)(num_pages * block_size);
+    if ((rc = tensor_map(k_cache, slots, G * d, block_size, &mk)) != HFB_OK) return rc;
+    if ((rc = tensor_map(v_cache, slots, G * d, block_size, &mv)) != HFB_OK) return rc;
+    AttnParams p;
+    p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
+    p.out = (__nv_bfloat16 *)out; p.block_table = block_table; p.positions = positions;
+    p.tile_seq = tile_seq; p.tile_t0 = tile_t0; p.tile_nt = tile_nt;
+    p.part_o = (float *)scratch; p.part_ml = splits > 1 ? (float *)scratch + (size_t)T * H * splits * d : nullptr;
+    p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.splits = splits;
+    p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
+    cudaStream_t st = (cudaStream_t)s;
+    if (d == 128) rc = stages >= 4 ? launch_decode_tma<128, 4>(mk, mv, p, slots, n_tiles, st)
+                     : stages == 3 ? launch_decode_tma<128, 3>(mk, mv, p, slots, n_tiles, st) : launch_decode_tma<128, 2>(mk, mv, p, slots, n_tiles, st);
+    else rc = stages >= 4 ? launch_decode_tma<64, 4>(mk, mv, p, slots, n_tiles, st)
+            : stages == 3 ? launch_decode_tma<64, 3>(mk, mv, p, slots, n_tiles, st) : launch_decode_tma<64, 2>(mk, mv, p, slots, n_tiles, st);
+    if (rc != HFB_OK || splits == 1) return rc;
+    return launch_attention_combine(p, T, d, st);
+}

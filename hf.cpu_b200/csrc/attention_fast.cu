@@ -11,72 +11,18 @@
 //     so the result does not depend on how many CTAs ran at once.
 // Keys and values arrive by cp.async (16-byte chunks, zero fill for unmapped or out-of-range keys) into
 // swizzled shared memory, double buffered; fragments are read with ldmatrix.
-#include "common.cuh"
+#include "attention_common.cuh"
 
 static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the last launch_pdl returned
 
 namespace hfb {
 int *error_word();
 
-constexpr int ABN = 64;                 // keys per tile
-
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid)
-{
-    int sz = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
-{
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3)
-{
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float *c, const uint32_t *a, uint32_t b0, uint32_t b1)
-{
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// 2^x by the hardware approximation (relative error about 2^-22, far below bfloat16's own rounding)
-__device__ __forceinline__ float fast_exp2(float x)
-{
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
-{
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *(uint32_t *)&h;
-}
-
-struct AttnParams {
-    const __nv_bfloat16 *q, *k_cache, *v_cache;
-    __nv_bfloat16 *out;
-    const int32_t *block_table, *positions, *tile_seq, *tile_t0, *tile_nt;
-    float *part_o, *part_ml;            // split mode: [T*H, splits, D] and [T*H, splits, 2]
-    int max_blocks, block_size, window, H, G, splits;
-    long long num_pages;
-    float scale_log2;                   // scale * log2(e)
-};
-
-// Byte offset of 16-byte chunk `c` of row `row` in a tile whose rows hold D bf16 (D = 64 or 128).
-template <int D> __device__ __forceinline__ uint32_t swz(int row, int c)
-{
-    return (uint32_t)(row * (D * 2) + ((c ^ (row & 7)) << 4));
-}
-
 template <int D, int WARPS, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_fast_kernel(AttnParams p, int *err)
 {
+    HFB_TRACE_ENTRY(12);
     pdl_sync();
     constexpr int BM = 16 * WARPS, CH = D / 8, NT = WARPS * 32;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -266,6 +212,7 @@ template <int D, int STAGES>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(AttnParams p, int *err)
 {
+    HFB_TRACE_ENTRY(3);
     pdl_sync();
     constexpr int CH = D / 8, NT = 128;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -292,19 +239,34 @@ attention_decode_kernel(AttnParams p, int *err)
         cp_async16(sq + swz<D>(row, c), src, valid);
     }
     cp_async_commit();
+    // Where each key row of a tile lives in the cache (token slot = page * block_size + place in the page, -1 for
+    // none) is looked up by the first 64 threads one tile ahead of the copy that needs it, so that no copy waits
+    // for a block-table entry.
+    __shared__ int s_slot[STAGES][ABN];
+    auto lookup = [&](int kt) -> int {
+        const int key = kt * ABN + (int)threadIdx.x;
+        const int blk = key / p.block_size;
+        if (kt >= kt_hi || key > pos_last || blk >= p.max_blocks) return -1;
+        const long long page = table[blk];
+        return (page >= 0 && page < p.num_pages) ? (int)(page * p.block_size + key % p.block_size) : -1;
+    };
     auto load_kv = [&](int kt, int stage) {
+        const int *slots = s_slot[(kt - kt_lo) % STAGES];
         for (int i = threadIdx.x; i < ABN * CH; i += NT) {
             int kr = i / CH, c = i % CH;
-            int key = kt * ABN + kr;
-            int blk = key / p.block_size;
-            long long page = (key <= pos_last && blk < p.max_blocks) ? table[blk] : -1;
-            bool valid = page >= 0 && page < p.num_pages;
-            size_t off = valid ? (((size_t)page * p.block_size + key % p.block_size) * p.G + g) * D + c * 8 : 0;
+            const int slot = slots[kr];
+            const bool valid = slot >= 0;
+            size_t off = valid ? ((size_t)slot * p.G + g) * D + c * 8 : 0;
             cp_async16(sk + stage * (ABN * D * 2) + swz<D>(kr, c), p.k_cache + off, valid);
             cp_async16(sv + stage * (ABN * D * 2) + swz<D>(kr, c), p.v_cache + off, valid);
         }
         cp_async_commit();
     };
+    if (threadIdx.x < ABN) {
+#pragma unroll
+        for (int st = 0; st < STAGES; st++) s_slot[st][threadIdx.x] = lookup(kt_lo + st);
+    }
+    __syncthreads();
 #pragma unroll
     for (int st = 0; st < STAGES - 1; st++) {
         if (kt_lo + st < kt_hi) load_kv(kt_lo + st, st);
@@ -326,6 +288,8 @@ attention_decode_kernel(AttnParams p, int *err)
         const int stage = (kt - kt_lo) % STAGES;
         if (kt + STAGES - 1 < kt_hi) load_kv(kt + STAGES - 1, (kt + STAGES - 1 - kt_lo) % STAGES);
         else cp_async_commit();
+        // the slots of the tile after that one: asked for now, stored at the end of this round
+        const int slot_ahead = (threadIdx.x < ABN && kt + STAGES < kt_hi) ? lookup(kt + STAGES) : -1;
         cp_async_wait<STAGES - 1>();
         __syncthreads();
         if (!q_loaded) {
@@ -381,6 +345,7 @@ attention_decode_kernel(AttnParams p, int *err)
             mma_bf16(o[2 * dn], pf, b0, b1);
             mma_bf16(o[2 * dn + 1], pf, b2, b3);
         }
+        if (threadIdx.x < ABN) s_slot[(kt + STAGES - kt_lo) % STAGES][threadIdx.x] = slot_ahead;   // last read a round ago
         __syncthreads();
     }
     cp_async_wait<0>();
@@ -447,6 +412,7 @@ static int launch_attention_decode(const AttnParams &p, int n_tiles, cudaStream_
 template <int D>
 __global__ void attention_combine_kernel(const float *part_o, const float *part_ml, int splits, __nv_bfloat16 *out)
 {
+    HFB_TRACE_ENTRY(4);
     pdl_sync();
     const size_t th = blockIdx.x;
     const float *ml = part_ml + th * splits * 2;
@@ -476,6 +442,14 @@ static int launch_attention(const AttnParams &p, int n_tiles, cudaStream_t st)
     dim3 grid(n_tiles, p.G, p.splits);
     g_launch_err = launch_pdl(attention_fast_kernel<D, WARPS, STAGES>, dim3(grid), dim3(WARPS * 32), smem, st, p, error_word());
     return check_pdl_launch(g_launch_err, "attention_fast");
+}
+
+int launch_attention_combine(const AttnParams &p, int T, int d, cudaStream_t st)
+{
+    const dim3 grid((unsigned)((size_t)T * p.H));
+    if (d == 128) g_launch_err = launch_pdl(attention_combine_kernel<128>, grid, dim3(128), 0, st, p.part_o, p.part_ml, p.splits, p.out);
+    else g_launch_err = launch_pdl(attention_combine_kernel<64>, grid, dim3(64), 0, st, p.part_o, p.part_ml, p.splits, p.out);
+    return check_pdl_launch(g_launch_err, "attention_combine");
 }
 
 }  // namespace hfb
@@ -523,8 +497,10 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
     if (warps == 2) {
         // the decode form: rows of one or two tokens, four warps sharing each tile's keys
         if (hfb_attention_fast_tile_tokens(H, G, 1) == 0) return fail(HFB_ENOTSUP, "attention_fast: %d heads per group exceed 16 rows", H / G);
-        rc = d == 128 ? (stages >= 3 ? launch_attention_decode<128, 3>(p, n_tiles, st) : launch_attention_decode<128, 2>(p, n_tiles, st))
-                      : (stages >= 3 ? launch_attention_decode<64, 3>(p, n_tiles, st) : launch_attention_decode<64, 2>(p, n_tiles, st));
+        if (d == 128) rc = stages >= 4 ? launch_attention_decode<128, 4>(p, n_tiles, st)
+                         : stages == 3 ? launch_attention_decode<128, 3>(p, n_tiles, st) : launch_attention_decode<128, 2>(p, n_tiles, st);
+        else rc = stages >= 4 ? launch_attention_decode<64, 4>(p, n_tiles, st)
+                : stages == 3 ? launch_attention_decode<64, 3>(p, n_tiles, st) : launch_attention_decode<64, 2>(p, n_tiles, st);
     } else if (d == 128) rc = warps == 8 ? launch_attention<128, 8, 2>(p, n_tiles, st)
                      : warps == 4 ? (deep ? launch_attention<128, 4, 4>(p, n_tiles, st) : launch_attention<128, 4, 2>(p, n_tiles, st))
                                   : launch_attention<128, 1, 2>(p, n_tiles, st);
@@ -532,7 +508,5 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
             : warps == 4 ? (deep ? launch_attention<64, 4, 4>(p, n_tiles, st) : launch_attention<64, 4, 2>(p, n_tiles, st))
                          : launch_attention<64, 1, 2>(p, n_tiles, st);
     if (rc != HFB_OK || splits == 1) return rc;
-    if (d == 128) g_launch_err = launch_pdl(attention_combine_kernel<128>, dim3((unsigned)((size_t)T * H)), dim3(128), 0, st, p.part_o, p.part_ml, splits, p.out);
-    else g_launch_err = launch_pdl(attention_combine_kernel<64>, dim3((unsigned)((size_t)T * H)), dim3(64), 0, st, p.part_o, p.part_ml, splits, p.out);
-    return check_pdl_launch(g_launch_err, "attention_combine");
+    return launch_attention_combine(p, T, d, st);
 }

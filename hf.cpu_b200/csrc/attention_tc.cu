@@ -58,6 +58,7 @@ __device__ __forceinline__ uint32_t sw_off(int row, int c16)
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnTcParams p, int *err)
 {
+    HFB_TRACE_ENTRY(13);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));

@@ -9,6 +9,7 @@ int *error_word();
 // ---- embedding (src/model.c:566-571) ---------------------------------------------------------
 __global__ void embed_kernel(const int32_t *ids, const void *table, int dt, float *out, int V, int E, int *err)
 {
+    HFB_TRACE_ENTRY(7);
     pdl_sync();
     int t = blockIdx.x;
     int id = ids[t];
@@ -25,6 +26,7 @@ __global__ void embed_kernel(const int32_t *ids, const void *table, int dt, floa
 __global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float eps, void *out, int out_dt,
                                const int32_t *rows, int E)
 {
+    HFB_TRACE_ENTRY(15);
     pdl_sync();
     int m = blockIdx.x;
     const float *xr = x + (size_t)(rows ? rows[m] : m) * E;
@@ -50,6 +52,7 @@ __global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float ep
 template <typename TW, typename TO>
 __global__ void rmsnorm_vec_kernel(const float *x, const TW *w, float eps, TO *out, const int32_t *rows, int E)
 {
+    HFB_TRACE_ENTRY(6);
     pdl_sync();
     int m = blockIdx.x;
     const float4 *xr = (const float4 *)(x + (size_t)(rows ? rows[m] : m) * E);
@@ -168,6 +171,7 @@ __global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int
 template <typename T>
 __global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total, int interleaved)
 {
+    HFB_TRACE_ENTRY(14);
     pdl_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;

@@ -16,6 +16,7 @@ int *error_word();
 __global__ void reduce_residual_norm_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
                                             float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt)
 {
+    HFB_TRACE_ENTRY(11);
     pdl_sync();
     const int m = blockIdx.x;
     const size_t MN = (size_t)M * N;
@@ -55,6 +56,7 @@ __global__ void __launch_bounds__(1024)
 reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, const void *bias, int bias_dt,
                                 float *residual, const TW *w, float eps, TO *xn)
 {
+    HFB_TRACE_ENTRY(5);
     pdl_sync();
     const int m = blockIdx.x, N4 = N >> 2;
     const size_t MN4 = ((size_t)M * N) >> 2;
@@ -118,6 +120,7 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
                                       const int32_t *slots, T *q_out, T *k_cache, T *v_cache, long long cache_slots,
                                       int H, int G, int d, int *err)
 {
+    HFB_TRACE_ENTRY(2);
     pdl_sync();
     const int t = blockIdx.x, head = blockIdx.y;
     const int N = (H + 2 * G) * d;
@@ -163,6 +166,7 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
 // arg-max in two passes so that many blocks share a row: (value, index) per chunk, then the best chunk.
 __global__ void argmax_chunks_kernel(const float *logits, int V, int chunk, float *best_v, int32_t *best_i)
 {
+    HFB_TRACE_ENTRY(9);
     pdl_sync();
     const int row = blockIdx.y, c = blockIdx.x;
     const float *p = logits + (size_t)row * V;
@@ -190,6 +194,7 @@ __global__ void argmax_chunks_kernel(const float *logits, int V, int chunk, floa
 
 __global__ void argmax_final_kernel(const float *best_v, const int32_t *best_i, int chunks, int32_t *out)
 {
+    HFB_TRACE_ENTRY(10);
     pdl_sync();
     const int row = blockIdx.x;
     float best = 0.f;

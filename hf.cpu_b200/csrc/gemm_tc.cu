@@ -187,6 +187,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, GemmParams p, int *err)
 {
+    HFB_TRACE_ENTRY(1);
     constexpr uint32_t Y_BYTES = BN * BK * 2;
     constexpr int TCOLS = tmem_cols<BN>();
     extern __shared__ uint8_t smem_raw[];
@@ -344,6 +345,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 __global__ void splitk_reduce_kernel(const float *partial, int splits, size_t MN, int N, const void *bias, int bias_dt,
                                      void *out, int out_dt, int mode)
 {
+    HFB_TRACE_ENTRY(8);
     pdl_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= MN) return;

@@ -44,7 +44,49 @@ int *error_word()
     return ptr[dev];
 }
 
+#ifdef HFB_TRACE
+static void (*g_trace_setters[32])(void *);
+static int g_trace_setter_n = 0;
+static unsigned long long *g_trace_buf = nullptr;
+void trace_register(void (*setter)(void *)) { if (g_trace_setter_n < 32) g_trace_setters[g_trace_setter_n++] = setter; }
+#endif
+
 }  // namespace hfb
+
+// Kernel timeline of a -DHFB_TRACE build: start (or restart) logging; copy out up to `max` (tag, nanoseconds) pairs.
+extern "C" int hfb_trace_start(void)
+{
+#ifdef HFB_TRACE
+    using namespace hfb;
+    const size_t bytes = (2 + 2 * HFB_TRACE_CAP) * sizeof(unsigned long long);
+    if (!g_trace_buf && cudaMalloc(&g_trace_buf, bytes) != cudaSuccess) return fail(HFB_ECUDA, "trace: cannot allocate the log");
+    cudaDeviceSynchronize();
+    cudaMemset(g_trace_buf, 0, bytes);
+    for (int i = 0; i < g_trace_setter_n; i++) g_trace_setters[i](g_trace_buf);
+    return HFB_OK;
+#else
+    return hfb::fail(HFB_ENOTSUP, "trace: this library was built without -DHFB_TRACE");
+#endif
+}
+
+extern "C" long long hfb_trace_take(unsigned long long *pairs, long long max)
+{
+#ifdef HFB_TRACE
+    using namespace hfb;
+    if (!g_trace_buf) return 0;
+    cudaDeviceSynchronize();
+    unsigned long long n = 0;
+    cudaMemcpy(&n, g_trace_buf, sizeof n, cudaMemcpyDeviceToHost);
+    if (n > HFB_TRACE_CAP) n = HFB_TRACE_CAP;
+    if ((long long)n > max) n = (unsigned long long)max;
+    cudaMemcpy(pairs, g_trace_buf + 2, n * 2 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    cudaMemset(g_trace_buf, 0, sizeof(unsigned long long));
+    return (long long)n;
+#else
+    (void)pairs; (void)max;
+    return 0;
+#endif
+}
 
 extern "C" const char *hfb_last_error(void) { return hfb::g_msg; }
 extern "C" int hfb_version(void) { return 1; }

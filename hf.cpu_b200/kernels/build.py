@@ -23,6 +23,11 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 
 
+def _flags() -> List[str]:
+    """The fixed flags plus what HFB_NVCC_EXTRA adds (for instance -DHFB_TRACE for the kernel timeline)."""
+    return NVCC_FLAGS + os.environ.get("HFB_NVCC_EXTRA", "").split()
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and os.path.exists(cand):
@@ -42,7 +47,7 @@ def _digest() -> str:
             h.update(f.encode())
             with open(os.path.join(CSRC, f), "rb") as fh:
                 h.update(fh.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     return h.hexdigest()[:16]
 
 
@@ -73,7 +78,7 @@ def build(verbose: bool = True, force: bool = False) -> str:
     procs = []
     for f in srcs:
         obj = os.path.join(build_dir, f[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", os.path.join(CSRC, f), "-o", obj]
+        cmd = [nvcc, *_flags(), "-I", CSRC, "-c", os.path.join(CSRC, f), "-o", obj]
         procs.append((f, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     pending = list(procs)
     last = time.time()

@@ -53,8 +53,9 @@ class NativeBackend:
         self.gemv_max = int(os.environ.get("HFB_GEMV_MAX", "0"))
         self.attention_tc = os.environ.get("HFB_ATTN_TC", "1") != "0"     # tcgen05 attention for prompt portions
         self.decode_ctas_per_sm = int(os.environ.get("HFB_DECODE_CTAS", "2"))
-        self.decode_stages = int(os.environ.get("HFB_DECODE_STAGES", "2"))
+        self.decode_stages = int(os.environ.get("HFB_DECODE_STAGES", "3"))
         self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "2"))
+        self.decode_tma = os.environ.get("HFB_DECODE_TMA", "1") != "0"
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         # "tc": tensor-core products where the operands allow; "plain": the float32-accumulating SIMT kernel always
         self.gemm = os.environ.get("HFB_GEMM", "tc")
@@ -160,6 +161,17 @@ class NativeBackend:
                     stages = self.decode_stages if warps in (2, 4) else 2
                 need = self.lib.hfb_attention_fast_scratch(c_int(T), c_int(H), c_int(d), c_int(splits))
                 scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
+                if decode and warps == 2 and self.decode_tma and meta.block_size >= 8:
+                    # the keys and values come by TMA, a warp of their own keeps them coming
+                    self._check(self.lib.hfb_attention_decode(
+                        _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
+                        _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(stages), c_int(splits),
+                        c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out),
+                        _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), self._stream()),
+                        "attention_decode")
+                    if splits > 1:
+                        self.launches += 1
+                    return
                 self._check(self.lib.hfb_attention_fast(
                     _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
                     _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(warps), c_int(stages), c_int(splits),
