@@ -19,6 +19,19 @@ __global__ void embed_kernel(const int32_t *ids, const void *table, int dt, floa
         return;
     }
     size_t base = (size_t)id * E;
+    if (dt == HFB_BF16 && (E & 7) == 0 && ((uintptr_t)table & 15) == 0) {
+        // eight values per 16-byte read
+        const uint4 *src = (const uint4 *)((const __nv_bfloat16 *)table + base);
+        float4 *dst = (float4 *)(out + (size_t)t * E);
+        for (int i = threadIdx.x; i < (E >> 3); i += blockDim.x) {
+            const uint4 v = src[i];
+            const __nv_bfloat162 *h = (const __nv_bfloat162 *)&v;
+            const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c = __bfloat1622float2(h[2]), e = __bfloat1622float2(h[3]);
+            dst[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+            dst[2 * i + 1] = make_float4(c.x, c.y, e.x, e.y);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)t * E + i] = load_any(table, dt, base + i);
 }
 

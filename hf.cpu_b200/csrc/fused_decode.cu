@@ -57,8 +57,20 @@ reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, 
                                 float *residual, const TW *w, float eps, TO *xn)
 {
     HFB_TRACE_ENTRY(5);
-    pdl_sync();
     const int m = blockIdx.x, N4 = N >> 2;
+    // the norm's weights and the bias do not come from the kernel in front: fetch them while it finishes
+    float4 wv[RRN_VEC], bv[RRN_VEC];
+#pragma unroll
+    for (int j = 0; j < RRN_VEC; j++) {
+        const int i = threadIdx.x + j * blockDim.x;
+        wv[j] = bv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < N4) {
+            if (xn) wv[j] = make_float4(to_f32(w[4 * i]), to_f32(w[4 * i + 1]), to_f32(w[4 * i + 2]), to_f32(w[4 * i + 3]));
+            if (bias) bv[j] = make_float4(load_any(bias, bias_dt, 4 * i), load_any(bias, bias_dt, 4 * i + 1),
+                                          load_any(bias, bias_dt, 4 * i + 2), load_any(bias, bias_dt, 4 * i + 3));
+        }
+    }
+    pdl_sync();
     const size_t MN4 = ((size_t)M * N) >> 2;
     const float4 *part = (const float4 *)partial + (size_t)m * N4;
     float4 *res = (float4 *)(residual + (size_t)m * N);
@@ -67,16 +79,14 @@ reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, 
 #pragma unroll
     for (int j = 0; j < RRN_VEC; j++) {
         const int i = threadIdx.x + j * blockDim.x;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 v = bv[j];
         if (i < N4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int s = 0; s < splits; s++) {
                 float4 q = part[(size_t)s * MN4 + i];
-                v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
             }
-            if (bias) {
-                v.x += load_any(bias, bias_dt, 4 * i); v.y += load_any(bias, bias_dt, 4 * i + 1);
-                v.z += load_any(bias, bias_dt, 4 * i + 2); v.w += load_any(bias, bias_dt, 4 * i + 3);
-            }
+            v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;       // (sum of the splits) + bias, as before
             float4 r = res[i];
             v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
             res[i] = v;
@@ -102,8 +112,8 @@ reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, 
         const int i = threadIdx.x + j * blockDim.x;
         if (i >= N4) continue;
         const float4 v = vals[j];
-        float y0 = (v.x * r) * to_f32(w[4 * i]), y1 = (v.y * r) * to_f32(w[4 * i + 1]);
-        float y2 = (v.z * r) * to_f32(w[4 * i + 2]), y3 = (v.w * r) * to_f32(w[4 * i + 3]);
+        float y0 = (v.x * r) * wv[j].x, y1 = (v.y * r) * wv[j].y;
+        float y2 = (v.z * r) * wv[j].z, y3 = (v.w * r) * wv[j].w;
         TO *o = xn + (size_t)m * N + 4 * i;
         if (sizeof(TO) == 4) *(float4 *)o = make_float4(y0, y1, y2, y3);
         else {
@@ -121,36 +131,47 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
                                       int H, int G, int d, int *err)
 {
     HFB_TRACE_ENTRY(2);
-    pdl_sync();
+    // The slot, the position, the rotation's cosines and sines and the bias are inputs of the step or constants:
+    // they are fetched before the wait for the product in front, whose partial sums are read after it.
     const int t = blockIdx.x, head = blockIdx.y;
     const int N = (H + 2 * G) * d;
     const size_t TN = (size_t)Tn * N, row = (size_t)t * N + (size_t)head * d;
-    T *dst;
-    bool rotate;
+    T *dst = nullptr;
+    bool rotate, live = true;
     if (head < H) {
         dst = q_out + (size_t)t * H * d + (size_t)head * d;
         rotate = true;
     } else {
-        if (!slots) return;
-        long long slot = slots[t];
-        if (slot < 0) return;
-        if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); return; }
+        long long slot = slots ? slots[t] : -1;
+        if (slot >= cache_slots) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_SLOT); slot = -1; }
+        live = slot >= 0;
+        if (!live) slot = 0;
         if (head < H + G) { dst = k_cache + ((size_t)slot * G + (head - H)) * d; rotate = true; }
         else { dst = v_cache + ((size_t)slot * G + (head - H - G)) * d; rotate = false; }
     }
+    const int half = n_rot / 2;
+    const float *cs = cos_sin;
+    float c0 = 1.f, s0 = 0.f;                             // of this thread's first pair
+    if (live && rotate && half > 0) {
+        int pos = positions[t];
+        if (pos < 0 || pos >= n_positions) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+        cs = cos_sin + (size_t)pos * half * 2;
+        if ((int)threadIdx.x < half) { c0 = cs[2 * threadIdx.x]; s0 = cs[2 * threadIdx.x + 1]; }
+    }
+    const float b0 = (bias && (int)threadIdx.x < d) ? load_any(bias, bias_dt, (size_t)head * d + threadIdx.x) : 0.f;
+    const float b1 = (bias && (int)threadIdx.x + half < d) ? load_any(bias, bias_dt, (size_t)head * d + threadIdx.x + half) : 0.f;
+    pdl_sync();
+    if (!live) return;
     auto value = [&](int i) {
         float v = 0.f;
         for (int s = 0; s < splits; s++) v += partial[(size_t)s * TN + row + i];
-        if (bias) v += load_any(bias, bias_dt, (size_t)head * d + i);
+        if (bias) v += (i == (int)threadIdx.x) ? b0 : (i == (int)threadIdx.x + half) ? b1 : load_any(bias, bias_dt, (size_t)head * d + i);
         return v;
     };
-    const int half = n_rot / 2;
     if (rotate && half > 0) {
-        int pos = positions[t];
-        if (pos < 0 || pos >= n_positions) { if (threadIdx.x == 0) atomicOr(err, HFB_ERR_POSITION); pos = 0; }
-        const float *cs = cos_sin + (size_t)pos * half * 2;
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            float c = cs[2 * i], s = cs[2 * i + 1];
+            const bool first = i == (int)threadIdx.x;
+            float c = first ? c0 : cs[2 * i], s = first ? s0 : cs[2 * i + 1];
             float a = value(i), b = value(i + half);
             // the separate kernels round q|k|v to the run type before rotating; keep the same values
             a = to_f32(from_f32<T>(a)); b = to_f32(from_f32<T>(b));
