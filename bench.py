@@ -51,7 +51,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -130,7 +130,7 @@ def time_decode(engine, batch, steps, warmup, vocab, seed, sampler=None):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=192)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the 28 of the configuration (named in config)")
@@ -225,7 +225,7 @@ def main():
                "d2h_bytes_per_step": 4 * args.batch}
 
     line = {
-        "metric": "Qwen2.5-7B bf16: decode tok/s @ batch 8 (2,048-token prompts, 4,096 max context)",
+        "metric": f"Qwen2.5-7B bf16: decode tok/s @ batch {args.batch} (2,048-token prompts, 4,096 max context)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random-init weights)",
