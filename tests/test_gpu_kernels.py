@@ -439,3 +439,22 @@ def test_attention_tensor_core_prompt_portions(geom):
             again = _run_attention(native(), case, H, G, d, window)
             assert torch.equal(out, again)
     kernels.check_device_errors()
+
+
+@pytest.mark.parametrize("lens_q", [[1, 1], [1, 300]])
+def test_attention_long_context_far_keys(lens_q):
+    """33,000 cached keys: a decode token (the keys split over many CTAs) and a 300-token portion (hundreds of
+    tiles per query tile), with one key made to stand out near the start, in the middle and at the very end."""
+    H, G, d, bs = 28, 4, 128, 16
+    lens_kv = [700, 33000]
+    for key_pos in (3, 16384, 32999 - (lens_q[1] - 1)):
+        q_off = 0 if key_pos > 30000 else lens_q[1] - 1
+        case = _attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, 0, spike=(1, key_pos, q_off), seed=7)
+        case = _with_tiles(case, lens_q, lens_kv, H, G, wide=True)
+        out, ref = _run_attention(native(), case, H, G, d, 0), _run_attention(EmuBackend(), case, H, G, d, 0)
+        assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, key_pos)
+        t = sum(lens_q[:1]) + q_off
+        row = out.view(-1, H, d)[t].float()
+        assert rel(row, ref.view(-1, H, d)[t].float()) < TOL["bfloat16"]
+    from hfcpu_b200 import kernels
+    kernels.check_device_errors()
