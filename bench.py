@@ -100,15 +100,21 @@ def time_decode(engine, batch, steps, warmup, vocab, seed, sampler=None):
     from hfcpu_b200 import StepEntry, kernels
     tag = f"dec{batch}"
     toks = prefill_requests(engine, synthetic_prompts(batch, PROMPT, vocab, seed), tag)
-    out = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    outs = [torch.empty(batch, dtype=torch.int32, device=engine.device) for _ in range(2)]
+    entries = [StepEntry((tag, b), [0], [0]) for b in range(batch)]
+    prev = torch.tensor(toks, dtype=torch.int32, device=engine.device)
+    n_done = 0
 
-    def one_step(toks):
-        logits = engine.step([StepEntry((tag, b), [toks[b]], [0]) for b in range(batch)])
-        kernels.argmax(logits, out)
-        return out.tolist()                       # the device-to-host read of the step's result
+    def one_step():
+        # the ids the arg-max kernel wrote feed the next step on the device: the GPU never waits for the host
+        nonlocal prev, n_done
+        logits = engine.step(entries, token_source=prev)
+        prev = outs[n_done & 1]
+        kernels.argmax(logits, prev)
+        n_done += 1
 
     for _ in range(warmup):
-        toks = one_step(toks)
+        one_step()
     torch.cuda.synchronize()
     launches0 = kernels.backend().launches
     if sampler:
@@ -116,7 +122,7 @@ def time_decode(engine, batch, steps, warmup, vocab, seed, sampler=None):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        toks = one_step(toks)
+        one_step()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps

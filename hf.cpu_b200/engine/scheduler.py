@@ -13,6 +13,12 @@ request here, for many requests at once:
   it generated and its generator state, and it returns to the head of the waiting queue to be
   recomputed as prompt + generated tokens, so the tokens it samples do not change;
 * a request that cannot fit even alone fails with ENOMEM, and only that request.
+
+While every running request decodes and none is about to reach its limit, ``run`` keeps one step ahead of
+the host: the next step is launched with the token ids the sampling kernel has just written on the device,
+before the host has read them, so that planning, the copies and the events of one step hide behind the GPU's
+work on the next.  A request that turns out to have ended (an end token) has run one token too far; that
+token is dropped.
 """
 from __future__ import annotations
 
@@ -97,6 +103,16 @@ class FinishEvent:
 
 
 @dataclass
+class Flight:
+    """A step that has been launched and whose sampled tokens have not been read yet."""
+    sampled: List["Request"]
+    logits: Optional[torch.Tensor]
+    pending: object = None             # sampling.device.Pending, or None when the tokens are in ``tokens`` already
+    tokens: Optional[list] = None
+    rows: Optional[np.ndarray] = None
+
+
+@dataclass
 class StepPlan:
     entries: List[StepEntry]
     requests: List[Request]
@@ -117,8 +133,12 @@ class Scheduler:
         self.running: List[Request] = []
         self.requests: Dict[Hashable, Request] = {}
         self._arrivals = 0
-        self.stats = {"steps": 0, "preemptions": 0, "tokens_in": 0, "tokens_out": 0, "finished": 0, "errors": 0}
+        self.stats = {"steps": 0, "preemptions": 0, "tokens_in": 0, "tokens_out": 0, "finished": 0, "errors": 0,
+                      "steps_ahead": 0}
         self.cancelled = set()
+        self.run_ahead = self.device_sampling            # run() launches steady decode steps one ahead of the host
+        self._host_ring = None                           # pinned buffers the sampled ids are copied into
+        self._ring_at = 0
 
     # ---- submission ---------------------------------------------------------------------------
     def submit(self, req: Request) -> None:
@@ -273,6 +293,14 @@ class Scheduler:
 
     def step(self) -> list:
         """One scheduling round: plan, run the engine's step, sample, emit events."""
+        events, flight = self._begin()
+        if flight is not None:
+            events += self._end(flight)
+        return events
+
+    def _begin(self):
+        """Housekeeping, the plan, the engine's step and the launch of the sampling.  Returns the events so far
+        and the step in flight (None when nothing was sampled)."""
         events: list = []
         now = time.perf_counter()
         for r in list(self.running) + list(self.waiting):
@@ -289,7 +317,7 @@ class Scheduler:
             r.status = FINISHED
             self._finish(r, "error", events, "ENOMEM: the page pool cannot hold this request")
         if not plan.entries:
-            return events
+            return events, None
         logits = self.engine.step(plan.entries)
         self.stats["steps"] += 1
         self.stats["tokens_in"] += sum(len(e.tokens) for e in plan.entries)
@@ -297,9 +325,52 @@ class Scheduler:
         for r, e in zip(plan.requests, plan.entries):
             r.computed += len(e.tokens)
         if not sampled:
-            return events
-        tokens, rows = self._sample(logits, sampled)
-        for i, r in enumerate(sampled):
+            return events, None
+        return events, self._launch_sampling(logits, sampled)
+
+    def _launch_sampling(self, logits: torch.Tensor, sampled: List[Request]) -> Flight:
+        """On the GPU the sampling kernels run and only token ids come back; the host mirror serves the
+        stand-in backend of the tests."""
+        if self.device_sampling:
+            from .. import sampling
+            if self._host_ring is None:
+                self._host_ring = [torch.empty(max(self.engine.max_requests, 1), dtype=torch.int32, pin_memory=True)
+                                   for _ in range(4)]
+            self._ring_at = (self._ring_at + 1) % len(self._host_ring)
+            return Flight(sampled, logits, pending=sampling.device.sample_rows_async(logits, sampled, self._host_ring[self._ring_at]))
+        rows = logits.float().cpu().numpy()
+        return Flight(sampled, logits, tokens=[sample_host(rows[i], r.params, r.rng) for i, r in enumerate(sampled)], rows=rows)
+
+    def _can_run_ahead(self, flight: Flight) -> bool:
+        """True when the step after ``flight`` is known without its tokens: the same requests decode again, nobody
+        waits, nobody reaches a limit or a deadline, nobody wants log-probabilities, and the pages are there."""
+        if not (self.run_ahead and flight.pending is not None) or self.waiting or self.cancelled:
+            return False
+        if len(flight.sampled) != len(self.running) or len(self.running) > self.max_num_batched_tokens:
+            return False
+        for r, q in zip(flight.sampled, self.running):
+            if r is not q or r.pending != 0 or r.timeout > 0 or r.params.logprobs > 0 or len(r.generated) + 2 > r.budget:
+                return False
+        return self.engine.cache.can_reserve([(r.id, r.computed + 1) for r in self.running])
+
+    def _begin_ahead(self, flight: Flight) -> Flight:
+        """Launches the next decode step of the requests of ``flight`` on the token ids it is still sampling."""
+        entries = [StepEntry(r.id, [0], [0]) for r in flight.sampled]
+        logits = self.engine.step(entries, token_source=flight.pending.device)
+        self.stats["steps"] += 1
+        self.stats["steps_ahead"] += 1
+        self.stats["tokens_in"] += len(entries)
+        for r in flight.sampled:
+            r.computed += 1
+        return self._launch_sampling(logits, list(flight.sampled))
+
+    def _end(self, flight: Flight) -> list:
+        """Reads the sampled tokens of a step, emits their events and ends the requests that are done."""
+        events: list = []
+        tokens = flight.tokens if flight.pending is None else flight.pending.tokens()
+        for i, r in enumerate(flight.sampled):
+            if r.status == FINISHED:
+                continue                                  # ended while this step was in flight: its token is dropped
             tok = int(tokens[i])
             if not r.t_first:
                 r.t_first = time.perf_counter()
@@ -308,7 +379,7 @@ class Scheduler:
                 continue
             ev = TokenEvent(r.id, len(r.generated), tok)
             if r.params.logprobs > 0:
-                row = rows[i] if rows is not None else logits[i].float().cpu().numpy()
+                row = flight.rows[i] if flight.rows is not None else flight.logits[i].float().cpu().numpy()
                 ev.logprob, ev.top = logprob(row, tok), top_logprobs(row, r.params.logprobs)
             r.generated.append(tok)
             self.stats["tokens_out"] += 1
@@ -317,21 +388,24 @@ class Scheduler:
                 self._finish(r, r.limit_reason, events)
         return events
 
-    def _sample(self, logits: torch.Tensor, reqs: List[Request]):
-        """Next token for each row.  On the GPU the sampling kernels run and only token ids come back;
-        the host mirror serves the stand-in backend of the tests."""
-        if self.device_sampling:
-            from .. import sampling
-            return sampling.device.sample_rows(logits, reqs), None
-        rows = logits.float().cpu().numpy()
-        return [sample_host(rows[i], r.params, r.rng) for i, r in enumerate(reqs)], rows
-
     def run(self, on_event: Optional[Callable] = None) -> list:
         """Step until every submitted request is finished; returns (and reports) all events."""
         out = []
-        while self.has_work():
-            for ev in self.step():
+
+        def emit(events):
+            for ev in events:
                 out.append(ev)
                 if on_event:
                     on_event(ev)
+
+        flight = None
+        while flight is not None or self.has_work():
+            if flight is None:
+                events, flight = self._begin()
+                emit(events)
+                if flight is None:
+                    continue
+            ahead = self._begin_ahead(flight) if self._can_run_ahead(flight) else None
+            emit(self._end(flight))
+            flight = ahead
         return out

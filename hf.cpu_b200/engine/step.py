@@ -337,13 +337,20 @@ class Engine:
             backend.launches += state[3]
         return state[2]
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one step; returns float32 logits ``[wanted, vocab]`` (device), in the order of the entries and
         of their ``want`` lists, or None when nothing is wanted.  The returned tensor is scratch that the
-        next step overwrites."""
+        next step overwrites.
+
+        ``token_source`` (int32 on the device, one id per token of the step) replaces the entries' token ids:
+        the ids a sampling kernel has just written can be fed back without the host having seen them."""
         entries = list(entries)
         graphable = self.use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
         ctx = self.prepare(entries, static=graphable)
+        if token_source is not None:
+            if token_source.dtype != torch.int32 or token_source.numel() != ctx.num_tokens:
+                raise ValueError("token_source must hold one int32 id per token of the step")
+            ctx.token_ids[:ctx.num_tokens].copy_(token_source.reshape(-1), non_blocking=True)
         if graphable:
             logits = self._replay(ctx)
         else:

@@ -6,7 +6,7 @@ draws does not depend on batching or on preemption.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import numpy as np
 import torch
@@ -14,13 +14,31 @@ import torch
 from .. import kernels
 
 
-def sample_rows(logits: torch.Tensor, reqs) -> List[int]:
-    """``reqs[i]`` (with ``.params`` and ``.rng``) owns row i of the float32 ``logits`` [M, V]."""
+class Pending:
+    """Token ids a sampling kernel is writing: ``device`` holds them for a step that runs ahead of the host,
+    ``tokens()`` waits for the copy to the host and returns them."""
+
+    def __init__(self, device: torch.Tensor, host: Optional[torch.Tensor] = None):
+        self.device = device
+        # ``host``: a pinned buffer of the caller's that stays untouched until tokens() has returned
+        self._host = host[:device.numel()] if host is not None else torch.empty(device.shape, dtype=device.dtype, pin_memory=True)
+        self._host.copy_(device, non_blocking=True)
+        self._event = torch.cuda.Event()
+        self._event.record()
+
+    def tokens(self) -> List[int]:
+        self._event.synchronize()
+        return self._host.tolist()
+
+
+def launch_rows(logits: torch.Tensor, reqs) -> torch.Tensor:
+    """Launches the sampling of ``reqs[i]`` (with ``.params`` and ``.rng``) from row i of the float32 ``logits``
+    [M, V]; returns the int32 token ids on the device."""
     M = logits.shape[0]
+    out = torch.empty(M, dtype=torch.int32, device=logits.device)
     if all(r.params.temp <= 0 for r in reqs):
-        out = torch.empty(M, dtype=torch.int32, device=logits.device)
         kernels.argmax(logits.contiguous(), out)             # greedy rows need no parameters and no draws
-        return out.tolist()
+        return out
     host = np.zeros((5, M), dtype=np.float32)
     for i, r in enumerate(reqs):
         p = r.params
@@ -28,6 +46,14 @@ def sample_rows(logits: torch.Tensor, reqs) -> List[int]:
         host[1, i] = np.int32(p.top_k).view(np.float32)
         host[4, i] = r.rng.uniform() if p.temp > 0 else 0.0
     dev = torch.from_numpy(host).to(logits.device, non_blocking=True)
-    out = torch.empty(M, dtype=torch.int32, device=logits.device)
     kernels.sample(logits.contiguous(), dev[0], dev[1].view(torch.int32), dev[2], dev[3], dev[4], out)
-    return out.tolist()
+    return out
+
+
+def sample_rows_async(logits: torch.Tensor, reqs, host: Optional[torch.Tensor] = None) -> Pending:
+    return Pending(launch_rows(logits, reqs), host)
+
+
+def sample_rows(logits: torch.Tensor, reqs) -> List[int]:
+    """``reqs[i]`` (with ``.params`` and ``.rng``) owns row i of the float32 ``logits`` [M, V]."""
+    return launch_rows(logits, reqs).tolist()

@@ -77,3 +77,36 @@ def test_many_requests_under_pressure_match_plain(tiny_folders):
     assert st["preemptions"] > 0 and st["steps"] > 20
     sess.engine.cache.check()
     assert sess.engine.cache.pages_in_use() == 0 and sess.engine.slots.free_count == 4
+
+
+@pytest.mark.parametrize("dtype,name", [("float32", "A"), ("bfloat16", "B16")])
+def test_running_ahead_of_the_host_changes_no_token(tiny_folders, dtype, name):
+    """Steady decode steps are launched on the ids the sampling kernel has just written, before the host reads
+    them.  The tokens must equal those of the step-by-step loop: greedy and sampled, requests of different
+    lengths and limits, and an end token that arrives while the next step is already in flight."""
+    import hfcpu_b200
+    base = "A" if name == "A" else "B"
+    prompts = list(make_requests(base, [5, 23, 40], seed=9).values())
+    kw = dict(kv_block=BLOCK[base], kv_pages=96, max_seqs=4)
+    for opts in (dict(temp=0, max_tokens=24), dict(temp=0.9, top_k=50, top_p=0.9, seed=3, max_tokens=21, n=2)):
+        ahead_s = hfcpu_b200.Session(tiny_folders[name], dtype=dtype, **kw)
+        ahead = ahead_s.generate(prompts, **opts)
+        assert ahead_s.scheduler.stats["steps_ahead"] > 5
+        plain_s = hfcpu_b200.Session(tiny_folders[name], dtype=dtype, **kw)
+        plain_s.scheduler.run_ahead = False
+        stepwise = plain_s.generate(prompts, **opts)
+        assert plain_s.scheduler.stats["steps_ahead"] == 0
+        assert [[c.tokens for c in comps] for comps in ahead] == [[c.tokens for c in comps] for comps in stepwise]
+        assert ahead_s.engine.cache.pages_in_use() == 0
+    # an end token in the middle: take a token the greedy run produced as the end token of a second run
+    ref = hfcpu_b200.Session(tiny_folders[name], dtype=dtype, **kw).generate(prompts, temp=0, max_tokens=24)
+    eos = ref[1][0].tokens[9]
+    outs = []
+    for ahead_on in (True, False):
+        s = hfcpu_b200.Session(tiny_folders[name], dtype=dtype, eos_ids=[eos], **kw)
+        s.scheduler.run_ahead = ahead_on
+        outs.append(s.generate(prompts, temp=0, max_tokens=24))
+        assert s.engine.cache.pages_in_use() == 0
+        s.engine.cache.check()
+    assert [[(c.tokens, c.stop) for c in comps] for comps in outs[0]] == [[(c.tokens, c.stop) for c in comps] for comps in outs[1]]
+    assert outs[0][1][0].stop == "eos" and eos not in outs[0][1][0].tokens
