@@ -99,22 +99,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 
     if (warp == 0) {
         // ---- producer: K and V tiles, page by page ----------------------------------------------------
-        if (lane == 0) {
-            const int32_t *table = p.block_table + (size_t)seq * p.max_blocks;
-            const int bs = p.block_size, pages = TKEYS / bs;
-            for (int j = 0; j < n_kt; j++) {
-                const int s = j & 1;
-                if (!mbar_wait(kv_empty0 + 8 * s, ((j >> 1) & 1) ^ 1, abort_flag, err)) break;
-                mbar_arrive_expect_tx(kv_full0 + 8 * s, 2 * KV_STAGE);
-                for (int pg = 0; pg < pages; pg++) {
-                    const int key0 = (kt_lo + j) * TKEYS + pg * bs, blk = key0 / bs;
-                    const int page = (key0 <= pos_last && blk < p.max_blocks) ? table[blk] : -1;
-                    const int row = page >= 0 ? page * bs : p.num_slots;             // out of range: zeros
-                    const uint32_t off = (uint32_t)s * KV_STAGE + (uint32_t)pg * bs * 128u;
+        // The lanes read 32 entries of the block table at a time (one coalesced read for several tiles); lane 0 then
+        // asks for tile after tile without a round trip to L2 per page.
+        const int32_t *table = p.block_table + (size_t)seq * p.max_blocks;
+        const int bs = p.block_size, pages = TKEYS / bs, tiles_per_round = 32 / pages;
+        bool ok = true;
+        for (int j0 = 0; j0 < n_kt && ok; j0 += tiles_per_round) {
+            const int key0 = (kt_lo + j0) * TKEYS + lane * bs, blk = key0 / bs;
+            const bool mapped = lane < tiles_per_round * pages && j0 + lane / pages < n_kt && key0 <= pos_last && blk < p.max_blocks;
+            const int page = mapped ? table[blk] : -1;
+            const int my_row = page >= 0 ? page * bs : p.num_slots;                  // out of range: zeros
+            for (int t = 0; t < tiles_per_round && j0 + t < n_kt && ok; t++) {
+                const int j = j0 + t, s = j & 1;
+                if (lane == 0) {
+                    ok = mbar_wait(kv_empty0 + 8 * s, ((j >> 1) & 1) ^ 1, abort_flag, err);
+                    if (ok) mbar_arrive_expect_tx(kv_full0 + 8 * s, 2 * KV_STAGE);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                for (int pg = 0; pg < pages && ok; pg++) {
+                    const int row = __shfl_sync(0xffffffffu, my_row, t * pages + pg);
+                    if (lane == 0) {
+                        const uint32_t off = (uint32_t)s * KV_STAGE + (uint32_t)pg * bs * 128u;
 #pragma unroll
-                    for (int half = 0; half < 2; half++) {
-                        tma_load_2d(sK + off + half * SUB, &map_k, g * TD + half * 64, row, kv_full0 + 8 * s);
-                        tma_load_2d(sV + off + half * SUB, &map_v, g * TD + half * 64, row, kv_full0 + 8 * s);
+                        for (int half = 0; half < 2; half++) {
+                            tma_load_2d(sK + off + half * SUB, &map_k, g * TD + half * 64, row, kv_full0 + 8 * s);
+                            tma_load_2d(sV + off + half * SUB, &map_v, g * TD + half * 64, row, kv_full0 + 8 * s);
+                        }
                     }
                 }
             }
@@ -191,7 +201,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const int key0 = (kt_lo + j) * TKEYS + half * 64;         // first key of this thread's half
             if (!mbar_wait(s_full, j & 1, abort_flag, err)) { ok = false; break; }
             tc_fence_after();
-            const bool all_visible = valid && key0 + 63 <= pos && key0 >= lo;
+            // rows beyond the tile's tokens (zero queries, nothing of them is written) go with the rows that see
+            // every key, so that their warp is not split over both branches
+            const bool all_visible = !valid || (key0 + 63 <= pos && key0 >= lo);
             uint32_t sv[64];
             tmem_ld16(tS, sv); tmem_ld16(tS + 16, sv + 16); tmem_ld16(tS + 32, sv + 32); tmem_ld16(tS + 48, sv + 48);
             tmem_wait_ld();
@@ -224,9 +236,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             for (int i = 0; i < 64; i += 2) {
                 float a = ex2(__uint_as_float(sv[i]) * p.scale_log2 - bs), b = ex2(__uint_as_float(sv[i + 1]) * p.scale_log2 - bs);
                 __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                float2 back = __bfloat1622float2(h);                // the sum runs over the rounded values the product uses
-                sum += back.x + back.y;
-                pk[i >> 1] = *(uint32_t *)&h;
+                const uint32_t hb = *(uint32_t *)&h;                // the sum runs over the rounded values the product uses:
+                sum += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
+                pk[i >> 1] = hb;
             }
 #pragma unroll
             for (int q = 0; q < 8; q++)

@@ -223,25 +223,28 @@ class Engine:
         MB = self.max_blocks if static else max(1, (max(kv_lens) + bs - 1) // bs)
         # rows of an attention tile: 16 per warp; long portions get the wide tile (keys are read half as often)
         warps = 1 if max_q == 1 else (8 if max_q >= 64 and self.wide_attention_tiles else 4)
-        tilings = []
+        tilings = []                          # (heads per group, warps, tile_seq, tile_t0, tile_nt)
+        # 16 "warps" names the tiles of the kernel that takes two 128-row tiles per CTA: twice the tokens of one
+        widths = [warps, 16] if warps == 8 else [warps]
         for ratio in self._tile_ratios:
-            per = (16 * warps) // ratio
-            if per < 1:
-                continue
-            if max_q == 1:
-                t_seq = t_t0 = np.arange(S, dtype=np.int32)
-                t_nt = np.ones(S, dtype=np.int32)
-            else:
-                ls, lt, ln, t0 = [], [], [], 0
-                for s_i, n in enumerate(q_lens):
-                    for a in range(0, n, per):
-                        ls.append(s_i)
-                        lt.append(t0 + a)
-                        ln.append(min(per, n - a))
-                    t0 += n
-                t_seq, t_t0, t_nt = (np.asarray(x, dtype=np.int32) for x in (ls, lt, ln))
-            tilings.append((ratio, t_seq, t_t0, t_nt))
-        total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB) + sum(3 * len(t[1]) for t in tilings)
+            for w in widths:
+                per = (16 * w) // ratio if w < 16 else 2 * (128 // ratio)
+                if per < 1:
+                    continue
+                if max_q == 1:
+                    t_seq = t_t0 = np.arange(S, dtype=np.int32)
+                    t_nt = np.ones(S, dtype=np.int32)
+                else:
+                    ls, lt, ln, t0 = [], [], [], 0
+                    for s_i, n in enumerate(q_lens):
+                        for a in range(0, n, per):
+                            ls.append(s_i)
+                            lt.append(t0 + a)
+                            ln.append(min(per, n - a))
+                        t0 += n
+                    t_seq, t_t0, t_nt = (np.asarray(x, dtype=np.int32) for x in (ls, lt, ln))
+                tilings.append((ratio, w, t_seq, t_t0, t_nt))
+        total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB) + sum(3 * len(t[2]) for t in tilings)
         # one flat int32 buffer, filled through its numpy view: a single host-to-device copy per step
         ring_slot = self._meta_buffers(total)
         h, d = ring_slot[0], ring_slot[1]
@@ -276,7 +279,7 @@ class Engine:
             blk = pos // bs
             put(tables[seq, blk] * bs + pos % bs)                                  # cache slot of every token
             put(tables.reshape(-1))
-        for _, t_seq, t_t0, t_nt in tilings:
+        for _, _, t_seq, t_t0, t_nt in tilings:
             put(t_seq), put(t_t0), put(t_nt)
         assert o == total
         d[:total].copy_(h[:total], non_blocking=True)
@@ -296,10 +299,10 @@ class Engine:
         ctx.cu_tokens, ctx.kv_lens, ctx.seq_slots, ctx.logit_rows = take(S + 1), take(S), take(S), take(M)
         for g in groups:
             ctx._groups.append(GroupMeta(g.index, take(T), take(S * MB, (S, MB)), bs, MB))
-        for ratio, t_seq, _, _ in tilings:
+        for ratio, w, t_seq, _, _ in tilings:
             n = len(t_seq)
-            ctx._tiles[(ratio, warps)] = (take(n), take(n), take(n), n)
-            if warps == 1 and 64 // ratio >= 1:
+            ctx._tiles[(ratio, w)] = (take(n), take(n), take(n), n)
+            if w == 1 and 64 // ratio >= 1:
                 ctx._tiles[(ratio, 4)] = ctx._tiles[(ratio, 1)]        # one token a tile fits the wider kernel too
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, M
         ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots

@@ -52,6 +52,8 @@ class NativeBackend:
         # products with at most this many rows take the weight-streaming mma.sync kernel instead of tcgen05
         self.gemv_max = int(os.environ.get("HFB_GEMV_MAX", "0"))
         self.attention_tc = os.environ.get("HFB_ATTN_TC", "1") != "0"     # tcgen05 attention for prompt portions
+        self.attention_tc2 = os.environ.get("HFB_ATTN_TC2", "1") != "0"   # its form with two query tiles per CTA
+        self.tc2_min_rounds = float(os.environ.get("HFB_ATTN_TC2_ROUNDS", "3"))
         self.decode_ctas_per_sm = int(os.environ.get("HFB_DECODE_CTAS", "2"))
         self.decode_stages = int(os.environ.get("HFB_DECODE_STAGES", "3"))
         self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "2"))
@@ -137,6 +139,17 @@ class NativeBackend:
             decode = ctx.max_q_len == 1
             if (not decode and self.attention_tc and d == 128 and meta.block_size >= 8 and 128 % meta.block_size == 0
                     and H // G <= 128):
+                # two 128-row tiles per CTA once there are CTAs for three rounds over the SMs: it does more per key
+                # fetched and overlaps softmax and products, but halves the number of CTAs to balance
+                tiling = tiles(H // G, 16) if self.attention_tc2 else None
+                if tiling is not None and (tiling[3] * G >= self.tc2_min_rounds * self.sm_count):
+                    tile_seq, tile_t0, tile_nt, n_tiles = tiling
+                    self._check(self.lib.hfb_attention_tc2(
+                        _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
+                        _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(meta.block_size),
+                        c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out), c_int(T), c_int(H), c_int(G),
+                        c_int(d), self._stream()), "attention_tc2")
+                    return
                 tiling = tiles(H // G, 8)                    # tiles of 128 rows, as the 8-warp kernel's
                 if tiling is not None:
                     tile_seq, tile_t0, tile_nt, n_tiles = tiling

@@ -22,6 +22,17 @@ def native():
     return kernels
 
 
+@pytest.fixture
+def both_tc_forms():
+    """Lets small cases reach the attention kernel with two query tiles per CTA, which otherwise waits for enough
+    CTAs to fill the SMs three times."""
+    b = native().backend()
+    old = b.tc2_min_rounds
+    b.tc2_min_rounds = 0
+    yield b
+    b.tc2_min_rounds = old
+
+
 def rel(a, b):
     return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
 
@@ -264,19 +275,22 @@ def _with_tiles(case, lens_q, lens_kv, H, G, wide=False):
     """Adds what the tiled kernel needs to a case's context: the tile lists and the step's extents."""
     q, kc, vc, meta, ctx = case
     warps = 1 if max(lens_q) == 1 else (8 if wide else 4)
-    per = (16 * warps) // (H // G)
-    t_seq, t_t0, t_nt, t0 = [], [], [], 0
-    for s, n in enumerate(lens_q):
-        for a in range(0, n, per):
-            t_seq.append(s); t_t0.append(t0 + a); t_nt.append(min(per, n - a))
-        t0 += n
     dev = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    tiles = (dev(t_seq), dev(t_t0), dev(t_nt), len(t_seq))
+
+    def tiling(per):
+        t_seq, t_t0, t_nt, t0 = [], [], [], 0
+        for s, n in enumerate(lens_q):
+            for a in range(0, n, per):
+                t_seq.append(s); t_t0.append(t0 + a); t_nt.append(min(per, n - a))
+            t0 += n
+        return (dev(t_seq), dev(t_t0), dev(t_nt), len(t_seq))
+    tiles = tiling((16 * warps) // (H // G))
+    double = tiling(2 * (128 // (H // G))) if wide else None      # the kernel with two 128-row tiles per CTA
     ws = {}
 
     def buf(name, shape, dtype):
         return ws.setdefault((name, shape, dtype), torch.empty(shape, dtype=dtype, device=DEV))
-    ctx.attn_tiles = lambda ratio, w: tiles if ratio == H // G and (w == warps or (warps == 1 and 64 // ratio >= 1)) else None
+    ctx.attn_tiles = lambda ratio, w: (double if w == 16 else tiles if ratio == H // G and (w == warps or (warps == 1 and 64 // ratio >= 1)) else None)
     ctx.max_q_len, ctx.max_kv_len, ctx.buf = max(lens_q), max(lens_kv), buf
     return case
 
@@ -311,7 +325,7 @@ def test_attention_tiled_mixed_and_decode(geom, window):
     kernels.check_device_errors()
 
 
-def test_attention_tiled_far_key_window_edge_and_page_edges():
+def test_attention_tiled_far_key_window_edge_and_page_edges(both_tc_forms):
     H, G, d, bs = 28, 4, 128, 16
     for lens_q, lens_kv, spike_req in (([1, 1], [200, 600], 1), ([5, 40], [200, 600], 1)):
         for key_pos in (0, 15, 16, 63, 64, 303, 304, 559, 560, 599):
@@ -319,10 +333,15 @@ def test_attention_tiled_far_key_window_edge_and_page_edges():
             if key_pos > lens_kv[spike_req] - lens_q[spike_req] + q_off:
                 continue
             for window in (0, 40):
-                for wide in (False, True):            # wide: 128-row tiles, the tcgen05 kernel for prompt portions
+                for wide in (False, True, "single"):  # wide: 128-row tiles, the tcgen05 kernels for prompt portions
                     case = _attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, 0, spike=(spike_req, key_pos, q_off), seed=key_pos)
-                    case = _with_tiles(case, lens_q, lens_kv, H, G, wide)
-                    out, ref = _run_attention(native(), case, H, G, d, window), _run_attention(EmuBackend(), case, H, G, d, window)
+                    case = _with_tiles(case, lens_q, lens_kv, H, G, bool(wide))
+                    native().backend().attention_tc2 = wide != "single"
+                    try:
+                        out = _run_attention(native(), case, H, G, d, window)
+                    finally:
+                        native().backend().attention_tc2 = True
+                    ref = _run_attention(EmuBackend(), case, H, G, d, window)
                     assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, key_pos, window, wide)
 
 
@@ -417,19 +436,25 @@ def test_linear_weight_streaming(shape):
 
 
 @pytest.mark.parametrize("geom", [(28, 4, 128, 16), (4, 4, 128, 8), (16, 1, 128, 128), (5, 5, 128, 32)])
-def test_attention_tensor_core_prompt_portions(geom):
+def test_attention_tensor_core_prompt_portions(geom, both_tc_forms):
     """The tcgen05 attention kernel (head_dim 128): long portions over long histories, several requests, windows,
-    against the torch reference and against the mma.sync kernel."""
+    in both forms (two query tiles per CTA, one), against the torch reference and against the mma.sync kernel."""
     from hfcpu_b200 import kernels
     H, G, d, bs = geom
     b = kernels.backend()
-    assert b.attention_tc
+    assert b.attention_tc and b.attention_tc2
     for lens_q, lens_kv in (([300, 1, 40], [300, 900, 417]), ([130, 64], [700, 64]), ([2, 1], [2, 1])):
         for window in (0, 100):
             case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window, seed=len(lens_q)), lens_q, lens_kv, H, G, wide=True)
-            out = _run_attention(native(), case, H, G, d, window)
+            out = _run_attention(native(), case, H, G, d, window)          # two query tiles per CTA
             ref = _run_attention(EmuBackend(), case, H, G, d, window)
             assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, window)
+            b.attention_tc2 = False
+            try:
+                single = _run_attention(native(), case, H, G, d, window)   # one query tile per CTA
+            finally:
+                b.attention_tc2 = True
+            assert rel(single.float(), ref.float()) < TOL["bfloat16"], (lens_q, window)
             b.attention_tc = False
             try:
                 other = _run_attention(native(), case, H, G, d, window)
@@ -442,7 +467,7 @@ def test_attention_tensor_core_prompt_portions(geom):
 
 
 @pytest.mark.parametrize("lens_q", [[1, 1], [1, 300]])
-def test_attention_long_context_far_keys(lens_q):
+def test_attention_long_context_far_keys(lens_q, both_tc_forms):
     """33,000 cached keys: a decode token (the keys split over many CTAs) and a 300-token portion (hundreds of
     tiles per query tile), with one key made to stand out near the start, in the middle and at the very end."""
     H, G, d, bs = 28, 4, 128, 16
