@@ -8,8 +8,8 @@
 //   softmax     eight warps, two threads per row (64 keys and 64 output columns each): the scores come from TMEM
 //               with tcgen05.ld and stay in registers; the two halves of a row exchange their maxima through
 //               shared memory; P (bf16) goes to shared memory as the next A operand;
-//   PV = P V    tcgen05.mma, M = 128, N = 2 x 64 of head_dim, K = 128 keys; V is the B operand in MN-major form,
-//               which is how the cache holds it (a key's 64 values are one 128-byte row); the result lands in
+//   PV = P V    tcgen05.mma, M = 128, N = head_dim, K = 128 keys; V is the B operand in MN-major form, which is
+//               how the cache holds it (a key's values are two 128-byte rows, one sub-tile apart); the result lands in
 //               TMEM and is added into the row's running output, which lives in the thread's registers.
 // K and V tiles are gathered page by page with TMA (one box of block_size keys x 64 values per page and half of
 // head_dim), double buffered; pages that are not mapped or lie beyond the last key are requested out of
@@ -116,23 +116,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     if (ok) mbar_arrive_expect_tx(kv_full0 + 8 * s, 2 * KV_STAGE);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
-                for (int pg = 0; pg < pages && ok; pg++) {
-                    const int row = __shfl_sync(0xffffffffu, my_row, t * pages + pg);
-                    if (lane == 0) {
-                        const uint32_t off = (uint32_t)s * KV_STAGE + (uint32_t)pg * bs * 128u;
-#pragma unroll
-                        for (int half = 0; half < 2; half++) {
-                            tma_load_2d(sK + off + half * SUB, &map_k, g * TD + half * 64, row, kv_full0 + 8 * s);
-                            tma_load_2d(sV + off + half * SUB, &map_v, g * TD + half * 64, row, kv_full0 + 8 * s);
-                        }
-                    }
+                // one copy per page and half of the head for K and for V, each pair issued by a lane of its own
+                const int pg = lane >> 1, half = lane & 1;
+                const int row = __shfl_sync(0xffffffffu, my_row, t * pages + min(pg, pages - 1));
+                if (ok && pg < pages) {
+                    const uint32_t off = (uint32_t)s * KV_STAGE + (uint32_t)pg * bs * 128u + half * SUB;
+                    tma_load_2d(sK + off, &map_k, g * TD + half * 64, row, kv_full0 + 8 * s);
+                    tma_load_2d(sV + off, &map_v, g * TD + half * 64, row, kv_full0 + 8 * s);
                 }
             }
         }
     } else if (warp == 1) {
         // ---- tensor-core issue ------------------------------------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_s = bf16_idesc(TQ, TKEYS, false), idesc_pv = bf16_idesc(TQ, 64, true);
+            constexpr uint32_t idesc_s = bf16_idesc(TQ, TKEYS, false), idesc_pv = bf16_idesc(TQ, TD, true);
             const uint32_t tS = tmem_base, tPV = tmem_base + 128;
             auto issue_s = [&](int stage) {
 #pragma unroll
@@ -152,13 +149,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 if (!mbar_wait(p_ready, j & 1, abort_flag, err)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-#pragma unroll
-                    for (int kk = 0; kk < TKEYS / 16; kk++) {
-                        const uint32_t a = sP + (uint32_t)(kk >> 2) * SUB + (uint32_t)(kk & 3) * 32u;
-                        const uint32_t b = sV + s * KV_STAGE + half * SUB + (uint32_t)kk * 2048u;     // 16 keys further
-                        tc_mma_bf16(tPV + half * 64, sw128_desc(a), sw128_desc(b), idesc_pv, kk > 0 ? 1u : 0u);
-                    }
+                for (int kk = 0; kk < TKEYS / 16; kk++) {
+                    const uint32_t a = sP + (uint32_t)(kk >> 2) * SUB + (uint32_t)(kk & 3) * 32u;
+                    const uint32_t b = sV + s * KV_STAGE + (uint32_t)kk * 2048u;                 // 16 keys further
+                    // one product for both halves of the head: the second 64 values lie one sub-tile further
+                    tc_mma_bf16(tPV, sw128_desc(a), sw128_desc_mn(b, SUB), idesc_pv, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(pv_full);
                 tc_commit(kv_empty0 + 8 * s);

@@ -138,24 +138,21 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                         if (ok) mbar_arrive_expect_tx(full, U_TILE);
                     }
                     ok = __shfl_sync(0xffffffffu, ok, 0);
-                    for (int pg = 0; pg < pages && ok; pg++) {
-                        const int row = __shfl_sync(0xffffffffu, my_row, t * pages + pg);
-                        if (lane == 0) {
-                            const uint32_t off = (uint32_t)pg * bs * 128u;
-                            tma_load_2d(dst + off, kv ? &map_v : &map_k, g * U_D, row, full);
-                            tma_load_2d(dst + off + U_SUB, kv ? &map_v : &map_k, g * U_D + 64, row, full);
-                        }
-                    }
+                    // one copy per page and half of the head, each issued by a lane of its own
+                    const int pg = lane >> 1, half = lane & 1;
+                    const int row = __shfl_sync(0xffffffffu, my_row, t * pages + min(pg, pages - 1));
+                    if (ok && pg < pages)
+                        tma_load_2d(dst + (uint32_t)pg * bs * 128u + half * U_SUB, kv ? &map_v : &map_k, g * U_D + half * 64, row, full);
                 }
             }
         }
     } else if (warp == 1) {
         // ---- tensor-core issue ------------------------------------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_s = bf16_idesc(U_ROWS, U_KEYS, false), idesc_pv = bf16_idesc(U_ROWS, 64, true);
+            constexpr uint32_t idesc_s = bf16_idesc(U_ROWS, U_KEYS, false), idesc_pv = bf16_idesc(U_ROWS, U_D, true);
             // Every operand sits at a fixed place, so all descriptors are made once: a single thread issues 48
             // products per step, and what it computes between two of them is time the tensor core waits.
-            uint64_t dq[2][U_D / 16], dk[U_D / 16], dp[2][U_KEYS / 16], dv[2][U_KEYS / 16];
+            uint64_t dq[2][U_D / 16], dk[U_D / 16], dp[2][U_KEYS / 16], dv[U_KEYS / 16];
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
                 const uint32_t o = (uint32_t)(kk >> 2) * U_SUB + (uint32_t)(kk & 3) * 32u;
@@ -164,8 +161,8 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 for (int i = 0; i < 2; i++) {
                     dq[i][kk] = sw128_desc(sQ + i * U_TILE + o);
                     dp[i][kk] = sw128_desc(sP + i * U_TILE + o);
-                    dv[i][kk] = sw128_desc(sV + i * U_SUB + (uint32_t)kk * 2048u);       // [half][16 keys further]
                 }
+                dv[kk] = sw128_desc_mn(sV + (uint32_t)kk * 2048u, U_SUB);                // 16 keys further; both halves of the head
             }
             const uint32_t tS0 = tmem_base, tO0 = tmem_base + 256;
             auto issue_s = [&](int i) {
@@ -176,12 +173,8 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             };
             auto issue_pv = [&](int i, bool accumulate, uint64_t v_stage) {      // v_stage: 0 or the second V buffer
 #pragma unroll
-                for (int half = 0; half < 2; half++) {
-#pragma unroll
-                    for (int kk = 0; kk < U_KEYS / 16; kk++)
-                        tc_mma_bf16(tO0 + i * 128 + half * 64, i ? dp[1][kk] : dp[0][kk], dv[half][kk] + v_stage, idesc_pv,
-                                    (accumulate || kk > 0) ? 1u : 0u);
-                }
+                for (int kk = 0; kk < U_KEYS / 16; kk++)
+                    tc_mma_bf16(tO0 + i * 128, i ? dp[1][kk] : dp[0][kk], dv[kk] + v_stage, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
                 tc_commit(pv_done + 8 * i);
             };
             bool ok = mbar_wait(q_ready, 0, abort_flag, err);
@@ -200,29 +193,31 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 const int st = j & 1;
                 const uint64_t v_stage = st ? (uint64_t)(U_TILE >> 4) : 0;          // added to a descriptor's address field
                 if (!mbar_wait(v_full + 8 * st, (j >> 1) & 1, abort_flag, err)) { ok = false; break; }
+                // a tile's next scores come before its P V product: its softmax warps are what the step waits for
                 if (j < n_kt0) {
                     if (!mbar_wait(p_ready, j & 1, abort_flag, err)) { ok = false; break; }
                     tc_fence_after();
-                    issue_pv(0, j > 0, v_stage);
                     if (j + 1 < n_kt0) {
                         if (!mbar_wait(k_full, (j + 1) & 1, abort_flag, err)) { ok = false; break; }
                         tc_fence_after();
                         k_next = true;
                         issue_s(0);
+                        if (j + 1 >= n_kt1) tc_commit(k_empty);      // the other tile has no step j + 1: K is free after this
                     }
+                    issue_pv(0, j > 0, v_stage);
                 }
                 if (j < n_kt1) {
                     if (!mbar_wait(p_ready + 8, j & 1, abort_flag, err)) { ok = false; break; }
                     tc_fence_after();
+                    if (j + 1 < n_kt1) {
+                        if (!k_next && !mbar_wait(k_full, (j + 1) & 1, abort_flag, err)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_s(1);
+                        tc_commit(k_empty);                          // both tiles' products with K of step j + 1 are queued
+                    }
                     issue_pv(1, j > 0, v_stage);
                 }
                 tc_commit(v_empty + 8 * st);
-                if (j + 1 < n_kt) {
-                    if (!k_next && !mbar_wait(k_full, (j + 1) & 1, abort_flag, err)) { ok = false; break; }
-                    tc_fence_after();
-                    if (j + 1 < n_kt1) issue_s(1);
-                    tc_commit(k_empty);
-                }
             }
             // nothing of this CTA's is in flight once the last release of V has landed
             if (ok && n_kt > 0) mbar_wait(v_empty + 8 * ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, abort_flag, err);

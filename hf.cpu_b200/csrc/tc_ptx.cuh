@@ -97,6 +97,14 @@ __device__ __forceinline__ uint64_t sw128_desc(uint32_t addr)
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
+// Descriptor of an MN-major operand wider than one swizzled sub-tile: as sw128_desc, with the leading-dimension
+// offset naming the distance from one 64-element block of the MN dimension to the next.
+__device__ __forceinline__ uint64_t sw128_desc_mn(uint32_t addr, uint32_t block_stride)
+{
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(block_stride >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
 // Instruction descriptor for kind::f16: D float32, A and B bfloat16, M x N, A K-major, B K-major or MN-major.
 __host__ __device__ constexpr uint32_t bf16_idesc(int m, int n, bool b_mn_major)
 {
