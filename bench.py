@@ -134,6 +134,7 @@ def time_decode(engine, batch, steps, warmup, vocab, seed, sampler=None):
 
 
 def main():
+    global PROMPT, CTX_MAX
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=192)
@@ -141,8 +142,12 @@ def main():
     ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the 28 of the configuration (named in config)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (the record uses 2,048; others are for profiling)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
     args = ap.parse_args()
+    if args.prompt != PROMPT:
+        PROMPT = args.prompt
+        CTX_MAX = max(CTX_MAX, 2 * PROMPT)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -231,7 +236,7 @@ def main():
                "d2h_bytes_per_step": 4 * args.batch}
 
     line = {
-        "metric": f"Qwen2.5-7B bf16: decode tok/s @ batch {args.batch} (2,048-token prompts, 4,096 max context)",
+        "metric": f"Qwen2.5-7B bf16: decode tok/s @ batch {args.batch} ({PROMPT:,}-token prompts, {CTX_MAX:,} max context)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random-init weights)",

@@ -104,6 +104,7 @@ __global__ void rope_kv_write_kernel(const T *qkv, const float *cos_sin, int n_r
                                      const int32_t *positions, const int32_t *slots, T *q_out, T *k_cache,
                                      T *v_cache, long long cache_slots, int H, int G, int d, int *err)
 {
+    HFB_TRACE_ENTRY(16);
     pdl_sync();
     int t = blockIdx.x, head = blockIdx.y;
     const T *src = qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d;
@@ -143,6 +144,7 @@ __global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int
                                          const int32_t *positions, const int32_t *slots, T *q_out, T *k_cache,
                                          T *v_cache, long long cache_slots, int H, int G, int d, int *err)
 {
+    HFB_TRACE_ENTRY(16);
     pdl_sync();
     constexpr int VEC = 16 / sizeof(T);
     struct alignas(16) Pack { T e[VEC]; };
