@@ -167,9 +167,13 @@ __global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int
         const T *src = row + (size_t)head * d;
         if (rotate && e0 < half) {
             Pack a = *(const Pack *)(src + e0), b = *(const Pack *)(src + e0 + half), ra, rb;
+            // the VEC (cos, sin) pairs of these elements: 16-byte reads (VEC is even, the table's rows are 8-byte pairs)
+            float csv[2 * VEC];
+#pragma unroll
+            for (int i = 0; i < VEC / 2; i++) *(float4 *)(csv + 4 * i) = *(const float4 *)(cs + 2 * e0 + 4 * i);
 #pragma unroll
             for (int i = 0; i < VEC; i++) {
-                float c = cs[2 * (e0 + i)], sn = cs[2 * (e0 + i) + 1];
+                float c = csv[2 * i], sn = csv[2 * i + 1];
                 float x = to_f32(a.e[i]), y = to_f32(b.e[i]);
                 ra.e[i] = from_f32<T>(x * c - y * sn);
                 rb.e[i] = from_f32<T>(x * sn + y * c);
@@ -242,7 +246,8 @@ extern "C" int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, v
     if (!valid_dt(w_dt) || !valid_dt(out_dt) || E <= 0) return fail(HFB_EINVAL, "rmsnorm: bad arguments");
     int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
     cudaStream_t st = (cudaStream_t)s;
-    if ((E & 3) == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+    const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    if ((E & 3) == 0 && aligned) {
         if (w_dt == HFB_F32 && out_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<float, float>, dim3(M), dim3(threads), 0, st, x, (const float *)w, eps, (float *)out, rows, E);
         else if (w_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<float, __nv_bfloat16>, dim3(M), dim3(threads), 0, st, x, (const float *)w, eps, (__nv_bfloat16 *)out, rows, E);
         else if (out_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<__nv_bfloat16, float>, dim3(M), dim3(threads), 0, st, x, (const __nv_bfloat16 *)w, eps, (float *)out, rows, E);
@@ -263,7 +268,7 @@ extern "C" int hfb_rope_kv_write(const void *qkv, int dt, const float *cos_sin, 
     if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "rope_kv_write: rotation needs a table and positions");
     if (H + 2 * G > 65535) return fail(HFB_ENOTSUP, "rope_kv_write: %d heads exceed the grid limit", H + 2 * G);
     const int vec = dt == HFB_F32 ? 4 : 8;
-    if (d % vec == 0 && (n_rot / 2) % vec == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+    if (d % vec == 0 && (n_rot / 2) % vec == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)cos_sin & 15) == 0 &&
         ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0) {
         int items = (H + 2 * G) * (d / vec);
         int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
