@@ -105,12 +105,13 @@ int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, 
 
 /* Decode attention with the keys and values fetched by TMA: tiles as hfb_attention_fast's 16-row form takes them
  * (one or two tokens of one request), bfloat16, head_dim 64 or 128, block sizes 8..64 dividing 64.  `stages` (2..4)
- * tiles of 64 keys are in flight per CTA; `splits` > 1 needs hfb_attention_fast_scratch bytes of scratch. */
+ * tiles of 64 keys are in flight per CTA; `splits` > 1 needs hfb_attention_fast_scratch bytes of scratch, or, with
+ * `cluster` set and 2..8 splits, none: the CTAs of a request merge through distributed shared memory. */
 int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                          int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                          const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size, int64_t num_pages,
                          int window, float scale, void *out, void *scratch, size_t scratch_bytes, int T, int H, int G,
-                         int d, hfb_stream s);
+                         int d, int cluster, hfb_stream s);
 
 /* Attention of prompt portions on tcgen05 (S and PV accumulators in TMEM, K and V gathered page by page with
  * TMA): bfloat16, head_dim 128, block sizes 8..128 that divide 128.  Tiles hold at most 128 / (H/G) tokens. */
