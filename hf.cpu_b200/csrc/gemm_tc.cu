@@ -503,8 +503,8 @@ static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const
     case 64: return shallow() ? launch<64, 4>(mx, my, p, st) : launch<64, 8>(mx, my, p, st);
     case 128: return launch<128, 6>(mx, my, p, st);
     case 192: return launch<192, 5>(mx, my, p, st);
-    case 208: return launch<208, 4>(mx, my, p, st);
-    case 224: return launch<224, 4>(mx, my, p, st);
+    case 208: return launch<208, 5>(mx, my, p, st);
+    case 224: return launch<224, 5>(mx, my, p, st);
     case 240: return launch<240, 4>(mx, my, p, st);
     default: return launch<256, 4>(mx, my, p, st);
     }
