@@ -1,5 +1,6 @@
-"""Generality of the parts: a toy mixer with state of its own, a layer that runs twice, a layer that reads
-another layer's cache — all registered from here, without a change to the framework's files.
+"""Generality of the parts: a toy mixer with state of its own, a feed-forward that routes tokens to experts, another
+position encoding, a layer that runs twice, a layer that reads another layer's cache — all registered from here,
+without a change to the framework's files.
 
 Each case runs on the CPU with the torch stand-in for the kernels and, marked gpu, on the CUDA library.
 """
@@ -213,3 +214,167 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(backend, tmp_path):
         got = traces.run_in_process(eng, steps, check=eng.cache.check)
         bad = traces.first_bad(got, ref, 1e-4)
         assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
+
+
+# ---- a feed-forward with routing and another position encoding, both defined here -------------------------
+def _routed_ffn_part():
+    from hfcpu_b200.parts import FeedForward
+    from hfcpu_b200.weights import TensorSpec
+
+    class Top1Experts(FeedForward):
+        """Router logits in float32; the best expert's ``relu(x W1^T) W2^T`` weighted by its softmax share."""
+
+        def __init__(self, hidden_size, inner, experts, prefix, **_):
+            self.E, self.F, self.n, self.p = hidden_size, inner, experts, prefix
+            self.router = self.w1 = self.w2 = None
+
+        def tensor_specs(self):
+            return [TensorSpec(f"{self.p}.router", (self.n, self.E)), TensorSpec(f"{self.p}.w1", (self.n, self.F, self.E)),
+                    TensorSpec(f"{self.p}.w2", (self.n, self.E, self.F))]
+
+        def bind(self, tensors, run_dtype, device):
+            self.router, self.w1, self.w2 = (tensors[f"{self.p}.{k}"].float() for k in ("router", "w1", "w2"))
+
+        def forward(self, ctx, xn, residual):
+            x = xn.float()
+            share = torch.softmax(x @ self.router.T, dim=-1)
+            best = share.argmax(dim=-1)
+            for e in range(self.n):
+                rows = (best == e).nonzero().flatten()
+                if rows.numel():
+                    y = torch.relu(x[rows] @ self.w1[e].T) @ self.w2[e].T
+                    residual[rows] += y * share[rows, e:e + 1]
+    return Top1Experts
+
+
+def _scaled_rotary_part():
+    from hfcpu_b200.parts import PositionEncoding
+
+    class ScaledRotary(PositionEncoding):
+        """Rotary angles of positions divided by ``factor``, over the first ``n_rot`` dimensions of a head only.
+        The attention part takes any position part that offers ``cos_sin`` [positions, n_rot/2, 2] and ``n_rot``."""
+        graph_safe = True
+
+        def __init__(self, head_dim, n_rot, theta, factor, **_):
+            self.head_dim, self.n_rot, self.theta, self.factor, self.cos_sin = head_dim, n_rot, theta, factor, None
+
+        def prepare(self, max_positions, device):
+            half = self.n_rot // 2
+            inv = torch.tensor(self.theta, dtype=torch.float64) ** (-2.0 * torch.arange(half, dtype=torch.float64) / self.n_rot)
+            ang = (torch.arange(max_positions, dtype=torch.float64) / self.factor)[:, None] * inv[None, :]
+            self.cos_sin = torch.stack([ang.cos(), ang.sin()], dim=-1).float().contiguous().to(device)
+    return ScaledRotary
+
+
+@dataclass
+class RoutedConfig:
+    architecture: str = "RoutedToyForCausalLM"
+    layers: int = 3
+    hidden: int = 40
+    heads: int = 5
+    kv_heads: int = 1
+    head_dim: int = 16
+    n_rot: int = 8
+    factor: float = 2.5
+    inner: int = 24
+    experts: int = 4
+    vocab: int = 77
+    positions: int = 256
+
+    from_dict = classmethod(lambda cls, d: cls(**{k: v for k, v in d.items() if k in {f.name for f in dataclasses.fields(cls)}}))
+
+    def to_dict(self):
+        d = dataclasses.asdict(self)
+        d["architectures"] = [d.pop("architecture")]
+        return d
+
+    def save(self, folder):
+        import json, os
+        os.makedirs(folder, exist_ok=True)
+        json.dump(self.to_dict(), open(os.path.join(folder, "config.json"), "w"))
+
+    def plan(self):
+        from hfcpu_b200.config import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+        E = self.hidden
+        norm = lambda n: PartSpec("rmsnorm", {"size": E, "eps": 1e-6, "tensor": n})
+        layers = []
+        for l in range(self.layers):
+            p = f"rt.{l}"
+            mixer = PartSpec("paged_attention", {"hidden_size": E, "num_heads": self.heads, "num_kv_heads": self.kv_heads,
+                                                 "head_dim": self.head_dim, "qkv_bias": True, "out_bias": False,
+                                                 "window": 0, "position": "scaled", "prefix": f"{p}.attn"})
+            ffn = PartSpec("toy_top1_experts", {"hidden_size": E, "inner": self.inner, "experts": self.experts, "prefix": f"{p}.moe"})
+            layers.append(LayerSpec(p, PartSpec("prenorm_residual"), norm(f"{p}.n1"), mixer, norm(f"{p}.n2"), ffn))
+        return ModelPlan(E, self.vocab, self.positions,
+                         PartSpec("embedding", {"vocab_size": self.vocab, "hidden_size": E, "tensor": "rt.embed"}),
+                         {"scaled": PartSpec("toy_scaled_rotary", {"head_dim": self.head_dim, "n_rot": self.n_rot, "theta": 100.0,
+                                                                   "factor": self.factor})},
+                         layers, [ScheduleEntry(l) for l in range(self.layers)], norm("rt.norm"),
+                         PartSpec("linear_head", {"vocab_size": self.vocab, "hidden_size": E, "tensor": "rt.head"}))
+
+
+def _routed_reference(cfg, W, ids):
+    """The routed toy model on one whole sequence in float64.  Also returns the first position at which a router's
+    two best experts are closer than a rounding error could decide (rows from there on are not compared)."""
+    W = {k: v.double() for k, v in W.items()}
+    x = plain.embed(ids, W["rt.embed"])
+    T, H, G, d = len(ids), cfg.heads, cfg.kv_heads, cfg.head_dim
+    half = cfg.n_rot // 2
+    inv = torch.tensor(100.0, dtype=torch.float64) ** (-2.0 * torch.arange(half, dtype=torch.float64) / cfg.n_rot)
+    ang = (torch.arange(T, dtype=torch.float64) / cfg.factor)[:, None] * inv[None, :]
+    cos, sin = ang.cos(), ang.sin()
+    unsure = T
+    for l in range(cfg.layers):
+        p = f"rt.{l}"
+        xn = plain.rmsnorm(x, W[f"{p}.n1"], 1e-6)
+        q = plain.rope((xn @ W[f"{p}.attn.q_proj.weight"].T + W[f"{p}.attn.q_proj.bias"]).view(T, H, d), cos, sin, cfg.n_rot)
+        k = plain.rope((xn @ W[f"{p}.attn.k_proj.weight"].T + W[f"{p}.attn.k_proj.bias"]).view(T, G, d), cos, sin, cfg.n_rot)
+        v = (xn @ W[f"{p}.attn.v_proj.weight"].T + W[f"{p}.attn.v_proj.bias"]).view(T, G, d)
+        x = x + plain.attention(q, k, v, H, G, 0).reshape(T, H * d) @ W[f"{p}.attn.o_proj.weight"].T
+        xn = plain.rmsnorm(x, W[f"{p}.n2"], 1e-6)
+        share = torch.softmax(xn @ W[f"{p}.moe.router"].T, dim=-1)
+        top = share.topk(2, dim=-1).values
+        close = ((top[:, 0] - top[:, 1]) < 1e-4).nonzero().flatten()
+        if close.numel():
+            unsure = min(unsure, int(close[0]))
+        best = share.argmax(dim=-1)
+        y = torch.stack([torch.relu(xn[t] @ W[f"{p}.moe.w1"][best[t]].T) @ W[f"{p}.moe.w2"][best[t]].T * share[t, best[t]] for t in range(T)])
+        x = x + y
+    return plain.rmsnorm(x, W["rt.norm"], 1e-6) @ W["rt.head"].T, unsure
+
+
+@pytest.mark.parametrize("backend", DEVICES, indirect=True)
+def test_routed_feed_forward_and_another_position_encoding(backend, tmp_path):
+    """A feed-forward that routes each token to one of four experts and a rotary encoding with scaled positions
+    over half of each head, registered from here: the framework's attention, cache and step function run them
+    unchanged, in every way of cutting the requests."""
+    import hfcpu_b200
+    from hfcpu_b200.config import unregister_architecture
+    from hfcpu_b200.parts import unregister_part
+    hfcpu_b200.register_part("ffn", "toy_top1_experts", _routed_ffn_part())
+    hfcpu_b200.register_part("position", "toy_scaled_rotary", _scaled_rotary_part())
+    hfcpu_b200.register_architecture("RoutedToyForCausalLM", RoutedConfig)
+    try:
+        cfg = RoutedConfig()
+        folder = hfcpu_b200.write_random_model(cfg, str(tmp_path / "routed"), seed=9, dtype=torch.float32, std=0.3)
+        model = hfcpu_b200.load_model(folder, torch.float32, backend)
+        assert type(model.config).__name__ == "RoutedConfig"
+        g = torch.Generator().manual_seed(1)
+        reqs = {f"r{i}": torch.randint(0, cfg.vocab, (n,), generator=g).tolist() for i, n in enumerate([33, 70, 12, 51])}
+        _, W = plain.read_folder(folder)
+        ref, sure = {}, {}
+        for r, ids in reqs.items():
+            ref[r], sure[r] = _routed_reference(cfg, W, ids)
+        assert sum(sure.values()) > 0.8 * sum(len(v) for v in reqs.values()), "the routers are too often undecided to test anything"
+        experts_used = set()
+        for steps in (traces.whole(reqs), traces.portions(reqs), traces.mixed(reqs, max_live=3)):
+            eng = hfcpu_b200.Engine(model, block_size=8, max_tokens=traces.peak_tokens(steps), max_requests=3)
+            got = traces.run_in_process(eng, steps, check=eng.cache.check)
+            got = {(r, pos): row for (r, pos), row in got.items() if pos < sure[r]}
+            assert len(got) > 50
+            bad = traces.first_bad(got, ref, 1e-4)
+            assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
+    finally:
+        unregister_part("ffn", "toy_top1_experts")
+        unregister_part("position", "toy_scaled_rotary")
+        unregister_architecture("RoutedToyForCausalLM")
