@@ -74,6 +74,27 @@ def test_cuttings_match_plain(tiny_folders, name, dtype, family):
         assert bad is None, f"differs from the whole-prompt run at request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
 
 
+@pytest.mark.parametrize("family", ["whole", "portions", "mixed"])
+def test_cuttings_match_plain_with_two_query_tiles_per_cta(tiny_folders, family):
+    """The head_dim-128 configuration in bfloat16 with the attention kernel that takes two query tiles per CTA, which
+    small prompts do not reach by themselves (it waits for enough CTAs to fill the SMs twice)."""
+    from hfcpu_b200 import kernels
+    b = kernels.backend()
+    old, b.tc2_min_rounds = b.tc2_min_rounds, 0
+    try:
+        folder = folder_for(tiny_folders, "C", "bfloat16")
+        reqs = make_requests("C", [3, 150, 64, 129, 260, 400], seed=5)
+        steps = FAMILIES[family](reqs)
+        eng = engine_for(folder, "C", "bfloat16", traces.peak_tokens(steps))
+        got = traces.run_in_process(eng, steps, check=eng.cache.check)
+        check_clean(eng)
+        ref = {r: plain_logits(folder, ids) for r, ids in reqs.items()}
+        bad = traces.first_bad(got, ref, TOL["bfloat16"])
+        assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} (error {bad[2]:.3g})"
+    finally:
+        b.tc2_min_rounds = old
+
+
 @pytest.mark.parametrize("name", ["B", "C"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_past_the_window(tiny_folders, dtype, name):
