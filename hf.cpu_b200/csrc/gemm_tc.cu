@@ -43,6 +43,7 @@ enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
 struct GemmParams {
     int M, N, K;                       // logical sizes: tokens, output features, inner
     int swapped;                       // X = weights, Y = activations
+    int pair;                          // tiles of 256 tokens on pairs of CTAs (gemm_tc_pair_kernel)
     int tiles_x, tiles_y, splits, kb_total, kb_per_split;
     void *out; int out_dt;             // [M, N]
     const void *bias; int bias_dt;     // [N] or null
@@ -341,6 +342,187 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
 }
 
+
+// ---- the same product on pairs of SMs (cta_group::2), for many tokens ---------------------------------------
+// Two CTAs of a thread-block cluster share a tile of 256 tokens x BN features.  Each loads its 128 rows of the
+// activations and its half of the weight tile (BN/2 rows); the tensor cores of both SMs read both halves, so a k
+// block costs each SM 32 KB of shared-memory traffic for 128 x 256 x 64 products instead of 48 KB, which is what
+// bounds the single-CTA kernel.  The even CTA of the pair issues every product (tcgen05.mma.cta_group::2, M = 256)
+// and releases stages and accumulators in both CTAs with one multicast commit; the copies of both CTAs complete on
+// the even CTA's "full" barrier (the loads themselves are plain, not multicast); each CTA drains its own 128 rows
+// of the accumulator from its own TMEM.  Waits are bounded as everywhere; the cluster barriers at both ends are
+// reached on every path.
+__device__ __forceinline__ uint32_t cluster_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// a plain (not multicast) tiled copy whose bytes are counted on a barrier that may lie in the other CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar_cluster_addr)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, once the products issued so far are done, on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, GemmParams p, int *err)
+{
+    HFB_TRACE_ENTRY(1);
+    constexpr uint32_t Y_BYTES = (BN / 2) * BK * 2;          // this CTA's half of the weight tile
+    constexpr int TCOLS = tmem_cols<BN>();
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sx = base, sy = base + STAGES * X_BYTES;
+    const uint32_t bars = sy + STAGES * Y_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + STAGES * 8, tfull0 = bars + 2 * STAGES * 8, tempty0 = tfull0 + 16;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen_base + STAGES * (X_BYTES + Y_BYTES) + (2 * STAGES + 4) * 8);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                    // 0: issues the products; 1: its peer
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 8); }   // 4 warps of 2 CTAs
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void *)tmem_slot)), "r"(TCOLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_barrier();                                       // both CTAs' barriers exist before either is signalled
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_sync();
+
+    const int pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
+    const int total_items = p.tiles_x * p.tiles_y;           // tiles_x counts tiles of 256 tokens here
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int item = pair; item < total_items && ok; item += pairs) {
+                const int tx = item % p.tiles_x, ty = item / p.tiles_x;
+                for (int kb = 0; kb < p.kb_total; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * (X_BYTES + Y_BYTES));
+                    const uint32_t full_leader = map_to_rank(full0 + 8 * s, 0);
+                    tma_load_2d_pair(sx + s * X_BYTES, &map_x, kb * BK, tx * 256 + (int)rank * TILE_X, full_leader);
+                    tma_load_2d_pair(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN + (int)rank * (BN / 2), full_leader);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            int last_s = -1;
+            uint32_t last_ph = 0;
+            for (int item = pair; item < total_items && ok; item += pairs, tile_it++) {
+                const int a = tile_it & 1;
+                const uint32_t aph = (tile_it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * a, aph ^ 1, abort_flag, err)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d = tmem_base + a * BN;
+                for (int kb = 0; kb < p.kb_total; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, ph, abort_flag, err)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t dx = smem_desc(sx + s * X_BYTES), dy = smem_desc(sy + s * Y_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        tc_mma_bf16_pair(d, dx + 2 * k, dy + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit_pair(empty0 + 8 * s);
+                    last_s = s;
+                    last_ph = ph;
+                }
+                if (ok) tc_commit_pair(tfull0 + 8 * a);
+            }
+            if (ok && last_s >= 0) mbar_wait(empty0 + 8 * last_s, last_ph, abort_flag, err);
+        }
+    } else {
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        uint32_t tile_it = 0;
+        bool ok = true;
+        for (int item = pair; item < total_items && ok; item += pairs, tile_it++) {
+            const int tx = item % p.tiles_x, ty = item / p.tiles_x;
+            const int a = tile_it & 1;
+            const uint32_t aph = (tile_it >> 1) & 1;
+            if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag, err)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
+            const int xr = tx * 256 + (int)rank * TILE_X + row;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t v[32];
+                const bool two = c0 + 16 < BN;
+                tmem_ld16(taddr + c0, v);
+                if (two) tmem_ld16(taddr + c0 + 16, v + 16);
+                tmem_wait_ld();
+                epilogue_chunk(p, v, xr, ty * BN + c0, 0, lane);
+                if (two) epilogue_chunk(p, v + 16, xr, ty * BN + c0 + 16, 0, lane);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(tempty0 + 8 * a);
+                else mbar_arrive_remote(map_to_rank(tempty0 + 8 * a, 0));
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && threadIdx.x == 0) {
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);
+    }
+    __syncthreads();
+    cluster_barrier();                                       // neither CTA leaves while the other may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TCOLS) : "memory");
+    }
+}
+
 // Sums split-K partials in split order and applies the epilogue.
 __global__ void splitk_reduce_kernel(const float *partial, int splits, size_t MN, int N, const void *bias, int bias_dt,
                                      void *out, int out_dt, int mode)
@@ -455,6 +637,43 @@ static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams
     return check_pdl_launch(g_launch_err, "gemm_tc");
 }
 
+
+template <int BN, int STAGES>
+static int launch_pair(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams &p, cudaStream_t st)
+{
+    constexpr uint32_t smem = 1024 + STAGES * (X_BYTES + (BN / 2) * BK * 2) + (2 * STAGES + 4) * 8 + 16;
+    static_assert(smem <= 227 * 1024, "the stages do not fit");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail(HFB_ECUDA, "gemm_tc: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int items = p.tiles_x * p.tiles_y, pairs_cap = sm_count() / 2;
+    const int pairs = items < pairs_cap ? items : pairs_cap;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    n_attr++;
+    if (pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        n_attr++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    g_launch_err = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BN, STAGES>, mx, my, p, error_word());
+    return check_pdl_launch(g_launch_err, "gemm_tc_pair");
+}
+
 }  // namespace hfb
 
 using namespace hfb;
@@ -477,19 +696,23 @@ static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb:
         if ((rc = tensor_map(w, N, K, TILE_X, &mx)) != HFB_OK) return rc;
         if ((rc = tensor_map(a, M, K, bn, &my)) != HFB_OK) return rc;
     } else {
-        // the tile width that needs the fewest column-rounds over the SMs (every CTA walks its tiles in turn)
-        p.tiles_x = (M + TILE_X - 1) / TILE_X;
+        // the tile width that needs the fewest column-rounds over the SMs (every CTA walks its tiles in turn);
+        // from 256 tokens on, tiles of 256 tokens on pairs of SMs
+        static const int pair_min = env_int("HFB_GEMM_PAIR", 256);            // 0: never
+        p.pair = pair_min > 0 && M >= pair_min && sm_count() >= 2;
+        const int rows = p.pair ? 2 * TILE_X : TILE_X, units = p.pair ? sm_count() / 2 : sm_count();
+        p.tiles_x = (M + rows - 1) / rows;
         const int widths[6] = {256, 240, 224, 208, 192, 128};
         long best = -1;
         bn = 256;
         for (int i = 0; i < 6; i++) {
             long tiles = (long)p.tiles_x * ((N + widths[i] - 1) / widths[i]);
-            long cost = (tiles + sm_count() - 1) / sm_count() * widths[i];
+            long cost = (tiles + units - 1) / units * widths[i];
             if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
         }
         p.tiles_y = (N + bn - 1) / bn;
         if ((rc = tensor_map(a, M, K, TILE_X, &mx)) != HFB_OK) return rc;
-        if ((rc = tensor_map(w, N, K, bn, &my)) != HFB_OK) return rc;
+        if ((rc = tensor_map(w, N, K, p.pair ? bn / 2 : bn, &my)) != HFB_OK) return rc;
     }
     return HFB_OK;
 }
@@ -497,6 +720,16 @@ static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb:
 static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const hfb::GemmParams &p, cudaStream_t st)
 {
     using namespace hfb;
+    if (p.pair) {
+        switch (bn) {
+        case 128: return launch_pair<128, 7>(mx, my, p, st);
+        case 192: return launch_pair<192, 7>(mx, my, p, st);
+        case 208: return launch_pair<208, 7>(mx, my, p, st);
+        case 224: return launch_pair<224, 7>(mx, my, p, st);
+        case 240: return launch_pair<240, 7>(mx, my, p, st);
+        default: return launch_pair<256, 7>(mx, my, p, st);
+        }
+    }
     switch (bn) {
     case 16: return shallow() ? launch<16, 5>(mx, my, p, st) : launch<16, 10>(mx, my, p, st);
     case 32: return shallow() ? launch<32, 5>(mx, my, p, st) : launch<32, 9>(mx, my, p, st);

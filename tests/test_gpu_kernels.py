@@ -232,7 +232,9 @@ def test_refuses_unsupported_head_dim():
 
 TC_SHAPES = [(1, 128, 64), (1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (16, 1000, 192), (17, 320, 72),
              (64, 3584, 2048), (100, 1000, 200), (128, 512, 512), (129, 256, 64), (130, 1000, 192), (300, 777 * 8, 136),
-             (2048, 1024, 512), (1000, 4608, 3584), (5, 152064, 256)]
+             (2048, 1024, 512), (1000, 4608, 3584), (5, 152064, 256),
+             # from 256 rows on, pairs of CTAs share tiles of 256 rows (cta_group::2): edges of the pair's halves
+             (256, 96, 64), (257, 136, 192), (384, 1000, 72), (511, 3000, 320), (1024, 208, 128), (640, 37888 // 8, 256)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
