@@ -76,13 +76,15 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     // per query tile i: q_ready + 8i, s_full + 8i, p_ready + 8i, pv_done + 8i; per V stage s: v_full + 8s, v_empty + 8s
     const uint32_t q_ready = bars, s_full = bars + 16, p_ready = bars + 32, pv_done = bars + 48;
     const uint32_t k_full = bars + 64, k_empty = bars + 72, v_full = bars + 80, v_empty = bars + 96;
-    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen + 7 * U_TILE + 112);
+    const uint32_t s_free = bars + 112;              // + 8i: tile i's scores have been read out of TMEM
+    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen + 7 * U_TILE + 128);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; i++) {
             mbar_init(q_ready + 8 * i, 4); mbar_init(s_full + 8 * i, 1); mbar_init(p_ready + 8 * i, 4); mbar_init(pv_done + 8 * i, 1);
+            mbar_init(s_free + 8 * i, 4);
         }
         mbar_init(k_full, 1); mbar_init(k_empty, 1);
         for (int st = 0; st < 2; st++) { mbar_init(v_full + 8 * st, 1); mbar_init(v_empty + 8 * st, 1); }
@@ -189,32 +191,34 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 }
             }
             for (int j = 0; j < n_kt && ok; j++) {
-                bool k_next = false;                 // K of step j + 1 has been waited for
                 const int st = j & 1;
                 const uint64_t v_stage = st ? (uint64_t)(U_TILE >> 4) : 0;          // added to a descriptor's address field
+                // The scores of step j + 1 are queued as soon as those of step j have left TMEM for the softmax
+                // threads' registers, long before their exponentials are done: a tile's softmax warps then go from
+                // one step to the next without waiting for the tensor core.
+                if (j + 1 < n_kt) {
+                    if (!mbar_wait(k_full, (j + 1) & 1, abort_flag, err)) { ok = false; break; }
+                    if (j + 1 < n_kt0) {
+                        if (!mbar_wait(s_free, j & 1, abort_flag, err)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_s(0);
+                    }
+                    if (j + 1 < n_kt1) {
+                        if (!mbar_wait(s_free + 8, j & 1, abort_flag, err)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_s(1);
+                    }
+                    tc_commit(k_empty);                              // both tiles' products with K of step j + 1 are queued
+                }
                 if (!mbar_wait(v_full + 8 * st, (j >> 1) & 1, abort_flag, err)) { ok = false; break; }
-                // a tile's next scores come before its P V product: its softmax warps are what the step waits for
                 if (j < n_kt0) {
                     if (!mbar_wait(p_ready, j & 1, abort_flag, err)) { ok = false; break; }
                     tc_fence_after();
-                    if (j + 1 < n_kt0) {
-                        if (!mbar_wait(k_full, (j + 1) & 1, abort_flag, err)) { ok = false; break; }
-                        tc_fence_after();
-                        k_next = true;
-                        issue_s(0);
-                        if (j + 1 >= n_kt1) tc_commit(k_empty);      // the other tile has no step j + 1: K is free after this
-                    }
                     issue_pv(0, j > 0, v_stage);
                 }
                 if (j < n_kt1) {
                     if (!mbar_wait(p_ready + 8, j & 1, abort_flag, err)) { ok = false; break; }
                     tc_fence_after();
-                    if (j + 1 < n_kt1) {
-                        if (!k_next && !mbar_wait(k_full, (j + 1) & 1, abort_flag, err)) { ok = false; break; }
-                        tc_fence_after();
-                        issue_s(1);
-                        tc_commit(k_empty);                          // both tiles' products with K of step j + 1 are queued
-                    }
                     issue_pv(1, j > 0, v_stage);
                 }
                 tc_commit(v_empty + 8 * st);
@@ -255,6 +259,9 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
 #pragma unroll
             for (int c = 0; c < 8; c++) tmem_ld16(tS + 16 * c, sv + 16 * c);
             tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free + 8 * i);             // the tensor core may write the next scores
             float mx = -INFINITY;
             // rows beyond the tile's tokens (their queries are zeros, nothing of them is written) go with the rows
             // that see every key, so that their warp is not split over both branches
@@ -383,7 +390,7 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.num_slots = slots;
     p.per = U_ROWS / (H / G);
     p.scale_log2 = scale * 1.4426950408889634f;
-    constexpr uint32_t smem = 1024 + 7 * U_TILE + 128;
+    constexpr uint32_t smem = 1024 + 7 * U_TILE + 160;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
