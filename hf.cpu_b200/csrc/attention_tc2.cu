@@ -40,6 +40,7 @@ struct AttnTc2Params {
     const int32_t *block_table, *positions, *tile_seq, *tile_t0, *tile_nt;
     int max_blocks, block_size, window, H, G;
     int per;                                         // tokens per query tile: 128 / (H / G)
+    int n_tiles;                                     // double tiles in all
     int num_slots;                                   // pages * block_size: a row coordinate beyond it reads zeros
     float scale_log2;
 };
@@ -103,48 +104,64 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
     pdl_sync();                                      // queries and cache come from the kernels in front
 
-    // tiles late in a prompt see the most keys: they go first
-    const int tile = gridDim.x - 1 - blockIdx.x, g = blockIdx.y;
+    // Work items are (double tile, key/value head), heaviest first (tiles late in a prompt see the most keys).  A CTA
+    // takes one item per round, the rounds running over the CTAs forwards and backwards in turn, so that every CTA
+    // gets long and short items; barriers, TMEM and shared memory are set up once.  Each role walks the same items
+    // and keeps count of how often every barrier has been used.
     const int r = p.H / p.G;
-    const int seq = p.tile_seq[tile], t0 = p.tile_t0[tile], nt = p.tile_nt[tile];
-    const int nt0 = min(nt, p.per), nt1 = nt - nt0;                     // tokens of the two query tiles
-    const int pos_first = p.positions[t0];
-    const int pos_last0 = p.positions[t0 + nt0 - 1], pos_last = p.positions[t0 + nt - 1];
-    const int lo_all = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int kt_lo = lo_all / U_KEYS;
-    const int n_kt0 = pos_last0 / U_KEYS + 1 - kt_lo, n_kt1 = nt1 > 0 ? pos_last / U_KEYS + 1 - kt_lo : 0;
-    const int n_kt = max(n_kt0, n_kt1);
+    const int n_items = p.n_tiles * p.G, n_ctas = gridDim.x;
+    struct Item { int g, seq, t0, nt0, nt1, pos_last, kt_lo, n_kt0, n_kt1, n_kt; };
+    auto item_of = [&](int round, Item &it) -> bool {
+        const int idx = round * n_ctas + ((round & 1) ? n_ctas - 1 - (int)blockIdx.x : (int)blockIdx.x);
+        if (idx >= n_items) return false;
+        const int tile = p.n_tiles - 1 - idx / p.G;
+        it.g = idx % p.G;
+        it.seq = p.tile_seq[tile]; it.t0 = p.tile_t0[tile];
+        const int nt = p.tile_nt[tile];
+        it.nt0 = min(nt, p.per); it.nt1 = nt - it.nt0;                  // tokens of the two query tiles
+        const int pos_first = p.positions[it.t0], pos_last0 = p.positions[it.t0 + it.nt0 - 1];
+        it.pos_last = p.positions[it.t0 + nt - 1];
+        const int lo_all = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+        it.kt_lo = lo_all / U_KEYS;
+        it.n_kt0 = pos_last0 / U_KEYS + 1 - it.kt_lo;
+        it.n_kt1 = it.nt1 > 0 ? it.pos_last / U_KEYS + 1 - it.kt_lo : 0;
+        it.n_kt = max(it.n_kt0, it.n_kt1);
+        return true;
+    };
+    const int n_rounds = (n_items + n_ctas - 1) / n_ctas;
 
     if (warp == 0) {
-        // ---- producer: one K and one V tile at a time, page by page -----------------------------------
-        // The lanes read 32 entries of the block table at a time (the pages of several tiles, one coalesced read);
-        // lane 0 then asks for tile after tile without waiting for a table entry, which would cost a round trip
-        // to L2 per page and leave the tensor core waiting for keys.
-        const int32_t *table = p.block_table + (size_t)seq * p.max_blocks;
-        const int bs = p.block_size, pages = U_KEYS / bs, tiles_per_round = 32 / pages;
+        // ---- producer: one K tile and (in two buffers) one V tile per step, page by page ----------------------
+        // The lanes read 32 entries of the block table at a time (the pages of several steps, one coalesced read);
+        // the copies of a step, one per page and half of the head, are issued by as many lanes.
+        const int bs = p.block_size, pages = U_KEYS / bs, steps_per_round = 32 / pages;
         bool ok = true;
-        for (int j0 = 0; j0 < n_kt && ok; j0 += tiles_per_round) {
-            const int key0 = (kt_lo + j0) * U_KEYS + lane * bs, blk = key0 / bs;
-            const bool mapped = lane < tiles_per_round * pages && j0 + lane / pages < n_kt && key0 <= pos_last && blk < p.max_blocks;
-            const int page = mapped ? table[blk] : -1;
-            const int my_row = page >= 0 ? page * bs : p.num_slots;                  // out of range: zeros
-            for (int t = 0; t < tiles_per_round && j0 + t < n_kt && ok; t++) {
-                const int j = j0 + t;
+        uint32_t gs = 0;                                  // steps so far: K's use count, V's use count
+        for (int round = 0; round < n_rounds && ok; round++) {
+            Item it;
+            if (!item_of(round, it)) continue;
+            const int32_t *table = p.block_table + (size_t)it.seq * p.max_blocks;
+            for (int j0 = 0; j0 < it.n_kt && ok; j0 += steps_per_round) {
+                const int key0 = (it.kt_lo + j0) * U_KEYS + lane * bs, blk = key0 / bs;
+                const bool mapped = lane < steps_per_round * pages && j0 + lane / pages < it.n_kt && key0 <= it.pos_last && blk < p.max_blocks;
+                const int page = mapped ? table[blk] : -1;
+                const int my_row = page >= 0 ? page * bs : p.num_slots;              // out of range: zeros
+                for (int t = 0; t < steps_per_round && j0 + t < it.n_kt && ok; t++, gs++) {
 #pragma unroll 1
-                for (int kv = 0; kv < 2 && ok; kv++) {
-                    const int st = j & 1;                        // V's stage
-                    const uint32_t full = kv ? v_full + 8 * st : k_full, empty = kv ? v_empty + 8 * st : k_empty;
-                    const uint32_t dst = kv ? sV + st * U_TILE : sK;
-                    if (lane == 0) {
-                        ok = mbar_wait(empty, kv ? (((j >> 1) & 1) ^ 1) : ((j & 1) ^ 1), abort_flag, err);
-                        if (ok) mbar_arrive_expect_tx(full, U_TILE);
+                    for (int kv = 0; kv < 2 && ok; kv++) {
+                        const uint32_t st = gs & 1;                                   // V's stage
+                        const uint32_t full = kv ? v_full + 8 * st : k_full, empty = kv ? v_empty + 8 * st : k_empty;
+                        const uint32_t dst = kv ? sV + st * U_TILE : sK;
+                        if (lane == 0) {
+                            ok = mbar_wait(empty, kv ? (((gs >> 1) & 1) ^ 1) : ((gs & 1) ^ 1), abort_flag, err);
+                            if (ok) mbar_arrive_expect_tx(full, U_TILE);
+                        }
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                        const int pg = lane >> 1, half = lane & 1;
+                        const int row = __shfl_sync(0xffffffffu, my_row, t * pages + min(pg, pages - 1));
+                        if (ok && pg < pages)
+                            tma_load_2d(dst + (uint32_t)pg * bs * 128u + half * U_SUB, kv ? &map_v : &map_k, it.g * U_D + half * 64, row, full);
                     }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    // one copy per page and half of the head, each issued by a lane of its own
-                    const int pg = lane >> 1, half = lane & 1;
-                    const int row = __shfl_sync(0xffffffffu, my_row, t * pages + min(pg, pages - 1));
-                    if (ok && pg < pages)
-                        tma_load_2d(dst + (uint32_t)pg * bs * 128u + half * U_SUB, kv ? &map_v : &map_k, g * U_D + half * 64, row, full);
                 }
             }
         }
@@ -152,7 +169,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         // ---- tensor-core issue ------------------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = bf16_idesc(U_ROWS, U_KEYS, false), idesc_pv = bf16_idesc(U_ROWS, U_D, true);
-            // Every operand sits at a fixed place, so all descriptors are made once: a single thread issues 48
+            // Every operand sits at a fixed place, so all descriptors are made once: a single thread issues 32
             // products per step, and what it computes between two of them is time the tensor core waits.
             uint64_t dq[2][U_D / 16], dk[U_D / 16], dp[2][U_KEYS / 16], dv[U_KEYS / 16];
 #pragma unroll
@@ -179,169 +196,180 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                     tc_mma_bf16(tO0 + i * 128, i ? dp[1][kk] : dp[0][kk], dv[kk] + v_stage, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
                 tc_commit(pv_done + 8 * i);
             };
-            bool ok = mbar_wait(q_ready, 0, abort_flag, err);
-            if (ok && n_kt1 > 0) ok = mbar_wait(q_ready + 8, 0, abort_flag, err);
-            if (ok && n_kt > 0) {
-                ok = mbar_wait(k_full, 0, abort_flag, err);
-                if (ok) {
-                    tc_fence_after();
-                    if (n_kt0 > 0) issue_s(0);
-                    if (n_kt1 > 0) issue_s(1);
-                    tc_commit(k_empty);
-                }
-            }
-            for (int j = 0; j < n_kt && ok; j++) {
-                const int st = j & 1;
-                const uint64_t v_stage = st ? (uint64_t)(U_TILE >> 4) : 0;          // added to a descriptor's address field
-                // The scores of step j + 1 are queued as soon as those of step j have left TMEM for the softmax
-                // threads' registers, long before their exponentials are done: a tile's softmax warps then go from
-                // one step to the next without waiting for the tensor core.
-                if (j + 1 < n_kt) {
-                    if (!mbar_wait(k_full, (j + 1) & 1, abort_flag, err)) { ok = false; break; }
-                    if (j + 1 < n_kt0) {
-                        if (!mbar_wait(s_free, j & 1, abort_flag, err)) { ok = false; break; }
+            bool ok = true;
+            uint32_t gs = 0, g_tile[2] = {0, 0}, q_uses[2] = {0, 0};      // steps so far, per tile, and items per tile
+            for (int round = 0; round < n_rounds && ok; round++) {
+                Item it;
+                if (!item_of(round, it)) continue;
+                const int n_of[2] = {it.n_kt0, it.n_kt1};
+                for (int i = 0; i < 2 && ok; i++)
+                    if (n_of[i] > 0) ok = mbar_wait(q_ready + 8 * i, q_uses[i]++ & 1, abort_flag, err);
+                if (ok && it.n_kt > 0) {
+                    ok = mbar_wait(k_full, gs & 1, abort_flag, err);
+                    if (ok) {
                         tc_fence_after();
-                        issue_s(0);
+                        if (it.n_kt0 > 0) issue_s(0);
+                        if (it.n_kt1 > 0) issue_s(1);
+                        tc_commit(k_empty);
                     }
-                    if (j + 1 < n_kt1) {
-                        if (!mbar_wait(s_free + 8, j & 1, abort_flag, err)) { ok = false; break; }
-                        tc_fence_after();
-                        issue_s(1);
+                }
+                for (int j = 0; j < it.n_kt && ok; j++, gs++) {
+                    const uint32_t st = gs & 1;
+                    const uint64_t v_stage = st ? (uint64_t)(U_TILE >> 4) : 0;      // added to a descriptor's address field
+                    // The scores of step j + 1 are queued as soon as those of step j have left TMEM for the softmax
+                    // threads' registers, long before their exponentials are done: a tile's softmax warps then go
+                    // from one step to the next without waiting for the tensor core.
+                    if (j + 1 < it.n_kt) {
+                        if (!mbar_wait(k_full, (gs + 1) & 1, abort_flag, err)) { ok = false; break; }
+                        for (int i = 0; i < 2 && ok; i++) {
+                            if (j + 1 < n_of[i]) {
+                                ok = mbar_wait(s_free + 8 * i, (g_tile[i] + j) & 1, abort_flag, err);
+                                if (ok) { tc_fence_after(); issue_s(i); }
+                            }
+                        }
+                        if (!ok) break;
+                        tc_commit(k_empty);                          // both tiles' products with K of step j + 1 are queued
                     }
-                    tc_commit(k_empty);                              // both tiles' products with K of step j + 1 are queued
+                    if (!mbar_wait(v_full + 8 * st, (gs >> 1) & 1, abort_flag, err)) { ok = false; break; }
+                    for (int i = 0; i < 2 && ok; i++) {
+                        if (j < n_of[i]) {
+                            ok = mbar_wait(p_ready + 8 * i, (g_tile[i] + j) & 1, abort_flag, err);
+                            if (ok) { tc_fence_after(); issue_pv(i, j > 0, v_stage); }
+                        }
+                    }
+                    if (!ok) break;
+                    tc_commit(v_empty + 8 * st);
                 }
-                if (!mbar_wait(v_full + 8 * st, (j >> 1) & 1, abort_flag, err)) { ok = false; break; }
-                if (j < n_kt0) {
-                    if (!mbar_wait(p_ready, j & 1, abort_flag, err)) { ok = false; break; }
-                    tc_fence_after();
-                    issue_pv(0, j > 0, v_stage);
-                }
-                if (j < n_kt1) {
-                    if (!mbar_wait(p_ready + 8, j & 1, abort_flag, err)) { ok = false; break; }
-                    tc_fence_after();
-                    issue_pv(1, j > 0, v_stage);
-                }
-                tc_commit(v_empty + 8 * st);
+                g_tile[0] += it.n_kt0; g_tile[1] += it.n_kt1;
             }
             // nothing of this CTA's is in flight once the last release of V has landed
-            if (ok && n_kt > 0) mbar_wait(v_empty + 8 * ((n_kt - 1) & 1), ((n_kt - 1) >> 1) & 1, abort_flag, err);
+            if (ok && gs > 0) mbar_wait(v_empty + 8 * ((gs - 1) & 1), ((gs - 1) >> 1) & 1, abort_flag, err);
         }
     } else {
         // ---- softmax and output: one thread per row --------------------------------------------------------
         const int i = (warp - 2) >> 2;                                   // query tile
         const int row = (warp & 3) * 32 + lane;                          // TMEM lane = row; a warp reads its own quarter
-        const int n_mine = i ? n_kt1 : n_kt0, nt_mine = i ? nt1 : nt0, t_first = t0 + i * p.per;
         const int tl = row / r, hl = row % r;
-        const bool valid = tl < nt_mine;
-        const size_t th = ((size_t)(t_first + (valid ? tl : 0)) * p.H + g * r + hl) * U_D;
-        if (n_mine > 0) {
-            const uint4 *src = (const uint4 *)(p.q + th);
-#pragma unroll
-            for (int c = 0; c < 16; c++) {
-                uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + i * U_TILE + u_sw_off(row, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(q_ready + 8 * i);
-        }
-        const int pos = valid ? p.positions[t_first + tl] : -1;
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t tS = lane_base + i * 128, tO = lane_base + 256 + i * 128;
-        float m_ref = -INFINITY, l = 0.f;            // the maximum the exponentials refer to, and the sum in its scale
+        uint32_t g_mine = 0;                                             // this tile's steps so far
         bool ok = true;
-        for (int j = 0; j < n_mine && ok; j++) {
-            const int key0 = (kt_lo + j) * U_KEYS;
-            if (!mbar_wait(s_full + 8 * i, j & 1, abort_flag, err)) { ok = false; break; }
-            tc_fence_after();
-            uint32_t sv[128];
+        for (int round = 0; round < n_rounds && ok; round++) {
+            Item it;
+            if (!item_of(round, it)) continue;
+            const int n_mine = i ? it.n_kt1 : it.n_kt0, nt_mine = i ? it.nt1 : it.nt0, t_first = it.t0 + i * p.per;
+            if (n_mine <= 0) continue;
+            const bool valid = tl < nt_mine;
+            const size_t th = ((size_t)(t_first + (valid ? tl : 0)) * p.H + it.g * r + hl) * U_D;
+            {
+                // the tile's products of the item before are done (their scores have all been waited for)
+                const uint4 *src = (const uint4 *)(p.q + th);
 #pragma unroll
-            for (int c = 0; c < 8; c++) tmem_ld16(tS + 16 * c, sv + 16 * c);
-            tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free + 8 * i);             // the tensor core may write the next scores
-            float mx = -INFINITY;
-            // rows beyond the tile's tokens (their queries are zeros, nothing of them is written) go with the rows
-            // that see every key, so that their warp is not split over both branches
-            const bool all_visible = !valid || (key0 + U_KEYS - 1 <= pos && key0 >= lo);
-            if (all_visible) {
-#pragma unroll
-                for (int c = 0; c < 128; c++) mx = fmaxf(mx, __uint_as_float(sv[c]));
-            } else {
-#pragma unroll
-                for (int c = 0; c < 128; c++) {
-                    const int key = key0 + c;
-                    const bool see = valid && key >= lo && key <= pos;
-                    if (!see) sv[c] = 0xff800000u;                  // -inf: contributes neither to the maximum nor to the sum
-                    mx = fmaxf(mx, __uint_as_float(sv[c]));
+                for (int c = 0; c < 16; c++) {
+                    uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + i * U_TILE + u_sw_off(row, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(q_ready + 8 * i);
             }
-            mx *= p.scale_log2;                                      // scale > 0 commutes with the maximum
-            // raise the reference only when the row's maximum has outgrown it by 2^TAU (or there was none yet)
-            float corr = 1.f;
-            if (mx > m_ref + U_TAU || (m_ref == -INFINITY && mx > -INFINITY)) {
-                corr = m_ref == -INFINITY ? 0.f : u_ex2(m_ref - mx);
-                m_ref = mx;
-            }
-            const float bs = m_ref == -INFINITY ? 0.f : m_ref;
-            float sum = 0.f;
-            uint32_t pk[64];
-#pragma unroll
-            for (int c = 0; c < 128; c += 2) {
-                const float a = u_ex2(__uint_as_float(sv[c]) * p.scale_log2 - bs), b = u_ex2(__uint_as_float(sv[c + 1]) * p.scale_log2 - bs);
-                __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-                const uint32_t hb = *(uint32_t *)&h;                // the sum runs over the rounded values the product uses:
-                sum += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
-                pk[c >> 1] = hb;
-            }
-            l = l * corr + sum;
-            if (j > 0) {
-                // P of the step before has been used, and O holds everything up to it
-                if (!mbar_wait(pv_done + 8 * i, (j - 1) & 1, abort_flag, err)) { ok = false; break; }
+            const int pos = valid ? p.positions[t_first + tl] : -1;
+            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            float m_ref = -INFINITY, l = 0.f;        // the maximum the exponentials refer to, and the sum in its scale
+            for (int j = 0; j < n_mine && ok; j++) {
+                const uint32_t ph = (g_mine + j) & 1;
+                const int key0 = (it.kt_lo + j) * U_KEYS;
+                if (!mbar_wait(s_full + 8 * i, ph, abort_flag, err)) { ok = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll 1
-                    for (int c = 0; c < 8; c++) {
-                        uint32_t ov[16];
-                        tmem_ld16(tO + 16 * c, ov);
-                        tmem_wait_ld();
+                uint32_t sv[128];
 #pragma unroll
-                        for (int e = 0; e < 16; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * corr);
-                        tmem_st16(tO + 16 * c, ov);
-                    }
-                    tmem_wait_st();
-                }
-            }
-#pragma unroll
-            for (int q = 0; q < 16; q++)
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sP + i * U_TILE + u_sw_off(row, q)), "r"(pk[4 * q]),
-                             "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready + 8 * i);
-        }
-        if (ok && n_mine > 0) ok = mbar_wait(pv_done + 8 * i, (n_mine - 1) & 1, abort_flag, err);
-        if (ok && n_mine > 0) {
-            tc_fence_after();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            uint4 *dst = (uint4 *)(p.out + th);
-#pragma unroll 1
-            for (int c = 0; c < 8; c++) {
-                uint32_t ov[16];
-                tmem_ld16(tO + 16 * c, ov);                           // all lanes of the warp take part, valid row or not
+                for (int c = 0; c < 8; c++) tmem_ld16(tS + 16 * c, sv + 16 * c);
                 tmem_wait_ld();
-                if (valid) {
-                    __nv_bfloat162 h[8];
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_free + 8 * i);         // the tensor core may write the next scores
+                float mx = -INFINITY;
+                // rows beyond the tile's tokens (their queries are zeros, nothing of them is written) go with the
+                // rows that see every key, so that their warp is not split over both branches
+                const bool all_visible = !valid || (key0 + U_KEYS - 1 <= pos && key0 >= lo);
+                if (all_visible) {
 #pragma unroll
-                    for (int e = 0; e < 8; e++) h[e] = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
-                    dst[2 * c] = *(uint4 *)&h[0];
-                    dst[2 * c + 1] = *(uint4 *)&h[4];
+                    for (int c = 0; c < 128; c++) mx = fmaxf(mx, __uint_as_float(sv[c]));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 128; c++) {
+                        const int key = key0 + c;
+                        const bool see = valid && key >= lo && key <= pos;
+                        if (!see) sv[c] = 0xff800000u;              // -inf: contributes neither to the maximum nor to the sum
+                        mx = fmaxf(mx, __uint_as_float(sv[c]));
+                    }
                 }
+                mx *= p.scale_log2;                                  // scale > 0 commutes with the maximum
+                // raise the reference only when the row's maximum has outgrown it by 2^TAU (or there was none yet)
+                float corr = 1.f;
+                if (mx > m_ref + U_TAU || (m_ref == -INFINITY && mx > -INFINITY)) {
+                    corr = m_ref == -INFINITY ? 0.f : u_ex2(m_ref - mx);
+                    m_ref = mx;
+                }
+                const float bs = m_ref == -INFINITY ? 0.f : m_ref;
+                float sum = 0.f;
+                uint32_t pk[64];
+#pragma unroll
+                for (int c = 0; c < 128; c += 2) {
+                    const float a = u_ex2(__uint_as_float(sv[c]) * p.scale_log2 - bs), b = u_ex2(__uint_as_float(sv[c + 1]) * p.scale_log2 - bs);
+                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                    const uint32_t hb = *(uint32_t *)&h;            // the sum runs over the rounded values the product uses:
+                    sum += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
+                    pk[c >> 1] = hb;
+                }
+                l = l * corr + sum;
+                if (j > 0) {
+                    // P of the step before has been used, and O holds everything up to it
+                    if (!mbar_wait(pv_done + 8 * i, ph ^ 1, abort_flag, err)) { ok = false; break; }
+                    tc_fence_after();
+                    if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+                        for (int c = 0; c < 8; c++) {
+                            uint32_t ov[16];
+                            tmem_ld16(tO + 16 * c, ov);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 16; e++) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * corr);
+                            tmem_st16(tO + 16 * c, ov);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 16; q++)
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sP + i * U_TILE + u_sw_off(row, q)), "r"(pk[4 * q]),
+                                 "r"(pk[4 * q + 1]), "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3]) : "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_ready + 8 * i);
             }
-            tc_fence_before();
+            g_mine += n_mine;
+            if (ok) ok = mbar_wait(pv_done + 8 * i, (g_mine - 1) & 1, abort_flag, err);
+            if (ok) {
+                tc_fence_after();
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                uint4 *dst = (uint4 *)(p.out + th);
+#pragma unroll 1
+                for (int c = 0; c < 8; c++) {
+                    uint32_t ov[16];
+                    tmem_ld16(tO + 16 * c, ov);                       // all lanes of the warp take part, valid row or not
+                    tmem_wait_ld();
+                    if (valid) {
+                        __nv_bfloat162 h[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) h[e] = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
+                        dst[2 * c] = *(uint4 *)&h[0];
+                        dst[2 * c + 1] = *(uint4 *)&h[4];
+                    }
+                }
+                tc_fence_before();
+            }
         }
     }
 
@@ -389,6 +417,7 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
     p.block_table = block_table; p.positions = positions; p.tile_seq = tile_seq; p.tile_t0 = tile_t0; p.tile_nt = tile_nt;
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.num_slots = slots;
     p.per = U_ROWS / (H / G);
+    p.n_tiles = n_tiles;
     p.scale_log2 = scale * 1.4426950408889634f;
     constexpr uint32_t smem = 1024 + 7 * U_TILE + 160;
     static bool configured = false;
@@ -397,6 +426,11 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
         if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_tc2: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    g_launch_err = launch_pdl(attention_tc2_kernel, dim3(n_tiles, G), dim3(U_THREADS), smem, (cudaStream_t)s, mk, mv, p, error_word());
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long items = (long long)n_tiles * G;
+    const int grid = (int)(items < sms ? items : (sms > 0 ? sms : 1));      // one CTA per SM walks its share of the items
+    g_launch_err = launch_pdl(attention_tc2_kernel, dim3(grid), dim3(U_THREADS), smem, (cudaStream_t)s, mk, mv, p, error_word());
     return check_pdl_launch(g_launch_err, "attention_tc2");
 }

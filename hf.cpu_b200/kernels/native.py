@@ -53,7 +53,7 @@ class NativeBackend:
         self.gemv_max = int(os.environ.get("HFB_GEMV_MAX", "0"))
         self.attention_tc = os.environ.get("HFB_ATTN_TC", "1") != "0"     # tcgen05 attention for prompt portions
         self.attention_tc2 = os.environ.get("HFB_ATTN_TC2", "1") != "0"   # its form with two query tiles per CTA
-        self.tc2_min_rounds = float(os.environ.get("HFB_ATTN_TC2_ROUNDS", "2"))
+        self.tc2_min_rounds = float(os.environ.get("HFB_ATTN_TC2_ROUNDS", "1"))
         self.decode_ctas_per_sm = int(os.environ.get("HFB_DECODE_CTAS", "2"))
         self.decode_stages = int(os.environ.get("HFB_DECODE_STAGES", "3"))
         self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "2"))
@@ -143,8 +143,8 @@ class NativeBackend:
             decode = ctx.max_q_len == 1
             if (not decode and self.attention_tc and d == 128 and meta.block_size >= 8 and 128 % meta.block_size == 0
                     and H // G <= 128):
-                # two 128-row tiles per CTA once there are CTAs for two rounds over the SMs: it does more per key
-                # fetched and overlaps softmax and products, but halves the number of CTAs to balance
+                # two 128-row tiles per CTA once there is an item for every SM: it does more per key fetched and overlaps
+                # softmax and products, but has half as many items to spread
                 tiling = tiles(H // G, 16) if self.attention_tc2 else None
                 if tiling is not None and (tiling[3] * G >= self.tc2_min_rounds * self.sm_count):
                     tile_seq, tile_t0, tile_nt, n_tiles = tiling
