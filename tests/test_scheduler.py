@@ -127,3 +127,43 @@ def test_eos_and_fanout_seeds(tiny_folders, emu):
     first = three[0].tokens
     cut = sess.generate(prompt, temp=1.0, top_k=0, top_p=1.0, min_p=0.0, seed=7, max_tokens=12, eos_ids=[first[3]])
     assert cut[0].stop == "eos" and cut[0].tokens == first[:first.index(first[3])]
+
+
+def test_running_ahead_of_the_host_on_the_stand_in(tiny_folders, emu, monkeypatch):
+    """The run loop launches the next steady decode step on token ids the host has not read yet.  Here the sampling
+    "kernel" is a host function that hands its ids back as a tensor, so that the bookkeeping (limits, an end token
+    that arrives while the next step is in flight, pages given back, the token computed too far being dropped) is
+    tested without a GPU: tokens and stop reasons must equal those of the step-by-step loop."""
+    import numpy as np
+    from hfcpu_b200 import sampling
+    from hfcpu_b200.sampling import sample_host
+
+    class HostPending:
+        def __init__(self, logits, reqs, host=None):
+            rows = logits.float().cpu().numpy()
+            self.device = torch.tensor([sample_host(rows[i], r.params, r.rng) for i, r in enumerate(reqs)], dtype=torch.int32)
+
+        def tokens(self):
+            return self.device.tolist()
+
+    monkeypatch.setattr(sampling.device, "sample_rows_async", HostPending)
+    prompts = list(make_requests("A", [5, 23, 40, 9], seed=9).values())
+    ref_sess = _session(tiny_folders["A"], "A", 96)
+    ref = ref_sess.generate(prompts, temp=0, max_tokens=20)
+    eos = ref[1][0].tokens[7]
+    for opts in (dict(temp=0, max_tokens=20), dict(temp=0.9, top_k=30, seed=4, max_tokens=17, n=2),
+                 dict(temp=0, max_tokens=20, eos_ids=[eos])):
+        outs = []
+        for ahead in (False, True):
+            sess = _session(tiny_folders["A"], "A", 96)
+            sch = sess.scheduler
+            if ahead:
+                sch.device_sampling = sch.run_ahead = True
+                sch._host_ring = [torch.empty(8, dtype=torch.int32) for _ in range(4)]
+            outs.append(sess.generate(prompts, **opts))
+            assert (sch.stats["steps_ahead"] > 5) == ahead
+            sess.engine.cache.check()
+            assert sess.engine.cache.pages_in_use() == 0 and sess.engine.slots.free_count == 4
+        flat = [[[(c.tokens, c.stop) for c in comps] for comps in o] for o in outs]
+        assert flat[0] == flat[1]
+    assert any(c.stop == "eos" for comps in outs[1] for c in comps)
