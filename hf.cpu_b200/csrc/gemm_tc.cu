@@ -8,6 +8,7 @@
 //   * few tokens (decode): X = weights, Y = activations (tile 128 features x BN tokens, "swapped"),
 //     so that the tensor core's 128 rows are filled by the weight matrix that has to be streamed
 //     from HBM anyway, with split-K when there are fewer weight tiles than SMs.
+// Above 128 tokens the inner dimension is split as well when the output has few tiles and K is long (mid_splits).
 // Pipeline per CTA (persistent over work items): warp 0 issues TMA loads of 128-byte-swizzled K
 // blocks into a ring of shared-memory stages; warp 1 issues tcgen05.mma from shared memory into one
 // of two TMEM accumulators and commits to the stage's "empty" barrier; warps 2..5 read a finished
@@ -429,15 +430,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     pdl_sync();
 
     const int pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
-    const int total_items = p.tiles_x * p.tiles_y;           // tiles_x counts tiles of 256 tokens here
+    const int per_split = p.tiles_x * p.tiles_y;             // tiles_x counts tiles of 256 tokens here
+    const int total_items = per_split * p.splits;
 
     if (warp == 0) {
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
             for (int item = pair; item < total_items && ok; item += pairs) {
-                const int tx = item % p.tiles_x, ty = item / p.tiles_x;
-                for (int kb = 0; kb < p.kb_total; kb++, it++) {
+                const int split = item / per_split, t = item % per_split;
+                const int tx = t % p.tiles_x, ty = t / p.tiles_x;
+                const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
@@ -461,7 +465,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 if (!mbar_wait(tempty0 + 8 * a, aph ^ 1, abort_flag, err)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + a * BN;
-                for (int kb = 0; kb < p.kb_total; kb++, it++) {
+                const int split = item / per_split;
+                const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(full0 + 8 * s, ph, abort_flag, err)) { ok = false; break; }
@@ -469,7 +475,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     const uint64_t dx = smem_desc(sx + s * X_BYTES), dy = smem_desc(sy + s * Y_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++)
-                        tc_mma_bf16_pair(d, dx + 2 * k, dy + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        tc_mma_bf16_pair(d, dx + 2 * k, dy + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     tc_commit_pair(empty0 + 8 * s);
                     last_s = s;
                     last_ph = ph;
@@ -484,7 +490,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         uint32_t tile_it = 0;
         bool ok = true;
         for (int item = pair; item < total_items && ok; item += pairs, tile_it++) {
-            const int tx = item % p.tiles_x, ty = item / p.tiles_x;
+            const int split = item / per_split, t = item % per_split;
+            const int tx = t % p.tiles_x, ty = t / p.tiles_x;
             const int a = tile_it & 1;
             const uint32_t aph = (tile_it >> 1) & 1;
             if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag, err)) { ok = false; break; }
@@ -498,8 +505,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 tmem_ld16(taddr + c0, v);
                 if (two) tmem_ld16(taddr + c0 + 16, v + 16);
                 tmem_wait_ld();
-                epilogue_chunk(p, v, xr, ty * BN + c0, 0, lane);
-                if (two) epilogue_chunk(p, v + 16, xr, ty * BN + c0 + 16, 0, lane);
+                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane);
+                if (two) epilogue_chunk(p, v + 16, xr, ty * BN + c0 + 16, split, lane);
             }
             tc_fence_before();
             __syncwarp();
@@ -649,7 +656,7 @@ static int launch_pair(const CUtensorMap &mx, const CUtensorMap &my, const GemmP
         if (e != cudaSuccess) return fail(HFB_ECUDA, "gemm_tc: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    const int items = p.tiles_x * p.tiles_y, pairs_cap = sm_count() / 2;
+    const int items = p.tiles_x * p.tiles_y * p.splits, pairs_cap = sm_count() / 2;
     const int pairs = items < pairs_cap ? items : pairs_cap;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
@@ -678,8 +685,38 @@ static int launch_pair(const CUtensorMap &mx, const CUtensorMap &my, const GemmP
 
 using namespace hfb;
 
-// Common set-up of the product's tiling: fills p (sizes, tiles, maps) for `bn`; no split.
-static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb::GemmParams &p, int &bn, CUtensorMap &mx, CUtensorMap &my)
+static int pair_min_tokens() { static const int v = hfb::env_int("HFB_GEMM_PAIR", 256); return v; }     // 0: never
+static bool takes_pairs(int M) { return pair_min_tokens() > 0 && M >= pair_min_tokens() && hfb::sm_count() >= 2; }
+
+// More than 128 tokens with so few output tiles that most SMs would stand idle or wait for a few (a product with
+// few output features and a long inner dimension, at a few hundred tokens): how many ways to split the inner
+// dimension.  The cost of a choice is counted in K blocks: the rounds the busiest SM (or pair) makes over its work
+// items of 128 (or 256) tokens x 256 features, times the blocks of a slice, plus the pass over the partial sums.
+// 1: no split.
+static int mid_splits(int M, int N, int K)
+{
+    using namespace hfb;
+    static const int on = env_int("HFB_GEMM_MID_SPLIT", 1);
+    if (!on || M <= 128) return 1;
+    const bool pair = takes_pairs(M);
+    const int rows = pair ? 2 * TILE_X : TILE_X, units = pair ? sm_count() / 2 : sm_count();
+    const long items = (long)((M + rows - 1) / rows) * ((N + 255) / 256);
+    const int kb = (K + BK - 1) / BK;
+    const int per_item = 6;                             // filling the pipeline and draining the accumulator
+    long best = (items + units - 1) / units * (kb + per_item);
+    int best_s = 1;
+    for (int s = 2; s <= 8 && kb / s >= 32; s++) {     // shorter slices do not pay for the pass over the partial sums (measured)
+        const long slice = (kb + s - 1) / s;
+        const long cost = (items * s + units - 1) / units * (slice + per_item) + 4 + (long)s * M * N / 100000;
+        if (cost < best) { best = cost; best_s = s; }
+    }
+    return best_s;
+}
+
+// Common set-up of the product's tiling: fills p (sizes, tiles, maps) for `bn`.  `splits` > 1 (more than 128 tokens
+// only; see mid_splits) asks for that many slices of the inner dimension; the caller then sets the partial-sum mode.
+static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb::GemmParams &p, int &bn, CUtensorMap &mx, CUtensorMap &my,
+                         int splits = 1)
 {
     using namespace hfb;
     p.M = M; p.N = N; p.K = K;
@@ -698,17 +735,21 @@ static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb:
     } else {
         // the tile width that needs the fewest column-rounds over the SMs (every CTA walks its tiles in turn);
         // from 256 tokens on, tiles of 256 tokens on pairs of SMs
-        static const int pair_min = env_int("HFB_GEMM_PAIR", 256);            // 0: never
-        p.pair = pair_min > 0 && M >= pair_min && sm_count() >= 2;
+        p.pair = takes_pairs(M);
         const int rows = p.pair ? 2 * TILE_X : TILE_X, units = p.pair ? sm_count() / 2 : sm_count();
         p.tiles_x = (M + rows - 1) / rows;
-        const int widths[6] = {256, 240, 224, 208, 192, 128};
-        long best = -1;
         bn = 256;
-        for (int i = 0; i < 6; i++) {
-            long tiles = (long)p.tiles_x * ((N + widths[i] - 1) / widths[i]);
-            long cost = (tiles + units - 1) / units * widths[i];
-            if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
+        if (splits > 1) {
+            p.kb_per_split = (p.kb_total + splits - 1) / splits;
+            p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+        } else {
+            const int widths[6] = {256, 240, 224, 208, 192, 128};
+            long best = -1;
+            for (int i = 0; i < 6; i++) {
+                long tiles = (long)p.tiles_x * ((N + widths[i] - 1) / widths[i]);
+                long cost = (tiles + units - 1) / units * widths[i];
+                if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
+            }
         }
         p.tiles_y = (N + bn - 1) / bn;
         if ((rc = tensor_map(a, M, K, TILE_X, &mx)) != HFB_OK) return rc;
@@ -752,15 +793,23 @@ static int check_tc_args(const char *who, const void *a, const void *w, const vo
     return HFB_OK;
 }
 
-// Bytes of float32 workspace hfb_linear_tc may use for split-K partials with these sizes (0: none needed).
-extern "C" size_t hfb_linear_tc_workspace(int M, int N, int K)
+// Split-K partial sums of the few-token form (weights on the accumulator rows): bytes, 0 when there is no split.
+static size_t swapped_split_bytes(int M, int N, int K)
 {
-    if (M > 128) return 0;
+    using namespace hfb;
     int tiles = (N + TILE_X - 1) / TILE_X, kb = (K + BK - 1) / BK;
     int cap = sm_count() * env_int("HFB_CTAS_PER_SM", 1);
     int splits = tiles >= cap ? 1 : cap / tiles;                    // at most one work item per CTA slot
     if (splits > kb / 4) splits = kb / 4 > 0 ? kb / 4 : 1;
     if (splits > 16) splits = 16;
+    return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
+}
+
+// Bytes of float32 workspace hfb_linear_tc may use for split-K partials with these sizes (0: none needed).
+extern "C" size_t hfb_linear_tc_workspace(int M, int N, int K)
+{
+    if (M <= 128) return swapped_split_bytes(M, N, K);
+    const int splits = mid_splits(M, N, K);
     return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
 }
 
@@ -776,12 +825,14 @@ extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int
     GemmParams p{};
     CUtensorMap mx, my;
     int bn;
-    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
+    const size_t need = hfb_linear_tc_workspace(M, N, K);
+    const bool split_ok = need && workspace && workspace_bytes >= need;
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my, (M > 128 && split_ok) ? mid_splits(M, N, K) : 1)) != HFB_OK) return rc;
     p.out = out; p.out_dt = out_dt; p.bias = bias; p.bias_dt = bias_dt;
     p.mode = accumulate ? EPI_ADD : EPI_STORE;
+    if (!p.swapped && p.splits > 1) { p.partial = (float *)workspace; p.mode = EPI_PARTIAL; }
     if (p.swapped) {
-        size_t need = hfb_linear_tc_workspace(M, N, K);
-        if (need && workspace && workspace_bytes >= need) {
+        if (split_ok) {
             int splits = (int)(need / ((size_t)M * N * sizeof(float)));
             p.kb_per_split = (p.kb_total + splits - 1) / splits;
             p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
@@ -816,10 +867,12 @@ extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int
 }
 
 // Only the split-K partial sums: partial[s, M, N] float32 for s < *splits, in `workspace`
-// (hfb_linear_tc_partials_workspace bytes).  M <= 128.  A fused reduction kernel finishes the product.
+// (hfb_linear_tc_partials_workspace bytes; above 128 rows that is 0 for a product that is not split, which this
+// entry then refuses).  A fused reduction kernel finishes the product.
 extern "C" size_t hfb_linear_tc_partials_workspace(int M, int N, int K)
 {
     size_t need = hfb_linear_tc_workspace(M, N, K);
+    if (M > 128) return need;                        // 0: this product is not split, there are no partial sums to be had
     return need ? need : (size_t)M * N * sizeof(float);
 }
 
@@ -827,7 +880,7 @@ extern "C" int hfb_linear_tc_partials(const void *a, const void *w, int M, int N
                                       size_t workspace_bytes, int *splits, hfb_stream s)
 {
     if (M <= 0 || N <= 0) { *splits = 0; return HFB_OK; }
-    if (M > 128) return fail(HFB_ENOTSUP, "linear_tc_partials: at most 128 rows");
+    if (M > 128 && mid_splits(M, N, K) < 2) return fail(HFB_ENOTSUP, "linear_tc_partials: M=%d N=%d K=%d is not split (its workspace size is 0)", M, N, K);
     int rc = check_tc_args("linear_tc_partials", a, w, workspace, M, N, K);
     if (rc != HFB_OK) return rc;
     size_t need = hfb_linear_tc_partials_workspace(M, N, K);
@@ -835,10 +888,12 @@ extern "C" int hfb_linear_tc_partials(const void *a, const void *w, int M, int N
     GemmParams p{};
     CUtensorMap mx, my;
     int bn;
-    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
-    int want = (int)(need / ((size_t)M * N * sizeof(float)));
-    p.kb_per_split = (p.kb_total + want - 1) / want;
-    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my, mid_splits(M, N, K))) != HFB_OK) return rc;
+    if (p.swapped) {
+        int want = (int)(need / ((size_t)M * N * sizeof(float)));
+        p.kb_per_split = (p.kb_total + want - 1) / want;
+        p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    }
     p.partial = (float *)workspace;
     p.mode = EPI_PARTIAL;
     *splits = p.splits;
@@ -898,7 +953,7 @@ extern "C" int hfb_linear_tc_noalloc(const void *a, const void *w, const void *b
         return fail(HFB_ENOTSUP, "linear_tc_noalloc: operands must be 16-byte aligned");
     if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "linear_tc_noalloc: bad element types");
     if (accumulate && out_dt != HFB_F32) return fail(HFB_EINVAL, "linear_tc_noalloc: accumulation needs a float32 output");
-    size_t need = hfb_linear_tc_workspace(M, N, K);
+    size_t need = M <= 128 ? swapped_split_bytes(M, N, K) : 0;
     if (need > HFB_NOALLOC_SCRATCH_BYTES)
         return fail(HFB_ERANGE, "linear_tc_noalloc: split-K partial sums for M=%d N=%d K=%d take %zu bytes, the built-in "
                                 "array holds %u; use hfb_linear_tc with a workspace of your own", M, N, K, need,

@@ -39,9 +39,10 @@ int hfb_linear_plain(const void *a, int a_dt, const void *w, int w_dt, const voi
                      void *out, int out_dt, int accumulate, int M, int N, int K, hfb_stream s);
 
 /* The same product for bfloat16 a and w on the tensor cores (tcgen05, TMA, TMEM).  K must be a multiple of 8
- * and the operands 16-byte aligned, else HFB_ENOTSUP.  With few rows (M <= 128) the kernel may split K over
- * more CTAs and sum float32 partials kept in `workspace`; hfb_linear_tc_workspace gives the bytes that takes
- * (0 = none); with a smaller or null workspace it runs unsplit. */
+ * and the operands 16-byte aligned, else HFB_ENOTSUP.  Where there are fewer output tiles than SMs (few rows; or a
+ * few hundred rows, few output features and a long K) the kernel may split K over more CTAs and sum float32
+ * partials kept in `workspace`; hfb_linear_tc_workspace gives the bytes that takes (0 = none); with a smaller or
+ * null workspace it runs unsplit. */
 size_t hfb_linear_tc_workspace(int M, int N, int K);
 int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
                   int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s);
@@ -55,8 +56,9 @@ int hfb_linear_mma(const void *a, const void *w, const void *bias, int bias_dt, 
 /* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
 int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
 
-/* Only the split-K partial sums partial[*splits, M, N] (float32) of a product with M <= 128 rows, for a fused
- * reduction to finish; `workspace` must hold hfb_linear_tc_partials_workspace bytes. */
+/* Only the split-K partial sums partial[*splits, M, N] (float32) of a product, for a fused reduction to finish;
+ * `workspace` must hold hfb_linear_tc_partials_workspace bytes.  Above 128 rows that size is 0 for a product that
+ * would not be split, and this entry refuses it (HFB_ENOTSUP). */
 size_t hfb_linear_tc_partials_workspace(int M, int N, int K);
 int hfb_linear_tc_partials(const void *a, const void *w, int M, int N, int K, void *workspace, size_t workspace_bytes,
                            int *splits, hfb_stream s);

@@ -233,7 +233,7 @@ class NativeBackend:
 
     def _workspace(self, device):
         if self._ws is None or self._ws.device != device:
-            self._ws = torch.empty(16 << 20, dtype=torch.uint8, device=device)     # split-K partials never need more
+            self._ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)     # split-K partials never need more
         return self._ws
 
     def _partials(self, a, w):
@@ -242,7 +242,7 @@ class NativeBackend:
         N = w.shape[0]
         ws = self._workspace(a.device)
         need = self.lib.hfb_linear_tc_partials_workspace(c_int(M), c_int(N), c_int(K))
-        if need > ws.numel():
+        if need == 0 or need > ws.numel():                      # 0: above 128 rows, and not a product that is split
             return None
         splits = c_int(0)
         self._check(self.lib.hfb_linear_tc_partials(_p(a), _p(w), c_int(M), c_int(N), c_int(K), _p(ws),
@@ -276,7 +276,7 @@ class NativeBackend:
         M, K = a.shape
         N = w.shape[0]
         small = M <= self.gemv_max and self._tc_ok(a, w)
-        part = self._partials(a, w) if (M <= 128 and not small and self._tc_ok(a, w)) else None
+        part = self._partials(a, w) if (not small and self._tc_ok(a, w)) else None
         if part is None:
             self.linear(a, w, bias, residual, True)
             if xn_out is not None:
@@ -292,7 +292,7 @@ class NativeBackend:
         self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
         M, K = a.shape
         small = M <= self.gemv_max and self._tc_ok(a, w)
-        part = self._partials(a, w) if (M <= 128 and not small and self._tc_ok(a, w)) else None
+        part = self._partials(a, w) if (not small and self._tc_ok(a, w)) else None
         if part is None:
             self.linear(a, w, bias, qkv_buf, False)
             self.rope_kv_write(qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d)

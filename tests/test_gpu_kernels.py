@@ -234,7 +234,9 @@ TC_SHAPES = [(1, 128, 64), (1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (
              (64, 3584, 2048), (100, 1000, 200), (128, 512, 512), (129, 256, 64), (130, 1000, 192), (300, 777 * 8, 136),
              (2048, 1024, 512), (1000, 4608, 3584), (5, 152064, 256),
              # from 256 rows on, pairs of CTAs share tiles of 256 rows (cta_group::2): edges of the pair's halves
-             (256, 96, 64), (257, 136, 192), (384, 1000, 72), (511, 3000, 320), (1024, 208, 128), (640, 37888 // 8, 256)]
+             (256, 96, 64), (257, 136, 192), (384, 1000, 72), (511, 3000, 320), (1024, 208, 128), (640, 37888 // 8, 256),
+             # a few hundred rows, few output tiles and a long inner dimension: split over K (one CTA, and pairs; ragged K)
+             (192, 512, 4096), (300, 256, 4168), (384, 520, 1096), (512, 3584, 18944)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
@@ -363,7 +365,7 @@ def test_linear_swiglu_fused(shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 3584, 3584), (8, 3584, 18944), (8, 192, 320), (64, 3584, 512), (128, 1000, 64),
-                                   (200, 512, 256), (5, 64, 44)])
+                                   (200, 512, 256), (5, 64, 44), (200, 512, 4096), (512, 200, 4104), (320, 1000, 1032)])
 @pytest.mark.parametrize("with_norm", [True, False])
 def test_linear_residual_norm_fused(shape, with_norm):
     M, N, K = shape
@@ -379,12 +381,13 @@ def test_linear_residual_norm_fused(shape, with_norm):
         assert rel(xn, res_ref * r * nw.double()) < 1e-2
 
 
-@pytest.mark.parametrize("geom", [(28, 4, 128, 3584, 8), (6, 3, 32, 192, 5), (4, 2, 16, 64, 1), (8, 8, 64, 512, 130), (5, 1, 48, 100, 3)])
+@pytest.mark.parametrize("geom", [(28, 4, 128, 3584, 8), (6, 3, 32, 192, 5), (4, 2, 16, 64, 1), (8, 8, 64, 512, 130), (5, 1, 48, 100, 3),
+                                  (28, 4, 128, 3584, 512), (4, 2, 64, 4096, 200)])
 def test_linear_rope_kv_fused(geom):
     H, G, d, K, T = geom
     N = (H + 2 * G) * d
     a, w, bias = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N, dtype=torch.bfloat16)
-    pages, bs, P = 40, 4, 64
+    pages, bs, P = max(40, T // 4 + 8), 4, 64
     ang = torch.rand(P, d // 2, device=DEV, dtype=torch.float64) * 6
     cos_sin = torch.stack([ang.cos(), ang.sin()], -1).float().contiguous()
     positions = torch.randint(0, P, (T,), device=DEV, dtype=torch.int32)
