@@ -68,12 +68,16 @@ class Session:
     def generate(self, prompt_ids: Union[Sequence[int], Sequence[Sequence[int]]], *, temp: float = 0.8,
                  top_k: int = 40, top_p: float = 0.95, min_p: float = 0.05, seed: int = 0, max_tokens: int = 512,
                  n: int = 1, logprobs: int = 0, timeout: float = 0.0, eos_ids: Optional[Sequence[int]] = None,
-                 on_event: Optional[Callable] = None) -> Union[List[Completion], List[List[Completion]]]:
+                 on_event: Optional[Callable] = None, keep_cache: bool = False,
+                 prefix_cache: bool = True) -> Union[List[Completion], List[List[Completion]]]:
         """Generate ``n`` completions for one prompt (a list of ids) or for each of several prompts.
 
         Returns a list of ``n`` completions for one prompt, or one such list per prompt.  All run together
-        through the scheduler.  ``on_event`` sees every TokenEvent / FinishEvent as it happens; event request
-        ids are ``(serial, prompt index, sequence index)``."""
+        through the scheduler; requests with the same first tokens share the cache pages of those tokens.
+        ``keep_cache`` keeps the pages of the last prompt's first completion after it has ended, so that the next
+        call can start on them where its first tokens are the same (a conversation's next turn), which
+        ``prefix_cache=False`` forbids.  ``on_event`` sees every TokenEvent / FinishEvent as it happens; event
+        request ids are ``(serial, prompt index, sequence index)``."""
         single = len(prompt_ids) > 0 and not isinstance(prompt_ids[0], (list, tuple))
         prompts = [list(prompt_ids)] if single else [list(p) for p in prompt_ids]
         eos = list(eos_ids) if eos_ids is not None else self.eos_ids
@@ -85,7 +89,8 @@ class Session:
                 results[rid] = Completion()
                 params = SamplingParams(temp=temp, top_k=top_k, top_p=top_p, min_p=min_p, seed=seed + si,
                                         max_tokens=max_tokens, logprobs=logprobs)
-                self.scheduler.submit(Request(rid, prompt, params, eos_ids=eos, timeout=timeout))
+                self.scheduler.submit(Request(rid, prompt, params, eos_ids=eos, timeout=timeout, reuse_cache=prefix_cache,
+                                              keep_cache=keep_cache and si == 0 and pi == len(prompts) - 1))
 
         def handle(ev):
             c = results[ev.req]

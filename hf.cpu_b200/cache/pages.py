@@ -7,6 +7,13 @@ addresses the same slot in every layer of a *group*; groups exist because layers
 different things of the cache (all keys, or a window of them), and each group has its own pool
 and its own block table per request.  Pages go back to the pool when a request ends and, in a
 windowed group, as soon as the window has passed them; the pool hands them out again.
+
+A request may start on the full pages of another whose first tokens are the same (``fork``): the reference
+shares full blocks read-only between a context and its forks and copies the partial one (src/model.c:268-301),
+for the continuations of one prompt (src/ops.c:808-825) and for a prompt that begins like the previous one
+(src/ops.c:771-776).  Here a shared page is held once per block table that maps it (the pool counts the holders),
+nobody writes to it again because every holder only appends behind it, and the partial block is not copied but
+computed again by the new request, which has to run its last prompt token in any case.
 """
 from __future__ import annotations
 
@@ -203,6 +210,33 @@ class KVCacheManager:
                 t[b] = g.pool.alloc()
                 g.np_tables[req][b] = t[b]
 
+    def fork(self, src, dst, n_tokens: int) -> int:
+        """``dst`` (live, holding nothing yet) starts on the pages of ``src``'s first tokens: as many full blocks of
+        the first ``n_tokens`` as ``src`` has computed and, in a windowed group, still holds where a query behind
+        them would look.  Returns how many tokens ``dst`` now holds (a multiple of the block size, maybe 0)."""
+        if self.lengths[dst] != 0 or any(g.tables[dst] for g in self.groups):
+            raise ValueError(f"request {dst!r} already holds pages")
+        if src == dst:
+            raise ValueError("a request cannot start on its own pages")
+        n = min(int(n_tokens), self.lengths[src]) // self.block_size * self.block_size
+        nb = n // self.block_size
+        if nb == 0:
+            return 0
+        for g in self.groups:
+            t = g.tables[src]
+            if len(t) < nb or any(t[b] < 0 for b in range(g.first_needed_block(n), nb)):
+                return 0                   # a window has passed pages of src that a query at position n still sees
+        for g in self.groups:
+            ts, td, first = g.tables[src], g.tables[dst], g.first_needed_block(n)
+            for b in range(nb):
+                page = ts[b] if b >= first else -1
+                td.append(page)
+                if page >= 0:
+                    g.pool.share(page)
+                    g.np_tables[dst][b] = page
+        self.lengths[dst] = n
+        return n
+
     def advance(self, req, new_len: int) -> None:
         """The request now holds ``new_len`` tokens; pages a window has passed go back to the pool."""
         self.lengths[req] = new_len
@@ -227,11 +261,15 @@ class KVCacheManager:
         """No page lost, held twice or freed twice."""
         for g in self.groups:
             g.pool.check()
-            held = [p for t in g.tables.values() for p in t if p >= 0]
-            assert len(held) == len(set(held)), f"group {g.index}: a page is in two block tables"
-            assert len(held) == g.pool.used_count, \
-                f"group {g.index}: {g.pool.used_count} pages in use but {len(held)} in block tables"
-            for p in held:
-                assert g.pool.refcount(p) == 1
+            holders: Dict[int, int] = {}
+            for t in g.tables.values():
+                pages = [p for p in t if p >= 0]
+                assert len(pages) == len(set(pages)), f"group {g.index}: a page is in one block table twice"
+                for p in pages:
+                    holders[p] = holders.get(p, 0) + 1
+            assert len(holders) == g.pool.used_count, \
+                f"group {g.index}: {g.pool.used_count} pages in use but {len(holders)} in block tables"
+            for p, n in holders.items():
+                assert g.pool.refcount(p) == n, f"group {g.index}: page {p} is in {n} block tables, held {g.pool.refcount(p)} times"
             for req, t in g.tables.items():
                 assert g.np_tables[req][:len(t)].tolist() == t and (g.np_tables[req][len(t):] == -1).all()

@@ -143,7 +143,9 @@ class App:
                 p = SamplingParams(temp=eff["temp"], top_k=eff["top_k"], top_p=eff["top_p"], min_p=eff["min_p"],
                                    seed=(eff["seed"] + i) & ((1 << 64) - 1), max_tokens=eff["max_tokens"],
                                    logprobs=eff["logprobs"])
-                r = Request((serial, i), ids, p, eos_ids=sess.eos_ids, timeout=eff["timeout"])
+                # the cache of a request stays behind it, as the reference's one context does (src/ops.c:760-776)
+                r = Request((serial, i), ids, p, eos_ids=sess.eos_ids, timeout=eff["timeout"], keep_cache=i == 0,
+                            reuse_cache=eff["prefix_cache"])
                 sch.submit(r)
                 reqs.append(r)
         except RequestError as e:
@@ -169,8 +171,9 @@ class App:
                 events = sch.step()
             if t_prefill is None and all(r.computed >= len(r.prompt) or r.status == "finished" for r in reqs):
                 t_prefill = time.perf_counter() - t0
-                self.out.event("prefill", tokens=len(ids), cached=0, ms=f"{t_prefill * 1e3:.1f}",
-                               tok_per_s=f"{len(ids) * nseq / t_prefill if t_prefill > 0 else 0:.2f}",
+                cached = sum(r.shared for r in reqs)
+                self.out.event("prefill", tokens=len(ids), cached=reqs[0].shared, ms=f"{t_prefill * 1e3:.1f}",
+                               tok_per_s=f"{(len(ids) * nseq - cached) / t_prefill if t_prefill > 0 else 0:.2f}",
                                kv_bytes=sess.engine.cache.bytes_in_use())
                 if prof:
                     prof.emit(self.out, "prefill")

@@ -12,7 +12,12 @@ request here, for many requests at once:
   fit, the most recently admitted running request is preempted: its pages go back, it keeps the tokens
   it generated and its generator state, and it returns to the head of the waiting queue to be
   recomputed as prompt + generated tokens, so the tokens it samples do not change;
-* a request that cannot fit even alone fails with ENOMEM, and only that request.
+* a request that cannot fit even alone fails with ENOMEM, and only that request;
+* a request whose first tokens are those of a running request starts on that request's full cache pages and
+  computes only the rest (the reference forks the context of a prompt for its ``--n`` continuations,
+  src/ops.c:808-825); while the other is still computing the tokens they share, it waits for them.  With
+  ``keep_cache`` a finished request's pages are kept until the next request has had the chance to start on them
+  (``--prefix-cache``, src/ops.c:771-776); they are the first to go when pages or slots are short.
 
 While every running request decodes and none is about to reach its limit, ``run`` keeps one step ahead of
 the host: the next step is launched with the token ids the sampling kernel has just written on the device,
@@ -67,6 +72,9 @@ class Request:
     t_first: float = 0.0
     t_done: float = 0.0
     logprobs: List = field(default_factory=list)
+    keep_cache: bool = False           # when it ends, its pages stay until the next request could start on them
+    reuse_cache: bool = True           # it may start on pages kept of a finished request
+    shared: int = 0                    # tokens it did not compute: it started on another request's pages
 
     def tokens(self) -> List[int]:
         return self.prompt + self.generated
@@ -123,7 +131,7 @@ class StepPlan:
 
 class Scheduler:
     def __init__(self, engine: Engine, max_num_seqs: int = 0, max_num_batched_tokens: int = 2048,
-                 prefill_chunk: int = 0, device_sampling: bool = True):
+                 prefill_chunk: int = 0, device_sampling: bool = True, share_prefixes: bool = True):
         self.engine = engine
         self.max_num_seqs = min(max_num_seqs or engine.max_requests, engine.max_requests)
         self.max_num_batched_tokens = int(max_num_batched_tokens)
@@ -134,7 +142,9 @@ class Scheduler:
         self.requests: Dict[Hashable, Request] = {}
         self._arrivals = 0
         self.stats = {"steps": 0, "preemptions": 0, "tokens_in": 0, "tokens_out": 0, "finished": 0, "errors": 0,
-                      "steps_ahead": 0}
+                      "steps_ahead": 0, "tokens_shared": 0}
+        self.share_prefixes = share_prefixes
+        self.retained: Optional[Request] = None          # a finished request whose pages are kept (keep_cache)
         self.cancelled = set()
         self.run_ahead = self.device_sampling            # run() launches steady decode steps one ahead of the host
         self._host_ring = None                           # pinned buffers the sampled ids are copied into
@@ -146,6 +156,8 @@ class Scheduler:
         (src/ops.c:752-756); ``max_tokens`` is clipped to the room left, stop reason ``ctx`` (src/ops.c:757-758)."""
         if req.id in self.requests and self.requests[req.id].status != FINISHED:
             raise RequestError("EINVAL", f"request id {req.id!r} is already in use")
+        if self.retained is not None and self.retained.id == req.id:
+            self.drop_retained()
         req.params.validate()
         V = self.engine.model.plan.vocab_size
         if len(req.prompt) == 0:
@@ -174,7 +186,7 @@ class Scheduler:
     def _preempt(self, req: Request) -> None:
         self.engine.finish_request(req.id)
         self.running.remove(req)
-        req.status, req.computed = WAITING, 0
+        req.status, req.computed, req.shared = WAITING, 0, 0
         req.preemptions += 1
         self.stats["preemptions"] += 1
         self.waiting.appendleft(req)
@@ -192,6 +204,8 @@ class Scheduler:
             chosen, admitted = self._choose(preempted, failed)
             if chosen or not self.running:
                 break
+            if self.drop_retained():
+                continue
             # running requests exist but nothing can move: every page is held by requests that all need more
             victim = max(self.running, key=lambda r: r.arrival)
             if len(self.running) == 1:
@@ -214,6 +228,8 @@ class Scheduler:
         # 1. decodes: one token for every running request with a single pending token
         decodes = [r for r in self.running if r.pending == 1 and r.computed > 0]
         while decodes and not cache.can_reserve([(r.id, r.computed + 1) for r in decodes]):
+            if self.drop_retained():
+                continue
             victim = max(self.running, key=lambda r: r.arrival)
             if len(self.running) == 1:
                 # alone and still short of pages: the pool cannot hold this request at all
@@ -256,33 +272,99 @@ class Scheduler:
                 budget -= n
         # 3. admit waiting requests, first come first served
         admitted: List[Request] = []
-        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs \
-                and self.engine.slots.free_count > 0:
+        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
+            if self.engine.slots.free_count == 0 and not self.drop_retained():
+                break
             r = self.waiting[0]
             if r in preempted:
                 break                      # do not bring back in the same step what was just put out
+            donor, share, later = self._donor(r)
+            if later > share:
+                break                      # a running request is still computing tokens this one can start on
+            self.engine.add_request(r.id)
+            if share:
+                share = self.engine.fork_request(donor.id, r.id, share)
+            r.computed = r.shared = share
             n = fit_portion(r)
             if n == 0:
+                self.engine.finish_request(r.id)
+                r.computed = r.shared = 0
+                if self.drop_retained():
+                    continue
                 if not self.running and not chosen:
                     # nothing else holds pages and not even one token fits
                     failed.append(self.waiting.popleft())
                     continue
                 break
             self.waiting.popleft()
-            self.engine.add_request(r.id)
+            if self.retained is not None:
+                self.drop_retained()       # the request it was kept for has started, on it or not
+            self.stats["tokens_shared"] += share
             r.status = RUNNING
             self.running.append(r)
             admitted.append(r)
             chosen.append((r, n))
-            wants.append((r.id, n))
+            wants.append((r.id, r.computed + n))
             budget -= n
         return chosen, admitted
+
+    # ---- starting on another request's pages ------------------------------------------------------------
+    @staticmethod
+    def _common(a: List[int], b: List[int], limit: int) -> int:
+        """How many of the first ``limit`` tokens of a and b are the same."""
+        limit = min(limit, len(a), len(b))
+        n = 0
+        while n < limit:                   # whole slices first (compared at C speed), then the slice that differs
+            m = min(n + 512, limit)
+            if a[n:m] == b[n:m]:
+                n = m
+                continue
+            while a[n] == b[n]:
+                n += 1
+            break
+        return n
+
+    def _donor(self, r: Request):
+        """The request whose cache ``r`` can best start on: (donor, tokens shareable now, tokens shareable once
+        a running donor has computed what it has in common with r).  Whole blocks only, and never r's last
+        token: r has to run that one itself to have its logits."""
+        if not self.share_prefixes or r.computed or not self.engine.can_fork:
+            return None, 0, 0
+        bs = self.engine.block_size
+        mine = r.tokens()
+        cap = (len(mine) - 1) // bs * bs
+        if cap <= 0:
+            return None, 0, 0
+        best, best_now, best_later = None, 0, 0
+        for d in self.running + ([self.retained] if self.retained is not None and r.reuse_cache else []):
+            if d is r or not self.engine.has_request(d.id):
+                continue
+            theirs = d.tokens()
+            same = min(self._common(mine, theirs, cap), cap) // bs * bs
+            now = min(same, d.computed // bs * bs)
+            if now > best_now:
+                best, best_now = d, now
+            if d is not self.retained:
+                best_later = max(best_later, same)
+        return best, best_now, max(best_later, best_now)
+
+    def drop_retained(self) -> bool:
+        """Gives back the pages kept of a finished request; False when there were none."""
+        if self.retained is None:
+            return False
+        self.engine.finish_request(self.retained.id)
+        self.retained = None
+        return True
 
     # ---- running a step ---------------------------------------------------------------------------
     def _finish(self, r: Request, stop: str, events: list, error: Optional[str] = None) -> None:
         if r in self.running:
             self.running.remove(r)
-            self.engine.finish_request(r.id)
+            if r.keep_cache and self.share_prefixes and error is None and stop != "cancel":
+                self.drop_retained()
+                self.retained = r
+            else:
+                self.engine.finish_request(r.id)
         elif r in self.waiting:
             self.waiting.remove(r)
         r.status, r.stop, r.error, r.t_done = FINISHED, stop, error, time.perf_counter()

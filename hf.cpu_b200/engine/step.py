@@ -150,6 +150,18 @@ class Engine:
         self.cache.add(req)
         return slot
 
+    def fork_request(self, src: Hashable, dst: Hashable, n_tokens: int) -> int:
+        """``dst`` (just added) starts on the cache pages of ``src``'s first ``n_tokens`` tokens, which must be
+        the same tokens; returns how many tokens ``dst`` holds afterwards.  0 when some mixer keeps state of fixed
+        size per request: its state behind the shared tokens is not to be had from ``src``, which has moved on."""
+        if not self.can_fork:
+            return 0
+        return self.cache.fork(src, dst, n_tokens)
+
+    @property
+    def can_fork(self) -> bool:
+        return not self.slots.tensors
+
     def finish_request(self, req: Hashable) -> None:
         self.cache.release(req)
         self.slots.release(req)

@@ -117,6 +117,31 @@ def test_generate_events_and_errors(tiny_folders):
     assert r.stderr.decode().count("model loaded") == 1          # the model stays resident between requests
 
 
+def test_the_next_request_starts_on_the_previous_requests_cache(tiny_folders):
+    """--prefix-cache (on by default, src/opts.c:100): a prompt that begins like the previous request's tokens
+    reports them as cached (src/ops.c:771-776, :802) and generates what it generates without them."""
+    folder = tiny_folders["A"]
+    first = make_requests("A", [21], seed=6)["r0"]
+    cfg, W = plain.read_folder(folder)
+    said = plain.greedy(cfg, W, first, 4)
+    follow = first + said + make_requests("A", [6], seed=7)["r0"]
+    want = plain.greedy(cfg, W, follow, 3)
+    f, g = " ".join(map(str, first)), " ".join(map(str, follow))
+    common = ["--dtype", "fp32", "--kv-pages", "40", "--kv-block", "4", "--ctx-max", "256", "--model", folder]
+    for flag, cached in (("", (21 + 4 - 1) // 4 * 4), ("--no-prefix-cache", 0)):
+        script = (f"--op generate --prompt-ids '{f}' --temp 0 --max-tokens 4 --id a\n"
+                  f"--op generate --prompt-ids '{g}' --temp 0 --max-tokens 3 --id b {flag}\n").encode()
+        r = _run_cli(["--stdin-mode", "args", *common], script)
+        assert r.returncode == 0, r.stderr.decode()
+        lines = r.stdout.decode().splitlines()
+        prefills = [l for l in lines if l.startswith("@prefill")]
+        assert len(prefills) == 2, r.stdout.decode() + r.stderr.decode()
+        assert prefills[0].startswith("@prefill tokens=21 cached=0 ")
+        assert prefills[1].startswith(f"@prefill tokens={len(follow)} cached={cached} "), prefills[1]
+        toks = [int(l.split("id=")[1].split()[0]) for l in lines if l.startswith("@token")]
+        assert toks == said + want
+
+
 def test_startup_errors_exit_2():
     r = _run_cli(["--temp", "77"])
     assert r.returncode == 2 and b"--temp" in r.stderr

@@ -110,3 +110,46 @@ def test_running_ahead_of_the_host_changes_no_token(tiny_folders, dtype, name):
         s.engine.cache.check()
     assert [[(c.tokens, c.stop) for c in comps] for comps in outs[0]] == [[(c.tokens, c.stop) for c in comps] for comps in outs[1]]
     assert outs[0][1][0].stop == "eos" and eos not in outs[0][1][0].tokens
+
+
+@pytest.mark.parametrize("dtype,name", [("float32", "A"), ("float32", "B"), ("bfloat16", "A16"), ("bfloat16", "B16")])
+def test_continuations_share_the_prompts_pages(tiny_folders, dtype, name):
+    """Several completions of one prompt, and the next turn of a conversation: the tokens that are the same are
+    computed once; in 32-bit every completion samples what it samples when it computes everything itself."""
+    import hfcpu_b200
+    folder = tiny_folders[name]
+    name = name[:1]
+    bs = BLOCK[name]
+    prompt = make_requests(name, [150], seed=9)["r0"]
+    kw = dict(temp=0.8, top_k=20, seed=3, max_tokens=12, n=3)
+    outs = {}
+    for share in (True, False):
+        sess = hfcpu_b200.Session(folder, dtype=dtype, kv_block=bs, kv_pages=200, max_seqs=4, max_batched_tokens=64)
+        sess.scheduler.share_prefixes = share
+        outs[share] = [c.tokens for c in sess.generate(prompt, **kw)]
+        st = sess.scheduler.stats
+        assert st["tokens_shared"] == (2 * ((len(prompt) - 1) // bs * bs) if share else 0)
+        assert sess.engine.cache.pages_in_use() == 0
+        sess.engine.cache.check()
+    if dtype == "float32":
+        assert outs[True] == outs[False]
+    # greedy: the three completions of a shared prompt are one and the same
+    sess = hfcpu_b200.Session(folder, dtype=dtype, kv_block=bs, kv_pages=200, max_seqs=4, max_batched_tokens=64)
+    same = [c.tokens for c in sess.generate(prompt, temp=0, max_tokens=10, n=3)]
+    assert same[0] == same[1] == same[2]
+    # the next turn starts on the pages kept of this one
+    first = sess.generate(prompt, temp=0, max_tokens=10, keep_cache=True)[0].tokens
+    assert first == same[0] and sess.scheduler.retained is not None
+    follow = prompt + first + make_requests(name, [11], seed=10)["r0"]
+    turn = sess.generate(follow, temp=0, max_tokens=6)[0].tokens
+    rid = (sess._serial, 0, 0)
+    # (where layers keep a window of keys only, the finished request has let go of pages that a query at the
+    # start of the new tokens would still see: then nothing can be shared)
+    windowed = any(g.spec.window for g in sess.engine.cache.groups)
+    assert sess.scheduler.requests[rid].shared in ({0} if windowed else set()) | {(len(prompt) + len(first) - 1) // bs * bs}
+    assert sess.scheduler.retained is None and sess.engine.cache.pages_in_use() == 0
+    if dtype == "float32":
+        cfg, W = plain.read_folder(folder)
+        assert turn == plain.greedy(cfg, W, follow, 6)
+    from hfcpu_b200 import kernels
+    kernels.check_device_errors()

@@ -167,3 +167,89 @@ def test_running_ahead_of_the_host_on_the_stand_in(tiny_folders, emu, monkeypatc
         flat = [[[(c.tokens, c.stop) for c in comps] for comps in o] for o in outs]
         assert flat[0] == flat[1]
     assert any(c.stop == "eos" for comps in outs[1] for c in comps)
+
+
+def _drain(sch, check=True):
+    while sch.has_work():
+        sch.step()
+        if check:
+            sch.engine.cache.check()
+
+
+def test_continuations_of_one_prompt_start_on_its_pages(tiny_folders, emu):
+    """Requests with the same prompt: the first computes it, the others wait for it and start on its full pages;
+    what every one of them samples is what it samples without sharing."""
+    from hfcpu_b200.engine import Request
+    from hfcpu_b200 import SamplingParams
+    prompt = make_requests("A", [45], seed=5)["r0"]
+    bs = BLOCK["A"]
+    results = {}
+    for share in (False, True):
+        sess = _session(tiny_folders["A"], "A", 64, budget=16)
+        sch = sess.scheduler
+        sch.share_prefixes = share
+        for i in range(3):
+            sch.submit(Request(("n", i), prompt, SamplingParams(temp=0.9, top_k=8, seed=11 + i, max_tokens=6)))
+        _drain(sch)
+        results[share] = ([sch.requests[("n", i)].generated for i in range(3)], dict(sch.stats))
+        assert sess.engine.cache.pages_in_use() == 0
+    assert results[True][0] == results[False][0]
+    shared = (len(prompt) - 1) // bs * bs
+    assert results[True][1]["tokens_shared"] == 2 * shared and results[False][1]["tokens_shared"] == 0
+    assert results[False][1]["tokens_in"] - results[True][1]["tokens_in"] == 2 * shared
+
+
+def test_a_request_starts_on_a_running_request_with_the_same_first_tokens(tiny_folders, emu):
+    from hfcpu_b200.engine import Request
+    from hfcpu_b200 import SamplingParams
+    a = make_requests("B", [60], seed=7)["r0"]
+    b = a[:37] + make_requests("B", [20], seed=8)["r0"]            # the same first 37 tokens, then its own
+    bs = BLOCK["B"]
+    outs = {}
+    for share in (False, True):
+        sess = _session(tiny_folders["B"], "B", 200, budget=32)
+        sch = sess.scheduler
+        sch.share_prefixes = share
+        sch.submit(Request("a", a, SamplingParams(temp=0, max_tokens=12)))
+        sch.step(); sch.step(); sch.step()                         # a is decoding when b arrives
+        sch.submit(Request("b", b, SamplingParams(temp=0, max_tokens=5)))
+        _drain(sch)
+        outs[share] = (sch.requests["a"].generated, sch.requests["b"].generated, sch.requests["b"].shared)
+        assert sess.engine.cache.pages_in_use() == 0
+    assert outs[True][:2] == outs[False][:2]
+    assert outs[True][2] == 37 // bs * bs and outs[False][2] == 0
+
+
+def test_pages_kept_of_the_previous_request(tiny_folders, emu):
+    """keep_cache: the pages of a finished request stay until the next request has started, on them if its first
+    tokens are the same; they go at once when pages are short."""
+    from hfcpu_b200.engine import Request
+    from hfcpu_b200 import SamplingParams
+    bs = BLOCK["A"]
+    first = make_requests("A", [30], seed=3)["r0"]
+    sess = _session(tiny_folders["A"], "A", 64, budget=64)
+    sch = sess.scheduler
+    sch.submit(Request(1, first, SamplingParams(temp=0, max_tokens=10), keep_cache=True))
+    _drain(sch)
+    said = sch.requests[1].generated
+    assert sch.retained is sch.requests[1] and sess.engine.cache.pages_in_use() > 0
+    # the next turn: the whole exchange so far, and more
+    follow = first + said + make_requests("A", [9], seed=4)["r0"]
+    sch.submit(Request(2, follow, SamplingParams(temp=0, max_tokens=6)))
+    _drain(sch)
+    cached = (len(first) + len(said) - 1)                          # the last sampled token was never run
+    assert sch.requests[2].shared == min(cached, len(follow) - 1) // bs * bs > 0
+    assert sch.retained is None and sess.engine.cache.pages_in_use() == 0
+    fresh = _session(tiny_folders["A"], "A", 64, budget=64)
+    assert fresh.generate([follow], temp=0, max_tokens=6)[0][0].tokens == sch.requests[2].generated
+    # kept pages give way: a pool that cannot hold both
+    sess = _session(tiny_folders["A"], "A", (40 + bs - 1) // bs + 1, budget=64)
+    sch = sess.scheduler
+    sch.submit(Request(1, first, SamplingParams(temp=0, max_tokens=8), keep_cache=True))
+    _drain(sch)
+    assert sch.retained is not None
+    other = make_requests("A", [36], seed=9)["r0"]
+    sch.submit(Request(2, other, SamplingParams(temp=0, max_tokens=3)))
+    _drain(sch)
+    assert sch.requests[2].stop == "length" and sch.requests[2].shared == 0 and sch.retained is None
+    assert sess.engine.cache.pages_in_use() == 0
