@@ -32,6 +32,12 @@ __device__ __forceinline__ unsigned long long rank_key(float l, int id)
     return ((unsigned long long)u << 32) | (unsigned)(0xFFFFFFFFu - (unsigned)id);
 }
 
+__device__ __forceinline__ float key_logit(unsigned long long k)
+{
+    const unsigned u = (unsigned)(k >> 32);
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
+}
+
 struct Row {
     const float *l;
     int V;
@@ -117,6 +123,7 @@ struct Shared {
     unsigned long long result[2];
     float red[32];
     int n_cand;
+    int n_listed;
 };
 
 __device__ float block_sum(float v, float *red)
@@ -180,12 +187,18 @@ enum { BY_COUNT = 0, BY_MASS_GE = 1, BY_MASS_GT = 2 };
 // Finds the first candidate, in descending key order among those with key >= cut, at which the running
 // count reaches `target` (BY_COUNT) or the running mass p reaches / exceeds it.  Returns its key, or 0 when
 // the whole set stays below the target.
+//
+// Once a byte is fixed, the candidates that still match are usually few: while a CTA walks its slice for the next
+// byte it also lists the keys that match (in sh->cand, as long as they fit), and the bytes after that are read off
+// the list instead of the vocabulary.
 template <int MODE>
 __device__ unsigned long long descend(const Row &r, unsigned long long cut, float target, Shared *sh, unsigned &turn)
 {
     unsigned long long prefix = 0;          // the bytes fixed so far, in place
     float before = 0.f;                     // count or mass of candidates that rank above the current prefix
     bool found = true;
+    bool listed = false;                    // this CTA's candidates that match the prefix are in sh->cand[0 .. n_list)
+    int n_list = 0;
     for (int b = 7; b >= 0; b--) {
         if (b == 3) { prefix |= 0xFFull << 24; continue; }        // ids stay below 2^24: this byte is constant
         // Every warp has a histogram of its own (no two warps add to the same word) and every thread keeps the
@@ -194,14 +207,13 @@ __device__ unsigned long long descend(const Row &r, unsigned long long cut, floa
         // rank order.
         float *mine = sh->whist + (threadIdx.x >> 5) * 256;
         for (int i = threadIdx.x; i < 256 * (int)(blockDim.x >> 5); i += blockDim.x) sh->whist[i] = 0.f;
+        if (threadIdx.x == 0) sh->n_listed = 0;
         __syncthreads();
         int c_bin[4] = {-1, -1, -1, -1};
         float c_run[4] = {0.f, 0.f, 0.f, 0.f};
         int victim = 0;
-        unsigned long long hi_mask = b == 7 ? 0ull : (~0ull << (8 * (b + 1)));
-        scan_row(r, [&](int i, float logit) {
-            unsigned long long k = rank_key(logit, i);
-            if (k < cut || (k & hi_mask) != (prefix & hi_mask)) return;
+        const unsigned long long hi_mask = b == 7 ? 0ull : (~0ull << (8 * (b + 1)));
+        auto count_in = [&](unsigned long long k, float logit) {
             const int bin = (int)((k >> (8 * b)) & 0xFF);
             const float w = MODE == BY_COUNT ? 1.f : r.e_of(logit) / r.sum;
             if (bin == c_bin[0]) c_run[0] += w;
@@ -218,11 +230,29 @@ __device__ unsigned long long descend(const Row &r, unsigned long long cut, floa
                     }
                 victim = (victim + 1) & 3;
             }
-        });
+        };
+        if (listed) {
+            for (int i = threadIdx.x; i < n_list; i += blockDim.x) {
+                const unsigned long long k = sh->cand[i];
+                if ((k & hi_mask) == (prefix & hi_mask)) count_in(k, key_logit(k));
+            }
+        } else {
+            const bool list_them = b < 7;
+            scan_row(r, [&](int i, float logit) {
+                const unsigned long long k = rank_key(logit, i);
+                if (k < cut || (k & hi_mask) != (prefix & hi_mask)) return;
+                if (list_them && *(volatile int *)&sh->n_listed <= SMALL_K) {       // (no more additions once it is full)
+                    const int at = atomicAdd(&sh->n_listed, 1);
+                    if (at < SMALL_K) sh->cand[at] = k;
+                }
+                count_in(k, logit);
+            });
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++)
             if (c_bin[j] >= 0) atomicAdd(&mine[c_bin[j]], c_run[j]);
         __syncthreads();
+        if (!listed && b < 7 && sh->n_listed <= SMALL_K) { listed = true; n_list = sh->n_listed; }
         const unsigned t = turn++ & 1;
         for (int i = threadIdx.x; i < 256; i += blockDim.x) {
             float s = 0.f;
