@@ -69,4 +69,6 @@ def main(ref_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py PATH_OF_THE_HFCPU_SOURCE_TREE")
+    main(sys.argv[1])
