@@ -78,8 +78,13 @@ template <int BN, int STAGES> constexpr uint32_t gemm_smem_bytes()
 }
 
 // One chunk of 16 accumulator columns of one row: v[i] is element (xr, y0 + i) of X . Y^T.
-__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t *v, int xr, int y0, int split, int lane)
+// `live` false: the same instructions, nothing stored (the few-token form runs its epilogue once this way while the
+// first weights are on their way, so that its code is in the instruction cache when the first tile is done: fetched
+// at that moment it waits behind the weight stream, several microseconds for a 64-token tile).
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t *v, int xr, int y0, int split, int lane,
+                                               bool live = true)
 {
+    if (!live && !p.swapped) return;
     if (p.swapped && p.mode == EPI_SWIGLU) {
         // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2]
 #pragma unroll
@@ -87,7 +92,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
             float mine = __uint_as_float(v[i]);
             float other = __shfl_xor_sync(0xffffffffu, mine, 1);
             int tok = y0 + i;
-            if (!(lane & 1) && xr + 1 < p.N && tok < p.M)
+            if (live && !(lane & 1) && xr + 1 < p.N && tok < p.M)
                 store_any(p.out, p.out_dt, (size_t)tok * (p.N >> 1) + (xr >> 1), (mine / (1.0f + expf(-mine))) * other);
         }
     } else if (p.swapped) {
@@ -100,6 +105,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
                 if (tok >= p.M) break;
                 float val = __uint_as_float(v[i]) + b;
                 size_t o = (size_t)tok * p.N + xr;
+                if (!live) continue;
                 if (p.mode == EPI_PARTIAL) p.partial[(size_t)split * p.M * p.N + o] = val;
                 else if (p.mode == EPI_ADD) ((float *)p.out)[o] += val;
                 else store_any(p.out, p.out_dt, o, val);
@@ -299,18 +305,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else {
         // ---- epilogue: TMEM -> registers -> global ------------------------------------------------
-        pdl_sync();                                   // nothing is written before the kernel in front has finished
         const int q = warp & 3;                       // the TMEM lane quarter this warp may read
         const int row = q * 32 + lane;
         uint32_t tile_it = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, tile_it++) {
+        // With few tokens the first turn of this loop is a rehearsal: it reads whatever the accumulator holds and
+        // stores nothing, before the kernel in front is known to have finished (see epilogue_chunk).
+        bool rehearsal = p.swapped != 0;
+        if (!rehearsal) pdl_sync();                   // nothing is written before the kernel in front has finished
+        for (int item = blockIdx.x; item < total_items && ok;) {
             int split = item / per_split, t = item % per_split;
             int tx = t % p.tiles_x, ty = t / p.tiles_x;
             int a = tile_it & 1;
             uint32_t aph = (tile_it >> 1) & 1;
-            if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag, err)) { ok = false; break; }
-            tc_fence_after();
+            if (!rehearsal) {
+                if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag, err)) { ok = false; break; }
+                tc_fence_after();
+            }
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
             const int xr = tx * TILE_X + row;         // row of X this thread holds
 #pragma unroll 1
@@ -320,13 +331,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tmem_ld16(taddr + c0, v);
                 if (two) tmem_ld16(taddr + c0 + 16, v + (BN >= 32 ? 16 : 0));
                 tmem_wait_ld();
-                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane);
-                if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane);
+                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane, !rehearsal);
+                if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane, !rehearsal);
+            }
+            if (rehearsal) {
+                rehearsal = false;
+                pdl_sync();
+                continue;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * a);
+            item += gridDim.x;
+            tile_it++;
         }
+        if (rehearsal) pdl_sync();                    // (no work item at all)
     }
 
     // ---- teardown --------------------------------------------------------------------------------
