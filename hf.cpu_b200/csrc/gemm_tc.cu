@@ -86,29 +86,64 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
 {
     if (!live && !p.swapped) return;
     if (p.swapped && p.mode == EPI_SWIGLU) {
-        // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2]
+        // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2].  The two lanes
+        // of a pair exchange their values and share the work: of every two tokens the even lane finishes the first,
+        // the odd lane the second.
+        const int odd = lane & 1;
+        const int in_chunk = min(16, p.M - y0);                                  // the same for the whole warp
+        const int n_tok = (live && (xr | 1) < p.N) ? in_chunk : 0;
+        const size_t half_n = (size_t)(p.N >> 1), at = (size_t)y0 * half_n + (size_t)(xr >> 1);
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            float mine = __uint_as_float(v[i]);
-            float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-            int tok = y0 + i;
-            if (live && !(lane & 1) && xr + 1 < p.N && tok < p.M)
-                store_any(p.out, p.out_dt, (size_t)tok * (p.N >> 1) + (xr >> 1), (mine / (1.0f + expf(-mine))) * other);
+        for (int j = 0; j < 8; j++) {
+            if (2 * j >= in_chunk) break;
+            const float first = __uint_as_float(v[2 * j]), second = __uint_as_float(v[2 * j + 1]);
+            const float their_first = __shfl_xor_sync(0xffffffffu, first, 1);
+            const float their_second = __shfl_xor_sync(0xffffffffu, second, 1);
+            const float g = odd ? their_second : first, u = odd ? second : their_first;
+            const float h = (g / (1.0f + expf(-g))) * u;
+            const int i = 2 * j + odd;
+            if (i < n_tok) {
+                if (p.out_dt == HFB_BF16) ((__nv_bfloat16 *)p.out)[at + (size_t)i * half_n] = __float2bfloat16_rn(h);
+                else ((float *)p.out)[at + (size_t)i * half_n] = h;
+            }
         }
     } else if (p.swapped) {
-        // xr = output feature, y = token
+        // xr = output feature, y = token.  One warp per scheduler runs this, so the work per token is kept to a
+        // handful of instructions: the mode is decided outside the loops, the address is a base plus i rows.
         if (xr < p.N) {
-            float b = (p.bias && p.mode != EPI_PARTIAL) ? load_any(p.bias, p.bias_dt, xr) : 0.f;
+            const int n_tok = live ? min(16, p.M - y0) : 0;
+            const size_t at = (size_t)y0 * p.N + xr;
+            if (p.mode == EPI_PARTIAL) {
+                float *dst = p.partial + (size_t)split * p.M * p.N + at;
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
-                int tok = y0 + i;
-                if (tok >= p.M) break;
-                float val = __uint_as_float(v[i]) + b;
-                size_t o = (size_t)tok * p.N + xr;
-                if (!live) continue;
-                if (p.mode == EPI_PARTIAL) p.partial[(size_t)split * p.M * p.N + o] = val;
-                else if (p.mode == EPI_ADD) ((float *)p.out)[o] += val;
-                else store_any(p.out, p.out_dt, o, val);
+                for (int i = 0; i < 16; i++) {
+                    if (i >= n_tok) break;               // (the same for the whole warp: with one token, one turn)
+                    dst[(size_t)i * p.N] = __uint_as_float(v[i]);
+                }
+            } else {
+                const float b = p.bias ? load_any(p.bias, p.bias_dt, xr) : 0.f;
+                if (p.mode == EPI_ADD) {
+                    float *dst = (float *)p.out + at;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        if (i >= n_tok) break;
+                        dst[(size_t)i * p.N] += __uint_as_float(v[i]) + b;
+                    }
+                } else if (p.out_dt == HFB_BF16) {
+                    __nv_bfloat16 *dst = (__nv_bfloat16 *)p.out + at;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        if (i >= n_tok) break;
+                        dst[(size_t)i * p.N] = __float2bfloat16_rn(__uint_as_float(v[i]) + b);
+                    }
+                } else {
+                    float *dst = (float *)p.out + at;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        if (i >= n_tok) break;
+                        dst[(size_t)i * p.N] = __uint_as_float(v[i]) + b;
+                    }
+                }
             }
         }
     } else if (p.mode == EPI_SWIGLU) {
