@@ -253,3 +253,35 @@ def test_pages_kept_of_the_previous_request(tiny_folders, emu):
     _drain(sch)
     assert sch.requests[2].stop == "length" and sch.requests[2].shared == 0 and sch.retained is None
     assert sess.engine.cache.pages_in_use() == 0
+
+
+def test_a_request_waits_only_for_the_tokens_it_shares(tiny_folders, emu):
+    """Both arrive together; the second shares 37 tokens with the first, which needs several steps for its prompt:
+    the second waits until those tokens (whole blocks of them) are computed, not for the whole prompt."""
+    from hfcpu_b200.engine import Request
+    from hfcpu_b200 import SamplingParams
+    from hfcpu_b200.engine.scheduler import Scheduler
+    assert Scheduler._common([1, 2, 3, 4], [1, 2, 9, 4], 4) == 2 and Scheduler._common([1, 2], [1, 2, 3], 5) == 2
+    assert Scheduler._common(list(range(2000)), list(range(1500)) + [0] * 500, 2000) == 1500
+    a = make_requests("B", [60], seed=7)["r0"]
+    b = a[:37] + make_requests("B", [20], seed=8)["r0"]
+    bs = BLOCK["B"]
+    sess = _session(tiny_folders["B"], "B", 200, budget=24, chunk=16)   # a takes 16 tokens a step, 8 are left for b
+    sch = sess.scheduler
+    sch.submit(Request("a", a, SamplingParams(temp=0, max_tokens=4)))
+    sch.submit(Request("b", b, SamplingParams(temp=0, max_tokens=4)))
+    admitted_at = None
+    for step in range(1, 40):
+        sch.step()
+        sch.engine.cache.check()
+        if admitted_at is None and sch.requests["b"].status != "waiting":
+            admitted_at = step
+            assert sch.requests["a"].computed < len(a)            # a's own prompt is not through yet
+        if not sch.has_work():
+            break
+    share = 37 // bs * bs
+    assert sch.requests["b"].shared == share
+    assert admitted_at == share // 16 + 1                          # the step after a has computed the shared blocks
+    assert sess.engine.cache.pages_in_use() == 0
+    alone = _session(tiny_folders["B"], "B", 200, budget=16)
+    assert alone.generate([b], temp=0, max_tokens=4)[0][0].tokens == sch.requests["b"].generated
