@@ -51,10 +51,11 @@ class App:
         self.out.event("begin", id=rid, op=op)
         t0 = time.perf_counter()
         try:
-            handler = {"echo": self.op_echo, "generate": self.op_generate, "bench": self.op_bench}.get(op)
+            handler = {"echo": self.op_echo, "generate": self.op_generate, "bench": self.op_bench,
+                       "inspect": self.op_inspect}.get(op)
             if handler is None:
-                raise Failure("ENOTSUP" if op in ("inspect", "doctor", "tokenize") else "EINVAL",
-                              f"operation '{op}' is not supported (generate | bench | echo)")
+                raise Failure("ENOTSUP" if op in ("doctor", "tokenize") else "EINVAL",
+                              f"operation '{op}' is not supported (generate | bench | inspect | echo)")
             handler(eff, body)
         except Failure as f:
             self.n_errors += 1
@@ -125,6 +126,95 @@ class App:
         self.log("info", msg="model loaded", path=path, dtype=self.o["dtype"],
                  pages=self.session.engine.num_pages, ctx_max=self.session.engine.ctx_max)
         return self.session
+
+    def op_inspect(self, eff, body):
+        """What a model file holds, without loading it (src/ops.c:204-276): @file, @layout (GGUF), @arch, one @kv per
+        metadata key (for a folder: per config.json key), with --list-tensors one @tensor per tensor, @types per
+        tensor type, @summary.  Needs no GPU."""
+        import json
+        import mmap
+        from hfcpu_b200.config import known_architectures
+        from hfcpu_b200.weights import gguf as G
+        from hfcpu_b200.weights.safetensors_io import SafetensorsFile, WeightFormatError
+        path = eff["model"]
+        if not path:
+            raise Failure("EINVAL", "inspect needs --model PATH")
+        out, listing = self.out, eff["list_tensors"]
+        known = set(known_architectures())
+
+        def kv_event(key, kind, value):
+            if isinstance(value, list):
+                out.event("kv", key=key, type="array", elem=kind, count=len(value))
+            elif isinstance(value, str) and len(value) > 160:
+                out.event("kv", key=key, type=kind, value=value[:160], truncated_from=len(value))
+            elif isinstance(value, float):
+                out.event("kv", key=key, type=kind, value=f"{value:.9g}")
+            else:
+                out.event("kv", key=key, type=kind, value=value if isinstance(value, str) else json.dumps(value))
+
+        tensors = []                                  # (name, type name, dims as stored, offset, bytes, supported)
+        try:
+            if os.path.isdir(path):
+                cfg_path, st_path = os.path.join(path, "config.json"), os.path.join(path, "model.safetensors")
+                try:
+                    with open(cfg_path) as f:
+                        cfg = json.load(f)
+                except (OSError, ValueError) as e:
+                    raise Failure("EFORMAT", f"{cfg_path}: {e}") from None
+                with SafetensorsFile(st_path) as st:
+                    for name, (dt, shape, b, en) in st.entries.items():
+                        tensors.append((name, str(dt).replace("torch.", ""), "x".join(map(str, shape)), b, en - b, True))
+                    out.event("file", path=st_path, bytes=os.path.getsize(st_path), format="safetensors",
+                              tensors=len(tensors), kv=len(cfg))
+                arch = (cfg.get("architectures") or [cfg.get("model_type") or "(none)"])[0]
+                for key, value in cfg.items():
+                    kind = ("bool" if isinstance(value, bool) else "int" if isinstance(value, int) else
+                            "float" if isinstance(value, float) else "string" if isinstance(value, str) else
+                            "null" if value is None else "json")
+                    kv_event(key, kind, value if kind != "json" or isinstance(value, list) else json.dumps(value))
+            else:
+                try:
+                    f = open(path, "rb")
+                except OSError as e:
+                    raise Failure("EIO", f"{path}: {e.strerror}") from None
+                with f:
+                    size = os.fstat(f.fileno()).st_size
+                    if size == 0:
+                        raise WeightFormatError(f"{path}: empty file")
+                    with mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ) as mm:
+                        version, meta, kinds, infos, align, base = G.parse_gguf(mm, path)
+                out.event("file", path=path, bytes=size, gguf_version=version, tensors=len(infos), kv=len(meta))
+                out.event("layout", alignment=align, data_offset=base)
+                arch = meta.get("general.architecture") or "(none)"
+                for key, value in meta.items():
+                    shown = (key.startswith("general.") or key.startswith(f"{arch}.") or isinstance(value, (list, str))
+                             or key in ("tokenizer.ggml.model", "tokenizer.ggml.pre"))
+                    if shown or listing:
+                        kind = G.KV_TYPE_NAMES.get(kinds[key], str(kinds[key]))
+                        kv_event(key, kind, bool(value) if kind == "bool" else value)
+                for name, dims, tid, off in infos:
+                    count = 1
+                    for d in dims:
+                        count *= d
+                    esz = {0: 4, 1: 2, 30: 2}.get(tid)
+                    tensors.append((name, G.TYPE_NAMES.get(tid, f"type{tid}"), "x".join(map(str, dims)), off,
+                                    count * esz if esz else 0, esz is not None))
+        except WeightFormatError as e:
+            raise Failure("EFORMAT", str(e)) from None
+        supported = arch in known
+        out.event("arch", name=arch, supported="yes" if supported else "no",
+                  **({} if supported else {"reason": "no model is registered under this name"}))
+        by_type: Dict[str, list] = {}
+        for name, tname, dims, off, nbytes, ok in tensors:
+            if listing:
+                out.event("tensor", name=name, type=tname, dims=dims, offset=off, bytes=nbytes)
+            t = by_type.setdefault(tname, [0, 0, ok])
+            t[0] += 1
+            t[1] += nbytes
+        for tname, (n, nbytes, ok) in by_type.items():
+            out.event("types", name=tname, tensors=n, bytes=nbytes, supported="yes" if ok else "no")
+        out.event("summary", tensor_bytes=sum(t[4] for t in tensors),
+                  all_types_supported="yes" if all(t[5] for t in tensors) else "no")
 
     def op_generate(self, eff, body):
         from hfcpu_b200.engine import FinishEvent, Request, RequestError, TokenEvent

@@ -83,6 +83,7 @@ OPTIONS: List[Opt] = [
     Opt("stop-on-repeat", BOOL, REQUEST, True, "stop on repetition loops", note="ignored"),
     Opt("timeout", DBL, REQUEST, 0.0, "per-request time limit in seconds, 0 = none", 0, 1e7),
     Opt("profile", BOOL, REQUEST, False, "generate: report per-phase time of prefill and decode (@profile events)"),
+    Opt("list-tensors", BOOL, REQUEST, False, "inspect: list every tensor"),
     Opt("prefix-cache", BOOL, REQUEST, True, "generate: start on the cache pages of the previous request's tokens where "
         "the prompt begins with the same ones (default on)"),
     Opt("parse-special", BOOL, REQUEST, True, "tokenize: recognise special tokens in the text", note="text"),

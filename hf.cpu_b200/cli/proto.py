@@ -46,7 +46,7 @@ class EventWriter:
         except (BrokenPipeError, OSError):
             self.err = True
 
-    def event(self, name: str, **pairs) -> None:
+    def event(self, name: str, /, **pairs) -> None:
         parts = ["@" + name] + [f"{k}={quote('' if v is None else str(v))}" for k, v in pairs.items()]
         self._put((" ".join(parts) + "\n").encode("utf-8", "surrogateescape"))
         self.flush()

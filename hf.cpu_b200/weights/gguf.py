@@ -131,14 +131,18 @@ class _Reader:
         raise WeightFormatError(f"{self.path}: unknown metadata type {t} at byte {self.p}")
 
 
-def read_gguf(path: str) -> Tuple[Dict[str, Any], Dict[str, torch.Tensor]]:
-    """Returns (config.json-style dict, tensors by checkpoint name)."""
-    try:
-        data = open(path, "rb").read()
-    except FileNotFoundError:
-        raise WeightFormatError(f"{path}: no such file") from None
+TYPE_NAMES = {0: "F32", 1: "F16", 30: "BF16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 9: "Q8_1", 10: "Q2_K",
+              11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 15: "Q8_K"}
+KV_TYPE_NAMES = {0: "u8", 1: "i8", 2: "u16", 3: "i16", 4: "u32", 5: "i32", 6: "f32", 7: "bool", 8: "string", 9: "array",
+                 10: "u64", 11: "i64", 12: "f64"}
+
+
+def parse_gguf(data, path: str):
+    """The file's directory without its tensor data: (version, metadata {key: value}, metadata types {key: type id},
+    tensor infos [(name, dims innermost first, type id, offset)], alignment, offset of the data section).
+    ``data`` is the file's bytes or a memory map of it."""
     r = _Reader(data, path)
-    if data[:4] != b"GGUF":
+    if bytes(data[:4]) != b"GGUF":
         raise WeightFormatError(f"{path}: not a GGUF file")
     r.p = 4
     version, n_tensors, n_kv = r.take("<I"), r.take("<Q"), r.take("<Q")
@@ -146,10 +150,11 @@ def read_gguf(path: str) -> Tuple[Dict[str, Any], Dict[str, torch.Tensor]]:
         raise WeightFormatError(f"{path}: GGUF version {version} is not supported")
     if n_tensors > len(data) or n_kv > len(data):
         raise WeightFormatError(f"{path}: counts exceed the file size")
-    meta = {}
+    meta, kinds = {}, {}
     for _ in range(n_kv):
         key = r.string()
-        meta[key] = r.value(r.take("<I"))
+        kinds[key] = r.take("<I")
+        meta[key] = r.value(kinds[key])
     infos = []
     for _ in range(n_tensors):
         name = r.string()
@@ -160,6 +165,16 @@ def read_gguf(path: str) -> Tuple[Dict[str, Any], Dict[str, torch.Tensor]]:
         infos.append((name, dims, r.take("<I"), r.take("<Q")))
     align = int(meta.get("general.alignment", _ALIGN)) or _ALIGN
     base = (r.p + align - 1) // align * align
+    return version, meta, kinds, infos, align, base
+
+
+def read_gguf(path: str) -> Tuple[Dict[str, Any], Dict[str, torch.Tensor]]:
+    """Returns (config.json-style dict, tensors by checkpoint name)."""
+    try:
+        data = open(path, "rb").read()
+    except FileNotFoundError:
+        raise WeightFormatError(f"{path}: no such file") from None
+    version, meta, _, infos, align, base = parse_gguf(data, path)
     tensors, seen = {}, set()
     for name, dims, tid, off in infos:
         if name in seen:

@@ -145,3 +145,46 @@ def test_the_next_request_starts_on_the_previous_requests_cache(tiny_folders):
 def test_startup_errors_exit_2():
     r = _run_cli(["--temp", "77"])
     assert r.returncode == 2 and b"--temp" in r.stderr
+
+
+def test_inspect_lists_what_a_model_file_holds(tiny_folders, tmp_path):
+    """--op inspect (src/ops.c:204-276) on a model folder and on a GGUF file, without loading either."""
+    import torch
+    import hfcpu_b200
+    from hfcpu_b200.weights import gguf
+    folder = tiny_folders["A"]
+    r = _run_cli(["--stdin-mode", "none", "--op", "inspect", "--model", folder, "--list-tensors"])
+    assert r.returncode == 0, r.stderr.decode()
+    lines = r.stdout.decode().splitlines()
+    assert lines[1].startswith("@file path=") and "format=safetensors" in lines[1]
+    assert any(l.startswith("@arch name=Qwen2ForCausalLM supported=yes") for l in lines)
+    assert any(l.startswith("@kv key=hidden_size type=int value=") for l in lines)
+    tensors = [l for l in lines if l.startswith("@tensor ")]
+    assert any("name=model.embed_tokens.weight type=float32 dims=" in l for l in tensors)
+    summary = [l for l in lines if l.startswith("@summary")][0]
+    assert "all_types_supported=yes" in summary
+    total = sum(int(l.split("bytes=")[1].split()[0]) for l in tensors)
+    assert f"tensor_bytes={total}" in summary and lines[-1].startswith("@done status=ok")
+    # the same model as a GGUF file
+    model = hfcpu_b200.load_model(folder, torch.float32, "cpu")
+    path = str(tmp_path / "tiny.gguf")
+    import json, os
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    from hfcpu_b200.weights.safetensors_io import SafetensorsFile
+    with SafetensorsFile(os.path.join(folder, "model.safetensors")) as st:
+        gguf.write_gguf(path, cfg, {n: st.tensor(n) for n in st.names()})
+    r = _run_cli(["--stdin-mode", "none", "--op", "inspect", "--model", path])
+    assert r.returncode == 0, r.stderr.decode()
+    out = r.stdout.decode()
+    assert "@file path=" in out and "gguf_version=3" in out and "@layout alignment=32" in out
+    assert "@arch name=qwen2 supported=yes" in out and "@kv key=qwen2.block_count type=u32 value=" in out
+    # (the folder stores the tied head beside the embedding; the GGUF file, like the reference's, leaves it out)
+    head = sum(int(l.split("bytes=")[1].split()[0]) for l in tensors if "name=lm_head.weight " in l)
+    assert "@types name=F32 tensors=" in out and "@tensor " not in out and f"tensor_bytes={total - head}" in out
+    # not a model file
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(b"GGUX" + b"\0" * 40)
+    r = _run_cli(["--stdin-mode", "none", "--op", "inspect", "--model", str(bad)])
+    assert "@done status=error code=EFORMAT" in r.stdout.decode()
+    r = _run_cli(["--stdin-mode", "none", "--op", "inspect"])
+    assert "code=EINVAL" in r.stdout.decode() and "inspect needs --model" in r.stdout.decode()
