@@ -99,11 +99,11 @@ class App:
         import hfcpu_b200
         from hfcpu_b200.config import ConfigError, UnsupportedError
         from hfcpu_b200.weights import WeightError, WeightFormatError
-        wfile = os.path.join(path, "model.safetensors")
+        from hfcpu_b200.weights import find_weight_files
         try:
-            st = os.stat(wfile)
-            key = (os.path.abspath(path), st.st_size, st.st_mtime_ns)
-        except OSError:
+            files = find_weight_files(path)[0] if os.path.isdir(path) else [path]
+            key = (os.path.abspath(path),) + tuple((f, os.stat(f).st_size, os.stat(f).st_mtime_ns) for f in files)
+        except (OSError, WeightFormatError):
             key = (os.path.abspath(path), -1, -1)
         if self.session is not None and self.session_key == key:
             return self.session
@@ -155,17 +155,19 @@ class App:
         tensors = []                                  # (name, type name, dims as stored, offset, bytes, supported)
         try:
             if os.path.isdir(path):
-                cfg_path, st_path = os.path.join(path, "config.json"), os.path.join(path, "model.safetensors")
+                cfg_path = os.path.join(path, "config.json")
                 try:
                     with open(cfg_path) as f:
                         cfg = json.load(f)
                 except (OSError, ValueError) as e:
                     raise Failure("EFORMAT", f"{cfg_path}: {e}") from None
-                with SafetensorsFile(st_path) as st:
-                    for name, (dt, shape, b, en) in st.entries.items():
-                        tensors.append((name, str(dt).replace("torch.", ""), "x".join(map(str, shape)), b, en - b, True))
-                    out.event("file", path=st_path, bytes=os.path.getsize(st_path), format="safetensors",
-                              tensors=len(tensors), kv=len(cfg))
+                from hfcpu_b200.weights import find_weight_files
+                for st_path in find_weight_files(path)[0]:           # the single file, or every shard
+                    with SafetensorsFile(st_path) as st:
+                        for name, (dt, shape, b, en) in st.entries.items():
+                            tensors.append((name, str(dt).replace("torch.", ""), "x".join(map(str, shape)), b, en - b, True))
+                        out.event("file", path=st_path, bytes=os.path.getsize(st_path), format="safetensors",
+                                  tensors=len(st.entries), kv=len(cfg))
                 arch = (cfg.get("architectures") or [cfg.get("model_type") or "(none)"])[0]
                 for key, value in cfg.items():
                     kind = ("bool" if isinstance(value, bool) else "int" if isinstance(value, int) else

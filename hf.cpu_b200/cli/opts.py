@@ -63,7 +63,7 @@ OPTIONS: List[Opt] = [
     Opt("eos-ids", STR, SESSION, None, "end-of-generation token ids, space or comma separated (default: config.json)"),
 
     Opt("op", STR, REQUEST, "generate", "generate | bench | echo"),
-    Opt("model", STR, REQUEST, None, "model folder (config.json + model.safetensors)"),
+    Opt("model", STR, REQUEST, None, "model folder (config.json + safetensors, one file or shards) or a .gguf file"),
     Opt("id", STR, REQUEST, None, "request id echoed in the response"),
     Opt("chat", ENUM, REQUEST, None, "raw | auto | chatml | llama3", choices=("raw", "auto", "chatml", "llama3"), note="text"),
     Opt("system", STR, REQUEST, None, "system prompt text", note="text"),

@@ -15,7 +15,7 @@ import dataclasses
 import json
 import os
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional
+from typing import Any, ClassVar, Dict, List, Optional
 
 
 class ConfigError(ValueError):
@@ -104,6 +104,29 @@ class ModelConfig:
 
     def plan(self) -> ModelPlan:
         raise NotImplementedError
+
+    # ---- the GGUF side of an architecture (optional) ------------------------------------------------------
+    # ``general.architecture`` of the files this class reads and writes; the class is registered under it
+    gguf_architecture: ClassVar[Optional[str]] = None
+
+    @classmethod
+    def from_gguf(cls, meta: Dict[str, Any], shapes: Dict[str, tuple], where: str = "") -> "ModelConfig":
+        """The configuration a GGUF file's metadata describe.  ``shapes`` gives the shape (rows first) of every
+        tensor by its name in the file, for what the metadata leave to the tensors (the vocabulary size)."""
+        raise UnsupportedError(f"architecture '{cls.__name__}' does not read GGUF metadata")
+
+    def gguf_metadata(self) -> List[tuple]:
+        """(key, value type, value) for every metadata key of this configuration, with the format's type ids
+        (4 = u32, 6 = f32, 8 = string)."""
+        raise UnsupportedError(f"architecture '{type(self).__name__}' does not write GGUF metadata")
+
+    def gguf_names(self) -> Dict[str, str]:
+        """Checkpoint tensor name -> name in a GGUF file, for every tensor such a file stores."""
+        raise UnsupportedError(f"architecture '{type(self).__name__}' has no GGUF tensor names")
+
+    def gguf_left_out(self) -> List[str]:
+        """Checkpoint tensors that an export leaves out on purpose (a tied head's copy of the embedding)."""
+        return []
 
     def save(self, folder: str) -> None:
         os.makedirs(folder, exist_ok=True)

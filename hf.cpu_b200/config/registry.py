@@ -51,6 +51,20 @@ def config_from_dict(d: Dict[str, Any]) -> ModelConfig:
     return cfg
 
 
+def config_from_gguf(meta: Dict[str, Any], shapes: Dict[str, tuple], where: str = "") -> ModelConfig:
+    """The configuration of a GGUF file, through the class registered under its ``general.architecture``."""
+    arch = meta.get("general.architecture")
+    if not isinstance(arch, str):
+        raise ConfigError(f"{where}: general.architecture is missing")
+    cls = _ARCHITECTURES.get(arch)
+    known = sorted(n for n, c in _ARCHITECTURES.items() if getattr(c, "gguf_architecture", None) == n)
+    if arch not in known:
+        raise UnsupportedError(f"architecture '{arch}' is not supported yet (known: {', '.join(known)})")
+    cfg = cls.from_gguf(meta, shapes, where)
+    cfg.architecture = arch
+    return cfg
+
+
 def load_config(folder: str) -> ModelConfig:
     path = os.path.join(folder, "config.json")
     try:

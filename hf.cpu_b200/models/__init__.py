@@ -15,7 +15,7 @@ import torch
 from ..config import ModelConfig, load_config
 from ..config.base import ModelPlan
 from ..parts import make_part
-from ..weights import TensorSpec, load_tensors, random_tensors
+from ..weights import RandomSource, TensorSpec, load_tensors
 
 
 @dataclass
@@ -52,6 +52,7 @@ class Model:
         self.final_norm = make_part("norm", p.final_norm)
         self.head = make_part("head", p.head)
         self.bound = False
+        self.files: List[str] = []            # the weight files this model was loaded from
 
     # ---- weights ------------------------------------------------------------------------
     def all_parts(self):
@@ -71,7 +72,16 @@ class Model:
                 seen.setdefault(s.name, s)
         return list(seen.values())
 
-    def bind(self, tensors: Dict[str, torch.Tensor]) -> "Model":
+    def bind(self, tensors) -> "Model":
+        """Hand the weights to the parts.  ``tensors`` maps names to tensors: a dict, or a source that makes
+        each tensor when it is asked for, so that the parts take them one at a time."""
+        if hasattr(tensors, "keep"):
+            # a tensor that two parts bind (a tied head reads the embedding) is made once
+            count: Dict[str, int] = {}
+            for part in self.all_parts():
+                for s in part.tensor_specs():
+                    count[s.name] = count.get(s.name, 0) + 1
+            tensors.keep(n for n, c in count.items() if c > 1)
         for part in self.all_parts():
             part.bind(tensors, self.run_dtype, self.device)
         for pos in self.positions.values():
@@ -114,36 +124,40 @@ def build_model_specs(config: ModelConfig) -> List[TensorSpec]:
     return Model(config, torch.float32, torch.device("cpu")).tensor_specs()
 
 
-def load_model(folder: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0") -> Model:
-    """Read ``config.json`` and ``model.safetensors`` from ``folder``; the model class follows config.json."""
-    if os.path.isfile(folder) and folder.endswith(".gguf"):
-        return load_gguf_model(folder, dtype, device)
-    config = load_config(folder)
+def load_model(path: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0") -> Model:
+    """Load a model folder (``config.json`` + safetensors: one file, or shards with or without an index) or one of
+    the reference's GGUF files; the model class follows the configuration.  Every tensor is checked against the
+    model's declaration before any is read, and tensors go to the device one at a time."""
+    if os.path.isfile(path) and path.endswith(".gguf"):
+        return load_gguf_model(path, dtype, device)
+    config = load_config(path)
     model = Model(config, dtype, torch.device(device))
-    tensors = load_tensors(folder, model.tensor_specs(), dtype, model.device)
-    return model.bind(tensors)
+    tensors = load_tensors(path, model.tensor_specs(), dtype, model.device)
+    try:
+        model.bind(tensors)
+        model.files = tensors.paths()
+    finally:
+        tensors.close()
+    return model
 
 
 def load_gguf_model(path: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0") -> Model:
     """The same from one of the reference's own GGUF files (float tensor types only)."""
-    from ..config import config_from_dict
-    from ..weights.gguf import read_gguf
-    from ..weights.loader import WeightError, storage_dtype
-    cfg_dict, tensors = read_gguf(path)
-    model = Model(config_from_dict(cfg_dict), dtype, torch.device(device))
-    specs = {s.name: s for s in model.tensor_specs()}
-    missing = [n for n, s in specs.items() if n not in tensors and not s.optional]
-    unexpected = sorted(set(tensors) - set(specs))
-    misshapen = [(n, tuple(tensors[n].shape), tuple(specs[n].shape)) for n in sorted(set(tensors) & set(specs))
-                 if tuple(tensors[n].shape) != tuple(specs[n].shape)]
-    if missing or unexpected or misshapen:
-        raise WeightError(path, missing, unexpected, misshapen)
-    return model.bind({n: t.to(storage_dtype(t.dtype, dtype)).to(model.device) for n, t in tensors.items()})
+    from ..weights.gguf import GgufSource
+    tensors = GgufSource(path, dtype, torch.device(device))
+    try:
+        model = Model(tensors.config, dtype, torch.device(device))
+        tensors.check(model.tensor_specs())
+        model.bind(tensors)
+        model.files = [path]
+    finally:
+        tensors.close()
+    return model
 
 
 def random_model(config: ModelConfig, seed: int = 0, dtype: torch.dtype = torch.bfloat16, device="cuda:0",
                  std: float = 0.02) -> Model:
-    """A model with random weights made directly on ``device`` (no files)."""
+    """A model with random weights made directly on ``device`` (no files), one tensor at a time."""
     model = Model(config, dtype, torch.device(device))
     store = torch.float32 if dtype == torch.float32 else torch.bfloat16
-    return model.bind(random_tensors(model.tensor_specs(), seed, store, model.device, std=std))
+    return model.bind(RandomSource(model.tensor_specs(), seed, store, model.device, std=std))

@@ -15,7 +15,7 @@ import torch
 
 from .. import kernels
 from ..config.base import UnsupportedError
-from ..weights.loader import TensorSpec
+from ..weights.loader import TensorSpec, fused_rows
 from .base import CacheSpec, Mixer, register_part
 
 
@@ -62,16 +62,11 @@ class PagedAttention(Mixer):
             s.append(TensorSpec(self.names["o"] + ".bias", (self.E,)))
         return s
 
-    @staticmethod
-    def _cat(ts):
-        if len({t.dtype for t in ts}) > 1:
-            ts = [t.float() for t in ts]
-        return torch.cat(ts, dim=0).contiguous()
-
     def bind(self, tensors, run_dtype, device):
-        self.w_qkv = self._cat([tensors[self.names[x] + ".weight"] for x in "qkv"])
+        # q, k and v rows go straight into the one matrix the product reads, a tensor at a time
+        self.w_qkv = fused_rows(tensors, [self.names[x] + ".weight" for x in "qkv"], device)
         if self.qkv_bias:
-            self.b_qkv = self._cat([tensors[self.names[x] + ".bias"] for x in "qkv"])
+            self.b_qkv = fused_rows(tensors, [self.names[x] + ".bias" for x in "qkv"], device)
         self.w_o = tensors[self.names["o"] + ".weight"].contiguous()
         if self.out_bias:
             self.b_o = tensors[self.names["o"] + ".bias"].contiguous()

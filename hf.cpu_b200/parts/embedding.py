@@ -38,7 +38,11 @@ class LinearHead(Part):
 
     def tensor_specs(self):
         # a tied head reads the embedding; a checkpoint that carries a copy of the head anyway is accepted
-        return [TensorSpec(self.tensor, (self.vocab_size, self.hidden_size), optional=bool(self.tied_to))]
+        shape = (self.vocab_size, self.hidden_size)
+        specs = [TensorSpec(self.tensor, shape, optional=bool(self.tied_to))]
+        if self.tied_to:
+            specs.append(TensorSpec(self.tied_to, shape))       # declared by both: the loader makes it once
+        return specs
 
     def bind(self, tensors, run_dtype, device):
         self.weight = tensors[self.tied_to if self.tied_to else self.tensor].contiguous()

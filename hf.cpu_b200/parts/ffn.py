@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from ..weights.loader import TensorSpec
+from ..weights.loader import TensorSpec, fused_rows
 from .base import FeedForward, register_part
 
 
@@ -26,11 +26,8 @@ class SwiGlu(FeedForward):
                 TensorSpec(self.names["down"], (self.E, self.F))]
 
     def bind(self, tensors, run_dtype, device):
-        g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
-        if g.dtype != u.dtype:
-            g, u = g.float(), u.float()
         # rows alternate gate_i, up_i, so that a product's epilogue finds both of a pair side by side
-        self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * self.F, self.E).contiguous()
+        self.w_gate_up = fused_rows(tensors, [self.names["gate"], self.names["up"]], device, interleave=True)
         self.w_down = tensors[self.names["down"]].contiguous()
 
     def weight_bytes(self):

@@ -1,60 +1,38 @@
-"""The reference's own model file format, GGUF, for float types only (F32, F16, BF16).
+"""The reference's own model file format, GGUF, for float tensor types only (F32, F16, BF16).
 
-Reads and writes version 3 files with the tensor names and metadata keys the reference's loader uses
-(src/model.c:107-184): ``general.architecture``, ``<arch>.block_count``, ``.embedding_length``,
-``.feed_forward_length``, ``.attention.head_count``, ``.attention.head_count_kv``, ``.attention.key_length``,
-``.attention.layer_norm_rms_epsilon``, ``.rope.freq_base``, ``.context_length``; tensors ``token_embd.weight``,
-``output_norm.weight``, ``output.weight`` (absent = tied head), ``blk.N.attn_{q,k,v}.{weight,bias}``,
-``blk.N.attn_output.weight``, ``blk.N.attn_norm.weight``, ``blk.N.ffn_norm.weight``, ``blk.N.ffn_{gate,up,down}.weight``.
-Dimensions are stored innermost first (``ne[0]`` = columns, src/model.h:18-19).  Every offset and count is
-checked against the file size, as the reference's reader does (src/gguf.c:178-259).  Quantised tensor types
-are refused.
+This file knows the container, not the model: header, metadata key/values, tensor directory, aligned data
+section.  What the metadata keys mean and what the tensors are called is the architecture's business: the
+configuration class found in the registry under ``general.architecture`` turns metadata into a typed
+configuration (``from_gguf``) and gives the table from checkpoint names to the file's tensor names
+(``gguf_names``), as the reference's loader does per architecture (src/model.c:107-184).
+
+Dimensions are stored innermost first (``ne[0]`` = columns, src/model.h:18-19).  The file is mapped, not
+read (src/pal.c:33-52); every offset and count is checked against the file size before any data is touched,
+as the reference's reader does (src/gguf.c:178-259).  Quantised tensor types are refused.
 """
 from __future__ import annotations
 
-import re
+import mmap
+import os
 import struct
-from typing import Any, Dict, Tuple
+from typing import Any, Dict, Iterable, List, Sequence, Tuple
 
 import numpy as np
 import torch
 
+from .loader import TensorSource, check_against_specs, storage_dtype
 from .safetensors_io import WeightFormatError
 
 _TYPES = {0: (torch.float32, 4), 1: (torch.float16, 2), 30: (torch.bfloat16, 2)}
 _TYPE_ID = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 30}
 _ALIGN = 32
+# metadata value types of the format
+U32, F32, STRING = 4, 6, 8
 
-_LAYER_NAMES = {
-    "attn_norm.weight": "input_layernorm.weight", "ffn_norm.weight": "post_attention_layernorm.weight",
-    "attn_q.weight": "self_attn.q_proj.weight", "attn_k.weight": "self_attn.k_proj.weight",
-    "attn_v.weight": "self_attn.v_proj.weight", "attn_output.weight": "self_attn.o_proj.weight",
-    "attn_q.bias": "self_attn.q_proj.bias", "attn_k.bias": "self_attn.k_proj.bias", "attn_v.bias": "self_attn.v_proj.bias",
-    "ffn_gate.weight": "mlp.gate_proj.weight", "ffn_up.weight": "mlp.up_proj.weight", "ffn_down.weight": "mlp.down_proj.weight",
-}
-_TOP_NAMES = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight",
-              "output.weight": "lm_head.weight"}
-
-
-def to_checkpoint_name(gguf_name: str) -> str:
-    if gguf_name in _TOP_NAMES:
-        return _TOP_NAMES[gguf_name]
-    m = re.fullmatch(r"blk\.(\d+)\.(.+)", gguf_name)
-    if m and m.group(2) in _LAYER_NAMES:
-        return f"model.layers.{m.group(1)}.{_LAYER_NAMES[m.group(2)]}"
-    return gguf_name
-
-
-def to_gguf_name(name: str) -> str:
-    for k, v in _TOP_NAMES.items():
-        if v == name:
-            return k
-    m = re.fullmatch(r"model\.layers\.(\d+)\.(.+)", name)
-    if m:
-        for k, v in _LAYER_NAMES.items():
-            if v == m.group(2):
-                return f"blk.{m.group(1)}.{k}"
-    return name
+TYPE_NAMES = {0: "F32", 1: "F16", 30: "BF16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 9: "Q8_1", 10: "Q2_K",
+              11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 15: "Q8_K"}
+KV_TYPE_NAMES = {0: "u8", 1: "i8", 2: "u16", 3: "i16", 4: "u32", 5: "i32", 6: "f32", 7: "bool", 8: "string", 9: "array",
+                 10: "u64", 11: "i64", 12: "f64"}
 
 
 def _str(s: str) -> bytes:
@@ -62,42 +40,8 @@ def _str(s: str) -> bytes:
     return struct.pack("<Q", len(b)) + b
 
 
-def write_gguf(path: str, config: Dict[str, Any], tensors: Dict[str, torch.Tensor], arch: str = "qwen2") -> None:
-    """``config`` is a config.json dict; ``tensors`` carry checkpoint names."""
-    H = config["num_attention_heads"]
-    kv = [("general.architecture", 8, arch), ("general.name", 8, "hfb200 export"),
-          (f"{arch}.block_count", 4, config["num_hidden_layers"]),
-          (f"{arch}.context_length", 4, config.get("max_position_embeddings", 0)),
-          (f"{arch}.embedding_length", 4, config["hidden_size"]),
-          (f"{arch}.feed_forward_length", 4, config["intermediate_size"]),
-          (f"{arch}.attention.head_count", 4, H),
-          (f"{arch}.attention.head_count_kv", 4, config.get("num_key_value_heads", H)),
-          (f"{arch}.attention.key_length", 4, config.get("head_dim") or config["hidden_size"] // H),
-          (f"{arch}.attention.layer_norm_rms_epsilon", 6, config.get("rms_norm_eps", 1e-5)),
-          (f"{arch}.rope.freq_base", 6, config.get("rope_theta", 10000.0))]
-    head = b""
-    for key, t, v in kv:
-        head += _str(key) + struct.pack("<I", t)
-        head += _str(v) if t == 8 else struct.pack("<I" if t == 4 else "<f", v)
-    infos, blob = b"", b""
-    names = [n for n in tensors if not (n == "lm_head.weight" and config.get("tie_word_embeddings"))]
-    for name in names:
-        t = tensors[name].detach().cpu().contiguous()
-        if t.dtype not in _TYPE_ID:
-            raise WeightFormatError(f"tensor '{name}': dtype {t.dtype} cannot be stored in GGUF here")
-        blob += b"\0" * (-len(blob) % _ALIGN)
-        dims = list(reversed(t.shape))
-        infos += _str(to_gguf_name(name)) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims)
-        infos += struct.pack("<IQ", _TYPE_ID[t.dtype], len(blob))
-        blob += t.view(torch.uint8).numpy().tobytes() if t.dim() else t.reshape(1).view(torch.uint8).numpy().tobytes()
-    out = b"GGUF" + struct.pack("<IQQ", 3, len(names), len(kv)) + head + infos
-    out += b"\0" * (-len(out) % _ALIGN)
-    with open(path, "wb") as f:
-        f.write(out + blob)
-
-
 class _Reader:
-    def __init__(self, data: bytes, path: str):
+    def __init__(self, data, path: str):
         self.d, self.p, self.path = data, 0, path
 
     def take(self, fmt: str):
@@ -112,7 +56,7 @@ class _Reader:
         n = self.take("<Q")
         if n > len(self.d) - self.p:
             raise WeightFormatError(f"{self.path}: string of {n} bytes at byte {self.p} exceeds the file")
-        s = self.d[self.p:self.p + n]
+        s = bytes(self.d[self.p:self.p + n])
         self.p += n
         return s.decode("utf-8", "replace")
 
@@ -129,12 +73,6 @@ class _Reader:
                 raise WeightFormatError(f"{self.path}: array of {n} elements at byte {self.p} exceeds the file")
             return [self.value(et, 1) for _ in range(n)]
         raise WeightFormatError(f"{self.path}: unknown metadata type {t} at byte {self.p}")
-
-
-TYPE_NAMES = {0: "F32", 1: "F16", 30: "BF16", 2: "Q4_0", 3: "Q4_1", 6: "Q5_0", 7: "Q5_1", 8: "Q8_0", 9: "Q8_1", 10: "Q2_K",
-              11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K", 15: "Q8_K"}
-KV_TYPE_NAMES = {0: "u8", 1: "i8", 2: "u16", 3: "i16", 4: "u32", 5: "i32", 6: "f32", 7: "bool", 8: "string", 9: "array",
-                 10: "u64", 11: "i64", 12: "f64"}
 
 
 def parse_gguf(data, path: str):
@@ -168,46 +106,191 @@ def parse_gguf(data, path: str):
     return version, meta, kinds, infos, align, base
 
 
-def read_gguf(path: str) -> Tuple[Dict[str, Any], Dict[str, torch.Tensor]]:
-    """Returns (config.json-style dict, tensors by checkpoint name)."""
-    try:
-        data = open(path, "rb").read()
-    except FileNotFoundError:
-        raise WeightFormatError(f"{path}: no such file") from None
-    version, meta, _, infos, align, base = parse_gguf(data, path)
-    tensors, seen = {}, set()
-    for name, dims, tid, off in infos:
-        if name in seen:
-            raise WeightFormatError(f"{path}: tensor '{name}' appears twice")
-        seen.add(name)
-        if tid not in _TYPES:
-            raise WeightFormatError(f"{path}: tensor '{name}' has type {tid}; only F32, F16 and BF16 are supported")
-        dt, esz = _TYPES[tid]
-        count = 1
-        for d in dims:
-            count *= d
-        if base + off + count * esz > len(data):
-            raise WeightFormatError(f"{path}: tensor '{name}' runs past the end of the file")
-        raw = np.frombuffer(data, dtype=np.uint8, count=count * esz, offset=base + off).copy()
-        tensors[to_checkpoint_name(name)] = torch.from_numpy(raw).view(dt).reshape(list(reversed(dims)))
-    arch = meta.get("general.architecture")
-    if not isinstance(arch, str):
-        raise WeightFormatError(f"{path}: general.architecture is missing")
+class GgufFile:
+    """A mapped GGUF file: metadata and the tensor directory, tensors by the file's own names on demand."""
 
-    def need(key):
-        if f"{arch}.{key}" not in meta:
-            raise WeightFormatError(f"{path}: metadata key '{arch}.{key}' is missing")
-        return meta[f"{arch}.{key}"]
-    E, H = need("embedding_length"), need("attention.head_count")
-    if "model.embed_tokens.weight" not in tensors:
-        raise WeightFormatError(f"{path}: tensor 'token_embd.weight' is missing")
-    cfg = {"model_type": arch, "num_hidden_layers": need("block_count"), "hidden_size": E,
-           "intermediate_size": need("feed_forward_length"), "num_attention_heads": H,
-           "num_key_value_heads": meta.get(f"{arch}.attention.head_count_kv", H),
-           "head_dim": meta.get(f"{arch}.attention.key_length", E // H if H else 0),
-           "rms_norm_eps": float(meta.get(f"{arch}.attention.layer_norm_rms_epsilon", 1e-5)),
-           "rope_theta": float(meta.get(f"{arch}.rope.freq_base", 10000.0)),
-           "max_position_embeddings": meta.get(f"{arch}.context_length", 0) or 32768,
-           "vocab_size": tensors["model.embed_tokens.weight"].shape[0],
-           "tie_word_embeddings": "lm_head.weight" not in tensors}
-    return cfg, tensors
+    def __init__(self, path: str):
+        self.path = path
+        try:
+            self._f = open(path, "rb")
+        except FileNotFoundError:
+            raise WeightFormatError(f"{path}: no such file") from None
+        self._mm = None
+        try:
+            size = os.fstat(self._f.fileno()).st_size
+            if size == 0:
+                raise WeightFormatError(f"{path}: empty file")
+            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+            self.version, self.meta, self.kinds, self.infos, self.align, self.base = parse_gguf(self._mm, path)
+            self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int, int]] = {}
+            for name, dims, tid, off in self.infos:
+                if name in self.entries:
+                    raise WeightFormatError(f"{path}: tensor '{name}' appears twice")
+                if tid not in _TYPES:
+                    raise WeightFormatError(f"{path}: tensor '{name}' has type {TYPE_NAMES.get(tid, tid)}; only F32, "
+                                            f"F16 and BF16 are supported")
+                dt, esz = _TYPES[tid]
+                count = 1
+                for d in dims:
+                    count *= d
+                if self.base + off + count * esz > size:
+                    raise WeightFormatError(f"{path}: tensor '{name}' runs past the end of the file")
+                self.entries[name] = (dt, tuple(reversed(dims)), self.base + off, count * esz)
+        except WeightFormatError:
+            self.close()
+            raise
+
+    def names(self):
+        return self.entries.keys()
+
+    def shape(self, name: str) -> Tuple[int, ...]:
+        """Outermost dimension first ([rows, columns] for a matrix)."""
+        return self.entries[name][1]
+
+    def dtype(self, name: str) -> torch.dtype:
+        return self.entries[name][0]
+
+    def raw(self, name: str) -> np.ndarray:
+        _, _, at, nbytes = self.entries[name]
+        if nbytes == 0:
+            return np.empty(0, dtype=np.uint8)
+        return np.frombuffer(self._mm, dtype=np.uint8, count=nbytes, offset=at)
+
+    def tensor(self, name: str) -> torch.Tensor:
+        dt, shape, _, nbytes = self.entries[name]
+        if nbytes == 0:
+            return torch.empty(shape, dtype=dt)
+        return torch.from_numpy(self.raw(name).copy()).view(dt).reshape(shape)
+
+    def close(self) -> None:
+        if self._mm is not None:
+            try:
+                self._mm.close()
+            except BufferError:
+                pass
+            self._mm = None
+        self._f.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+
+def write_gguf_file(path: str, kv: Sequence[Tuple[str, int, Any]], tensors: Iterable[Tuple[str, torch.Tensor]]) -> None:
+    """Write a version-3 file: ``kv`` = (key, value type, value) with types ``U32``, ``F32`` and ``STRING``;
+    ``tensors`` = (name in the file, tensor), streamed in the order given."""
+    head = b""
+    for key, t, v in kv:
+        if t not in (U32, F32, STRING):
+            raise WeightFormatError(f"metadata key '{key}': value type {t} cannot be written here")
+        head += _str(key) + struct.pack("<I", t)
+        head += _str(v) if t == STRING else struct.pack("<I" if t == U32 else "<f", v)
+    infos, chunks, off, count = b"", [], 0, 0
+    for name, t in tensors:
+        t = t.detach().cpu().contiguous()
+        if t.dtype not in _TYPE_ID:
+            raise WeightFormatError(f"tensor '{name}': dtype {t.dtype} cannot be stored in GGUF here")
+        pad = -off % _ALIGN
+        if pad:
+            chunks.append(b"\0" * pad)
+            off += pad
+        dims = list(reversed(t.shape))
+        infos += _str(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims)
+        infos += struct.pack("<IQ", _TYPE_ID[t.dtype], off)
+        data = t.reshape(-1).view(torch.uint8).numpy().tobytes()
+        chunks.append(data)
+        off += len(data)
+        count += 1
+    out = b"GGUF" + struct.pack("<IQQ", 3, count, len(kv)) + head + infos
+    out += b"\0" * (-len(out) % _ALIGN)
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
+        f.write(out)
+        for c in chunks:
+            f.write(c)
+    os.replace(tmp, path)
+
+
+def write_gguf(path: str, config, tensors, name: str = "hfb200 export") -> None:
+    """Export a model: ``config`` is a configuration (or a config.json dict) whose class knows the format's
+    metadata keys and tensor names for its architecture; ``tensors`` carry checkpoint names.  Tensors the
+    architecture's table leaves out (a tied head's copy) are not written."""
+    from ..config import config_from_dict
+    cfg = config if hasattr(config, "gguf_names") else config_from_dict(config)
+    table = cfg.gguf_names()
+    unknown = sorted(n for n in tensors.keys() if n not in table and n not in cfg.gguf_left_out())
+    if unknown:
+        raise WeightFormatError(f"no GGUF name for tensor(s) {', '.join(unknown)} in architecture '{cfg.gguf_architecture}'")
+    kv = [("general.architecture", STRING, cfg.gguf_architecture), ("general.name", STRING, name)] + list(cfg.gguf_metadata())
+    write_gguf_file(path, kv, ((table[n], tensors[n]) for n in tensors.keys() if n in table))
+
+
+class GgufSource(TensorSource):
+    """The tensors of a GGUF file under their checkpoint names, read from the mapping on demand; ``config`` is the
+    configuration its metadata describe."""
+
+    def __init__(self, path: str, run_dtype: torch.dtype, device: torch.device):
+        super().__init__(run_dtype, device)
+        from ..config import config_from_gguf
+        self.file = GgufFile(path)
+        try:
+            self.config = config_from_gguf(self.file.meta, {n: self.file.shape(n) for n in self.file.names()}, path)
+            back = {g: c for c, g in self.config.gguf_names().items()}
+            self.where = {back.get(n, n): n for n in self.file.names()}
+        except Exception:
+            self.file.close()
+            raise
+        self._staging = None
+
+    def names(self):
+        return self.where.keys()
+
+    def __contains__(self, name):
+        return name in self.where
+
+    def stored(self, name):
+        g = self.where[name]
+        return self.file.dtype(g), self.file.shape(g)
+
+    def meta(self, name):
+        dt, shape = self.stored(name)
+        return storage_dtype(dt, self.run_dtype), shape
+
+    def _make(self, name):
+        dt, shape = self.stored(name)
+        want = storage_dtype(dt, self.run_dtype)
+        if self.device.type != "cuda":
+            return self.file.tensor(self.where[name]).to(want).to(self.device)
+        raw = self.file.raw(self.where[name])
+        if raw.shape[0] == 0:
+            return torch.empty(shape, dtype=want, device=self.device)
+        from .loader import _Staging
+        if self._staging is None:
+            self._staging = _Staging()
+        with torch.cuda.device(self.device):
+            t = self._staging.upload(raw, self.device).view(dt).reshape(shape)
+            return t if dt == want else t.to(want)
+
+    def check(self, specs) -> None:
+        check_against_specs(self.file.path, list(specs), {n: self.stored(n) for n in self.names()})
+
+    def close(self):
+        super().close()
+        if self._staging is not None:
+            for e in self._staging.events:
+                if e is not None:
+                    e.synchronize()
+            self._staging = None
+        self.file.close()
+
+
+def read_gguf(path: str):
+    """(configuration, {checkpoint name: CPU tensor}) of a whole file; for tools and tests, the engine loads
+    through :class:`GgufSource`."""
+    src = GgufSource(path, torch.float32, torch.device("cpu"))
+    try:
+        return src.config, {n: src.file.tensor(src.where[n]) for n in src.names()}
+    finally:
+        src.close()

@@ -83,17 +83,26 @@ class SafetensorsFile:
     def dtype(self, name: str) -> torch.dtype:
         return self.entries[name][0]
 
+    def raw(self, name: str) -> np.ndarray:
+        """The named tensor's bytes as a read-only view of the file mapping (nothing is copied)."""
+        _, _, b, en = self.entries[name]
+        if en == b:
+            return np.empty(0, dtype=np.uint8)
+        return np.frombuffer(self._mm, dtype=np.uint8, count=en - b, offset=self._data0 + b)
+
     def tensor(self, name: str) -> torch.Tensor:
         """A CPU tensor holding a copy of the named tensor's data."""
         tdt, shape, b, en = self.entries[name]
         if en == b:
             return torch.empty(shape, dtype=tdt)
-        raw = np.frombuffer(self._mm, dtype=np.uint8, count=en - b, offset=self._data0 + b)
-        return torch.from_numpy(raw.copy()).view(tdt).reshape(shape)
+        return torch.from_numpy(self.raw(name).copy()).view(tdt).reshape(shape)
 
     def close(self) -> None:
         if self._mm is not None:
-            self._mm.close()
+            try:
+                self._mm.close()
+            except BufferError:          # a view handed out by raw() is still alive; the mapping goes with it
+                pass
             self._mm = None
         self._f.close()
 
@@ -104,18 +113,22 @@ class SafetensorsFile:
         self.close()
 
 
-def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dict[str, str] = None) -> None:
+def write_safetensors(path: str, tensors, metadata: Dict[str, str] = None) -> None:
+    """Write ``tensors`` (a dict, or any mapping with ``meta(name) -> (dtype, shape)`` that makes its tensors on
+    demand) to ``path``; tensors are fetched and written one at a time."""
     header = {}
     off = 0
-    items = []
-    for name in sorted(tensors):
-        t = tensors[name].detach().cpu().contiguous()
-        if t.dtype not in _NAMES:
-            raise WeightFormatError(f"tensor '{name}': dtype {t.dtype} cannot be stored")
-        nbytes = t.numel() * t.element_size()
-        header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + nbytes]}
+    names = sorted(tensors.keys())
+    meta = getattr(tensors, "meta", None)
+    for name in names:
+        dtype, shape = meta(name) if meta is not None else (tensors[name].dtype, tuple(tensors[name].shape))
+        if dtype not in _NAMES:
+            raise WeightFormatError(f"tensor '{name}': dtype {dtype} cannot be stored")
+        nbytes = _DTYPES[_NAMES[dtype]][1]
+        for s_ in shape:
+            nbytes *= int(s_)
+        header[name] = {"dtype": _NAMES[dtype], "shape": list(shape), "data_offsets": [off, off + nbytes]}
         off += nbytes
-        items.append(t)
     if metadata:
         header["__metadata__"] = metadata
     blob = json.dumps(header, separators=(",", ":")).encode("utf-8")
@@ -124,8 +137,11 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dic
     with open(tmp, "wb") as f:
         f.write(struct.pack("<Q", len(blob)))
         f.write(blob)
-        for t in items:
+        for name in names:
+            t = tensors[name].detach().cpu().contiguous()
+            b, e = header[name]["data_offsets"]
+            if t.numel() * t.element_size() != e - b:
+                raise WeightFormatError(f"tensor '{name}' changed between the header and the data")
             if t.numel():
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.dim() else
-                        t.reshape(1).view(torch.uint8).numpy().tobytes())
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes())
     os.replace(tmp, path)

@@ -80,6 +80,27 @@ def make_requests(name, lengths, seed=0):
     return {f"r{i}": torch.randint(0, V, (n,), generator=g).tolist() for i, n in enumerate(lengths)}
 
 
+SAMPLER_VOCAB, SAMPLER_ROWS = 1000, 6
+
+
+def sampler_logits():
+    """Rows of synthetic logits made from integer arithmetic only (the same on every machine): values in
+    [-8, 8) on a grid of 2^-20, with ties at the top of some rows (lowest id wins) and one row that is nearly flat."""
+    import numpy as np
+    i = np.arange(SAMPLER_VOCAB, dtype=np.uint64)[None, :]
+    r = np.arange(SAMPLER_ROWS, dtype=np.uint64)[:, None]
+    x = (i * np.uint64(2654435761) + r * np.uint64(40503) + np.uint64(12345)) & np.uint64(0xFFFFFFFF)
+    x ^= (x << np.uint64(13)) & np.uint64(0xFFFFFFFF)
+    x ^= x >> np.uint64(17)
+    x ^= (x << np.uint64(5)) & np.uint64(0xFFFFFFFF)
+    L = ((x >> np.uint64(8)).astype(np.float32) / np.float32(1 << 24) * np.float32(16) - np.float32(8)).astype(np.float32)
+    L[1, 900] = L[1, 17] = L[1].max()                      # a tie at the top: the lower id comes first
+    L[2, 5] = L[2, 3] = L[2, 600] = np.float32(9.5)
+    L[3] = (L[3] * np.float32(1 / 64)).astype(np.float32)  # nearly flat: thousands of candidates survive
+    L[4, 123] = np.float32(30.0)                           # one token dominates
+    return np.ascontiguousarray(L)
+
+
 # Tolerances: max|a-b| / max|b| per logits row against the float64 plain implementation.
 TOL = {"float32": 1e-4, "bfloat16": 3e-2}
 

@@ -115,8 +115,9 @@ def layer(x, cfg, W, l, cos, sin):
     q = xn @ W[p + "self_attn.q_proj.weight"].T + W[p + "self_attn.q_proj.bias"]
     k = xn @ W[p + "self_attn.k_proj.weight"].T + W[p + "self_attn.k_proj.bias"]
     v = xn @ W[p + "self_attn.v_proj.weight"].T + W[p + "self_attn.v_proj.bias"]
-    q = rope(q.view(T, H, d), cos, sin, d)
-    k = rope(k.view(T, G, d), cos, sin, d)
+    n_rot = cfg.get("rope_dim") or d          # the reference's rope.dimension_count (src/model.c:132-133)
+    q = rope(q.view(T, H, d), cos, sin, n_rot)
+    k = rope(k.view(T, G, d), cos, sin, n_rot)
     att = attention(q, k, v.view(T, G, d), H, G, window_of_layer(cfg, l)).reshape(T, H * d)
     x = x + att @ W[p + "self_attn.o_proj.weight"].T
     xn = rmsnorm(x, W[p + "post_attention_layernorm.weight"], eps)
@@ -130,7 +131,7 @@ def forward(cfg, W, ids, dtype=torch.float64):
     H = cfg["num_attention_heads"]
     d = cfg.get("head_dim") or cfg["hidden_size"] // H
     x = embed(ids, W["model.embed_tokens.weight"])
-    cos, sin = rope_angles(range(len(ids)), d, cfg.get("rope_theta", 10000.0), dtype)
+    cos, sin = rope_angles(range(len(ids)), cfg.get("rope_dim") or d, cfg.get("rope_theta", 10000.0), dtype)
     for l in range(cfg["num_hidden_layers"]):
         x = layer(x, cfg, W, l, cos, sin)
     xn = rmsnorm(x, W["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5))

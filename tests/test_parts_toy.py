@@ -90,6 +90,25 @@ class ToyConfig:
         os.makedirs(folder, exist_ok=True)
         json.dump(self.to_dict(), open(os.path.join(folder, "config.json"), "w"))
 
+    # the architecture's side of a GGUF file: its metadata keys and its names for the tensors
+    gguf_architecture = "toy"
+
+    def gguf_metadata(self):
+        return ([(f"toy.{k}", 4, getattr(self, k)) for k in ("layers", "hidden", "heads", "head_dim", "ffn", "positions")]
+                + [("toy.decay", 6, self.decay)])
+
+    def gguf_names(self):
+        from hfcpu_b200.models import build_model_specs
+        return {s.name: "t/" + s.name.replace("toy.", "").replace(".", "/") for s in build_model_specs(self)}
+
+    def gguf_left_out(self):
+        return []
+
+    @classmethod
+    def from_gguf(cls, meta, shapes, where=""):
+        return cls(vocab=shapes["t/embed"][0], decay=round(meta["toy.decay"], 6),
+                   **{k: meta[f"toy.{k}"] for k in ("layers", "hidden", "heads", "head_dim", "ffn", "positions")})
+
     def plan(self):
         from hfcpu_b200.config import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
         E = self.hidden
@@ -164,6 +183,41 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(backend, tmp_path)
     finally:
         unregister_part("mixer", "toy_decaying_sum")
         unregister_architecture("ToyForCausalLM")
+
+
+def test_toy_architecture_brings_its_own_gguf_names(tmp_path, emu):
+    """An architecture registered from outside exports to and loads from GGUF with metadata keys and tensor names of
+    its own; the container code knows neither."""
+    import hfcpu_b200
+    from hfcpu_b200.config import unregister_architecture
+    from hfcpu_b200.parts import unregister_part
+    from hfcpu_b200.weights import load_tensors
+    from hfcpu_b200.weights.gguf import GgufFile, write_gguf
+    hfcpu_b200.register_part("mixer", "toy_decaying_sum", _toy_parts())
+    hfcpu_b200.register_architecture("ToyForCausalLM", ToyConfig)
+    hfcpu_b200.register_architecture("toy", ToyConfig)
+    try:
+        cfg = ToyConfig(layers=2, vocab=70)
+        folder = hfcpu_b200.write_random_model(cfg, str(tmp_path / "toy"), seed=4, dtype=torch.float32, std=0.3)
+        a = hfcpu_b200.load_model(folder, torch.float32, "cpu")
+        path = str(tmp_path / "toy.gguf")
+        write_gguf(path, cfg, load_tensors(folder, a.tensor_specs(), torch.float32, torch.device("cpu")))
+        with GgufFile(path) as f:
+            assert f.meta["general.architecture"] == "toy" and f.meta["toy.ffn"] == 80
+            assert "t/1/attn/q_proj/weight" in f.names() and "t/0/mix/w" in f.names() and f.shape("t/embed") == (70, 48)
+        b = hfcpu_b200.load_model(path, torch.float32, "cpu")
+        assert dataclasses.replace(b.config, architecture=cfg.architecture) == cfg
+        ids = [3, 9, 60, 2, 41]
+        outs = []
+        for m in (a, b):
+            eng = hfcpu_b200.Engine(m, block_size=8, max_tokens=64, max_requests=1)
+            eng.add_request("r")
+            outs.append(eng.step([hfcpu_b200.StepEntry("r", ids, [4])]).clone())
+        assert torch.equal(outs[0], outs[1])
+    finally:
+        unregister_part("mixer", "toy_decaying_sum")
+        unregister_architecture("ToyForCausalLM")
+        unregister_architecture("toy")
 
 
 # ---- the run order is data: a layer named twice, a layer reading another entry's cache --------------------

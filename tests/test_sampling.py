@@ -20,7 +20,8 @@ def test_host_sampler_equals_plain_sampler():
 
 
 def test_rng_sequence():
-    """xorshift64* with the reference's seeding (src/sample.c:9-23): values in [0, 1), seeds differ, seed 0 works."""
+    """xorshift64* with the reference's seeding (src/sample.c:9-23): values in [0, 1), seeds differ, seed 0 works.
+    (The draws themselves are pinned on the reference's own in tests/test_golden.py.)"""
     from hfcpu_b200.sampling import Rng
     a, b = Rng(0), Rng(1)
     xs, ys = [float(a.uniform()) for _ in range(1000)], [float(b.uniform()) for _ in range(1000)]

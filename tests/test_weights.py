@@ -115,3 +115,118 @@ def test_hostile_files_are_refused(tmp_path):
         for name in f.names():
             f.tensor(name)
         f.close()
+
+
+def _shard(folder, tensors, n_shards, with_index, cfg):
+    """Write ``tensors`` as ``n_shards`` files named like a published checkpoint's, optionally with an index."""
+    from hfcpu_b200.weights import write_safetensors
+    os.makedirs(folder, exist_ok=True)
+    cfg.save(folder)
+    names = sorted(tensors)
+    parts = [names[i::n_shards] for i in range(n_shards)]
+    wmap = {}
+    for i, part in enumerate(parts):
+        fn = f"model-{i + 1:05d}-of-{n_shards:05d}.safetensors"
+        write_safetensors(os.path.join(folder, fn), {n: tensors[n] for n in part})
+        wmap.update({n: fn for n in part})
+    if with_index:
+        with open(os.path.join(folder, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": 0}, "weight_map": wmap}, f)
+    return wmap
+
+
+@pytest.mark.parametrize("with_index", [True, False])
+def test_sharded_folders_load_like_a_single_file(tmp_path, with_index):
+    from hfcpu_b200.weights import find_weight_files, load_tensors, random_tensors, weights_path, write_safetensors
+    cfg, specs = _specs(TINY_B)
+    t = random_tensors(specs, 3, torch.bfloat16)
+    one, many = str(tmp_path / "one"), str(tmp_path / "many")
+    cfg.save(one)
+    write_safetensors(weights_path(one), t)
+    _shard(many, t, 3, with_index, cfg)
+    files, index = find_weight_files(many)
+    assert len(files) == 3 and (index is not None) == with_index
+    a = load_tensors(one, specs, torch.bfloat16, torch.device("cpu"))
+    b = load_tensors(many, specs, torch.bfloat16, torch.device("cpu"))
+    assert set(a.keys()) == set(b.keys()) == set(t)
+    assert all(torch.equal(a[n], b[n]) and torch.equal(a[n], t[n]) for n in t)
+    assert b.meta("model.layers.1.mlp.up_proj.weight") == (torch.bfloat16, (320, 192))
+    assert len(b.paths()) == 3
+
+
+def test_sharded_folder_errors(tmp_path):
+    from hfcpu_b200.weights import WeightError, WeightFormatError, load_tensors, random_tensors, write_safetensors
+    cfg, specs = _specs(TINY_A)
+    cpu = torch.device("cpu")
+    t = random_tensors(specs, 3, torch.float32)
+    # a tensor missing from its shard, one unexpected, one misshapen: one error over all shards
+    bad = dict(t)
+    del bad["model.layers.1.mlp.down_proj.weight"]
+    bad["model.layers.0.self_attn.k_proj.bias"] = torch.zeros(31)
+    bad["stray.weight"] = torch.zeros(2)
+    folder = str(tmp_path / "bad")
+    wmap = _shard(folder, bad, 3, True, cfg)
+    with pytest.raises(WeightError) as e:
+        load_tensors(folder, specs, torch.float32, cpu)
+    msg = str(e.value)
+    assert "missing (1): model.layers.1.mlp.down_proj.weight" in msg and "unexpected (1): stray.weight" in msg
+    assert "tensor 'model.layers.0.self_attn.k_proj.bias' has shape 31, expected 32" in msg
+    # the index names a tensor that its file does not hold
+    folder = str(tmp_path / "moved")
+    wmap = _shard(folder, t, 3, True, cfg)
+    wmap["model.norm.weight"] = [f for f in set(wmap.values()) if f != wmap["model.norm.weight"]][0]
+    json.dump({"weight_map": wmap}, open(os.path.join(folder, "model.safetensors.index.json"), "w"))
+    with pytest.raises(WeightError, match="tensor 'model.norm.weight' is not in the file the index names"):
+        load_tensors(folder, specs, torch.float32, cpu)
+    # a name in two shards
+    folder = str(tmp_path / "twice")
+    _shard(folder, t, 2, False, cfg)
+    write_safetensors(os.path.join(folder, "extra.safetensors"), {"model.norm.weight": t["model.norm.weight"]})
+    with pytest.raises(WeightFormatError, match="tensor 'model.norm.weight' is in extra.safetensors and model-0000"):
+        load_tensors(folder, specs, torch.float32, cpu)
+    # an index that names a file that is not there; an index that leaves the folder; no weights at all
+    folder = str(tmp_path / "gone")
+    wmap = _shard(folder, t, 3, True, cfg)
+    os.remove(os.path.join(folder, "model-00002-of-00003.safetensors"))
+    with pytest.raises(WeightFormatError, match="names model-00002-of-00003.safetensors, which is not in the folder"):
+        load_tensors(folder, specs, torch.float32, cpu)
+    json.dump({"weight_map": {"a": "../x.safetensors"}}, open(os.path.join(folder, "model.safetensors.index.json"), "w"))
+    with pytest.raises(WeightFormatError, match="leaves the model folder"):
+        load_tensors(folder, specs, torch.float32, cpu)
+    json.dump([1], open(os.path.join(folder, "model.safetensors.index.json"), "w"))
+    with pytest.raises(WeightFormatError, match="not an index"):
+        load_tensors(folder, specs, torch.float32, cpu)
+    empty = str(tmp_path / "empty")
+    os.makedirs(empty)
+    with pytest.raises(WeightFormatError, match="no such file"):
+        load_tensors(empty, specs, torch.float32, cpu)
+
+
+def test_tensors_are_made_one_at_a_time_and_shared_ones_once(tmp_path, emu):
+    """Binding asks the source for each tensor when its part needs it; the embedding of a tied head is made once."""
+    import hfcpu_b200
+    from hfcpu_b200.weights import CheckpointSource
+    cfg, specs = _specs(TINY_A)
+    folder = hfcpu_b200.write_random_model(cfg, str(tmp_path / "m"), seed=1, dtype=torch.float32)
+    made = []
+    orig = CheckpointSource._make
+
+    def spy(self, name):
+        made.append(name)
+        return orig(self, name)
+    CheckpointSource._make = spy
+    try:
+        model = hfcpu_b200.load_model(folder, torch.float32, "cpu")
+    finally:
+        CheckpointSource._make = orig
+    assert sorted(made) == sorted(s.name for s in specs if s.name != "lm_head.weight")        # each exactly once
+    assert model.head.weight.data_ptr() == model.embedding.table.data_ptr()
+    assert model.files == [os.path.join(folder, "model.safetensors")]
+    att = model.layers[0].mixer
+    assert att.w_qkv.shape == (4 * 16 + 2 * 2 * 16, 64) and model.layers[0].ffn.w_gate_up.shape == (2 * 176, 64)
+    # the fused buffers hold what stacking the loaded tensors would give
+    src = hfcpu_b200.weights.load_tensors(folder, specs, torch.float32, torch.device("cpu"))
+    p = "model.layers.0."
+    assert torch.equal(att.w_qkv, torch.cat([src[p + f"self_attn.{x}_proj.weight"] for x in "qkv"]))
+    g, u = src[p + "mlp.gate_proj.weight"], src[p + "mlp.up_proj.weight"]
+    assert torch.equal(model.layers[0].ffn.w_gate_up, torch.stack([g, u], 1).reshape(352, 64))
