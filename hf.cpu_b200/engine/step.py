@@ -59,6 +59,27 @@ class Workspace:
         return b[:n].view(*shape)
 
 
+@dataclass
+class StepBatch:
+    """The host's view of a step, handed to the mixers that build index arrays of their own for it."""
+    q_lens: List[int]                  # tokens each request brings
+    kv_lens: List[int]                 # tokens each request holds after the step
+    starts: List[int]                  # position of each request's first token of the step
+    block_size: int
+
+    @property
+    def num_seqs(self) -> int:
+        return len(self.q_lens)
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(self.q_lens)
+
+    @property
+    def max_q_len(self) -> int:
+        return max(self.q_lens)
+
+
 class StepContext:
     """Per-step batch description handed to every part."""
 
@@ -74,7 +95,7 @@ class StepContext:
         self.h_kv_lens: List[int] = []
         self.h_seq_slots: List[int] = []
         self._groups: List[GroupMeta] = []
-        self._tiles: Dict[tuple, tuple] = {}
+        self._arrays: Dict[Hashable, Dict[str, torch.Tensor]] = {}
 
     def buf(self, name, shape, dtype) -> torch.Tensor:
         return self.engine.workspace.get(name, shape, dtype)
@@ -88,10 +109,9 @@ class StepContext:
     def entry_state(self, entry: int):
         return self.engine.slots.entry_state(entry)
 
-    def attn_tiles(self, heads_per_group: int, warps: int):
-        """Tiles of the step's tokens for the tiled attention kernel: (tile_seq, tile_t0, tile_nt, count), or
-        None when that many heads per group do not fit a tile of 16 * warps rows."""
-        return self._tiles.get((heads_per_group, warps))
+    def arrays(self, key: Hashable) -> Dict[str, torch.Tensor]:
+        """The int32 device arrays a mixer asked for under ``key`` (``Mixer.step_arrays``), by name."""
+        return self._arrays.get(key, {})
 
 
 class Engine:
@@ -126,9 +146,13 @@ class Engine:
         for i, e in enumerate(plan.schedule):
             if e.cache_of is not None and e.cache_of not in cache_specs:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which keeps none")
-        # attention tilings the mixers will ask for: heads per key/value head of every paged-attention mixer
-        self._tile_ratios = sorted({m.H // m.G for m in (l.mixer for l in model.layers)
-                                    if hasattr(m, "H") and hasattr(m, "G") and m.G and m.H % m.G == 0})
+        # index arrays the mixers want built per step (tile lists of their kernels and the like): one owner per key,
+        # so that layers with the same needs share one set
+        self._array_owners: Dict[Hashable, object] = {}
+        for l in model.layers:
+            key = l.mixer.step_arrays_key()
+            if key is not None:
+                self._array_owners.setdefault(key, l.mixer)
         self.cache = KVCacheManager(cache_specs, self.block_size, self.num_pages, model.run_dtype,
                                     self.device, self.max_blocks)
         self.slots = StateSlots(state_specs, self.max_requests, self.device)
@@ -137,7 +161,6 @@ class Engine:
         # pure decode steps are captured once per (batch size, key-split bucket) as a CUDA graph and replayed
         self.use_graphs = (self._pinned and os.environ.get("HFB_GRAPHS", "1") != "0"
                            and all(getattr(p, "graph_safe", False) for p in model.all_parts()))
-        self.wide_attention_tiles = os.environ.get("HFB_PREFILL_WARPS", "8") == "8"
         self._graphs: Dict[tuple, tuple] = {}
         self._static_meta: Dict[int, torch.Tensor] = {}
         self._meta_ring = []            # [host buffer, device buffer, event of its last copy]
@@ -233,30 +256,10 @@ class Engine:
         kv_lens = [w[1] for w in wants]
         max_q = max(q_lens)
         MB = self.max_blocks if static else max(1, (max(kv_lens) + bs - 1) // bs)
-        # rows of an attention tile: 16 per warp; long portions get the wide tile (keys are read half as often)
-        warps = 1 if max_q == 1 else (8 if max_q >= 64 and self.wide_attention_tiles else 4)
-        tilings = []                          # (heads per group, warps, tile_seq, tile_t0, tile_nt)
-        # 16 "warps" names the tiles of the kernel that takes two 128-row tiles per CTA: twice the tokens of one
-        widths = [warps, 16] if warps == 8 else [warps]
-        for ratio in self._tile_ratios:
-            for w in widths:
-                per = (16 * w) // ratio if w < 16 else 2 * (128 // ratio)
-                if per < 1:
-                    continue
-                if max_q == 1:
-                    t_seq = t_t0 = np.arange(S, dtype=np.int32)
-                    t_nt = np.ones(S, dtype=np.int32)
-                else:
-                    ls, lt, ln, t0 = [], [], [], 0
-                    for s_i, n in enumerate(q_lens):
-                        for a in range(0, n, per):
-                            ls.append(s_i)
-                            lt.append(t0 + a)
-                            ln.append(min(per, n - a))
-                        t0 += n
-                    t_seq, t_t0, t_nt = (np.asarray(x, dtype=np.int32) for x in (ls, lt, ln))
-                tilings.append((ratio, w, t_seq, t_t0, t_nt))
-        total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB) + sum(3 * len(t[2]) for t in tilings)
+        batch = StepBatch(q_lens, kv_lens, starts, bs)
+        extras = [(key, {n: np.ascontiguousarray(v, dtype=np.int32) for n, v in mixer.step_arrays(batch).items()})
+                  for key, mixer in self._array_owners.items()]
+        total = 3 * T + (S + 1) + 2 * S + M + len(groups) * (T + S * MB) + sum(len(v) for _, arrs in extras for v in arrs.values())
         # one flat int32 buffer, filled through its numpy view: a single host-to-device copy per step
         ring_slot = self._meta_buffers(total)
         h, d = ring_slot[0], ring_slot[1]
@@ -291,8 +294,9 @@ class Engine:
             blk = pos // bs
             put(tables[seq, blk] * bs + pos % bs)                                  # cache slot of every token
             put(tables.reshape(-1))
-        for _, _, t_seq, t_t0, t_nt in tilings:
-            put(t_seq), put(t_t0), put(t_nt)
+        for _, arrs in extras:
+            for v in arrs.values():
+                put(v)
         assert o == total
         d[:total].copy_(h[:total], non_blocking=True)
         if self._pinned:
@@ -311,11 +315,8 @@ class Engine:
         ctx.cu_tokens, ctx.kv_lens, ctx.seq_slots, ctx.logit_rows = take(S + 1), take(S), take(S), take(M)
         for g in groups:
             ctx._groups.append(GroupMeta(g.index, take(T), take(S * MB, (S, MB)), bs, MB))
-        for ratio, w, t_seq, _, _ in tilings:
-            n = len(t_seq)
-            ctx._tiles[(ratio, w)] = (take(n), take(n), take(n), n)
-            if w == 1 and 64 // ratio >= 1:
-                ctx._tiles[(ratio, 4)] = ctx._tiles[(ratio, 1)]        # one token a tile fits the wider kernel too
+        for key, arrs in extras:
+            ctx._arrays[key] = {n: take(len(v)) for n, v in arrs.items()}
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, M
         ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots
         ctx.max_q_len = max_q

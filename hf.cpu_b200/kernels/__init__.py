@@ -77,11 +77,45 @@ def rope_kv_write(qkv, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache
     backend().rope_kv_write(qkv, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache, H, G, d)
 
 
-def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out) -> None:
+def attention_step_arrays(q_lens, heads_per_group: int):
+    """Tile lists of a step's tokens for the tiled attention kernels, as named int32 arrays.
+
+    A tile holds consecutive tokens of one request: its request index (``seq``), its first token's index in the
+    step (``t0``) and its token count (``nt``).  The heads that share a key/value head are packed into a tile's rows
+    beside the tokens, so a tile of R rows takes R // heads_per_group tokens.  Tile heights: "1" = 16 rows (a step of
+    single tokens; the decode kernels), "4" = 64 rows (short portions), "8" = 128 rows and "16" = two tiles of 128
+    rows per work item (portions of 64 tokens and more).  A height too small for the heads per group is left out."""
+    import numpy as np
+    max_q, S = max(q_lens), len(q_lens)
+    heights = ["1"] if max_q == 1 else (["8", "16"] if max_q >= 64 else ["4"])
+    out = {}
+    for h in heights:
+        per = (16 * int(h)) // heads_per_group if h != "16" else 2 * (128 // heads_per_group)
+        if per < 1:
+            continue
+        if max_q == 1:
+            seq = t0 = np.arange(S, dtype=np.int32)
+            nt = np.ones(S, dtype=np.int32)
+        else:
+            ls, lt, ln, at = [], [], [], 0
+            for s_i, n in enumerate(q_lens):
+                for a in range(0, n, per):
+                    ls.append(s_i)
+                    lt.append(at + a)
+                    ln.append(min(per, n - a))
+                at += n
+            seq, t0, nt = (np.asarray(x, dtype=np.int32) for x in (ls, lt, ln))
+        out[h + ".seq"], out[h + ".t0"], out[h + ".nt"] = seq, t0, nt
+    return out
+
+
+def paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None) -> None:
+    """``tiles``: the device arrays of :func:`attention_step_arrays` for this step (without them only the plain
+    kernel runs)."""
     check_head_dim(d)
     _need(q.shape[1] == H * d and out.shape == q.shape, "attention: shape mismatch")
     _need(q.dtype == k_cache.dtype == v_cache.dtype == out.dtype, "attention: element types differ")
-    backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out)
+    backend().paged_attention(q, k_cache, v_cache, meta, ctx, H, G, d, int(window), float(scale), out, tiles or {})
 
 
 def swiglu(gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:

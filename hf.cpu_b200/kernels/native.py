@@ -134,13 +134,22 @@ class NativeBackend:
                                                c_int64(cache_slots), c_int(T), c_int(H), c_int(G), c_int(d),
                                                self._stream()), "rope_kv_write")
 
-    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out):
+    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tile_arrays):
         self._on_gpu(q, k_cache, v_cache, meta.block_table, ctx.token_seq, ctx.positions, out)
         T = q.shape[0]
-        tiles = getattr(ctx, "attn_tiles", None)
-        if (self.attention == "fast" and tiles is not None and q.dtype == torch.bfloat16 and d in (64, 128)
+        if (self.attention == "fast" and tile_arrays and q.dtype == torch.bfloat16 and d in (64, 128)
                 and 64 % meta.block_size == 0):
             decode = ctx.max_q_len == 1
+
+            def tiles(ratio, height):
+                """(seq, t0, nt, count) of the tile list of that height, or None when the step brought none."""
+                h = str(height)
+                if h + ".seq" not in tile_arrays and decode and height == 4 and 64 // ratio >= 1:
+                    h = "1"                                   # one token a tile fits the wider kernel too
+                seq = tile_arrays.get(h + ".seq")
+                if seq is None:
+                    return None
+                return seq, tile_arrays[h + ".t0"], tile_arrays[h + ".nt"], seq.shape[0]
             if (not decode and self.attention_tc and d == 128 and meta.block_size >= 8 and 128 % meta.block_size == 0
                     and H // G <= 128):
                 # two 128-row tiles per CTA once there is an item for every SM: it does more per key fetched and overlaps

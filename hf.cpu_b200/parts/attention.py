@@ -50,6 +50,13 @@ class PagedAttention(Mixer):
     def cache_spec(self):
         return CacheSpec(self.G, self.d, self.window)
 
+    def step_arrays_key(self):
+        return ("paged_attention_tiles", self.H // self.G)
+
+    def step_arrays(self, batch):
+        # the tile lists of the attention kernels: how they cut the step's tokens is the kernels' business
+        return kernels.attention_step_arrays(batch.q_lens, self.H // self.G)
+
     def tensor_specs(self):
         s = [TensorSpec(self.names["q"] + ".weight", (self.QD, self.E)),
              TensorSpec(self.names["k"] + ".weight", (self.KD, self.E)),
@@ -86,7 +93,7 @@ class PagedAttention(Mixer):
                                meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
         att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
         kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
-                                self.window, self.scale, att)
+                                self.window, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()))
         return att
 
     def forward(self, ctx, xn, residual, cache, state, write_cache):

@@ -98,6 +98,18 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
+    def step_arrays_key(self) -> Optional[Any]:
+        """A hashable name for the int32 index arrays this mixer wants built for every step, or None.  Mixers that
+        return equal keys share one set (the layers of a model usually do)."""
+        return None
+
+    def step_arrays(self, batch) -> Dict[str, Any]:
+        """Called once per step and key with the host's view of the step (``batch.q_lens``, ``.kv_lens``, ``.starts``,
+        ``.block_size``): returns named integer arrays (numpy), which the engine appends to the step's one
+        host-to-device copy.  ``forward`` finds them on the device as ``ctx.arrays(key)[name]``.  For a step of
+        single tokens the sizes must depend on the number of requests only (such steps are replayed as a graph)."""
+        return {}
+
     def forward(self, ctx, xn: torch.Tensor, residual: torch.Tensor, cache, state, write_cache: bool) -> None:
         """Mix ``xn`` ([T, hidden], run dtype) across tokens and add the result into the float32
         ``residual``.  ``cache`` is the entry's :class:`LayerCache` (or None), ``state`` the entry's

@@ -48,7 +48,7 @@ class EmuBackend:
         kf[slots[ok].long()] = rot(x[:, H:H + G])[ok].to(k_cache.dtype)
         vf[slots[ok].long()] = x[:, H + G:][ok].to(v_cache.dtype)
 
-    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out):
+    def paged_attention(self, q, k_cache, v_cache, meta, ctx, H, G, d, window, scale, out, tiles=None):
         T = q.shape[0]
         bs = meta.block_size
         kf, vf = k_cache.view(-1, G, d).float(), v_cache.view(-1, G, d).float()

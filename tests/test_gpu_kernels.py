@@ -154,7 +154,7 @@ def _attention_case(dtype, H, G, d, bs, lens_q, lens_kv, window, spike=None, see
 def _run_attention(impl, case, H, G, d, window):
     q, kc, vc, meta, ctx = case
     out = torch.empty_like(q)
-    impl.paged_attention(q, kc, vc, meta, ctx, H, G, d, window, 1.0 / math.sqrt(d), out)
+    impl.paged_attention(q, kc, vc, meta, ctx, H, G, d, window, 1.0 / math.sqrt(d), out, tiles=getattr(ctx, "tiles", None))
     return out
 
 
@@ -287,14 +287,14 @@ def _with_tiles(case, lens_q, lens_kv, H, G, wide=False):
             for a in range(0, n, per):
                 t_seq.append(s); t_t0.append(t0 + a); t_nt.append(min(per, n - a))
             t0 += n
-        return (dev(t_seq), dev(t_t0), dev(t_nt), len(t_seq))
-    tiles = tiling((16 * warps) // (H // G))
-    double = tiling(2 * (128 // (H // G))) if wide else None      # the kernel with two 128-row tiles per CTA
+        return {"seq": dev(t_seq), "t0": dev(t_t0), "nt": dev(t_nt)}
+    ctx.tiles = {f"{warps}.{k}": v for k, v in tiling((16 * warps) // (H // G)).items()}
+    if wide:                                                      # the kernel with two 128-row tiles per CTA
+        ctx.tiles.update({f"16.{k}": v for k, v in tiling(2 * (128 // (H // G))).items()})
     ws = {}
 
     def buf(name, shape, dtype):
         return ws.setdefault((name, shape, dtype), torch.empty(shape, dtype=dtype, device=DEV))
-    ctx.attn_tiles = lambda ratio, w: (double if w == 16 else tiles if ratio == H // G and (w == warps or (warps == 1 and 64 // ratio >= 1)) else None)
     ctx.max_q_len, ctx.max_kv_len, ctx.buf = max(lens_q), max(lens_kv), buf
     return case
 

@@ -270,6 +270,98 @@ def test_schedule_names_a_layer_twice_and_shares_a_cache(backend, tmp_path):
         assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
 
 
+# ---- a toy mixer with a paged cache and index arrays of its own for every step -------------------------------
+def _toy_paged_mixer():
+    from hfcpu_b200.parts import CacheSpec, Mixer
+    from hfcpu_b200.weights import TensorSpec
+
+    class CachedMean(Mixer):
+        """v_t = x_t W^T goes into the paged cache; out_t = mean of v_0..v_t.  It cuts a step into tiles of three
+        tokens (a tile shape no kernel of the framework has) and asks the engine for the tile list and for every
+        token's cache slots as index arrays: the engine builds neither itself."""
+
+        def __init__(self, hidden_size, prefix, **_):
+            self.E, self.name, self.w = hidden_size, f"{prefix}.w", None
+
+        def cache_spec(self):
+            return CacheSpec(1, self.E, 0)
+
+        def tensor_specs(self):
+            return [TensorSpec(self.name, (self.E, self.E))]
+
+        def bind(self, tensors, run_dtype, device):
+            self.w = tensors[self.name].float()
+
+        def step_arrays_key(self):
+            return ("cached_mean_tiles", 3)
+
+        def step_arrays(self, batch):
+            seq, t0, nt, at = [], [], [], 0
+            for s, n in enumerate(batch.q_lens):
+                for a in range(0, n, 3):
+                    seq.append(s), t0.append(at + a), nt.append(min(3, n - a))
+                at += n
+            return {"seq": seq, "t0": t0, "nt": nt, "first_pos": batch.starts}
+
+        def forward(self, ctx, xn, residual, cache, state, write_cache):
+            meta = ctx.group_meta(cache.group)
+            arr = {k: v.tolist() for k, v in ctx.arrays(self.step_arrays_key()).items()}
+            assert len(arr["first_pos"]) == ctx.num_seqs and sum(arr["nt"]) == ctx.num_tokens
+            v = xn.float() @ self.w.T
+            vf = cache.v.view(-1, self.E)
+            vf[meta.slots.long()] = v.to(vf.dtype)
+            table, bs = meta.block_table.tolist(), meta.block_size
+            for s, t0, nt in zip(arr["seq"], arr["t0"], arr["nt"]):             # one tile of its own shape at a time
+                for t in range(t0, t0 + nt):
+                    pos = arr["first_pos"][s] + (t - ctx.h_cu_tokens[s])
+                    slots = torch.tensor([table[s][j // bs] * bs + j % bs for j in range(pos + 1)], device=vf.device)
+                    residual[t] += vf[slots].float().mean(0)
+    return CachedMean
+
+
+@pytest.mark.parametrize("backend", DEVICES, indirect=True)
+def test_toy_paged_mixer_brings_its_own_step_arrays(backend):
+    import hfcpu_b200
+    from hfcpu_b200.config import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+    from hfcpu_b200.parts import unregister_part
+    from hfcpu_b200.weights import RandomSource
+    hfcpu_b200.register_part("mixer", "toy_cached_mean", _toy_paged_mixer())
+    try:
+        E, V, L = 24, 50, 2
+        norm = lambda n: PartSpec("rmsnorm", {"size": E, "eps": 1e-5, "tensor": n})
+        layers = [LayerSpec(f"t.{l}", PartSpec("prenorm_residual"), norm(f"t.{l}.n1"),
+                            PartSpec("toy_cached_mean", {"hidden_size": E, "prefix": f"t.{l}.mix"}), norm(f"t.{l}.n2"),
+                            PartSpec("swiglu", {"hidden_size": E, "intermediate_size": 40, "prefix": f"t.{l}.ffn"}))
+                  for l in range(L)]
+        plan = ModelPlan(E, V, 128, PartSpec("embedding", {"vocab_size": V, "hidden_size": E, "tensor": "t.embed"}), {},
+                         layers, [ScheduleEntry(l) for l in range(L)], norm("t.norm"),
+                         PartSpec("linear_head", {"vocab_size": V, "hidden_size": E, "tensor": "t.head"}))
+        model = hfcpu_b200.Model(None, torch.float32, torch.device(backend), plan=plan)
+        src = RandomSource(model.tensor_specs(), 3, torch.float32, model.device, std=0.3)
+        W = {n: src[n].double().cpu() for n in src.names()}
+        model.bind(src)
+
+        def reference(ids):
+            x = plain.embed(ids, W["t.embed"])
+            for l in range(L):
+                v = plain.rmsnorm(x, W[f"t.{l}.n1"], 1e-5) @ W[f"t.{l}.mix.w"].T
+                x = x + torch.cumsum(v, 0) / torch.arange(1, len(ids) + 1, dtype=torch.float64)[:, None]
+                x = x + plain.swiglu_ffn(plain.rmsnorm(x, W[f"t.{l}.n2"], 1e-5), W[f"t.{l}.ffn.gate_proj.weight"],
+                                         W[f"t.{l}.ffn.up_proj.weight"], W[f"t.{l}.ffn.down_proj.weight"])
+            return plain.rmsnorm(x, W["t.norm"], 1e-5) @ W["t.head"].T
+        g = torch.Generator().manual_seed(1)
+        reqs = {f"r{i}": torch.randint(0, V, (n,), generator=g).tolist() for i, n in enumerate([37, 8, 50])}
+        ref = {r: reference(ids) for r, ids in reqs.items()}
+        for steps in (traces.whole(reqs), traces.portions(reqs), traces.mixed(reqs, max_live=2)):
+            eng = hfcpu_b200.Engine(model, block_size=4, max_tokens=traces.peak_tokens(steps), max_requests=2)
+            assert list(eng._array_owners) == [("cached_mean_tiles", 3)]
+            got = traces.run_in_process(eng, steps, check=eng.cache.check)
+            bad = traces.first_bad(got, ref, 1e-4)
+            assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} ({bad[2]:.3g})"
+    finally:
+        unregister_part("mixer", "toy_cached_mean")
+
+
 # ---- a feed-forward with routing and another position encoding, both defined here -------------------------
 def _routed_ffn_part():
     from hfcpu_b200.parts import FeedForward
