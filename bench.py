@@ -28,16 +28,94 @@ QWEN25_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hid
                  max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
                  use_sliding_window=False, hidden_act="silu")
 PROMPT, CTX_MAX, BLOCK = 2048, 4096, 16
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+REF_DIR = os.path.join(ROOT, "baseline", "_ref", "hf.cpu")     # a copy of the reference's source tree, built by make
 
 
-def peaks():
+def metric_name(batch):
+    return f"Qwen2.5-7B bf16: decode tok/s @ batch {batch} ({PROMPT:,}-token prompts, {CTX_MAX:,} max context)"
+
+
+def run_reference(args):
+    """The reference arm: the unmodified reference (a C99 CPU program) built by its own Makefile, run through its own
+    command line on the same layer sizes with the same seeded random bf16 weights, written as one of its GGUF files.
+
+        hfcpu --stdin-mode args --model M.gguf ...   with two request lines
+        --op generate --prompt-ids "<2,048 ids>" --n 8 --temp 0 --max-tokens W+1     (warm-up)
+        --op generate --prompt-ids "<the same>"  --n 8 --temp 0 --max-tokens K+1     (timed by the reference itself)
+
+    ``--n 8`` decodes eight continuations of the prompt together, one forward of eight tokens a step
+    (src/ops.c:808-893); the second request starts on the first one's cache of the prompt (src/ops.c:771-776) and its
+    ``@genall ms=`` covers exactly K decode steps.  It is a CPU program, so it runs ``--ref-layers`` of the 28 layers
+    to stay within minutes; ``config`` names both numbers."""
+    import shutil
+    import tempfile
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    if args.gpus != 1:
+        return unavailable("the reference is a single-process CPU program; it has no multi-GPU form")
+    if not os.path.isdir(REF_DIR):
+        if not os.path.isdir("/root/reference"):
+            return unavailable(f"no copy of the reference's source tree at {os.path.relpath(REF_DIR, ROOT)}")
+        shutil.copytree("/root/reference", REF_DIR)
+    exe = os.path.join(REF_DIR, "hfcpu")
+    if not os.path.exists(exe):
+        try:
+            r = subprocess.run(["make", "-C", REF_DIR, "hfcpu"], capture_output=True, text=True, timeout=600)
+        except (OSError, subprocess.TimeoutExpired) as e:
+            return unavailable(f"make -C {os.path.relpath(REF_DIR, ROOT)} hfcpu: {e}")
+        if r.returncode != 0 or not os.path.exists(exe):
+            return unavailable(f"make -C {os.path.relpath(REF_DIR, ROOT)} hfcpu failed: " + (r.stderr or r.stdout).strip()[-300:].replace("\n", " | "))
+    import torch
+    import hfcpu_b200
+    from hfcpu_b200.config import config_from_dict
+    from hfcpu_b200.models import build_model_specs
+    from hfcpu_b200.weights import RandomSource
+    from hfcpu_b200.weights.gguf import write_gguf
+    cfg_d = dict(QWEN25_7B, num_hidden_layers=min(args.ref_layers, QWEN25_7B["num_hidden_layers"]))
+    cfg = config_from_dict(cfg_d)
+    warmup, steps = max(args.warmup, 3), args.steps
+    work = tempfile.mkdtemp(prefix="hfb_ref_")
     try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            p = json.load(f)
-        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"])}, "measured"
-    except (OSError, KeyError, ValueError, TypeError):
-        return dict(FALLBACK_PEAKS), "fallback"
+        gguf = os.path.join(work, "model.gguf")
+        write_gguf(gguf, cfg, RandomSource(build_model_specs(cfg), 0, torch.bfloat16, torch.device("cpu")))
+        ids = " ".join(map(str, synthetic_prompts(1, PROMPT, cfg.vocab_size, seed=1)[0]))
+        script = "".join(f"--op generate --prompt-ids '{ids}' --n {args.batch} --temp 0 --max-tokens {n + 1} --id {tag}\n"
+                         for tag, n in (("warm", warmup), ("timed", steps)))
+        t0 = time.perf_counter()
+        try:
+            r = subprocess.run([exe, "--stdin-mode", "args", "--model", gguf, "--ctx-max", str(CTX_MAX), "--batch", "64",
+                                "--log-level", "error"], input=script, capture_output=True, text=True, timeout=args.ref_timeout)
+        except subprocess.TimeoutExpired:
+            return unavailable(f"the reference did not finish {PROMPT} prompt tokens and {warmup + steps} decode steps at "
+                               f"{cfg.num_hidden_layers} layers on this machine's CPU within {args.ref_timeout} s")
+        wall = time.perf_counter() - t0
+        genall = [l for l in r.stdout.splitlines() if l.startswith("@genall")]
+        if r.returncode != 0 or len(genall) != 2:
+            return unavailable("hfcpu --op generate failed: " + (r.stdout + r.stderr).strip()[-300:].replace("\n", " | "))
+        f = dict(kv.split("=", 1) for kv in genall[1].split()[1:])
+        ms = float(f["ms"]) / steps
+        value = args.batch * steps / (float(f["ms"]) * 1e-3)
+        prefill = [l for l in r.stdout.splitlines() if l.startswith("@prefill")][0]
+        pf = dict(kv.split("=", 1) for kv in prefill.split()[1:])
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+    print(json.dumps({
+        "metric": metric_name(args.batch), "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random-init weights)", "impl": "reference",
+        "device": "cpu", "gpu_launches": 0,
+        "config": {"model": "Qwen2.5-7B layer sizes", "layers": cfg.num_hidden_layers, "layers_full": QWEN25_7B["num_hidden_layers"],
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "ffn": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": PROMPT, "ctx_max": CTX_MAX, "kv_block": 64, "kv_dtype": "f16",
+                   "parallelism": "CPU threads (the reference has no GPU path)",
+                   "how": "hfcpu --op generate --n 8 --temp 0, timed by its own @genall"},
+        "prefill": {"value": float(pf["tok_per_s"]), "tokens": int(pf["tokens"]), "ms": float(pf["ms"])},
+        "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": round(wall, 1)}))
+    return 0
 
 
 class ClockSampler:
@@ -144,16 +222,15 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (the record uses 2,048; others are for profiling)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
+    ap.add_argument("--ref-layers", type=int, default=4, help="layers the reference arm runs (it is a CPU program)")
+    ap.add_argument("--ref-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = ap.parse_args()
     if args.prompt != PROMPT:
         PROMPT = args.prompt
         CTX_MAX = max(CTX_MAX, 2 * PROMPT)
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "pip cannot install ebowh/hf.cpu offline: it has neither setup.py nor pyproject.toml "
-                          "(a C99 CPU program built by make; no GPU path, no bf16 safetensors input)"}))
-        return 0
+        return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -163,6 +240,7 @@ def main():
     import hfcpu_b200
     from hfcpu_b200 import StepEntry, kernels
     from hfcpu_b200.config import config_from_dict
+    from hfcpu_b200.engine import measure
 
     cfg_d = dict(QWEN25_7B)
     layers_full = cfg_d["num_hidden_layers"]
@@ -176,13 +254,11 @@ def main():
     max_b = max(64, args.batch)
     pages = max_b * ((PROMPT + warmup + args.steps + 64 + BLOCK - 1) // BLOCK + 1)
     engine = hfcpu_b200.Engine(model, block_size=BLOCK, num_pages=pages, max_requests=max_b, ctx_max=CTX_MAX)
-    pk, pk_src = peaks()
-    weight_bytes = model.weight_bytes_per_step()
-    kv_per_token = sum(g.page_bytes for g in engine.cache.groups) // BLOCK
+    pk, pk_src = measure.load_peaks(ROOT)
 
-    # ---- prefill: one prompt of 2,048 tokens -------------------------------------------------------
+    # ---- prefill: one prompt of 2,048 tokens, eight times over; the median of the last six ----------------
     pre_ms = []
-    for i, ids in enumerate(synthetic_prompts(4, PROMPT, V, seed=100)):
+    for i, ids in enumerate(synthetic_prompts(8, PROMPT, V, seed=100)):
         engine.add_request(("pre", i))
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -192,21 +268,21 @@ def main():
         torch.cuda.synchronize()
         pre_ms.append(e0.elapsed_time(e1))
         engine.finish_request(("pre", i))
-    pre = min(pre_ms[1:])
+    kernels.check_device_errors()
+    pre = statistics.median(pre_ms[2:])
     L, E, F = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size
-    QD, KD = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
-    per_token = 2 * L * (E * (QD + 2 * KD) + QD * E + 3 * E * F)
-    flops = PROMPT * per_token + L * 2 * QD * PROMPT * PROMPT + 2 * E * V      # causal attention: 4*QD*T^2/2
+    flops = measure.step_flops(model, [PROMPT], [PROMPT], 1)
     prefill = {"value": round(PROMPT / pre * 1e3, 1), "tokens": PROMPT, "ms": round(pre, 3),
                "frac": round(flops / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflop": round(flops / 1e12, 2),
-               "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src}
+               "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src, "best_ms": round(min(pre_ms[2:]), 3)}
 
     # ---- decode: the default batch, timed with clocks sampled ------------------------------------------
     sampler = ClockSampler()
     ms, ctx_mid, launches = time_decode(engine, args.batch, args.steps, warmup, V, seed=1, sampler=sampler)
     clocks = sampler.stop()
+    kernels.check_device_errors()          # a number from a step whose kernels gave up is no number
     value = args.batch / ms * 1e3
-    step_bytes = weight_bytes + args.batch * ctx_mid * kv_per_token
+    step_bytes = measure.decode_step_bytes(engine, [ctx_mid] * args.batch)
     achieved = step_bytes / (ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk_src,
@@ -217,6 +293,7 @@ def main():
         for b in (1, 64):
             pms, _, _ = time_decode(engine, b, args.steps, warmup, V, seed=2 + b)
             points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+        kernels.check_device_errors()
         # ---- end to end through the Python entry point: host ids in, host ids out -----------------------
         del engine
         torch.cuda.empty_cache()
@@ -236,7 +313,7 @@ def main():
                "d2h_bytes_per_step": 4 * args.batch}
 
     line = {
-        "metric": f"Qwen2.5-7B bf16: decode tok/s @ batch {args.batch} ({PROMPT:,}-token prompts, {CTX_MAX:,} max context)",
+        "metric": metric_name(args.batch),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random-init weights)",

@@ -103,7 +103,13 @@ class Session:
                 c.stop, c.error = ev.stop, ev.error
             if on_event:
                 on_event(ev)
-        self.scheduler.run(handle)
+        try:
+            self.scheduler.run(handle)
+        except BaseException:
+            # nothing of a failed call stays behind to be scheduled with the next one
+            self.scheduler.abort(list(results))
+            self.scheduler.drop_retained()
+            raise
         out = [[results[(self._serial, pi, si)] for si in range(n)] for pi in range(len(prompts))]
         return out[0] if single else out
 

@@ -28,6 +28,8 @@ class Failure(Exception):
 
 
 class App:
+    device = "cuda:0"               # where --random-weights models are made (the engine has no CPU path)
+
     def __init__(self, session_opts: Dict[str, Any], out: EventWriter):
         self.o, self.out = session_opts, out
         self.n_requests = self.n_errors = 0
@@ -92,19 +94,45 @@ class App:
         if body:
             raise Failure("ENOTSUP", "a text prompt needs a tokenizer, which this engine does not have; use --prompt-ids")
 
+    def _random_model(self):
+        """The model of --random-weights CONFIG.json: the configuration's class from the registry, weights drawn on
+        the device from --weights-seed (the role of the reference's tools/mkmodel.pl:104-119, without a file)."""
+        import json
+        import torch
+        import hfcpu_b200
+        from hfcpu_b200.config import config_from_dict
+        path = self.o["random_weights"]
+        try:
+            with open(path) as f:
+                d = json.load(f)
+        except OSError as e:
+            raise Failure("EIO", f"{path}: {e.strerror}") from None
+        except ValueError as e:
+            raise Failure("EFORMAT", f"{path}: not valid JSON ({e})") from None
+        if not isinstance(d, dict):
+            raise Failure("EFORMAT", f"{path}: top level must be an object")
+        seed = self.o["weights_seed"] if self.o["weights_seed"] is not None else self.o["seed"]
+        dtype = torch.float32 if self.o["dtype"] in ("fp32", "float32") else torch.bfloat16
+        return hfcpu_b200.random_model(config_from_dict(d), seed=int(seed), dtype=dtype, device=self.device,
+                                       std=float(self.o["weights_std"]))
+
     def _resident(self, eff):
         path = eff["model"]
-        if not path:
-            raise Failure("EINVAL", f"{eff['op'] or 'generate'} needs --model PATH")
+        random = self.o["random_weights"]
+        if not path and not random:
+            raise Failure("EINVAL", f"{eff['op'] or 'generate'} needs --model PATH (or --random-weights CONFIG.json)")
         import hfcpu_b200
         from hfcpu_b200.config import ConfigError, UnsupportedError
         from hfcpu_b200.weights import WeightError, WeightFormatError
+        if not path:
+            path = "random:" + os.path.abspath(random)
         from hfcpu_b200.weights import find_weight_files
         try:
-            files = find_weight_files(path)[0] if os.path.isdir(path) else [path]
-            key = (os.path.abspath(path),) + tuple((f, os.stat(f).st_size, os.stat(f).st_mtime_ns) for f in files)
+            files = ([random] if path.startswith("random:") else
+                     find_weight_files(path)[0] if os.path.isdir(path) else [path])
+            key = (path,) + tuple((f, os.stat(f).st_size, os.stat(f).st_mtime_ns) for f in files)
         except (OSError, WeightFormatError):
-            key = (os.path.abspath(path), -1, -1)
+            key = (path, -1, -1)
         if self.session is not None and self.session_key == key:
             return self.session
         self.session = None
@@ -113,7 +141,7 @@ class App:
             eos = parse_ids(self.o["eos_ids"], 1 << 31)
         try:
             self.session = hfcpu_b200.Session(
-                path, dtype=self.o["dtype"], ctx_max=int(self.o["ctx_max"]), batch=int(self.o["batch"]),
+                self._random_model() if path.startswith("random:") else path, dtype=self.o["dtype"], ctx_max=int(self.o["ctx_max"]), batch=int(self.o["batch"]),
                 kv_block=self.o["kv_block"], kv_pages=int(self.o["kv_pages"]), kv_mem=int(self.o["kv_mem"]),
                 max_seqs=self.o["max_seqs"], max_batched_tokens=self.o["max_batched_tokens"], eos_ids=eos)
         except UnsupportedError as e:
@@ -259,8 +287,16 @@ class App:
                 for r in reqs:
                     sch.cancel(r.id)
                 self.cancel_requested = False
-            with (prof.phase("decode" if t_prefill is not None else "prefill") if prof else _null()):
-                events = sch.step()
+            try:
+                with (prof.phase("decode" if t_prefill is not None else "prefill") if prof else _null()):
+                    events = sch.step()
+            except Exception as e:
+                # nothing of this request stays behind in the resident session
+                sch.abort([r.id for r in reqs])
+                sch.drop_retained()
+                if prof:
+                    prof.close()
+                raise Failure(_code_of(e), str(e)) from None
             if t_prefill is None and all(r.computed >= len(r.prompt) or r.status == "finished" for r in reqs):
                 t_prefill = time.perf_counter() - t0
                 cached = sum(r.shared for r in reqs)
@@ -279,11 +315,12 @@ class App:
                     self.out.event("token", **seq, pos=ev.pos, id=ev.token, **extra)
                 elif ev.error:
                     errors.append(ev.error)
+        if prof:
+            prof.emit(self.out, "decode")
+            prof.close()
         if errors:
             code, _, msg = errors[0].partition(": ")
             raise Failure(code, msg)
-        if prof:
-            prof.emit(self.out, "decode")
         dt = time.perf_counter() - (t_dec0 if t_prefill is not None else t0)
         total = 0
         for r in reqs:
@@ -297,12 +334,16 @@ class App:
 
     def op_bench(self, eff, body):
         """Prefill and decode speed over synthetic ids (src/ops.c:942-1031): ids from xorshift modulo
-        min(V, 2000) (src/ops.c:977-979), median over --probe-reps runs, one @bench line per batch size."""
+        min(V, 2000) (src/ops.c:977-979), median over --probe-reps runs, one @bench line per batch size, with the
+        fraction of the measured memory bandwidth the decode steps reach and of the tensor-core peak the prefill."""
         import statistics
         import torch
-        from hfcpu_b200.engine import StepEntry
+        from hfcpu_b200 import kernels
+        from hfcpu_b200.cache import OutOfPages, OutOfSlots
+        from hfcpu_b200.engine import StepEntry, measure
         sess = self._resident(eff)
         eng = sess.engine
+        cuda = eng.device.type == "cuda"
         V = min(eng.model.plan.vocab_size, 2000)
         n_prompt, n_gen = eff["bench_prompt"], eff["bench_gen"]
         if n_prompt + n_gen > eng.ctx_max:
@@ -311,11 +352,15 @@ class App:
             batches = [int(x) for x in str(eff["bench_batch"]).replace(",", " ").split()]
         except ValueError:
             raise Failure("EINVAL", "--bench-batch must be a list of integers") from None
+        peaks, peak_source = measure.load_peaks()
+        chunk = sess.scheduler.prefill_chunk
         x = 0x9E3779B97F4A7C15
+        sync = (lambda: torch.cuda.synchronize(eng.device)) if cuda else (lambda: None)
         for B in batches:
             if B < 1 or B > eng.max_requests:
                 raise Failure("ERANGE", f"--bench-batch {B} exceeds --max-seqs {eng.max_requests}")
-            pre, dec = [], []
+            pre, dec, pre_flops = [], [], 0.0
+            ids_dev = [torch.empty(B, dtype=torch.int32, device=eng.device) for _ in range(2)]
             for _ in range(eff["probe_reps"]):
                 prompts = []
                 for b in range(B):
@@ -326,29 +371,55 @@ class App:
                     prompts.append(ids)
                     eng.add_request(("bench", b))
                 try:
-                    torch.cuda.synchronize() if eng.device.type == "cuda" else None
+                    first = torch.empty(1, dtype=torch.int32, device=eng.device)
+                    sync()
                     t0 = time.perf_counter()
+                    pre_flops = 0.0
                     for b in range(B):
-                        for a in range(0, n_prompt, sess.scheduler.prefill_chunk):
-                            chunk = prompts[b][a:a + sess.scheduler.prefill_chunk]
-                            last = a + len(chunk) == n_prompt
-                            logits = eng.step([StepEntry(("bench", b), chunk, [len(chunk) - 1] if last else [])])
-                        prompts[b] = int(torch.argmax(logits[0]))
-                    torch.cuda.synchronize() if eng.device.type == "cuda" else None
-                    pre.append(B * n_prompt / (time.perf_counter() - t0))
+                        for a in range(0, n_prompt, chunk):
+                            part = prompts[b][a:a + chunk]
+                            last = a + len(part) == n_prompt
+                            logits = eng.step([StepEntry(("bench", b), part, [len(part) - 1] if last else [])])
+                            pre_flops += measure.step_flops(eng.model, [len(part)], [a + len(part)], 1 if last else 0)
+                        kernels.argmax(logits, first)
+                        ids_dev[0][b:b + 1].copy_(first)
+                    sync()
+                    pre.append(time.perf_counter() - t0)
+                    entries = [StepEntry(("bench", b), [0], [0]) for b in range(B)]
                     t0 = time.perf_counter()
-                    toks = prompts
-                    for _ in range(n_gen):
-                        logits = eng.step([StepEntry(("bench", b), [toks[b]], [0]) for b in range(B)])
-                        toks = torch.argmax(logits, dim=-1).tolist()
-                    dec.append(B * n_gen / (time.perf_counter() - t0))
-                except Exception as e:      # out of pages and the like
+                    for i in range(n_gen):
+                        # the ids the arg-max kernel wrote feed the next step on the device
+                        logits = eng.step(entries, token_source=ids_dev[i & 1])
+                        kernels.argmax(logits, ids_dev[(i + 1) & 1])
+                    sync()
+                    dec.append(time.perf_counter() - t0)
+                    kernels.check_device_errors()
+                except (OutOfPages, OutOfSlots) as e:
                     raise Failure("ENOMEM", str(e)) from None
+                except Exception as e:
+                    raise Failure(_code_of(e), str(e)) from None
                 finally:
                     for b in range(B):
                         eng.finish_request(("bench", b))
-            self.out.event("bench", batch=B, prefill_tok_s=f"{statistics.median(pre):.2f}",
-                           decode_tok_s=f"{statistics.median(dec):.2f}", prompt_tokens=n_prompt, gen_tokens=n_gen)
+            t_pre, t_dec = statistics.median(pre), statistics.median(dec)
+            frac = measure.fractions(eng, decode_ms=t_dec / n_gen * 1e3, decode_kv_lens=[n_prompt + n_gen // 2] * B, peaks=peaks)
+            mma = pre_flops / t_pre / (peaks["bf16_tflops"] * 1e12) if t_pre > 0 else 0.0
+            self.out.event("bench", batch=B, prefill_tok_s=f"{B * n_prompt / t_pre:.2f}",
+                           decode_tok_s=f"{B * n_gen / t_dec:.2f}", prompt_tokens=n_prompt, gen_tokens=n_gen,
+                           hbm_frac=f"{frac.get('hbm_frac', 0.0):.4g}", mma_frac=f"{mma:.4g}", peaks=peak_source)
+
+
+def _code_of(e: Exception) -> str:
+    """The status name of an exception that ended a request."""
+    from hfcpu_b200.cache import OutOfPages, OutOfSlots
+    from hfcpu_b200.config import UnsupportedError
+    if isinstance(e, (OutOfPages, OutOfSlots, MemoryError)):
+        return "ENOMEM"
+    if isinstance(e, UnsupportedError):
+        return "ENOTSUP"
+    if isinstance(e, (ValueError, KeyError)):
+        return "EINVAL"
+    return "EIO"
 
 
 class _null:
@@ -360,11 +431,20 @@ class _null:
 
 
 class Profiler:
-    """Wall-clock per stage for ``--profile`` (the reference reports per-phase accumulators, src/ops.c:593-604)."""
+    """``--profile``: per stage (prefill, decode) the steps, their wall-clock time and where the device spent it, with
+    the reference's phase names (src/model.h:75-79; its @profile line, src/ops.c:593-604): embed, glue (norms), qkv,
+    attn, wo, gate_up, silu, down, head, quant, and ``sample``; ``host`` is the wall-clock time not covered by the
+    phases.  While it is on, steps run kernel by kernel with CUDA events around each part's kernels, not as graphs."""
 
     def __init__(self):
+        from hfcpu_b200 import kernels
+        self.kernels = kernels
         self.acc: Dict[str, float] = {}
         self.steps: Dict[str, int] = {}
+        kernels.profile.enable(True)
+
+    def close(self):
+        self.kernels.profile.enable(False)
 
     def phase(self, name):
         prof = self
@@ -380,7 +460,10 @@ class Profiler:
         return P()
 
     def emit(self, out, stage):
-        out.event("profile", stage=stage, steps=self.steps.get(stage, 0), step_ms=f"{self.acc.get(stage, 0.0) * 1e3:.1f}")
+        phases = self.kernels.profile.take()
+        wall = self.acc.get(stage, 0.0) * 1e3
+        out.event("profile", stage=stage, steps=self.steps.get(stage, 0), step_ms=f"{wall:.1f}",
+                  **{k: f"{v:.1f}" for k, v in phases.items()}, host=f"{max(wall - sum(phases.values()), 0.0):.1f}")
 
 
 def parse_ids(text: str, vocab: int) -> List[int]:

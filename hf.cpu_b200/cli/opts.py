@@ -61,6 +61,10 @@ OPTIONS: List[Opt] = [
     Opt("max-seqs", INT, SESSION, 64, "requests decoded together at most", 1, 4096),
     Opt("max-batched-tokens", INT, SESSION, 2048, "tokens per step at most", 1, 1 << 20),
     Opt("eos-ids", STR, SESSION, None, "end-of-generation token ids, space or comma separated (default: config.json)"),
+    Opt("random-weights", STR, SESSION, None, "a config.json: run a model of that configuration with seeded random "
+        "weights made on the device (no --model needed)"),
+    Opt("weights-seed", U64, SESSION, None, "seed of --random-weights (default: the command line's --seed)"),
+    Opt("weights-std", DBL, SESSION, 0.02, "standard deviation of --random-weights", 0, 10),
 
     Opt("op", STR, REQUEST, "generate", "generate | bench | echo"),
     Opt("model", STR, REQUEST, None, "model folder (config.json + safetensors, one file or shards) or a .gguf file"),

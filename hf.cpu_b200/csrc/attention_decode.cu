@@ -32,29 +32,7 @@ __device__ __forceinline__ uint32_t tma_off(int row, int c)
     return (uint32_t)(c >> 3) * ADT_SUB + (uint32_t)row * 128u + (uint32_t)(((c & 7) ^ (row & 7)) << 4);
 }
 
-// Thread-block clusters: the address of a shared-memory word in another CTA of the cluster, a read from there, and
-// the cluster-wide barrier (every thread of every CTA of the cluster takes part).
-__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank)
-{
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr)
-{
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-    return v;
-}
-__device__ __forceinline__ void cluster_sync_all()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// CLUSTER: the CTAs that share a request's keys (blockIdx.z = 0 .. splits - 1) form a thread-block cluster and merge
-// their results through distributed shared memory, in split order, instead of through global memory and a second
-// kernel.
-template <int D, int STAGES, bool CLUSTER>
+template <int D, int STAGES>
 __global__ void __launch_bounds__(ADT_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p,
                             int num_slots, int *err)
@@ -228,7 +206,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     // ---- merge the four warps (they saw disjoint keys) in warp order -------------------------------------
     __syncthreads();                                      // every tile has been used: its buffers are free
     const bool dead = *abort_flag != 0;
-    if (dead && !CLUSTER) {
+    if (dead) {
         // a wait ran out: give copies that are still in flight time to land before the shared memory goes away
         if (threadIdx.x == 0)
             for (int i = 0; i < 2000; i++) __nanosleep(1000);
@@ -238,7 +216,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     float *mo = (float *)gen;                             // [4][16][D]
     float *mml = mo + 4 * 16 * D;                         // [4][16][2]
     float *fac = mml + 4 * 16 * 2;                        // [16][4] weights of the warps, then [16] maxima and [16] sums
-    float *mine = fac + 96;                               // [16][D]: this CTA's merged, unnormalised rows (cluster form)
     if (warp < 4) {
 #pragma unroll
         for (int i = 0; i < D / 8; i++) {
@@ -278,54 +255,24 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const float denom = fac[80 + row];
         const int tok = t0 + row / r, head = g * r + row % r;
         const size_t th = (size_t)tok * p.H + head;
-        if (CLUSTER) {
-            mine[idx] = acc;
-        } else if (p.splits > 1) {
+        if (p.splits > 1) {
             p.part_o[(th * p.splits + split) * D + col] = acc;
             if (col == 0) *(float2 *)(p.part_ml + (th * p.splits + split) * 2) = make_float2(fac[64 + row], denom);
         } else {
             p.out[th * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
         }
     }
-    if (CLUSTER) {
-        // every CTA of the cluster has its rows, maxima and sums in place; each then merges a share of the output
-        // elements over all CTAs, in split order
-        cluster_sync_all();
-        const int total = rows * D, share = (total + p.splits - 1) / p.splits;
-        const uint32_t a_mine = smem_u32(mine), a_max = smem_u32(fac + 64), a_sum = smem_u32(fac + 80);
-        for (int idx = split * share + threadIdx.x; idx < min(total, (split + 1) * share) && !dead; idx += ADT_THREADS) {
-            const int row = idx / D, col = idx % D;
-            float m = -INFINITY;
-            for (int s = 0; s < p.splits; s++) m = fmaxf(m, ld_cluster_f32(cluster_map(a_max + 4 * row, s)));
-            float denom = 0.f, acc = 0.f;
-            for (int s = 0; s < p.splits; s++) {
-                const float ms = ld_cluster_f32(cluster_map(a_max + 4 * row, s));
-                if (ms == -INFINITY) continue;
-                const float f = fast_exp2(ms - m);
-                denom += ld_cluster_f32(cluster_map(a_sum + 4 * row, s)) * f;
-                acc += ld_cluster_f32(cluster_map(a_mine + 4 * idx, s)) * f;
-            }
-            const int tok = t0 + row / r, head = g * r + row % r;
-            p.out[((size_t)tok * p.H + head) * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
-        }
-        cluster_sync_all();                               // nobody leaves while its shared memory may still be read
-        if (dead) {
-            if (threadIdx.x == 0)
-                for (int i = 0; i < 2000; i++) __nanosleep(1000);
-            __syncthreads();
-        }
-    }
 }
 
-template <int D, int STAGES, bool CLUSTER>
+template <int D, int STAGES>
 static int launch_decode_tma(const CUtensorMap &mk, const CUtensorMap &mv, const AttnParams &p, int num_slots, int n_tiles, cudaStream_t st)
 {
     constexpr uint32_t TILE = (D / 64) * ADT_SUB;
     constexpr int smem = 1024 + 2 * STAGES * TILE + 16 * D * 2 + 16 * STAGES + 16;
-    static_assert(2 * STAGES * TILE >= (4 * 16 * (D + 2) + 96 + 16 * D) * 4, "the merge reuses the tile buffers");
+    static_assert(2 * STAGES * TILE >= (4 * 16 * (D + 2) + 96) * 4, "the merge reuses the tile buffers");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, STAGES, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_decode: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -341,25 +288,18 @@ static int launch_decode_tma(const CUtensorMap &mk, const CUtensorMap &mv, const
         attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
         n_attr++;
     }
-    if (CLUSTER) {
-        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-        attr[n_attr].val.clusterDim.x = 1;
-        attr[n_attr].val.clusterDim.y = 1;
-        attr[n_attr].val.clusterDim.z = p.splits;
-        n_attr++;
-    }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    g_launch_err = cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<D, STAGES, CLUSTER>, mk, mv, p, num_slots, error_word());
+    g_launch_err = cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<D, STAGES>, mk, mv, p, num_slots, error_word());
     return check_pdl_launch(g_launch_err, "attention_decode");
 }
 
-template <int D, bool CLUSTER>
+template <int D>
 static int launch_decode_stages(int stages, const CUtensorMap &mk, const CUtensorMap &mv, const AttnParams &p, int num_slots, int n_tiles, cudaStream_t st)
 {
-    return stages >= 4 ? launch_decode_tma<D, 4, CLUSTER>(mk, mv, p, num_slots, n_tiles, st)
-         : stages == 3 ? launch_decode_tma<D, 3, CLUSTER>(mk, mv, p, num_slots, n_tiles, st)
-                       : launch_decode_tma<D, 2, CLUSTER>(mk, mv, p, num_slots, n_tiles, st);
+    return stages >= 4 ? launch_decode_tma<D, 4>(mk, mv, p, num_slots, n_tiles, st)
+         : stages == 3 ? launch_decode_tma<D, 3>(mk, mv, p, num_slots, n_tiles, st)
+                       : launch_decode_tma<D, 2>(mk, mv, p, num_slots, n_tiles, st);
 }
 
 }  // namespace hfb
@@ -369,13 +309,13 @@ using namespace hfb;
 // Decode attention (tiles of one or two tokens of one request each, as hfb_attention_fast's 16-row form makes
 // them): bfloat16, head_dim 64 or 128, block sizes 8..64 that divide 64, at most 16 query rows per tile.
 // `stages` tiles of 64 keys are in flight per CTA (2..4); `splits` > 1 cuts each request's keys over that many
-// CTAs and needs hfb_attention_fast_scratch(T, H, d, splits) bytes of float32 scratch, unless `cluster` is set:
-// then the 2..8 CTAs of a request form a thread-block cluster and merge through distributed shared memory.
+// CTAs and needs hfb_attention_fast_scratch(T, H, d, splits) bytes of float32 scratch; a second kernel merges the
+// splits in split order.
 extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                                     int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                                     const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size,
                                     int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
-                                    int T, int H, int G, int d, int cluster, hfb_stream s)
+                                    int T, int H, int G, int d, hfb_stream s)
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_decode: head_dim %d (64 and 128 only)", d);
@@ -385,8 +325,7 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
     if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
         return fail(HFB_ENOTSUP, "attention_decode: operands must be 16-byte aligned");
     if (splits < 1 || G > 65535 || splits > 65535) return fail(HFB_EINVAL, "attention_decode: bad split or group count");
-    if (cluster && (splits < 2 || splits > 8)) return fail(HFB_EINVAL, "attention_decode: a cluster takes 2 to 8 splits (got %d)", splits);
-    if (!cluster && splits > 1 && (!scratch || scratch_bytes < (size_t)T * H * splits * (d + 2) * sizeof(float)))
+    if (splits > 1 && (!scratch || scratch_bytes < (size_t)T * H * splits * (d + 2) * sizeof(float)))
         return fail(HFB_EINVAL, "attention_decode: scratch of %zu bytes is too small for %d splits", scratch_bytes, splits);
     CUtensorMap mk, mv;
     int rc;
@@ -401,10 +340,8 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.splits = splits;
     p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
     cudaStream_t st = (cudaStream_t)s;
-    if (cluster) return d == 128 ? launch_decode_stages<128, true>(stages, mk, mv, p, slots, n_tiles, st)
-                                 : launch_decode_stages<64, true>(stages, mk, mv, p, slots, n_tiles, st);
-    rc = d == 128 ? launch_decode_stages<128, false>(stages, mk, mv, p, slots, n_tiles, st)
-                  : launch_decode_stages<64, false>(stages, mk, mv, p, slots, n_tiles, st);
+    rc = d == 128 ? launch_decode_stages<128>(stages, mk, mv, p, slots, n_tiles, st)
+                  : launch_decode_stages<64>(stages, mk, mv, p, slots, n_tiles, st);
     if (rc != HFB_OK || splits == 1) return rc;
     return launch_attention_combine(p, T, d, st);
 }

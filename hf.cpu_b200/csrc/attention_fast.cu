@@ -205,209 +205,6 @@ attention_fast_kernel(AttnParams p, int *err)
     }
 }
 
-// Decode form: at most 16 rows (the query heads of one key/value head for one or two tokens), four warps that
-// share every 64-key tile between them, 16 keys each, each with a running maximum and sum of its own; at the
-// end the four partial results are merged in warp order through shared memory, exactly as splits are.
-template <int D, int STAGES>
-__global__ void __launch_bounds__(128)
-attention_decode_kernel(AttnParams p, int *err)
-{
-    HFB_TRACE_ENTRY(3);
-    pdl_sync();
-    constexpr int CH = D / 8, NT = 128;
-    extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t sq = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t sk = sq + 16 * D * 2, sv = sk + STAGES * ABN * D * 2;
-    const int tile = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = p.H / p.G;
-    const int seq = p.tile_seq[tile], t0 = p.tile_t0[tile], nt = p.tile_nt[tile];
-    const int32_t *table = p.block_table + (size_t)seq * p.max_blocks;
-    const int pos_first = p.positions[t0], pos_last = p.positions[t0 + nt - 1];
-    const int lo_all = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    int kt_lo = lo_all / ABN, kt_hi = pos_last / ABN + 1;
-    if (p.splits > 1) {
-        int per = (kt_hi - kt_lo + p.splits - 1) / p.splits;
-        kt_lo = kt_lo + split * per;
-        kt_hi = min(kt_hi, kt_lo + per);
-    }
-    for (int i = threadIdx.x; i < 16 * CH; i += NT) {
-        int row = i / CH, c = i % CH;
-        int tl = row / r, hl = row % r;
-        bool valid = tl < nt;
-        const __nv_bfloat16 *src = p.q + ((size_t)(t0 + (valid ? tl : 0)) * p.H + g * r + hl) * D + c * 8;
-        cp_async16(sq + swz<D>(row, c), src, valid);
-    }
-    cp_async_commit();
-    // Where each key row of a tile lives in the cache (token slot = page * block_size + place in the page, -1 for
-    // none) is looked up by the first 64 threads one tile ahead of the copy that needs it, so that no copy waits
-    // for a block-table entry.
-    __shared__ int s_slot[STAGES][ABN];
-    auto lookup = [&](int kt) -> int {
-        const int key = kt * ABN + (int)threadIdx.x;
-        const int blk = key / p.block_size;
-        if (kt >= kt_hi || key > pos_last || blk >= p.max_blocks) return -1;
-        const long long page = table[blk];
-        return (page >= 0 && page < p.num_pages) ? (int)(page * p.block_size + key % p.block_size) : -1;
-    };
-    auto load_kv = [&](int kt, int stage) {
-        const int *slots = s_slot[(kt - kt_lo) % STAGES];
-        for (int i = threadIdx.x; i < ABN * CH; i += NT) {
-            int kr = i / CH, c = i % CH;
-            const int slot = slots[kr];
-            const bool valid = slot >= 0;
-            size_t off = valid ? ((size_t)slot * p.G + g) * D + c * 8 : 0;
-            cp_async16(sk + stage * (ABN * D * 2) + swz<D>(kr, c), p.k_cache + off, valid);
-            cp_async16(sv + stage * (ABN * D * 2) + swz<D>(kr, c), p.v_cache + off, valid);
-        }
-        cp_async_commit();
-    };
-    if (threadIdx.x < ABN) {
-#pragma unroll
-        for (int st = 0; st < STAGES; st++) s_slot[st][threadIdx.x] = lookup(kt_lo + st);
-    }
-    __syncthreads();
-#pragma unroll
-    for (int st = 0; st < STAGES - 1; st++) {
-        if (kt_lo + st < kt_hi) load_kv(kt_lo + st, st);
-        else cp_async_commit();
-    }
-    const int row0 = lane >> 2, row1 = row0 + 8;
-    const int tl0 = row0 / r, tl1 = row1 / r;
-    const bool v0 = tl0 < nt, v1 = tl1 < nt;
-    const int pos0 = v0 ? p.positions[t0 + tl0] : -1, pos1 = v1 ? p.positions[t0 + tl1] : -1;
-    const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, pos1 - p.window + 1) : 0;
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    uint32_t qf[D / 16][4];
-    bool q_loaded = false;
-
-    for (int kt = kt_lo; kt < kt_hi; kt++) {
-        const int stage = (kt - kt_lo) % STAGES;
-        if (kt + STAGES - 1 < kt_hi) load_kv(kt + STAGES - 1, (kt + STAGES - 1 - kt_lo) % STAGES);
-        else cp_async_commit();
-        // the slots of the tile after that one: asked for now, stored at the end of this round
-        const int slot_ahead = (threadIdx.x < ABN && kt + STAGES < kt_hi) ? lookup(kt + STAGES) : -1;
-        cp_async_wait<STAGES - 1>();
-        __syncthreads();
-        if (!q_loaded) {
-#pragma unroll
-            for (int kk = 0; kk < D / 16; kk++)
-                ldsm_x4(sq + swz<D>(lane & 15, kk * 2 + (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
-            q_loaded = true;
-        }
-        const uint32_t ks = sk + stage * (ABN * D * 2), vs = sv + stage * (ABN * D * 2);
-        const int kbase = warp * 16;                 // this warp's 16 keys of the tile
-        float s[2][4];
-        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
-#pragma unroll
-        for (int kk = 0; kk < D / 16; kk++) {
-            uint32_t b0, b1, b2, b3;
-            int mi = lane >> 3;
-            ldsm_x4(ks + swz<D>(kbase + (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)), b0, b1, b2, b3);
-            mma_bf16(s[0], qf[kk], b0, b1);
-            mma_bf16(s[1], qf[kk], b2, b3);
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-#pragma unroll
-            for (int e = 0; e < 2; e++) {
-                int key = kt * ABN + kbase + i * 8 + (lane & 3) * 2 + e;
-                float a = s[i][e] * p.scale_log2, b = s[i][2 + e] * p.scale_log2;
-                a = (v0 && key >= lo0 && key <= pos0) ? a : -INFINITY;
-                b = (v1 && key >= lo1 && key <= pos1) ? b : -INFINITY;
-                s[i][e] = a; s[i][2 + e] = b;
-                mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b);
-            }
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
-        float c0 = fast_exp2(m0 - base0), c1 = fast_exp2(m1 - base1);
-        m0 = mn0; m1 = mn1;
-        uint32_t pf[4];
-        float p00 = fast_exp2(s[0][0] - base0), p01 = fast_exp2(s[0][1] - base0), p10 = fast_exp2(s[0][2] - base1), p11 = fast_exp2(s[0][3] - base1);
-        float q00 = fast_exp2(s[1][0] - base0), q01 = fast_exp2(s[1][1] - base0), q10 = fast_exp2(s[1][2] - base1), q11 = fast_exp2(s[1][3] - base1);
-        pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p10, p11); pf[2] = pack_bf16(q00, q01); pf[3] = pack_bf16(q10, q11);
-        l0 = l0 * c0 + (p00 + p01 + q00 + q01);
-        l1 = l1 * c1 + (p10 + p11 + q10 + q11);
-#pragma unroll
-        for (int i = 0; i < D / 8; i++) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
-#pragma unroll
-        for (int dn = 0; dn < D / 16; dn++) {
-            uint32_t b0, b1, b2, b3;
-            int mi = lane >> 3;
-            ldsm_x4_t(vs + swz<D>(kbase + (mi & 1) * 8 + (lane & 7), dn * 2 + (mi >> 1)), b0, b1, b2, b3);
-            mma_bf16(o[2 * dn], pf, b0, b1);
-            mma_bf16(o[2 * dn + 1], pf, b2, b3);
-        }
-        if (threadIdx.x < ABN) s_slot[(kt + STAGES - kt_lo) % STAGES][threadIdx.x] = slot_ahead;   // last read a round ago
-        __syncthreads();
-    }
-    cp_async_wait<0>();
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-
-    // ---- merge the four warps (they saw disjoint keys) in warp order -------------------------------------
-    __syncthreads();                                  // the tile buffers are free: reuse them
-    float *mo = (float *)(smem + 16 * D * 2);         // [4][16][D]
-    float *mml = mo + 4 * 16 * D;                     // [4][16][2]
-#pragma unroll
-    for (int i = 0; i < D / 8; i++) {
-        int col = i * 8 + (lane & 3) * 2;
-        *(float2 *)(mo + ((size_t)warp * 16 + row0) * D + col) = make_float2(o[i][0], o[i][1]);
-        *(float2 *)(mo + ((size_t)warp * 16 + row1) * D + col) = make_float2(o[i][2], o[i][3]);
-    }
-    if ((lane & 3) == 0) {
-        *(float2 *)(mml + (warp * 16 + row0) * 2) = make_float2(m0, l0);
-        *(float2 *)(mml + (warp * 16 + row1) * 2) = make_float2(m1, l1);
-    }
-    __syncthreads();
-    const int rows = nt * r;
-    for (int idx = threadIdx.x; idx < rows * D; idx += NT) {
-        const int row = idx / D, col = idx % D;
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; w++) m = fmaxf(m, mml[(w * 16 + row) * 2]);
-        float denom = 0.f, acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; w++) {
-            float mw = mml[(w * 16 + row) * 2];
-            float f = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
-            denom += mml[(w * 16 + row) * 2 + 1] * f;
-            acc += mo[((size_t)w * 16 + row) * D + col] * f;
-        }
-        const int tok = t0 + row / r, head = g * r + row % r;
-        const size_t th = (size_t)tok * p.H + head;
-        if (p.splits > 1) {
-            p.part_o[(th * p.splits + split) * D + col] = acc;
-            if (col == 0) *(float2 *)(p.part_ml + (th * p.splits + split) * 2) = make_float2(m, denom);
-        } else {
-            p.out[th * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
-        }
-    }
-}
-
-template <int D, int STAGES>
-static int launch_attention_decode(const AttnParams &p, int n_tiles, cudaStream_t st)
-{
-    constexpr int smem = (16 + 2 * STAGES * ABN) * D * 2;
-    static_assert(2 * STAGES * ABN * D * 2 >= 4 * 16 * (D + 2) * 4, "the merge reuses the tile buffers");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return fail(HFB_ECUDA, "attention: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
-    }
-    dim3 grid(n_tiles, p.G, p.splits);
-    g_launch_err = launch_pdl(attention_decode_kernel<D, STAGES>, grid, dim3(128), smem, st, p, error_word());
-    return check_pdl_launch(g_launch_err, "attention_decode");
-}
-
 // Merges the splits of one (token, head) in split order: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
 template <int D>
 __global__ void attention_combine_kernel(const float *part_o, const float *part_ml, int splits, __nv_bfloat16 *out)
@@ -478,9 +275,9 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_fast: head_dim %d (64 and 128 only; use the plain kernel)", d);
-    if (warps != 1 && warps != 2 && warps != 4 && warps != 8) return fail(HFB_EINVAL, "attention_fast: 1, 2 (decode form), 4 or 8 warps");
+    if (warps != 1 && warps != 4 && warps != 8) return fail(HFB_EINVAL, "attention_fast: 1, 4 or 8 warps");
     if (block_size <= 0 || ABN % block_size) return fail(HFB_ENOTSUP, "attention_fast: block size %d does not divide %d", block_size, ABN);
-    if (warps != 2 && hfb_attention_fast_tile_tokens(H, G, warps) == 0) return fail(HFB_ENOTSUP, "attention_fast: %d heads per key/value head do not fit a tile", G ? H / G : 0);
+    if (hfb_attention_fast_tile_tokens(H, G, warps) == 0) return fail(HFB_ENOTSUP, "attention_fast: %d heads per key/value head do not fit a tile", G ? H / G : 0);
     if (splits < 1 || G > 65535 || splits > 65535) return fail(HFB_EINVAL, "attention_fast: bad split or group count");
     if (splits > 1 && (!scratch || scratch_bytes < hfb_attention_fast_scratch(T, H, d, splits)))
         return fail(HFB_EINVAL, "attention_fast: scratch of %zu bytes is too small for %d splits", scratch_bytes, splits);
@@ -494,14 +291,7 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
     cudaStream_t st = (cudaStream_t)s;
     int rc;
     const bool deep = stages >= 4;              // a deeper pipeline for CTAs that have an SM to themselves (decode)
-    if (warps == 2) {
-        // the decode form: rows of one or two tokens, four warps sharing each tile's keys
-        if (hfb_attention_fast_tile_tokens(H, G, 1) == 0) return fail(HFB_ENOTSUP, "attention_fast: %d heads per group exceed 16 rows", H / G);
-        if (d == 128) rc = stages >= 4 ? launch_attention_decode<128, 4>(p, n_tiles, st)
-                         : stages == 3 ? launch_attention_decode<128, 3>(p, n_tiles, st) : launch_attention_decode<128, 2>(p, n_tiles, st);
-        else rc = stages >= 4 ? launch_attention_decode<64, 4>(p, n_tiles, st)
-                : stages == 3 ? launch_attention_decode<64, 3>(p, n_tiles, st) : launch_attention_decode<64, 2>(p, n_tiles, st);
-    } else if (d == 128) rc = warps == 8 ? launch_attention<128, 8, 2>(p, n_tiles, st)
+    if (d == 128) rc = warps == 8 ? launch_attention<128, 8, 2>(p, n_tiles, st)
                      : warps == 4 ? (deep ? launch_attention<128, 4, 4>(p, n_tiles, st) : launch_attention<128, 4, 2>(p, n_tiles, st))
                                   : launch_attention<128, 1, 2>(p, n_tiles, st);
     else rc = warps == 8 ? launch_attention<64, 8, 2>(p, n_tiles, st)

@@ -657,27 +657,30 @@ int tensor_map(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *o
     return HFB_OK;
 }
 
-static int sm_count()
+// Index of the current device (0 where it cannot be told), for what is remembered per device.
+static int current_device()
 {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 1;
-    }
-    return n;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    return dev;
 }
 
-// Experiment switches (environment): HFB_SHALLOW=1 picks the half-depth pipelines so that two CTAs fit an SM
-// (the next kernel's CTAs can then start beside this kernel's last ones); HFB_CTAS_PER_SM caps the grid.
+static int sm_count()
+{
+    static int n[64] = {0};
+    const int dev = current_device();
+    if (!n[dev]) {
+        cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (n[dev] <= 0) n[dev] = 1;
+    }
+    return n[dev];
+}
+
 static int env_int(const char *name, int dflt)
 {
     const char *v = getenv(name);
     return v && *v ? atoi(v) : dflt;
 }
-static int ctas_per_sm() { static int v = env_int("HFB_CTAS_PER_SM", 1); return v; }
-static bool shallow() { static int v = env_int("HFB_SHALLOW", 0); return v != 0; }
 
 template <int BN, int STAGES>
 static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams &p, cudaStream_t st)
@@ -685,14 +688,15 @@ static int launch(const CUtensorMap &mx, const CUtensorMap &my, const GemmParams
     constexpr uint32_t smem = gemm_smem_bytes<BN, STAGES>();
     // CTAs that can share an SM by shared memory must also all find their TMEM columns (512 per SM)
     static_assert((227 * 1024 / smem) * tmem_cols<BN>() <= 512, "co-resident CTAs would wait for TMEM columns");
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};                 // the opt-in is a property of the function on one device
+    const int dev = current_device();
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "gemm_tc: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        configured[dev] = true;
     }
     int items = p.tiles_x * p.tiles_y * p.splits;
-    int cap = sm_count() * ctas_per_sm();
+    int cap = sm_count();                          // one CTA per SM: the stages take most of its shared memory
     int grid = items < cap ? items : cap;
     g_launch_err = launch_pdl(gemm_tc_kernel<BN, STAGES>, dim3(grid), dim3(GEMM_THREADS), smem, st, mx, my, p, error_word());
     return check_pdl_launch(g_launch_err, "gemm_tc");
@@ -704,11 +708,12 @@ static int launch_pair(const CUtensorMap &mx, const CUtensorMap &my, const GemmP
 {
     constexpr uint32_t smem = 1024 + STAGES * (X_BYTES + (BN / 2) * BK * 2) + (2 * STAGES + 4) * 8 + 16;
     static_assert(smem <= 227 * 1024, "the stages do not fit");
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};
+    const int dev = current_device();
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "gemm_tc: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        configured[dev] = true;
     }
     const int items = p.tiles_x * p.tiles_y * p.splits, pairs_cap = sm_count() / 2;
     const int pairs = items < pairs_cap ? items : pairs_cap;
@@ -826,9 +831,9 @@ static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const
         }
     }
     switch (bn) {
-    case 16: return shallow() ? launch<16, 5>(mx, my, p, st) : launch<16, 10>(mx, my, p, st);
-    case 32: return shallow() ? launch<32, 5>(mx, my, p, st) : launch<32, 9>(mx, my, p, st);
-    case 64: return shallow() ? launch<64, 4>(mx, my, p, st) : launch<64, 8>(mx, my, p, st);
+    case 16: return launch<16, 10>(mx, my, p, st);
+    case 32: return launch<32, 9>(mx, my, p, st);
+    case 64: return launch<64, 8>(mx, my, p, st);
     case 128: return launch<128, 6>(mx, my, p, st);
     case 192: return launch<192, 5>(mx, my, p, st);
     case 208: return launch<208, 5>(mx, my, p, st);
@@ -838,11 +843,13 @@ static int launch_bn(int bn, const CUtensorMap &mx, const CUtensorMap &my, const
     }
 }
 
-static int check_tc_args(const char *who, const void *a, const void *w, const void *out, int M, int N, int K)
+static int check_tc_args(const char *who, const void *a, const void *w, const void *out, int M, int N, int K,
+                         const void *bias = nullptr)
 {
     if (K <= 0 || (K & 7)) return fail(HFB_ENOTSUP, "%s: K = %d must be a positive multiple of 8", who, K);
-    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
-        return fail(HFB_ENOTSUP, "%s: operands must be 16-byte aligned", who);
+    // (the many-token epilogue reads the bias sixteen bytes at a time)
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || ((uintptr_t)bias & 15))
+        return fail(HFB_ENOTSUP, "%s: operands (and the bias) must be 16-byte aligned", who);
     (void)M; (void)N;
     return HFB_OK;
 }
@@ -852,7 +859,7 @@ static size_t swapped_split_bytes(int M, int N, int K)
 {
     using namespace hfb;
     int tiles = (N + TILE_X - 1) / TILE_X, kb = (K + BK - 1) / BK;
-    int cap = sm_count() * env_int("HFB_CTAS_PER_SM", 1);
+    int cap = sm_count();
     int splits = tiles >= cap ? 1 : cap / tiles;                    // at most one work item per CTA slot
     if (splits > kb / 4) splits = kb / 4 > 0 ? kb / 4 : 1;
     if (splits > 16) splits = 16;
@@ -871,7 +878,7 @@ extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int
                              int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s)
 {
     if (M <= 0 || N <= 0) return HFB_OK;
-    int rc = check_tc_args("linear_tc", a, w, out, M, N, K);
+    int rc = check_tc_args("linear_tc", a, w, out, M, N, K, bias);
     if (rc != HFB_OK) return rc;
     if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "linear_tc: bad element types");
     if (accumulate && out_dt != HFB_F32) return fail(HFB_EINVAL, "linear_tc: accumulation needs a float32 output");
@@ -1003,8 +1010,8 @@ extern "C" int hfb_linear_tc_noalloc(const void *a, const void *w, const void *b
 {
     if (M <= 0 || N <= 0) return HFB_OK;
     if (K <= 0 || (K & 7)) return fail(HFB_ENOTSUP, "linear_tc_noalloc: K = %d must be a positive multiple of 8", K);
-    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15))
-        return fail(HFB_ENOTSUP, "linear_tc_noalloc: operands must be 16-byte aligned");
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || ((uintptr_t)bias & 15))
+        return fail(HFB_ENOTSUP, "linear_tc_noalloc: operands (and the bias) must be 16-byte aligned");
     if (!valid_dt(out_dt) || (bias && !valid_dt(bias_dt))) return fail(HFB_EINVAL, "linear_tc_noalloc: bad element types");
     if (accumulate && out_dt != HFB_F32) return fail(HFB_EINVAL, "linear_tc_noalloc: accumulation needs a float32 output");
     size_t need = M <= 128 ? swapped_split_bytes(M, N, K) : 0;

@@ -47,12 +47,6 @@ size_t hfb_linear_tc_workspace(int M, int N, int K);
 int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
                   int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s);
 
-/* The product for at most 16 rows of bfloat16 a (decode): weights stream from global memory straight into
- * mma.sync fragments, no partial sums leave the CTA.  mode 0: store (+bias); 1: accumulate into a float32 out
- * (+bias); 2: SwiGLU of alternating gate/up rows of w, out [M, N/2]. */
-int hfb_linear_mma(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
-                   int mode, int M, int N, int K, hfb_stream s);
-
 /* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
 int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
 
@@ -107,13 +101,12 @@ int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, 
 
 /* Decode attention with the keys and values fetched by TMA: tiles as hfb_attention_fast's 16-row form takes them
  * (one or two tokens of one request), bfloat16, head_dim 64 or 128, block sizes 8..64 dividing 64.  `stages` (2..4)
- * tiles of 64 keys are in flight per CTA; `splits` > 1 needs hfb_attention_fast_scratch bytes of scratch, or, with
- * `cluster` set and 2..8 splits, none: the CTAs of a request merge through distributed shared memory. */
+ * tiles of 64 keys are in flight per CTA; `splits` > 1 needs hfb_attention_fast_scratch bytes of scratch. */
 int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                          int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                          const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size, int64_t num_pages,
                          int window, float scale, void *out, void *scratch, size_t scratch_bytes, int T, int H, int G,
-                         int d, int cluster, hfb_stream s);
+                         int d, hfb_stream s);
 
 /* Attention of prompt portions on tcgen05 (S and PV accumulators in TMEM, K and V gathered page by page with
  * TMA): bfloat16, head_dim 128, block sizes 8..128 that divide 128.  Tiles hold at most 128 / (H/G) tokens. */
@@ -144,6 +137,8 @@ int hfb_sample(const float *logits, int M, int V, const float *temps, const int3
 /* Device error word: kernels set bits instead of touching memory out of range.  Reading syncs the stream. */
 enum { HFB_ERR_TOKEN_ID = 1, HFB_ERR_PAGE = 2, HFB_ERR_SLOT = 4, HFB_ERR_WAIT = 8, HFB_ERR_POSITION = 16 };
 int hfb_error_word_take(int32_t *word, hfb_stream s);
+/* Queues a copy of the word into pinned host memory and returns; read it after your own wait on the stream. */
+int hfb_error_word_peek_async(int32_t *host_word, hfb_stream s);
 
 #ifdef __cplusplus
 }

@@ -17,11 +17,16 @@
  *  - Sizes: the partial sums take splits * M * N floats, where splits is what hfb_linear_tc would choose
  *    (at most one work item per SM, M <= 128 only).  If that exceeds the array the call fails with
  *    HFB_ERANGE and a message naming both numbers; nothing is launched.  Other argument rules are those of
- *    hfb_linear_tc (K a multiple of 8, 16-byte aligned operands).
+ *    hfb_linear_tc (K a multiple of 8; a, w, out and the bias 16-byte aligned, else HFB_ENOTSUP).
  *  - First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that device
- *    current) and opts the kernel in to its shared memory; both are remembered per device.  Make this first
- *    call before any stream capture begins.
- *  - It calls no cudaMalloc / cudaFree and no allocating library routine, on any call.
+ *    current), asks for the SM count and opts the kernel in to its shared memory; all three are remembered
+ *    per device.  Make this first call before any stream capture begins, and from one thread: the per-device
+ *    records are filled without a lock, so two threads must not make their first call on the same device at
+ *    the same time (later calls only read them).
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine, on any call.  Where the CUDA runtime
+ *    loads modules lazily, the first use of the library's kernels is what places its image, this array
+ *    included, on the device: the 8 MiB appear then, once, not per call, and the amount of free device memory
+ *    is the same before and after every later call.
  *  - Every call uses the same array and finds the previous call's numbers in it.  Nothing in it has to
  *    start at zero: each split overwrites its whole [M, N] slice before the reduction reads it.  For the
  *    same reason two calls whose kernels may run at the same time on one GPU (different streams, or several

@@ -91,6 +91,17 @@ extern "C" long long hfb_trace_take(unsigned long long *pairs, long long max)
 extern "C" const char *hfb_last_error(void) { return hfb::g_msg; }
 extern "C" int hfb_version(void) { return 1; }
 
+// Queues a copy of the error word into `host_word` (pinned host memory) on the stream and returns at once: the
+// caller reads it after an event or synchronisation of its own, beside the results it is waiting for anyway.
+extern "C" int hfb_error_word_peek_async(int32_t *host_word, hfb_stream s)
+{
+    int *p = hfb::error_word();
+    if (!p) return hfb::fail(HFB_ECUDA, "cannot locate the device error word");
+    cudaError_t e = cudaMemcpyAsync(host_word, p, sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)s);
+    if (e != cudaSuccess) return hfb::fail(HFB_ECUDA, "copying the device error word: %s", cudaGetErrorString(e));
+    return HFB_OK;
+}
+
 extern "C" int hfb_error_word_take(int32_t *word, hfb_stream s)
 {
     int *p = hfb::error_word();

@@ -35,6 +35,7 @@ from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import kernels
 from ..cache import OutOfPages
 from ..sampling import Rng, SamplingParams, logprob, sample_host, top_logprobs
 from .step import Engine, StepEntry
@@ -178,6 +179,17 @@ class Scheduler:
 
     def cancel(self, req_id) -> None:
         self.cancelled.add(req_id)
+
+    def abort(self, req_ids, why: str = "EIO: the step failed") -> list:
+        """Ends the named requests at once, running or waiting, and gives back what they hold: for a caller whose
+        step raised, so that nothing of the failed call is left to be scheduled with the next one."""
+        events: list = []
+        for rid in req_ids:
+            r = self.requests.get(rid)
+            if r is not None and r.status != FINISHED:
+                self._finish(r, "error", events, why)
+            self.cancelled.discard(rid)
+        return events
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
@@ -416,10 +428,13 @@ class Scheduler:
         if self.device_sampling:
             from .. import sampling
             if self._host_ring is None:
-                self._host_ring = [torch.empty(max(self.engine.max_requests, 1), dtype=torch.int32, pin_memory=True)
+                self._host_ring = [torch.empty(self.engine.max_requests + 1, dtype=torch.int32, pin_memory=True)
                                    for _ in range(4)]
             self._ring_at = (self._ring_at + 1) % len(self._host_ring)
-            return Flight(sampled, logits, pending=sampling.device.sample_rows_async(logits, sampled, self._host_ring[self._ring_at]))
+            from .. import kernels
+            with kernels.phase("sample"):
+                pending = sampling.device.sample_rows_async(logits, sampled, self._host_ring[self._ring_at])
+            return Flight(sampled, logits, pending=pending)
         rows = logits.float().cpu().numpy()
         return Flight(sampled, logits, tokens=[sample_host(rows[i], r.params, r.rng) for i, r in enumerate(sampled)], rows=rows)
 
@@ -449,7 +464,14 @@ class Scheduler:
     def _end(self, flight: Flight) -> list:
         """Reads the sampled tokens of a step, emits their events and ends the requests that are done."""
         events: list = []
-        tokens = flight.tokens if flight.pending is None else flight.pending.tokens()
+        try:
+            tokens = flight.tokens if flight.pending is None else flight.pending.tokens()
+        except kernels.DeviceFault as e:
+            # a bounded wait ran out or an index was refused on the device: the step's logits are not to be trusted
+            for r in flight.sampled:
+                if r.status != FINISHED:
+                    self._finish(r, "error", events, f"EIO: {e}")
+            return events
         for i, r in enumerate(flight.sampled):
             if r.status == FINISHED:
                 continue                                  # ended while this step was in flight: its token is dropped

@@ -361,7 +361,10 @@ class Engine:
         ``token_source`` (int32 on the device, one id per token of the step) replaces the entries' token ids:
         the ids a sampling kernel has just written can be fed back without the host having seen them."""
         entries = list(entries)
-        graphable = self.use_graphs and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries)
+        from .. import kernels
+        # (a step that is being profiled phase by phase runs kernel by kernel, not as a graph)
+        graphable = (self.use_graphs and not kernels.profile.enabled
+                     and all(len(e.tokens) == 1 and len(e.want) == 1 for e in entries))
         ctx = self.prepare(entries, static=graphable)
         if token_source is not None:
             if token_source.dtype != torch.int32 or token_source.numel() != ctx.num_tokens:

@@ -21,6 +21,58 @@ ERROR_BITS = {1: "a token id outside the vocabulary", 2: "a block-table entry th
               16: "a position outside the rotary table"}
 
 
+class PhaseProfile:
+    """Device time per phase of the forward pass, for ``--profile``: parts wrap their kernel calls in
+    ``kernels.phase(name)``; while the profile is on, each phase is bracketed by CUDA events on the current stream
+    and ``take()`` returns milliseconds per name and clears them.  Off, ``phase`` costs one attribute test.  The
+    reference keeps per-phase accumulators with the same names (src/model.h:75-79, src/ops.c:593-604)."""
+    NAMES = ("embed", "glue", "qkv", "attn", "wo", "gate_up", "silu", "down", "head", "quant", "sample")
+
+    class _Null:
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *a):
+            return False
+
+    class _Span:
+        def __init__(self, owner, name):
+            self.owner, self.name = owner, name
+
+        def __enter__(self):
+            self.a, self.b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.a.record()
+            return self
+
+        def __exit__(self, *a):
+            self.b.record()
+            self.owner.spans.append((self.name, self.a, self.b))
+            return False
+
+    def __init__(self):
+        self.enabled, self.spans, self._null = False, [], self._Null()
+
+    def enable(self, on: bool) -> None:
+        self.enabled = bool(on) and torch.cuda.is_available()
+        self.spans = []
+
+    def phase(self, name: str):
+        return self._Span(self, name) if self.enabled else self._null
+
+    def take(self) -> dict:
+        out = {n: 0.0 for n in self.NAMES}
+        if self.spans:
+            torch.cuda.synchronize()
+            for name, a, b in self.spans:
+                out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        self.spans = []
+        return out
+
+
+profile = PhaseProfile()
+phase = profile.phase
+
+
 def backend():
     global _backend
     if _backend is None:
@@ -166,10 +218,17 @@ def sample(logits, temps, top_ks, top_ps, min_ps, uniforms, out) -> None:
     backend().sample(logits, temps, top_ks, top_ps, min_ps, uniforms, out)
 
 
+class DeviceFault(RuntimeError):
+    """A kernel recorded an error in the device error word; what it computed is not to be trusted."""
+
+    def __init__(self, word: int):
+        self.word = int(word)
+        super().__init__("a kernel met " + "; ".join(v for k, v in ERROR_BITS.items() if word & k))
+
+
 def check_device_errors() -> None:
     """Raise if any kernel recorded an error since the last check (synchronises the stream)."""
     b = backend()
     word = b.error_word() if hasattr(b, "error_word") else 0
     if word:
-        what = [v for k, v in ERROR_BITS.items() if word & k]
-        raise RuntimeError("a kernel met " + "; ".join(what))
+        raise DeviceFault(word)

@@ -49,19 +49,12 @@ class NativeBackend:
         self.lib.hfb_attention_fast_scratch.restype = ctypes.c_size_t
         # "fast": tiled tensor-core attention where the sizes allow; "plain": one block per (token, head) always
         self.attention = os.environ.get("HFB_ATTENTION", "fast")
-        # products with at most this many rows take the weight-streaming mma.sync kernel instead of tcgen05
-        self.gemv_max = int(os.environ.get("HFB_GEMV_MAX", "0"))
         self.attention_tc = os.environ.get("HFB_ATTN_TC", "1") != "0"     # tcgen05 attention for prompt portions
         self.attention_tc2 = os.environ.get("HFB_ATTN_TC2", "1") != "0"   # its form with two query tiles per CTA
-        self.tc2_min_rounds = float(os.environ.get("HFB_ATTN_TC2_ROUNDS", "1"))
-        self.decode_ctas_per_sm = int(os.environ.get("HFB_DECODE_CTAS", "2"))
-        self.decode_stages = int(os.environ.get("HFB_DECODE_STAGES", "3"))
-        self.decode_warps = int(os.environ.get("HFB_DECODE_WARPS", "2"))
-        self.decode_tma = os.environ.get("HFB_DECODE_TMA", "1") != "0"
-        # the splits of a request as a thread-block cluster that merges through distributed shared memory: faster alone
-        # (12.3 against 13.2 us at batch 8), slower inside the step (a cluster waits for room in one GPC while the
-        # kernels around it overlap), so it is off unless asked for
-        self.decode_cluster = os.environ.get("HFB_DECODE_CLUSTER", "0") != "0"
+        # the two-tile form takes over once there is a work item for every SM this many times over (tests set 0)
+        self.tc2_min_rounds = 1.0
+        self.decode_ctas_per_sm = 2               # CTAs of the decode attention kernel per SM, over all requests' splits
+        self.decode_stages = 3                    # tiles of 64 keys in flight per CTA
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
         # "tc": tensor-core products where the operands allow; "plain": the float32-accumulating SIMT kernel always
         self.gemm = os.environ.get("HFB_GEMM", "tc")
@@ -103,11 +96,9 @@ class NativeBackend:
         self._on_gpu(a, w, bias, out)
         M, K = a.shape
         N = w.shape[0]
-        if M <= self.gemv_max and self._tc_ok(a, w):
-            self._mma(a, w, bias, out, 1 if accumulate else 0)
-            return
         if (self.gemm == "tc" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
-                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+                and (bias is None or bias.data_ptr() % 16 == 0)):
             need = self.lib.hfb_linear_tc_workspace(c_int(M), c_int(N), c_int(K))
             if need:
                 self._workspace(a.device)
@@ -172,8 +163,11 @@ class NativeBackend:
                         c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out), c_int(T), c_int(H), c_int(G),
                         c_int(d), self._stream()), "attention_tc")
                     return
-            warps = self.decode_warps if decode else 4
-            tiling = tiles(H // G, 1 if warps == 2 else warps)        # the decode form (2) tiles like the 16-row kernel
+            # single tokens: the decode kernel (16 rows a tile, keys and values by TMA) where the pages are at least 8
+            # tokens; smaller pages take the 4-warp kernel with one token a tile
+            decode_tma = decode and meta.block_size >= 8
+            warps = 4
+            tiling = tiles(H // G, 1 if decode_tma else warps)
             if tiling is None and not decode:
                 warps = 8
                 tiling = tiles(H // G, 8)
@@ -184,24 +178,18 @@ class NativeBackend:
                     # about `decode_ctas_per_sm` CTAs per SM in all; with one per SM the deep pipeline fits
                     hint = getattr(ctx, "decode_split_hint", max(1, ((ctx.max_kv_len + 63) // 64) // 2))
                     splits = max(1, min(self.decode_ctas_per_sm * self.sm_count // max(1, n_tiles * G), hint))
-                    stages = self.decode_stages if warps in (2, 4) else 2
+                    stages = self.decode_stages
                 need = self.lib.hfb_attention_fast_scratch(c_int(T), c_int(H), c_int(d), c_int(splits))
                 scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
-                if decode and warps == 2 and self.decode_tma and meta.block_size >= 8:
+                if decode_tma:
                     # the keys and values come by TMA, a warp of their own keeps them coming
-                    cluster = 0
-                    if self.decode_cluster and splits >= 2:
-                        # the CTAs of a request as a thread-block cluster (2, 4 or 8): no partial results in global
-                        # memory and no second kernel
-                        splits = 1 << (min(splits, 8).bit_length() - 1)
-                        cluster, scratch, need = 1, None, 0
                     self._check(self.lib.hfb_attention_decode(
                         _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
                         _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(stages), c_int(splits),
                         c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out),
-                        _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), c_int(cluster), self._stream()),
+                        _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), self._stream()),
                         "attention_decode")
-                    if splits > 1 and not cluster:
+                    if splits > 1:
                         self.launches += 1
                     return
                 self._check(self.lib.hfb_attention_fast(
@@ -259,20 +247,10 @@ class NativeBackend:
                     "linear_tc_partials")
         return ws, splits.value
 
-    def _mma(self, a, w, bias, out, mode):
-        M, K = a.shape
-        N = w.shape[0]
-        self._check(self.lib.hfb_linear_mma(_p(a), _p(w), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(out),
-                                            c_int(_dt(out)), c_int(mode), c_int(M), c_int(N), c_int(K), self._stream()),
-                    "linear_mma")
-
     def linear_swiglu(self, a, w, gu_buf, out):
         self._on_gpu(a, w, out)
         M, K = a.shape
         N = w.shape[0]
-        if M <= self.gemv_max and self._tc_ok(a, w):
-            self._mma(a, w, None, out, 2)
-            return
         if self._tc_ok(a, w, out):
             self._check(self.lib.hfb_linear_tc_swiglu(_p(a), _p(w), _p(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),
                                                       self._stream()), "linear_tc_swiglu")
@@ -284,8 +262,7 @@ class NativeBackend:
         self._on_gpu(a, w, bias, residual, norm_w, xn_out)
         M, K = a.shape
         N = w.shape[0]
-        small = M <= self.gemv_max and self._tc_ok(a, w)
-        part = self._partials(a, w) if (not small and self._tc_ok(a, w)) else None
+        part = self._partials(a, w) if self._tc_ok(a, w) else None
         if part is None:
             self.linear(a, w, bias, residual, True)
             if xn_out is not None:
@@ -300,8 +277,7 @@ class NativeBackend:
     def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
         self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
         M, K = a.shape
-        small = M <= self.gemv_max and self._tc_ok(a, w)
-        part = self._partials(a, w) if (not small and self._tc_ok(a, w)) else None
+        part = self._partials(a, w) if self._tc_ok(a, w) else None
         if part is None:
             self.linear(a, w, bias, qkv_buf, False)
             self.rope_kv_write(qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d)
@@ -319,6 +295,12 @@ class NativeBackend:
         M, V = logits.shape
         self._check(self.lib.hfb_sample(_p(logits), c_int(M), c_int(V), _p(temps), _p(top_ks), _p(top_ps), _p(min_ps),
                                         _p(uniforms), _p(out), self._stream()), "sample")
+
+    def error_word_async(self, host_word: torch.Tensor) -> None:
+        """Queues a copy of the error word into ``host_word`` (pinned int32[1]); valid once the stream got there."""
+        rc = self.lib.hfb_error_word_peek_async(c_void_p(host_word.data_ptr()), self._stream())
+        if rc != 0:
+            raise KernelError(f"error word: {self.lib.hfb_last_error().decode()} (status {rc})")
 
     def error_word(self) -> int:
         w = ctypes.c_int32(0)

@@ -82,6 +82,16 @@ class PagedAttention(Mixer):
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.b_qkv, self.w_o, self.b_o)
                    if w is not None)
 
+    def flops(self, q_lens, kv_lens):
+        T = sum(q_lens)
+        seen = 0                        # (query, key) pairs: token i of n new ones over a history of m sees m - n + i + 1
+        for n, m in zip(q_lens, kv_lens):
+            for_all = n * (m - n) + n * (n + 1) // 2
+            if self.window > 0:
+                for_all = sum(min(self.window, m - n + i + 1) for i in range(n)) if m > self.window else for_all
+            seen += for_all
+        return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel()) + 4.0 * self.QD * seen
+
     def _attend(self, ctx, xn, cache, write_cache):
         T = xn.shape[0]
         qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
@@ -89,23 +99,28 @@ class PagedAttention(Mixer):
         meta = ctx.group_meta(cache.group)
         cos_sin = self.rotary.cos_sin if self.rotary is not None else None
         n_rot = self.rotary.n_rot if self.rotary is not None else 0
-        kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
-                               meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
+        with kernels.phase("qkv"):
+            kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
+                                   meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
         att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
-        kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
-                                self.window, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()))
+        with kernels.phase("attn"):
+            kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
+                                    self.window, self.scale, att, tiles=ctx.arrays(self.step_arrays_key()))
         return att
 
     def forward(self, ctx, xn, residual, cache, state, write_cache):
-        kernels.linear(self._attend(ctx, xn, cache, write_cache), self.w_o, self.b_o, residual, accumulate=True)
+        att = self._attend(ctx, xn, cache, write_cache)
+        with kernels.phase("wo"):
+            kernels.linear(att, self.w_o, self.b_o, residual, accumulate=True)
 
     def forward_then_norm(self, ctx, xn, residual, cache, state, write_cache, norm, out):
         args = norm.fused_args()
         if args is None:
             self.forward(ctx, xn, residual, cache, state, write_cache)
             return False
-        kernels.linear_residual_norm(self._attend(ctx, xn, cache, write_cache), self.w_o, self.b_o, residual,
-                                     args[0], args[1], out)
+        att = self._attend(ctx, xn, cache, write_cache)
+        with kernels.phase("wo"):
+            kernels.linear_residual_norm(att, self.w_o, self.b_o, residual, args[0], args[1], out)
         return True
 
 

@@ -74,6 +74,12 @@ class Part:
         """Bytes of weights a step reads from this part (for roofline accounting)."""
         return 0
 
+    def flops(self, *a) -> float:
+        """Floating-point operations of this part in one step (a multiply-add counts two), for the reported
+        fraction of the tensor-core peak.  Mixers are asked with (q_lens, kv_lens): the tokens each request brings
+        and holds afterwards; feed-forwards and the head with the number of rows they transform."""
+        return 0.0
+
 
 class Norm(Part):
     def fused_args(self):

@@ -24,7 +24,8 @@ class Embedding(Part):
         self.table = tensors[self.tensor].contiguous()
 
     def forward(self, token_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        kernels.embed(token_ids, self.table, out)
+        with kernels.phase("embed"):
+            kernels.embed(token_ids, self.table, out)
         return out
 
 
@@ -50,8 +51,12 @@ class LinearHead(Part):
     def weight_bytes(self):
         return self.weight.numel() * self.weight.element_size()
 
+    def flops(self, rows):
+        return 2.0 * rows * self.weight.numel()
+
     def forward(self, xn: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
-        kernels.linear(xn, self.weight, None, logits, accumulate=False)
+        with kernels.phase("head"):
+            kernels.linear(xn, self.weight, None, logits, accumulate=False)
         return logits
 
 

@@ -33,22 +33,30 @@ class SwiGlu(FeedForward):
     def weight_bytes(self):
         return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
 
+    def flops(self, rows):
+        return 2.0 * rows * (self.w_gate_up.numel() + self.w_down.numel())
+
     def _hidden(self, ctx, xn):
         T = xn.shape[0]
         gu = ctx.buf("ffn_gate_up", (T, 2 * self.F), xn.dtype)
         h = ctx.buf("ffn_h", (T, self.F), xn.dtype)
-        kernels.linear_swiglu(xn, self.w_gate_up, gu, h)
+        with kernels.phase("gate_up"):
+            kernels.linear_swiglu(xn, self.w_gate_up, gu, h)
         return h
 
     def forward(self, ctx, xn, residual):
-        kernels.linear(self._hidden(ctx, xn), self.w_down, None, residual, accumulate=True)
+        h = self._hidden(ctx, xn)
+        with kernels.phase("down"):
+            kernels.linear(h, self.w_down, None, residual, accumulate=True)
 
     def forward_then_norm(self, ctx, xn, residual, norm, out):
         args = norm.fused_args()
         if args is None:
             self.forward(ctx, xn, residual)
             return False
-        kernels.linear_residual_norm(self._hidden(ctx, xn), self.w_down, None, residual, args[0], args[1], out)
+        h = self._hidden(ctx, xn)
+        with kernels.phase("down"):
+            kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out)
         return True
 
 

@@ -25,7 +25,8 @@ class RmsNorm(Norm):
         return self.weight, self.eps
 
     def forward(self, x, out, rows=None):
-        kernels.rmsnorm(x, self.weight, self.eps, out, rows)
+        with kernels.phase("glue"):
+            kernels.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
 
 

@@ -20,14 +20,31 @@ class Pending:
 
     def __init__(self, device: torch.Tensor, host: Optional[torch.Tensor] = None):
         self.device = device
-        # ``host``: a pinned buffer of the caller's that stays untouched until tokens() has returned
-        self._host = host[:device.numel()] if host is not None else torch.empty(device.shape, dtype=device.dtype, pin_memory=True)
+        n = device.numel()
+        # ``host``: a pinned buffer of the caller's (one slot longer than the ids) that stays untouched until
+        # tokens() has returned; its last slot receives the device error word as it stands after this step
+        if host is None or host.numel() < n + 1:
+            host = torch.empty(n + 1, dtype=device.dtype, pin_memory=True)
+        self._host, self._word = host[:n], host[n:n + 1]
         self._host.copy_(device, non_blocking=True)
+        b = kernels.backend()
+        self._checked = hasattr(b, "error_word_async")
+        if self._checked:
+            b.error_word_async(self._word)
         self._event = torch.cuda.Event()
         self._event.record()
 
     def tokens(self) -> List[int]:
+        """The ids, once they are on the host.  Raises :class:`kernels.DeviceFault` when a kernel of this step (or
+        of one before it, since the last look) recorded an error: the ids are then worthless."""
         self._event.synchronize()
+        if self._checked and int(self._word[0]) != 0:
+            word = int(self._word[0])
+            try:
+                kernels.check_device_errors()          # reads the word again and clears it
+            except kernels.DeviceFault:
+                pass
+            raise kernels.DeviceFault(word)
         return self._host.tolist()
 
 

@@ -178,53 +178,68 @@ class GgufFile:
         self.close()
 
 
-def write_gguf_file(path: str, kv: Sequence[Tuple[str, int, Any]], tensors: Iterable[Tuple[str, torch.Tensor]]) -> None:
+def write_gguf_file(path: str, kv: Sequence[Tuple[str, int, Any]], tensors) -> None:
     """Write a version-3 file: ``kv`` = (key, value type, value) with types ``U32``, ``F32`` and ``STRING``;
-    ``tensors`` = (name in the file, tensor), streamed in the order given."""
+    ``tensors`` = (name in the file, tensor) pairs, or (name, dtype, shape, function returning the tensor) so that
+    the directory can be written before any tensor is made; data is streamed in the order given."""
     head = b""
     for key, t, v in kv:
         if t not in (U32, F32, STRING):
             raise WeightFormatError(f"metadata key '{key}': value type {t} cannot be written here")
         head += _str(key) + struct.pack("<I", t)
         head += _str(v) if t == STRING else struct.pack("<I" if t == U32 else "<f", v)
-    infos, chunks, off, count = b"", [], 0, 0
-    for name, t in tensors:
-        t = t.detach().cpu().contiguous()
-        if t.dtype not in _TYPE_ID:
-            raise WeightFormatError(f"tensor '{name}': dtype {t.dtype} cannot be stored in GGUF here")
-        pad = -off % _ALIGN
-        if pad:
-            chunks.append(b"\0" * pad)
-            off += pad
-        dims = list(reversed(t.shape))
+    entries = []
+    for e in tensors:
+        if len(e) == 2:
+            name, t = e
+            entries.append((name, t.dtype, tuple(t.shape), (lambda t=t: t)))
+        else:
+            entries.append(tuple(e))
+    infos, off, places = b"", 0, []
+    for name, dtype, shape, _ in entries:
+        if dtype not in _TYPE_ID:
+            raise WeightFormatError(f"tensor '{name}': dtype {dtype} cannot be stored in GGUF here")
+        off += -off % _ALIGN
+        dims = list(reversed(shape))
         infos += _str(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d) for d in dims)
-        infos += struct.pack("<IQ", _TYPE_ID[t.dtype], off)
-        data = t.reshape(-1).view(torch.uint8).numpy().tobytes()
-        chunks.append(data)
-        off += len(data)
-        count += 1
-    out = b"GGUF" + struct.pack("<IQQ", 3, count, len(kv)) + head + infos
+        infos += struct.pack("<IQ", _TYPE_ID[dtype], off)
+        nbytes = _TYPES[_TYPE_ID[dtype]][1]
+        for d in shape:
+            nbytes *= int(d)
+        places.append((off, nbytes))
+        off += nbytes
+    out = b"GGUF" + struct.pack("<IQQ", 3, len(entries), len(kv)) + head + infos
     out += b"\0" * (-len(out) % _ALIGN)
     tmp = path + ".tmp"
     with open(tmp, "wb") as f:
         f.write(out)
-        for c in chunks:
-            f.write(c)
+        at = 0
+        for (name, dtype, shape, get), (place, nbytes) in zip(entries, places):
+            f.write(b"\0" * (place - at))
+            t = get().detach().cpu().contiguous()
+            if t.dtype != dtype or tuple(t.shape) != tuple(shape):
+                raise WeightFormatError(f"tensor '{name}' is not what its directory entry says")
+            if nbytes:
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes())
+            at = place + nbytes
     os.replace(tmp, path)
 
 
 def write_gguf(path: str, config, tensors, name: str = "hfb200 export") -> None:
     """Export a model: ``config`` is a configuration (or a config.json dict) whose class knows the format's
-    metadata keys and tensor names for its architecture; ``tensors`` carry checkpoint names.  Tensors the
-    architecture's table leaves out (a tied head's copy) are not written."""
+    metadata keys and tensor names for its architecture; ``tensors`` carry checkpoint names (a dict, or a source that
+    makes each tensor when it is asked for).  Tensors the architecture's table leaves out (a tied head's copy) are
+    not written."""
     from ..config import config_from_dict
+    from .loader import tensor_meta
     cfg = config if hasattr(config, "gguf_names") else config_from_dict(config)
     table = cfg.gguf_names()
     unknown = sorted(n for n in tensors.keys() if n not in table and n not in cfg.gguf_left_out())
     if unknown:
         raise WeightFormatError(f"no GGUF name for tensor(s) {', '.join(unknown)} in architecture '{cfg.gguf_architecture}'")
     kv = [("general.architecture", STRING, cfg.gguf_architecture), ("general.name", STRING, name)] + list(cfg.gguf_metadata())
-    write_gguf_file(path, kv, ((table[n], tensors[n]) for n in tensors.keys() if n in table))
+    write_gguf_file(path, kv, [(table[n],) + tensor_meta(tensors, n) + ((lambda n=n: tensors[n]),)
+                               for n in tensors.keys() if n in table])
 
 
 class GgufSource(TensorSource):

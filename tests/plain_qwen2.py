@@ -41,7 +41,7 @@ def read_folder(folder, dtype=torch.float64):
 # ---- parts -------------------------------------------------------------------------------------
 def embed(ids, table):
     """x[t, :] = row id[t] of the embedding table (src/model.c:566-571)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rmsnorm(x, w, eps):
@@ -76,7 +76,7 @@ def attention(q, k, v, n_heads, n_kv_heads, window):
     rep = n_heads // n_kv_heads
     scale = 1.0 / math.sqrt(d)
     out = torch.zeros_like(q)
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window > 0:
         visible = visible & (pos[:, None] - pos[None, :] < window)
@@ -132,6 +132,7 @@ def forward(cfg, W, ids, dtype=torch.float64):
     d = cfg.get("head_dim") or cfg["hidden_size"] // H
     x = embed(ids, W["model.embed_tokens.weight"])
     cos, sin = rope_angles(range(len(ids)), cfg.get("rope_dim") or d, cfg.get("rope_theta", 10000.0), dtype)
+    cos, sin = cos.to(x.device), sin.to(x.device)
     for l in range(cfg["num_hidden_layers"]):
         x = layer(x, cfg, W, l, cos, sin)
     xn = rmsnorm(x, W["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5))

@@ -81,6 +81,7 @@ def _run_cli(args, stdin=b""):
             "orig = api.Session.__init__\n"
             "def init(self, model, **kw):\n    kw['device'] = 'cpu'; orig(self, model, **kw)\n"
             "api.Session.__init__ = init\n"
+            "import hfcpu_b200.cli.main as cm; cm.App.device = 'cpu'\n"
             "from hfcpu_b200.cli.main import main; sys.exit(main(sys.argv[1:]))")
     return subprocess.run([sys.executable, "-c", code, *args], input=stdin, capture_output=True, env=env, timeout=120)
 
@@ -188,3 +189,133 @@ def test_inspect_lists_what_a_model_file_holds(tiny_folders, tmp_path):
     assert "@done status=error code=EFORMAT" in r.stdout.decode()
     r = _run_cli(["--stdin-mode", "none", "--op", "inspect"])
     assert "code=EINVAL" in r.stdout.decode() and "inspect needs --model" in r.stdout.decode()
+
+
+def _golden_folder(tmp_path, name):
+    """The model of tests/golden/tiny_<name>.json as a folder (float32, window off, as the reference ran it)."""
+    import json
+    import torch
+    from hfcpu_b200.config import config_from_dict
+    from hfcpu_b200.weights import weights_path, write_safetensors
+    from test_golden import _weights
+    record = json.load(open(os.path.join(ROOT, "tests", "golden", f"tiny_{name}.json")))
+    folder = str(tmp_path / f"golden_{name}")
+    config_from_dict(record["config"]).save(folder)
+    write_safetensors(weights_path(folder), _weights(record))
+    return record, folder
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_logprob_values_are_the_references(tmp_path, name):
+    """--logprobs 5 on the models the reference ran (tests/golden): the same token ids, the same five candidates, and
+    log-probabilities within the bound its own oracle uses for float weights (4e-3; its cache is float16,
+    src/model.c:599-600).  Formula: src/sample.c:25-55."""
+    record, folder = _golden_folder(tmp_path, name)
+    worst = 0.0
+    for case in record["cases"]:
+        r = _run_cli(["--stdin-mode", "none", "--op", "generate", "--model", folder, "--dtype", "fp32", "--kv-pages", "64",
+                      "--kv-block", "8", "--ctx-max", "256", "--prompt-ids", " ".join(map(str, case["prompt"])),
+                      "--temp", "0", "--max-tokens", str(len(case["tokens"])), "--logprobs", "5"])
+        assert r.returncode == 0, r.stderr.decode()
+        toks = [l for l in r.stdout.decode().splitlines() if l.startswith("@token")]
+        assert len(toks) == len(case["tokens"])
+        for line, want in zip(toks, case["tokens"]):
+            f = dict(kv.split("=", 1) for kv in line.replace('top="', "top=").rstrip('"').split(" ", 4)[1:])
+            top = [(int(a.split(":")[0]), float(a.split(":")[1])) for a in f["top"].split()]
+            assert int(f["id"]) == want["id"] and top[0][0] == want["id"]
+            worst = max(worst, abs(float(f["logprob"]) - want["logprob"]))
+            theirs = dict((i, v) for i, v in want["top"])
+            for i, v in top:
+                if i in theirs:
+                    worst = max(worst, abs(v - theirs[i]))
+                else:                                  # fifth and sixth candidate closer than the bound
+                    assert abs(v - want["top"][-1][1]) < 8e-3
+    assert worst < 4e-3, worst
+
+
+def test_bench_random_weights_and_profile(tmp_path):
+    """--random-weights CONFIG.json (the role of tools/mkmodel.pl:104-119) serves --op generate and --op bench without a
+    model file; @bench carries the fractions beside the reference's fields (src/ops.c:1023); --profile splits a
+    stage into the reference's phases (src/ops.c:593-604)."""
+    import json
+    import torch
+    from conftest import TINY_A
+    from hfcpu_b200.config import config_from_dict
+    from hfcpu_b200.models import build_model_specs
+    from hfcpu_b200.weights import random_tensors
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(TINY_A))
+    common = ["--dtype", "fp32", "--kv-pages", "64", "--ctx-max", "256", "--random-weights", str(cfg_path),
+              "--weights-seed", "5", "--weights-std", "0.2"]
+    prompt = make_requests("A", [9], seed=4)["r0"]
+    script = (f"--op generate --prompt-ids '{' '.join(map(str, prompt))}' --temp 0 --max-tokens 4 --profile\n"
+              "--op bench --bench-prompt 24 --bench-gen 6 --bench-batch 1,3 --probe-reps 2\n").encode()
+    r = _run_cli(["--stdin-mode", "args", *common], script)
+    assert r.returncode == 0, r.stderr.decode()
+    lines = r.stdout.decode().splitlines()
+    W = random_tensors(build_model_specs(config_from_dict(TINY_A)), 5, torch.float32, std=0.2)
+    toks = [int(l.split("id=")[1].split()[0]) for l in lines if l.startswith("@token")]
+    assert toks == plain.greedy(TINY_A, W, prompt, 4)
+    prof = [l for l in lines if l.startswith("@profile")]
+    assert [l.split()[1] for l in prof] == ["stage=prefill", "stage=decode"]
+    for key in ("steps=", "step_ms=", "embed=", "glue=", "qkv=", "attn=", "wo=", "gate_up=", "silu=", "down=", "head=",
+                "quant=", "sample=", "host="):
+        assert key in prof[1], key
+    bench = [l for l in lines if l.startswith("@bench")]
+    assert len(bench) == 2 and bench[0].startswith("@bench batch=1 prefill_tok_s=") and "batch=3" in bench[1]
+    for l in bench:
+        f = dict(kv.split("=", 1) for kv in l.split()[1:])
+        assert f["prompt_tokens"] == "24" and f["gen_tokens"] == "6" and float(f["decode_tok_s"]) > 0
+        assert 0 < float(f["hbm_frac"]) < 1 and 0 < float(f["mma_frac"]) < 1 and f["peaks"] in ("measured", "fallback")
+    assert r.stderr.decode().count("model loaded") == 1
+    # a bench that cannot fit answers ERANGE / ENOMEM and leaves the session usable
+    script = ("--op bench --bench-prompt 250 --bench-gen 10\n--op bench --bench-prompt 200 --bench-gen 8 --bench-batch 2\n"
+              "--op bench --bench-prompt 8 --bench-gen 2\n").encode()
+    r = _run_cli(["--stdin-mode", "args", *common, "--kv-pages", "16"], script)
+    out = r.stdout.decode()
+    assert "code=ERANGE" in out and "code=ENOMEM" in out and out.count("@bench batch=1") == 1, out
+
+
+def test_interrupt_cancels_the_running_request_and_the_process_stays(tiny_folders):
+    """SIGINT while a request generates ends it with stop=cancel; the process stays and serves the next request
+    (src/main.c:20-27, src/ops.c:829-833)."""
+    import signal
+    import time
+    folder = tiny_folders["A"]
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([ROOT, os.path.join(ROOT, "tests")]))
+    code = ("import sys; from hfcpu_b200 import kernels; from emu_backend import EmuBackend; "
+            "kernels.set_backend(EmuBackend()); import hfcpu_b200.api as api; "
+            "orig = api.Session.__init__\n"
+            "def init(self, model, **kw):\n    kw['device'] = 'cpu'; orig(self, model, **kw)\n"
+            "api.Session.__init__ = init\n"
+            "from hfcpu_b200.cli.main import main; sys.exit(main(sys.argv[1:]))")
+    p = subprocess.Popen([sys.executable, "-c", code, "--stdin-mode", "args", "--dtype", "fp32", "--kv-pages", "64",
+                          "--ctx-max", "256", "--model", folder], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                         stderr=subprocess.PIPE, env=env)
+    try:
+        p.stdin.write(b"--op generate --prompt-ids '1 2 3' --temp 0 --max-tokens 200 --id long\n")
+        p.stdin.flush()
+        lines = []
+        while True:
+            line = p.stdout.readline().decode()
+            assert line, p.stderr.read().decode()
+            lines.append(line)
+            if line.startswith("@token"):
+                break
+        p.send_signal(signal.SIGINT)
+        while not lines[-1].startswith("@done"):
+            line = p.stdout.readline().decode()
+            assert line
+            lines.append(line)
+        gen = [l for l in lines if l.startswith("@gen ")][0]
+        assert gen.strip().endswith("stop=cancel") and lines[-1].startswith("@done status=ok")
+        assert 1 <= int(gen.split("tokens=")[1].split()[0]) < 200
+        p.stdin.write(b"--op generate --prompt-ids '4 5' --temp 0 --max-tokens 2 --id next\n!stats\n!quit\n")
+        p.stdin.flush()
+        out, _ = p.communicate(timeout=60)
+        out = out.decode()
+        assert "@begin id=next" in out and out.count("@token") == 2 and "stop=length" in out
+        assert "pages_used=" in out and p.returncode == 0
+    finally:
+        if p.poll() is None:
+            p.kill()

@@ -404,42 +404,6 @@ def test_linear_rope_kv_fused(geom):
         assert rel(x.float(), y.float()) < 1.5e-2
 
 
-@pytest.mark.parametrize("shape", [(1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (3, 1000, 192), (16, 320, 72), (9, 50, 40),
-                                   (13, 152064, 256), (8, 37888, 512)])
-def test_linear_weight_streaming(shape):
-    """The weight-streaming product for at most 16 rows (store, accumulate, SwiGLU) against float64 and against
-    the tcgen05 kernel."""
-    from hfcpu_b200 import kernels
-    b = kernels.backend()
-    old_max, b.gemv_max = b.gemv_max, 16
-    M, N, K = shape
-    a, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.05)
-    bias = rnd(N, dtype=torch.bfloat16)
-    ref = a.double() @ w.double().T
-    out = torch.empty(M, N, device=DEV)
-    native().linear(a, w, bias, out, False)
-    assert rel(out, ref + bias.double()) < 2e-5
-    again = torch.empty(M, N, device=DEV)
-    native().linear(a, w, bias, again, False)
-    assert torch.equal(out, again)
-    b.gemv_max = 0
-    tc = torch.empty(M, N, device=DEV)
-    native().linear(a, w, bias, tc, False)
-    b.gemv_max = 16
-    assert rel(out, tc) < 2e-5
-    res = rnd(M, N, seed=9)
-    want = res.double() + ref
-    native().linear(a, w, None, res, True)
-    assert rel(res, want) < 2e-5
-    if N % 2 == 0:
-        gu = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
-        h = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
-        native().linear_swiglu(a, w, gu, h)
-        g_, u_ = ref[:, 0::2], ref[:, 1::2]
-        assert rel(h, (g_ / (1 + torch.exp(-g_))) * u_) < 1.5e-2
-    b.gemv_max = old_max
-
-
 @pytest.mark.parametrize("geom", [(28, 4, 128, 16), (4, 4, 128, 8), (16, 1, 128, 128), (5, 5, 128, 32)])
 def test_attention_tensor_core_prompt_portions(geom, both_tc_forms):
     """The tcgen05 attention kernel (head_dim 128): long portions over long histories, several requests, windows,

@@ -1,5 +1,7 @@
-"""The tensor-core kernels at the layer sizes of the benchmark configurations (two layers each), against the plain
-kernels on the same bfloat16 model: a prompt in portions, then decode steps at batch 1, 5 and 64."""
+"""The tensor-core kernels at the layer sizes of the benchmark configurations (two layers each): a prompt in portions,
+then decode steps at batch 1, 5 and 64, against the plain implementation (tests/plain_qwen2.py, evaluated in float32 by
+torch on the GPU on the same bfloat16 weights) at the end of every portion, and against the engine's plain kernels
+everywhere."""
 import pytest
 import torch
 
@@ -67,3 +69,26 @@ def test_fast_kernels_agree_with_plain_kernels(name):
     for i, (x, y) in enumerate(zip(fast, plain)):
         err = float((x - y).abs().max() / y.abs().max())
         assert err < 3e-2, f"{name}: output {i} differs by {err:.3g}"
+    # the plain implementation, which shares nothing with the engine, at the end of every portion of every prompt
+    import plain_qwen2
+    from hfcpu_b200.weights import RandomSource
+    src = RandomSource(model.tensor_specs(), 1, torch.bfloat16, torch.device("cuda:0"), std=0.02)
+    W = {n: src[n].float() for n in src.names()}
+    old_tf32 = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        at = 0
+        for r, ids in prompts.items():
+            ref = plain_qwen2.forward(cfg.to_dict(), W, ids, dtype=torch.float32)
+            a = 0
+            for n in (300, 17, 128, 255):
+                if a >= len(ids):
+                    break
+                a = min(a + n, len(ids))
+                want = ref[a - 1].cpu()
+                err = float((fast[at] - want).abs().max() / want.abs().max())
+                assert err < 3e-2, f"{name}: request {r} position {a - 1} differs from the plain implementation by {err:.3g}"
+                at += 1
+            del ref
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old_tf32

@@ -285,3 +285,79 @@ def test_a_request_waits_only_for_the_tokens_it_shares(tiny_folders, emu):
     assert sess.engine.cache.pages_in_use() == 0
     alone = _session(tiny_folders["B"], "B", 200, budget=16)
     assert alone.generate([b], temp=0, max_tokens=4)[0][0].tokens == sch.requests["b"].generated
+
+
+def test_timeouts_end_requests_and_give_their_pages_back(tiny_folders, emu, monkeypatch):
+    """--timeout: past the limit a request that has its first token ends with stop=timeout (src/ops.c:829-833); one
+    that is still computing its prompt fails with ECANCEL (src/ops.c:790-791).  The clock is the test's."""
+    import hfcpu_b200.engine.scheduler as S
+    from hfcpu_b200 import SamplingParams
+    from hfcpu_b200.engine import FinishEvent, Request
+    now = [100.0]
+    monkeypatch.setattr(S.time, "perf_counter", lambda: now[0])
+    sess = _session(tiny_folders["A"], "A", 64, budget=16, chunk=8)
+    sch = sess.scheduler
+    reqs = make_requests("A", [6, 40, 5], seed=9)
+    sch.submit(Request("fast", reqs["r0"], SamplingParams(temp=0, max_tokens=50), timeout=5.0))
+    sch.submit(Request("slow", reqs["r1"], SamplingParams(temp=0, max_tokens=50), timeout=5.0))
+    sch.submit(Request("free", reqs["r2"], SamplingParams(temp=0, max_tokens=3)))                 # no limit of its own
+    events = []
+    for _ in range(2):                      # "fast" has its first token, "slow" is two portions into its prompt
+        now[0] += 1.0
+        events += sch.step()
+    fast, slow = sch.requests["fast"], sch.requests["slow"]
+    assert fast.generated and slow.computed < len(slow.prompt) and not slow.generated
+    now[0] += 10.0
+    events += sch.step()
+    ends = {e.req: e for e in events if isinstance(e, FinishEvent)}
+    assert ends["fast"].stop == "timeout" and ends["fast"].error is None and len(fast.generated) >= 1
+    assert ends["slow"].stop == "error" and ends["slow"].error.startswith("ECANCEL")
+    events += sch.run()
+    assert sch.requests["free"].stop == "length" and len(sch.requests["free"].generated) == 3
+    assert sess.engine.cache.pages_in_use() == 0 and not sess.engine.live_requests()
+    sess.engine.cache.check()
+
+
+def test_cancel_between_steps(tiny_folders, emu):
+    """Scheduler.cancel: a running request and a waiting one both end with stop=cancel at the next step; the others
+    go on and generate what they would have generated alone."""
+    from hfcpu_b200 import SamplingParams
+    from hfcpu_b200.engine import FinishEvent, Request
+    sess = _session(tiny_folders["A"], "A", 64, max_seqs=2)
+    sch = sess.scheduler
+    reqs = make_requests("A", [9, 12, 7], seed=5)
+    for name, ids in zip("abc", reqs.values()):
+        sch.submit(Request(name, ids, SamplingParams(temp=0, max_tokens=6)))
+    sch.step()
+    assert [r.id for r in sch.running] == ["a", "b"] and [r.id for r in sch.waiting] == ["c"]
+    sch.cancel("a")
+    sch.cancel("c")
+    events = sch.run()
+    ends = {e.req: e.stop for e in events if isinstance(e, FinishEvent)}
+    assert ends == {"a": "cancel", "c": "cancel", "b": "length"}
+    cfg, W = plain.read_folder(tiny_folders["A"])
+    assert sch.requests["b"].generated == plain.greedy(cfg, W, reqs["r1"], 6)
+    assert len(sch.requests["a"].generated) <= 1 and not sch.requests["c"].generated
+    assert sess.engine.cache.pages_in_use() == 0 and not sess.engine.live_requests()
+
+
+def test_a_step_that_raises_leaves_nothing_behind(tiny_folders, emu):
+    """When the engine's step fails, the call's requests are ended and their pages returned, so that the next call on
+    the same session runs alone and gives what it gives on a fresh one."""
+    sess = _session(tiny_folders["A"], "A", 64)
+    prompts = list(make_requests("A", [7, 16], seed=2).values())
+    real, calls = sess.engine.model.forward, [0]
+
+    def failing(ctx):
+        calls[0] += 1
+        if calls[0] == 3:
+            raise RuntimeError("a kernel met a device-side wait that ran out")
+        return real(ctx)
+    sess.engine.model.forward = failing
+    with pytest.raises(RuntimeError, match="ran out"):
+        sess.generate(prompts, temp=0, max_tokens=8)
+    sess.engine.model.forward = real
+    assert not sess.scheduler.has_work() and not sess.engine.live_requests() and sess.engine.cache.pages_in_use() == 0
+    out = sess.generate(prompts[0], temp=0, max_tokens=5)
+    cfg, W = plain.read_folder(tiny_folders["A"])
+    assert out[0].tokens == plain.greedy(cfg, W, prompts[0], 5)

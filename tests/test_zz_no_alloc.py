@@ -45,12 +45,19 @@ def test_noalloc_linear_matches_the_regular_entry_point_twice():
                                c_int(K), _ptr(ws), c_size_t(need), stream)
         assert rc == 0, lib.hfb_last_error().decode()
         ref = a.double() @ w.double().T + bias.double()
+        gots = [torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+        torch.cuda.synchronize()
+        free_before = None
         for call in range(2):
-            got = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+            got = gots[call]
+            if call == 1:
+                free_before = torch.cuda.mem_get_info()[0]      # the second call must leave the free memory as it is
             rc = lib.hfb_linear_tc_noalloc(_ptr(a), _ptr(w), _ptr(bias), c_int(1), _ptr(got), c_int(1), c_int(0), c_int(M),
                                            c_int(N), c_int(K), stream)
             assert rc == 0, lib.hfb_last_error().decode()
             torch.cuda.synchronize()
+            if call == 1:
+                assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
             assert torch.equal(got, want), f"call {call} differs from hfb_linear_tc at {M}x{N}x{K}"
             err = float((got.double() - ref).abs().max() / ref.abs().max())
             assert err < 1e-2, err                      # the tolerance of the bfloat16 product tests
@@ -80,10 +87,18 @@ def test_noalloc_linear_refuses_what_the_array_cannot_hold():
         assert rc == 4 and "built-in" in lib.hfb_last_error().decode()       # HFB_ERANGE, with both numbers
     else:
         assert rc == 0
-    rc = lib.hfb_linear_tc_noalloc(_ptr(a), _ptr(w), None, c_int(0), _ptr(out), c_int(1), c_int(0), c_int(128), c_int(9000),
+    # (operands sized for the call, in case the split count of this GPU lets it run)
+    w2 = torch.zeros(9000, 4096, device="cuda", dtype=torch.bfloat16)
+    out2 = torch.zeros(128, 9000, device="cuda", dtype=torch.bfloat16)
+    rc = lib.hfb_linear_tc_noalloc(_ptr(a), _ptr(w2), None, c_int(0), _ptr(out2), c_int(1), c_int(0), c_int(128), c_int(9000),
                                    c_int(4096), stream)
     need2 = lib.hfb_linear_tc_workspace(c_int(128), c_int(9000), c_int(4096))
     assert (rc == 4) == (need2 > (8 << 20))
+    # a bias that is not 16-byte aligned is refused before anything is launched
+    bias = torch.zeros(9008, device="cuda", dtype=torch.bfloat16)[1:9001]
+    rc = lib.hfb_linear_tc_noalloc(_ptr(a), _ptr(w2), _ptr(bias), c_int(1), _ptr(out2), c_int(1), c_int(0), c_int(8), c_int(9000),
+                                   c_int(4096), stream)
+    assert rc == 2 and "aligned" in lib.hfb_last_error().decode()
     rc = lib.hfb_linear_tc_noalloc(_ptr(a), _ptr(w), None, c_int(0), _ptr(out), c_int(1), c_int(0), c_int(8), c_int(64),
                                    c_int(12), stream)
     assert rc == 2                                      # K not a multiple of 8: HFB_ENOTSUP, as the regular entry point
