@@ -227,6 +227,19 @@ __global__ void argmax_kernel(const float *logits, int32_t *out, int V)
     if (threadIdx.x == 0) out[blockIdx.x] = si[0] < 0 ? 0 : si[0];
 }
 
+// a[m, :] *= rsqrt(sum_p sumsq[p, m] / E + eps): completes rows of an RMSNorm whose row factor was left to the consumer.
+template <typename T>
+__global__ void scale_rows_kernel(T *a, const float *sumsq, int parts, int M, int E, float eps)
+{
+    pdl_sync();
+    const int m = blockIdx.x;
+    float ss = 0.f;
+    for (int p = 0; p < parts; p++) ss += sumsq[(size_t)p * M + m];
+    const float r = 1.0f / sqrtf(ss / (float)E + eps);
+    T *row = a + (size_t)m * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) row[i] = from_f32<T>(to_f32(row[i]) * r);
+}
+
 }  // namespace hfb
 
 using namespace hfb;
@@ -310,4 +323,13 @@ extern "C" int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_s
     if (V <= 0) return fail(HFB_EINVAL, "argmax: empty vocabulary");
     g_launch_err = launch_pdl(argmax_kernel, dim3(M), dim3(1024), 0, (cudaStream_t)s, logits, out, V);
     return check_pdl_launch(g_launch_err, "argmax");
+}
+
+extern "C" int hfb_scale_rows(void *a, int dt, const float *sumsq, int parts, float eps, int M, int E, hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (!valid_dt(dt) || parts < 1 || E <= 0 || !sumsq) return fail(HFB_EINVAL, "scale_rows: bad arguments");
+    if (dt == HFB_F32) g_launch_err = launch_pdl(scale_rows_kernel<float>, dim3(M), dim3(256), 0, (cudaStream_t)s, (float *)a, sumsq, parts, M, E, eps);
+    else g_launch_err = launch_pdl(scale_rows_kernel<__nv_bfloat16>, dim3(M), dim3(256), 0, (cudaStream_t)s, (__nv_bfloat16 *)a, sumsq, parts, M, E, eps);
+    return check_pdl_launch(g_launch_err, "scale_rows");
 }

@@ -41,6 +41,28 @@ constexpr int GEMM_THREADS = 192;
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
 
+enum { FIN_NONE = 0, FIN_RESIDUAL = 1, FIN_ROPE_KV = 2 };
+
+// What the CTA that stores the last split of a weight tile does with the tile's sum (few-token form only): the
+// reduction of the split-K partial sums and the memory-bound step that follows it, without another kernel.
+//   FIN_RESIDUAL: residual[t, n] += sum (+ bias); y[t, n] = residual * norm_w[n] (the next RMSNorm without its row
+//     factor) and, per row and quarter of the tile, the sum of squares of the new residual in sumsq[tile * 4 + q, t]:
+//     whoever consumes y multiplies by rsqrt(sum of the parts / N + eps) per row.
+//   FIN_ROPE_KV: the tile holds whole heads of the q|k|v row (128 % d == 0): + bias, rotary encoding, q to q_out,
+//     k and v into the paged cache, as reduce_rope_kv_kernel does.
+struct FinishParams {
+    int kind;
+    int *counters;                     // one per weight tile; zero before the launch, zero again after it
+    float *residual; const void *norm_w; int norm_w_dt; void *y; int y_dt; float *sumsq;
+    const float *cos_sin; int n_rot, n_positions; const int32_t *positions, *slots;
+    void *q_out, *k_cache, *v_cache; long long cache_slots; int H, G, d;
+};
+
+// The activations are the rows of an RMSNorm still to be multiplied by their row factor: sumsq[parts, M] holds
+// partial sums of squares per row, summed in order here; the factor rsqrt(sum / width + eps) is applied to the
+// accumulators (a product is linear in its rows).  sumsq == null: the activations are complete.
+struct RowScale { const float *sumsq; int parts; float eps; int width; };
+
 struct GemmParams {
     int M, N, K;                       // logical sizes: tokens, output features, inner
     int swapped;                       // X = weights, Y = activations
@@ -50,6 +72,8 @@ struct GemmParams {
     const void *bias; int bias_dt;     // [N] or null
     int mode;
     float *partial;                    // [splits, M, N] when mode == EPI_PARTIAL
+    FinishParams fin;                  // few-token form with partial sums only
+    RowScale scale;                    // few-token form only
 };
 
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -65,6 +89,8 @@ __host__ __device__ constexpr uint32_t instr_desc(int n)
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_X >> 4) << 24);
 }
 
+constexpr uint32_t FIN_SMEM_BYTES = (128 + 2 * 128) * 4;     // row factors of up to 128 tokens; two buffers of one tile row
+
 template <int BN> constexpr int tmem_cols()
 {
     int need = 2 * BN, c = 32;
@@ -74,17 +100,23 @@ template <int BN> constexpr int tmem_cols()
 
 template <int BN, int STAGES> constexpr uint32_t gemm_smem_bytes()
 {
-    return 1024 + STAGES * (X_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
+    return 1024 + STAGES * (X_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + FIN_SMEM_BYTES;
 }
 
 // One chunk of 16 accumulator columns of one row: v[i] is element (xr, y0 + i) of X . Y^T.
 // `live` false: the same instructions, nothing stored (the few-token form runs its epilogue once this way while the
 // first weights are on their way, so that its code is in the instruction cache when the first tile is done: fetched
 // at that moment it waits behind the weight stream, several microseconds for a 64-token tile).
-__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t *v, int xr, int y0, int split, int lane,
-                                               bool live = true)
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t *v, int xr, int y0, int split, int lane,
+                                               bool live = true, const float *rstd = nullptr)
 {
     if (!live && !p.swapped) return;
+    if (rstd && p.mode != EPI_PARTIAL) {
+        // the tokens' row factors (all lanes read the same words of shared memory); partial sums are scaled when
+        // they are summed
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * rstd[(y0 + i) & 127]);
+    }
     if (p.swapped && p.mode == EPI_SWIGLU) {
         // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2].  The two lanes
         // of a pair exchange their values and share the work: of every two tokens the even lane finishes the first,
@@ -225,6 +257,88 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32
     }
 }
 
+// ---- finishing a weight tile in the CTA that stored its last split ----------------------------------------
+// The four epilogue warps (128 threads) meet on a named barrier of their own.
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+// Sum over the splits, in split order, of element (t, n) of the product; read past the L1 cache, which may hold
+// lines of an earlier launch's partial sums at the same addresses.
+__device__ __forceinline__ float sum_splits(const GemmParams &p, int t, int n)
+{
+    const float *src = p.partial + (size_t)t * p.N + n;
+    const size_t MN = (size_t)p.M * p.N;
+    float acc = 0.f;
+    for (int s = 0; s < p.splits; s++) acc += __ldcg(src + (size_t)s * MN);
+    return acc;
+}
+
+// f = 0..127: this thread's row of the tile; q = its warp among the four.
+__device__ __forceinline__ void finish_residual(const GemmParams &p, int tx, int f, int q, int lane)
+{
+    const FinishParams &fp = p.fin;
+    const int n = tx * TILE_X + f;
+    const bool live = n < p.N;
+    const float b = (live && p.bias) ? load_any(p.bias, p.bias_dt, n) : 0.f;
+    const float w = (live && fp.y) ? load_any(fp.norm_w, fp.norm_w_dt, n) : 0.f;
+#pragma unroll 2
+    for (int t = 0; t < p.M; t++) {
+        float v = 0.f;
+        if (live) {
+            float *res = fp.residual + (size_t)t * p.N + n;
+            v = (sum_splits(p, t, n) + b) + __ldcg(res);
+            *res = v;
+            if (fp.y) store_any(fp.y, fp.y_dt, (size_t)t * p.N + n, v * w);
+        }
+        if (fp.sumsq) {
+            const float ss = warp_sum(v * v);
+            if (lane == 0) fp.sumsq[(size_t)(tx * 4 + q) * p.M + t] = ss;
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void finish_rope_kv(const GemmParams &p, int tx, int f, const float *rstd, float *xch, int *err)
+{
+    const FinishParams &fp = p.fin;
+    const int n = tx * TILE_X + f, d = fp.d, half = fp.n_rot >> 1;
+    const bool live = n < p.N;
+    const int head = n / d, i = n - head * d;
+    const float b = (live && p.bias) ? load_any(p.bias, p.bias_dt, n) : 0.f;
+    const bool rotate = live && head < fp.H + fp.G && i < fp.n_rot;
+    for (int t = 0; t < p.M; t++) {
+        float v = 0.f;
+        if (live) {
+            v = sum_splits(p, t, n);
+            if (rstd) v *= rstd[t];
+            // the separate kernels round q|k|v to the run type before rotating; keep the same values
+            v = to_f32(from_f32<T>(v + b));
+        }
+        float *mine = xch + (t & 1) * TILE_X;
+        mine[f] = v;
+        epi_bar();                                        // (the buffer of token t - 1 is free again after this one)
+        if (!live) continue;
+        float out = v;
+        if (rotate) {
+            int pos = fp.positions[t];
+            if (pos < 0 || pos >= fp.n_positions) { atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+            const int k = i < half ? i : i - half;
+            const float2 cs = *(const float2 *)(fp.cos_sin + ((size_t)pos * half + k) * 2);
+            const float other = i < half ? mine[f + half] : mine[f - half];
+            out = i < half ? v * cs.x - other * cs.y : other * cs.y + v * cs.x;
+        }
+        if (head < fp.H) {
+            ((T *)fp.q_out)[((size_t)t * fp.H + head) * d + i] = from_f32<T>(out);
+        } else {
+            long long slot = fp.slots ? fp.slots[t] : -1;
+            if (slot >= fp.cache_slots) { atomicOr(err, HFB_ERR_SLOT); slot = -1; }
+            if (slot >= 0) {
+                if (head < fp.H + fp.G) ((T *)fp.k_cache)[((size_t)slot * fp.G + (head - fp.H)) * d + i] = from_f32<T>(out);
+                else ((T *)fp.v_cache)[((size_t)slot * fp.G + (head - fp.H - fp.G)) * d + i] = from_f32<T>(out);
+            }
+        }
+    }
+}
+
 // ---- the kernel ---------------------------------------------------------------------------------
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -241,6 +355,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
     volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen_base + STAGES * (X_BYTES + Y_BYTES) + (2 * STAGES + 4) * 8);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    volatile int *last_flag = (volatile int *)(tmem_slot + 2);       // this CTA stored a tile's last split
+    float *rstd_smem = (float *)(tmem_slot + 4);                     // [128] row factors, then [2][128] exchange
+    float *xch_smem = rstd_smem + 128;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -344,10 +461,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int row = q * 32 + lane;
         uint32_t tile_it = 0;
         bool ok = true;
+        const float *rstd = (p.swapped && p.scale.sumsq) ? rstd_smem : nullptr;
         // With few tokens the first turn of this loop is a rehearsal: it reads whatever the accumulator holds and
         // stores nothing, before the kernel in front is known to have finished (see epilogue_chunk).
         bool rehearsal = p.swapped != 0;
-        if (!rehearsal) pdl_sync();                   // nothing is written before the kernel in front has finished
+        auto after_wait = [&]() {
+            // what comes from the kernel in front: the rows' sums of squares.  Thread t sums the parts of token t in
+            // order and keeps the row factor where the four warps find it.
+            if (rstd) {
+                if (row < p.M) {
+                    float ss = 0.f;
+                    for (int i = 0; i < p.scale.parts; i++) ss += __ldcg(p.scale.sumsq + (size_t)i * p.M + row);
+                    rstd_smem[row] = 1.0f / sqrtf(ss / (float)p.scale.width + p.scale.eps);
+                }
+                epi_bar();
+            }
+        };
+        if (!rehearsal) { pdl_sync(); after_wait(); } // nothing is written before the kernel in front has finished
         for (int item = blockIdx.x; item < total_items && ok;) {
             int split = item / per_split, t = item % per_split;
             int tx = t % p.tiles_x, ty = t / p.tiles_x;
@@ -366,17 +496,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tmem_ld16(taddr + c0, v);
                 if (two) tmem_ld16(taddr + c0 + 16, v + (BN >= 32 ? 16 : 0));
                 tmem_wait_ld();
-                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane, !rehearsal);
-                if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane, !rehearsal);
+                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane, !rehearsal, rstd);
+                if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane, !rehearsal, rstd);
             }
             if (rehearsal) {
                 rehearsal = false;
                 pdl_sync();
+                after_wait();
                 continue;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * a);
+            if (p.swapped && p.fin.kind != FIN_NONE) {
+                // The split is in global memory.  Count it; the CTA that brings a tile's count to the number of
+                // splits sums the tile in split order, whichever CTA that is, and does the step that follows.
+                __threadfence();
+                epi_bar();
+                if (row == 0) {
+                    const int before = atomicAdd(&p.fin.counters[tx], 1);
+                    const int last = before == p.splits - 1;
+                    if (last) p.fin.counters[tx] = 0;            // every split has counted: ready for the next launch
+                    *last_flag = last;
+                }
+                epi_bar();
+                if (*last_flag) {
+                    __threadfence();
+                    if (p.fin.kind == FIN_RESIDUAL) finish_residual(p, tx, row, q, lane);
+                    else if (p.out_dt == HFB_BF16) finish_rope_kv<__nv_bfloat16>(p, tx, row, rstd, xch_smem, err);
+                    else finish_rope_kv<float>(p, tx, row, rstd, xch_smem, err);
+                }
+                epi_bar();                                       // the flag may be rewritten for the next item
+            }
             item += gridDim.x;
             tile_it++;
         }
@@ -913,18 +1064,34 @@ extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int
 
 // h[M, N/2] = silu(g) * u where row 2i of w holds gate feature i and row 2i+1 up feature i: the activation runs in
 // the product's epilogue, from the float32 accumulators.
-extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s)
+static int linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, const hfb::RowScale &scale,
+                            hfb_stream s)
 {
     if (M <= 0 || N <= 0) return HFB_OK;
     int rc = check_tc_args("linear_tc_swiglu", a, w, out, M, N, K);
     if (rc != HFB_OK) return rc;
     if ((N & 1) || !valid_dt(out_dt)) return fail(HFB_EINVAL, "linear_tc_swiglu: N must be even (gate and up rows alternate)");
+    if (scale.sumsq && M > 128) return fail(HFB_ENOTSUP, "linear_tc_swiglu: row factors are applied with at most 128 rows (got %d)", M);
     GemmParams p{};
     CUtensorMap mx, my;
     int bn;
     if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
     p.out = out; p.out_dt = out_dt; p.bias = nullptr; p.mode = EPI_SWIGLU;
+    p.scale = scale;
     return launch_bn(bn, mx, my, p, (cudaStream_t)s);
+}
+
+extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s)
+{
+    return linear_tc_swiglu(a, w, out, out_dt, M, N, K, hfb::RowScale{}, s);
+}
+
+// The same where the rows of `a` still lack their RMSNorm row factor (see hfb_linear_tc_residual_y): M <= 128.
+extern "C" int hfb_linear_tc_swiglu_scaled(const void *a, const void *w, void *out, int out_dt, int M, int N, int K,
+                                           const float *sumsq, int parts, float eps, hfb_stream s)
+{
+    if (!sumsq || parts < 1) return fail(HFB_EINVAL, "linear_tc_swiglu_scaled: no sums of squares");
+    return linear_tc_swiglu(a, w, out, out_dt, M, N, K, hfb::RowScale{sumsq, parts, eps, K}, s);
 }
 
 // Only the split-K partial sums: partial[s, M, N] float32 for s < *splits, in `workspace`
@@ -958,6 +1125,84 @@ extern "C" int hfb_linear_tc_partials(const void *a, const void *w, int M, int N
     p.partial = (float *)workspace;
     p.mode = EPI_PARTIAL;
     *splits = p.splits;
+    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
+}
+
+// ---- few tokens: the product, its split-K reduction and the step after it in one kernel ---------------------
+// Sets up the few-token product with partial sums in `workspace` (hfb_linear_tc_partials_workspace bytes) and checks
+// the tile counters.
+static int plan_fused(const char *who, const void *a, const void *w, int M, int N, int K, void *workspace, size_t workspace_bytes,
+                      int *counters, int counters_len, hfb::GemmParams &p, int &bn, CUtensorMap &mx, CUtensorMap &my)
+{
+    using namespace hfb;
+    if (M > 128) return fail(HFB_ENOTSUP, "%s: at most 128 rows (got %d)", who, M);
+    int rc = check_tc_args(who, a, w, workspace, M, N, K);
+    if (rc != HFB_OK) return rc;
+    const size_t need = hfb_linear_tc_partials_workspace(M, N, K);
+    if (!workspace || workspace_bytes < need) return fail(HFB_EINVAL, "%s: workspace of %zu bytes, %zu needed", who, workspace_bytes, need);
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
+    if (!counters || counters_len < p.tiles_x) return fail(HFB_EINVAL, "%s: %d tile counters needed, %d given", who, p.tiles_x, counters_len);
+    const int want = (int)(need / ((size_t)M * N * sizeof(float)));
+    p.kb_per_split = (p.kb_total + want - 1) / want;
+    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    p.partial = (float *)workspace;
+    p.mode = EPI_PARTIAL;
+    p.fin.counters = counters;
+    return HFB_OK;
+}
+
+// Row-factor parts hfb_linear_tc_residual_y writes per row for N output features.
+extern "C" int hfb_linear_tc_sumsq_parts(int N) { return 4 * ((N + hfb::TILE_X - 1) / hfb::TILE_X); }
+
+// residual[M, N] += a . w^T (+ bias), M <= 128, in one kernel: the CTA that stores the last split of a weight tile
+// sums the splits in split order and adds them into the float32 residual.  With `y`: y = residual * norm_w (the
+// next RMSNorm without its row factor) and sumsq[hfb_linear_tc_sumsq_parts(N), M] = partial sums of squares of the
+// new residual rows; the row factor is rsqrt(sum over the parts / N + eps), which hfb_linear_tc_swiglu_scaled and
+// hfb_linear_tc_rope_kv apply.  `counters`: at least ceil(N / 128) ints, zero before the first launch (every launch
+// leaves them zero).
+extern "C" int hfb_linear_tc_residual_y(const void *a, const void *w, const void *bias, int bias_dt, float *residual,
+                                        const void *norm_w, int norm_w_dt, void *y, int y_dt, float *sumsq, int M, int N, int K,
+                                        void *workspace, size_t workspace_bytes, int *counters, int counters_len, hfb_stream s)
+{
+    if (M <= 0 || N <= 0) return HFB_OK;
+    if ((bias && !valid_dt(bias_dt)) || (y && (!valid_dt(y_dt) || !valid_dt(norm_w_dt) || !norm_w || !sumsq)))
+        return fail(HFB_EINVAL, "linear_tc_residual_y: bad arguments");
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn, rc;
+    if ((rc = plan_fused("linear_tc_residual_y", a, w, M, N, K, workspace, workspace_bytes, counters, counters_len, p, bn, mx, my)) != HFB_OK) return rc;
+    p.bias = bias; p.bias_dt = bias_dt; p.out_dt = HFB_F32;
+    p.fin.kind = FIN_RESIDUAL;
+    p.fin.residual = residual; p.fin.norm_w = norm_w; p.fin.norm_w_dt = norm_w_dt; p.fin.y = y; p.fin.y_dt = y_dt;
+    p.fin.sumsq = y ? sumsq : nullptr;
+    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
+}
+
+// q|k|v = a . w^T (scaled by the rows' factors when `in_sumsq` is given) + bias, rotary encoding of q and k, q to q_out
+// [M, H*d], k and v into the paged cache at `slots` (null: q only), M <= 128, in one kernel; head sizes that divide
+// 128.  Element type `dt` of q_out and the cache.  Same arithmetic as hfb_reduce_rope_kv.
+extern "C" int hfb_linear_tc_rope_kv(const void *a, const void *w, const void *bias, int bias_dt, const float *in_sumsq, int in_parts,
+                                     float in_eps, const float *cos_sin, int n_rot, int n_positions, const int32_t *positions,
+                                     const int32_t *slots, void *q_out, void *k_cache, void *v_cache, int64_t cache_slots, int dt,
+                                     int M, int H, int G, int d, int K, void *workspace, size_t workspace_bytes, int *counters,
+                                     int counters_len, hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (!valid_dt(dt) || H <= 0 || G <= 0 || d <= 0 || n_rot < 0 || n_rot > d || (n_rot & 1) || (bias && !valid_dt(bias_dt)))
+        return fail(HFB_EINVAL, "linear_tc_rope_kv: bad arguments");
+    if (TILE_X % d) return fail(HFB_ENOTSUP, "linear_tc_rope_kv: head size %d does not divide %d", d, TILE_X);
+    if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "linear_tc_rope_kv: rotation needs a table and positions");
+    const int N = (H + 2 * G) * d;
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn, rc;
+    if ((rc = plan_fused("linear_tc_rope_kv", a, w, M, N, K, workspace, workspace_bytes, counters, counters_len, p, bn, mx, my)) != HFB_OK) return rc;
+    p.bias = bias; p.bias_dt = bias_dt; p.out_dt = dt;
+    if (in_sumsq) p.scale = RowScale{in_sumsq, in_parts, in_eps, K};
+    p.fin.kind = FIN_ROPE_KV;
+    p.fin.cos_sin = cos_sin; p.fin.n_rot = n_rot; p.fin.n_positions = n_positions; p.fin.positions = positions; p.fin.slots = slots;
+    p.fin.q_out = q_out; p.fin.k_cache = k_cache; p.fin.v_cache = v_cache; p.fin.cache_slots = cache_slots;
+    p.fin.H = H; p.fin.G = G; p.fin.d = d;
     return launch_bn(bn, mx, my, p, (cudaStream_t)s);
 }
 

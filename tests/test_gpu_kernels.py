@@ -452,29 +452,3 @@ def test_attention_long_context_far_keys(lens_q, both_tc_forms):
         assert rel(row, ref.view(-1, H, d)[t].float()) < TOL["bfloat16"]
     from hfcpu_b200 import kernels
     kernels.check_device_errors()
-
-
-@pytest.mark.parametrize("geom", [(28, 4, 128, 16), (14, 2, 64, 16), (8, 2, 128, 32)])
-def test_attention_decode_cluster_merge(geom):
-    """The decode kernel with the splits of a request as a thread-block cluster (merged through distributed shared
-    memory) gives what the form with a combine kernel gives."""
-    from hfcpu_b200 import kernels
-    H, G, d, bs = geom
-    b = kernels.backend()
-    lens_q, lens_kv = [1, 1, 1, 1, 1], [1, 64, 65, 1000, 2311]
-    for window in (0, 300):
-        case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window), lens_q, lens_kv, H, G)
-        ref = _run_attention(EmuBackend(), case, H, G, d, window)
-        plain = _run_attention(native(), case, H, G, d, window)
-        b.decode_cluster = True
-        try:
-            before = b.launches
-            out = _run_attention(native(), case, H, G, d, window)
-            assert b.launches - before == 1, "one kernel, no combine"
-            again = _run_attention(native(), case, H, G, d, window)
-        finally:
-            b.decode_cluster = False
-        assert rel(out.float(), ref.float()) < TOL["bfloat16"]
-        assert rel(out.float(), plain.float()) < TOL["bfloat16"]
-        assert torch.equal(out, again)
-    kernels.check_device_errors()
