@@ -49,6 +49,9 @@ struct AttnParams {
     __nv_bfloat16 *out;
     const int32_t *block_table, *positions, *tile_seq, *tile_t0, *tile_nt;
     float *part_o, *part_ml;            // split mode: [T*H, splits, D] and [T*H, splits, 2]
+    int *counters;                      // decode kernel, split mode: one per (tile, key/value head), zero between
+                                        // launches; the CTA that brings one to `splits` merges that tile (null: a
+                                        // second kernel merges)
     int max_blocks, block_size, window, H, G, splits;
     long long num_pages;
     float scale_log2;                   // scale * log2(e)

@@ -262,6 +262,73 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             p.out[th * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
         }
     }
+    if (p.splits > 1 && p.counters) {
+        // This split is in global memory.  Count it; the CTA that brings the count of its (tile, key/value head) to
+        // the number of splits merges them, in split order whichever CTA it is, with the arithmetic of
+        // attention_combine_kernel: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
+        volatile int *last_flag = abort_flag + 1;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();                              // (after the barrier: it covers every thread's stores)
+            int *cnt = p.counters + (size_t)tile * p.G + g;
+            const int last = atomicAdd(cnt, 1) == p.splits - 1;
+            if (last) *cnt = 0;
+            *last_flag = last;
+        }
+        __syncthreads();
+        if (!*last_flag) return;
+        __threadfence();
+        // What this costs is the latency of reads from the L2 cache, so they are issued many at a time.  First, per
+        // row, the weight of every split: f_s = 2^(m_s - m) / sum_s' l_s' 2^(m_s' - m).
+        constexpr int MAXS = 64;                          // (the host asks for no more splits than this)
+        float *fs = (float *)gen;                         // [16][MAXS]; the tile buffers are free
+        if (threadIdx.x < rows) {
+            const int row = threadIdx.x;
+            const size_t th = (size_t)(t0 + row / r) * p.H + g * r + row % r;
+            const float2 *ml = (const float2 *)(p.part_ml + th * p.splits * 2);
+            float m = -INFINITY;
+            for (int c = 0; c < p.splits; c += 16) {
+                float2 v[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) v[i] = c + i < p.splits ? __ldcg(ml + c + i) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    m = fmaxf(m, v[i].x);
+                    if (c + i < p.splits) { fs[row * MAXS + c + i] = v[i].x; fs[(16 + row) * MAXS + c + i] = v[i].y; }
+                }
+            }
+            float denom = 0.f;
+            for (int s = 0; s < p.splits; s++) {
+                const float ms = fs[row * MAXS + s];
+                const float f = ms == -INFINITY ? 0.f : exp2f(ms - m);
+                denom += fs[(16 + row) * MAXS + s] * f;
+                fs[row * MAXS + s] = f;
+            }
+            const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+            fs[(16 + row) * MAXS] = inv;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < rows * (D / 4); e += ADT_THREADS) {
+            const int row = e / (D / 4), c4 = e % (D / 4);
+            const size_t th = (size_t)(t0 + row / r) * p.H + g * r + row % r;
+            const float4 *src = (const float4 *)(p.part_o + th * p.splits * D) + c4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < p.splits; c += 16) {
+                float4 v[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++)
+                    v[i] = c + i < p.splits ? __ldcg(src + (size_t)(c + i) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 16; i++) {                 // in split order
+                    const float f = c + i < p.splits ? fs[row * MAXS + c + i] : 0.f;
+                    acc.x += v[i].x * f; acc.y += v[i].y * f; acc.z += v[i].z * f; acc.w += v[i].w * f;
+                }
+            }
+            const float inv = fs[(16 + row) * MAXS];
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+            *(uint2 *)(p.out + th * D + 4 * c4) = make_uint2(*(const uint32_t *)&lo, *(const uint32_t *)&hi);
+        }
+    }
 }
 
 template <int D, int STAGES>
@@ -269,7 +336,7 @@ static int launch_decode_tma(const CUtensorMap &mk, const CUtensorMap &mv, const
 {
     constexpr uint32_t TILE = (D / 64) * ADT_SUB;
     constexpr int smem = 1024 + 2 * STAGES * TILE + 16 * D * 2 + 16 * STAGES + 16;
-    static_assert(2 * STAGES * TILE >= (4 * 16 * (D + 2) + 96) * 4, "the merge reuses the tile buffers");
+    static_assert(2 * STAGES * TILE >= (4 * 16 * (D + 2) + 96) * 4 && 2 * STAGES * TILE >= 32 * 64 * 4, "the merge reuses the tile buffers");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -309,13 +376,14 @@ using namespace hfb;
 // Decode attention (tiles of one or two tokens of one request each, as hfb_attention_fast's 16-row form makes
 // them): bfloat16, head_dim 64 or 128, block sizes 8..64 that divide 64, at most 16 query rows per tile.
 // `stages` tiles of 64 keys are in flight per CTA (2..4); `splits` > 1 cuts each request's keys over that many
-// CTAs and needs hfb_attention_fast_scratch(T, H, d, splits) bytes of float32 scratch; a second kernel merges the
-// splits in split order.
+// CTAs and needs hfb_attention_fast_scratch(T, H, d, splits) bytes of float32 scratch.  The splits are merged in
+// split order: by the CTA that stores a tile's last split, when `counters` (n_tiles * G ints, zero before the first
+// launch; every launch leaves them zero) is given, else by a second kernel.
 extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                                     int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                                     const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size,
                                     int64_t num_pages, int window, float scale, void *out, void *scratch, size_t scratch_bytes,
-                                    int T, int H, int G, int d, hfb_stream s)
+                                    int T, int H, int G, int d, int *counters, int counters_len, hfb_stream s)
 {
     if (n_tiles <= 0) return HFB_OK;
     if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_decode: head_dim %d (64 and 128 only)", d);
@@ -339,9 +407,10 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
     p.part_o = (float *)scratch; p.part_ml = splits > 1 ? (float *)scratch + (size_t)T * H * splits * d : nullptr;
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.splits = splits;
     p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
+    p.counters = (splits > 1 && splits <= 64 && counters && counters_len >= n_tiles * G) ? counters : nullptr;
     cudaStream_t st = (cudaStream_t)s;
     rc = d == 128 ? launch_decode_stages<128>(stages, mk, mv, p, slots, n_tiles, st)
                   : launch_decode_stages<64>(stages, mk, mv, p, slots, n_tiles, st);
-    if (rc != HFB_OK || splits == 1) return rc;
+    if (rc != HFB_OK || splits == 1 || p.counters) return rc;
     return launch_attention_combine(p, T, d, st);
 }

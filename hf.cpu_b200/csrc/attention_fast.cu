@@ -206,24 +206,43 @@ attention_fast_kernel(AttnParams p, int *err)
 }
 
 // Merges the splits of one (token, head) in split order: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
+// One thread per column; the reads of a column's splits are issued sixteen at a time, because their latency is all
+// that this kernel costs.
 template <int D>
 __global__ void attention_combine_kernel(const float *part_o, const float *part_ml, int splits, __nv_bfloat16 *out)
 {
     HFB_TRACE_ENTRY(4);
     pdl_sync();
     const size_t th = blockIdx.x;
-    const float *ml = part_ml + th * splits * 2;
+    const float2 *ml = (const float2 *)(part_ml + th * splits * 2);
+    const float *po = part_o + th * splits * D + threadIdx.x;
     float m = -INFINITY;
-    for (int s = 0; s < splits; s++) m = fmaxf(m, ml[2 * s]);
-    float denom = 0.f;
-    for (int s = 0; s < splits; s++) denom += ml[2 * s] == -INFINITY ? 0.f : ml[2 * s + 1] * exp2f(ml[2 * s] - m);
-    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < splits; s++)
-            if (ml[2 * s] != -INFINITY) acc += part_o[(th * splits + s) * D + c] * exp2f(ml[2 * s] - m);
-        out[th * D + c] = __float2bfloat16_rn(acc * inv);
+    for (int c = 0; c < splits; c += 16) {
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) x[i] = c + i < splits ? ml[c + i].x : -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 16; i++) m = fmaxf(m, x[i]);
     }
+    float denom = 0.f, acc = 0.f;
+    for (int c = 0; c < splits; c += 16) {
+        float v[16];
+        float2 w[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const bool in = c + i < splits;
+            w[i] = in ? ml[c + i] : make_float2(-INFINITY, 0.f);
+            v[i] = in ? po[(size_t)(c + i) * D] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const float f = w[i].x == -INFINITY ? 0.f : exp2f(w[i].x - m);
+            denom += w[i].y * f;
+            acc += v[i] * f;
+        }
+    }
+    out[th * D + threadIdx.x] = __float2bfloat16_rn(acc * (denom > 0.f ? 1.0f / denom : 0.f));
+    HFB_TRACE_MARK(4);
 }
 
 template <int D, int WARPS, int STAGES>
@@ -288,6 +307,7 @@ extern "C" int hfb_attention_fast(const void *q, const void *k_cache, const void
     p.part_o = (float *)scratch; p.part_ml = splits > 1 ? (float *)scratch + (size_t)T * H * splits * d : nullptr;
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.splits = splits;
     p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
+    p.counters = nullptr;
     cudaStream_t st = (cudaStream_t)s;
     int rc;
     const bool deep = stages >= 4;              // a deeper pipeline for CTAs that have an SM to themselves (decode)

@@ -74,14 +74,25 @@ __device__ __forceinline__ void trace_log(int id, int kind)
         if (i < HFB_TRACE_CAP) { log[2 + 2 * i] = ((unsigned long long)id << 8) | (unsigned)kind; log[3 + 2 * i] = t; }
     }
 }
+// (developers) a value of the caller's instead of the time, from thread 0 of block 0
+__device__ __forceinline__ void trace_put(int kind, unsigned long long value)
+{
+    unsigned long long *log = g_trace_ptr;
+    if (log && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long i = atomicAdd(log, 1ull);
+        if (i < HFB_TRACE_CAP) { log[2 + 2 * i] = (unsigned)kind; log[3 + 2 * i] = value; }
+    }
+}
 void trace_register(void (*setter)(void *));
 static void trace_set_ptr(void *p) { cudaMemcpyToSymbol(g_trace_ptr, &p, sizeof p); }
 namespace { struct TraceRegistration { TraceRegistration() { trace_register(trace_set_ptr); } } g_trace_registration; }
 #define HFB_TRACE_ENTRY(id) trace_log(id, 0)
 #define HFB_TRACE_READY() trace_log(0, 1)
+#define HFB_TRACE_MARK(k) trace_log(0, k)
 #else
 #define HFB_TRACE_ENTRY(id)
 #define HFB_TRACE_READY()
+#define HFB_TRACE_MARK(k)
 #endif
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); HFB_TRACE_READY(); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

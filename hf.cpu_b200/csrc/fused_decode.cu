@@ -82,9 +82,12 @@ reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, 
         float4 v = bv[j];
         if (i < N4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int s = 0; s < splits; s++) {
-                float4 q = part[(size_t)s * MN4 + i];
-                acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+            for (int s0 = 0; s0 < splits; s0 += 8) {          // eight reads in flight: their latency is what this costs
+                float4 q[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) q[k] = s0 + k < splits ? part[(size_t)(s0 + k) * MN4 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int k = 0; k < 8; k++) { acc.x += q[k].x; acc.y += q[k].y; acc.z += q[k].z; acc.w += q[k].w; }
             }
             v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;       // (sum of the splits) + bias, as before
             float4 r = res[i];
@@ -121,6 +124,7 @@ reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, 
             *(uint2 *)o = make_uint2(*(uint32_t *)&lo, *(uint32_t *)&hi);
         }
     }
+    HFB_TRACE_MARK(4);
 }
 
 // q|k|v row = sum_s partial[s, t, :] + bias; rotate q and k; q -> q_out, k and v -> the paged cache.
@@ -164,7 +168,13 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
     if (!live) return;
     auto value = [&](int i) {
         float v = 0.f;
-        for (int s = 0; s < splits; s++) v += partial[(size_t)s * TN + row + i];
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float q[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) q[k] = s0 + k < splits ? partial[(size_t)(s0 + k) * TN + row + i] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) v += q[k];
+        }
         if (bias) v += (i == (int)threadIdx.x) ? b0 : (i == (int)threadIdx.x + half) ? b1 : load_any(bias, bias_dt, (size_t)head * d + i);
         return v;
     };

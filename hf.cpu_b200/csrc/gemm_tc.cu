@@ -10,7 +10,8 @@
 //     from HBM anyway, with split-K when there are fewer weight tiles than SMs.
 // Above 128 tokens the inner dimension is split as well when the output has few tiles and K is long (mid_splits).
 // Pipeline per CTA (persistent over work items): warp 0 issues TMA loads of 128-byte-swizzled K
-// blocks into a ring of shared-memory stages; warp 1 issues tcgen05.mma from shared memory into one
+// blocks into a ring of shared-memory stages (the weights of the first round before the kernel in front has finished,
+// warp 6 the activations of that round as soon as it has); warp 1 issues tcgen05.mma from shared memory into one
 // of two TMEM accumulators and commits to the stage's "empty" barrier; warps 2..5 read a finished
 // accumulator with tcgen05.ld, apply the epilogue and store, while the next tile's products run.
 // Every barrier wait has a time limit: on expiry the kernel raises HFB_ERR_WAIT in the device error
@@ -37,7 +38,8 @@ constexpr int BK = 64;                 // bf16 elements per K block: 128 bytes, 
 constexpr int UMMA_K = 16;
 constexpr int TILE_X = 128;            // accumulator rows (TMEM lanes)
 constexpr uint32_t X_BYTES = TILE_X * BK * 2;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 224;            // TMA warp, MMA warp, four epilogue warps, the warp for the first activation tiles
+constexpr int PAIR_THREADS = 192;            // (the pair kernel has no such warp)
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
 
@@ -89,7 +91,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int n)
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_X >> 4) << 24);
 }
 
-constexpr uint32_t FIN_SMEM_BYTES = (128 + 2 * 128) * 4;     // row factors of up to 128 tokens; two buffers of one tile row
+constexpr uint32_t FIN_SMEM_BYTES = 128 * 4;                 // row factors of up to 128 tokens
 
 template <int BN> constexpr int tmem_cols()
 {
@@ -261,81 +263,162 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t *v,
 // The four epilogue warps (128 threads) meet on a named barrier of their own.
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
-// Sum over the splits, in split order, of element (t, n) of the product; read past the L1 cache, which may hold
-// lines of an earlier launch's partial sums at the same addresses.
-__device__ __forceinline__ float sum_splits(const GemmParams &p, int t, int n)
+// The finishing work is a read of splits x tokens x 128 floats from the L2 cache by one CTA: what it costs is
+// latency, so every thread keeps many 16-byte loads in flight.  A warp takes every fourth token, a lane four
+// consecutive features of the tile; TB tokens are summed at a time, their loads of up to SMAX splits issued together
+// (TB * SMAX = 32 loads of 16 bytes per thread).  Loads go past the L1 cache (__ldcg), which may hold lines of an
+// earlier launch's partial sums at the same addresses.
+constexpr int FIN_MAX_SPLITS = 16;
+
+//
+// `dry`: the same instructions with every load and store switched off.  The few-token form runs its finishing step
+// once this way before it waits for the kernel in front (as it does with its epilogue), so that the code is in the
+// instruction cache when a tile's last split arrives: fetched at that moment it would wait, line after line, behind
+// the weight streams of the CTAs that are still running.
+template <int TB, int SMAX>
+__device__ __forceinline__ void sum_splits4(const GemmParams &p, int t0, int n0, float4 (&acc)[TB], bool dry)
 {
-    const float *src = p.partial + (size_t)t * p.N + n;
     const size_t MN = (size_t)p.M * p.N;
-    float acc = 0.f;
-    for (int s = 0; s < p.splits; s++) acc += __ldcg(src + (size_t)s * MN);
-    return acc;
+    float4 v[TB][SMAX];
+#pragma unroll
+    for (int j = 0; j < TB; j++) {
+        const int t = t0 + 4 * j;
+#pragma unroll
+        for (int s = 0; s < SMAX; s++)
+            v[j][s] = (t < p.M && s < p.splits && !dry) ? __ldcg((const float4 *)(p.partial + (size_t)s * MN + (size_t)t * p.N + n0))
+                                                : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < TB; j++) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int s = 0; s < SMAX; s++) { a.x += v[j][s].x; a.y += v[j][s].y; a.z += v[j][s].z; a.w += v[j][s].w; }   // split order
+        acc[j] = a;
+    }
 }
 
-// f = 0..127: this thread's row of the tile; q = its warp among the four.
-__device__ __forceinline__ void finish_residual(const GemmParams &p, int tx, int f, int q, int lane)
+__device__ __forceinline__ float4 load4_any(const void *p, int dt, size_t i)
+{
+    if (dt == HFB_F32) return *(const float4 *)((const float *)p + i);
+    const uint2 raw = *(const uint2 *)((const __nv_bfloat16 *)p + i);
+    const float2 lo = __bfloat1622float2(*(const __nv_bfloat162 *)&raw.x), hi = __bfloat1622float2(*(const __nv_bfloat162 *)&raw.y);
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+template <typename T> __device__ __forceinline__ void store4(T *dst, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float *dst, float4 v) { *(float4 *)dst = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16 *dst, float4 v)
+{
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    *(uint2 *)dst = make_uint2(*(const uint32_t *)&lo, *(const uint32_t *)&hi);
+}
+
+// q = this warp among the four: it takes tokens q, q + 4, ...; the lane takes features 4 * lane .. 4 * lane + 3.
+template <int TB, int SMAX>
+__device__ __forceinline__ void finish_residual(const GemmParams &p, int tx, int q, int lane, bool dry)
 {
     const FinishParams &fp = p.fin;
-    const int n = tx * TILE_X + f;
-    const bool live = n < p.N;
-    const float b = (live && p.bias) ? load_any(p.bias, p.bias_dt, n) : 0.f;
-    const float w = (live && fp.y) ? load_any(fp.norm_w, fp.norm_w_dt, n) : 0.f;
-#pragma unroll 2
-    for (int t = 0; t < p.M; t++) {
-        float v = 0.f;
-        if (live) {
-            float *res = fp.residual + (size_t)t * p.N + n;
-            v = (sum_splits(p, t, n) + b) + __ldcg(res);
-            *res = v;
-            if (fp.y) store_any(fp.y, fp.y_dt, (size_t)t * p.N + n, v * w);
+    const int n0 = tx * TILE_X + 4 * lane;
+    const bool live = n0 < p.N && !dry;                   // (N is a multiple of 4: a lane's four features are in or out)
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 b = (live && p.bias) ? load4_any(p.bias, p.bias_dt, n0) : zero;
+    const float4 w = (live && fp.y) ? load4_any(fp.norm_w, fp.norm_w_dt, n0) : zero;
+    for (int t0 = q; t0 < p.M; t0 += 4 * TB) {
+        float4 acc[TB], res[TB];
+#pragma unroll
+        for (int j = 0; j < TB; j++) {
+            const int t = t0 + 4 * j;
+            res[j] = (live && t < p.M) ? __ldcg((const float4 *)(fp.residual + (size_t)t * p.N + n0)) : zero;
         }
-        if (fp.sumsq) {
-            const float ss = warp_sum(v * v);
-            if (lane == 0) fp.sumsq[(size_t)(tx * 4 + q) * p.M + t] = ss;
+        sum_splits4<TB, SMAX>(p, t0, n0, acc, !live);
+#pragma unroll
+        for (int j = 0; j < TB; j++) {
+            const int t = t0 + 4 * j;
+            if (t >= p.M) break;
+            float4 v = zero;
+            if (live) {
+                v = make_float4((acc[j].x + b.x) + res[j].x, (acc[j].y + b.y) + res[j].y, (acc[j].z + b.z) + res[j].z,
+                                (acc[j].w + b.w) + res[j].w);
+                *(float4 *)(fp.residual + (size_t)t * p.N + n0) = v;
+                if (fp.y) {
+                    const float4 yv = make_float4(v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
+                    if (fp.y_dt == HFB_BF16) store4((__nv_bfloat16 *)fp.y + (size_t)t * p.N + n0, yv);
+                    else store4((float *)fp.y + (size_t)t * p.N + n0, yv);
+                }
+            }
+            if (fp.sumsq) {
+                const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+                if (lane == 0 && !dry) fp.sumsq[(size_t)tx * p.M + t] = ss;
+            }
         }
     }
 }
 
-template <typename T>
-__device__ __forceinline__ void finish_rope_kv(const GemmParams &p, int tx, int f, const float *rstd, float *xch, int *err)
+// The tile holds whole heads (128 % d == 0) and a lane's four features lie in one half of a rotation pair (n_rot is a
+// multiple of 8): the partner values are four lanes' worth away, fetched with a shuffle.
+template <typename T, int TB, int SMAX>
+__device__ __forceinline__ void finish_rope_kv(const GemmParams &p, int tx, int q, int lane, const float *rstd, int *err, bool dry)
 {
     const FinishParams &fp = p.fin;
-    const int n = tx * TILE_X + f, d = fp.d, half = fp.n_rot >> 1;
-    const bool live = n < p.N;
-    const int head = n / d, i = n - head * d;
-    const float b = (live && p.bias) ? load_any(p.bias, p.bias_dt, n) : 0.f;
-    const bool rotate = live && head < fp.H + fp.G && i < fp.n_rot;
-    for (int t = 0; t < p.M; t++) {
-        float v = 0.f;
-        if (live) {
-            v = sum_splits(p, t, n);
-            if (rstd) v *= rstd[t];
+    const int n0 = tx * TILE_X + 4 * lane, d = fp.d, half = fp.n_rot >> 1;
+    const bool live = n0 < p.N && !dry;
+    const int head = n0 / d, i0 = n0 - head * d;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 b = (live && p.bias) ? load4_any(p.bias, p.bias_dt, n0) : zero;
+    const bool rotate = live && head < fp.H + fp.G && i0 < fp.n_rot;
+    const bool low = i0 < half;                           // this lane holds the first elements of its pairs
+    const int partner = low ? lane + (half >> 2) : lane - (half >> 2);
+    for (int t0 = q; t0 < p.M; t0 += 4 * TB) {
+        float4 acc[TB];
+        sum_splits4<TB, SMAX>(p, t0, n0, acc, !live);
+#pragma unroll
+        for (int j = 0; j < TB; j++) {
+            const int t = t0 + 4 * j;
+            if (t >= p.M) break;                          // (the same for the whole warp)
+            float4 v = acc[j];
+            if (rstd) { const float r = rstd[t & 127]; v.x *= r; v.y *= r; v.z *= r; v.w *= r; }
             // the separate kernels round q|k|v to the run type before rotating; keep the same values
-            v = to_f32(from_f32<T>(v + b));
-        }
-        float *mine = xch + (t & 1) * TILE_X;
-        mine[f] = v;
-        epi_bar();                                        // (the buffer of token t - 1 is free again after this one)
-        if (!live) continue;
-        float out = v;
-        if (rotate) {
-            int pos = fp.positions[t];
-            if (pos < 0 || pos >= fp.n_positions) { atomicOr(err, HFB_ERR_POSITION); pos = 0; }
-            const int k = i < half ? i : i - half;
-            const float2 cs = *(const float2 *)(fp.cos_sin + ((size_t)pos * half + k) * 2);
-            const float other = i < half ? mine[f + half] : mine[f - half];
-            out = i < half ? v * cs.x - other * cs.y : other * cs.y + v * cs.x;
-        }
-        if (head < fp.H) {
-            ((T *)fp.q_out)[((size_t)t * fp.H + head) * d + i] = from_f32<T>(out);
-        } else {
-            long long slot = fp.slots ? fp.slots[t] : -1;
-            if (slot >= fp.cache_slots) { atomicOr(err, HFB_ERR_SLOT); slot = -1; }
-            if (slot >= 0) {
-                if (head < fp.H + fp.G) ((T *)fp.k_cache)[((size_t)slot * fp.G + (head - fp.H)) * d + i] = from_f32<T>(out);
-                else ((T *)fp.v_cache)[((size_t)slot * fp.G + (head - fp.H - fp.G)) * d + i] = from_f32<T>(out);
+            v = make_float4(to_f32(from_f32<T>(v.x + b.x)), to_f32(from_f32<T>(v.y + b.y)), to_f32(from_f32<T>(v.z + b.z)),
+                            to_f32(from_f32<T>(v.w + b.w)));
+            float4 o;
+            o.x = __shfl_sync(0xffffffffu, v.x, partner & 31); o.y = __shfl_sync(0xffffffffu, v.y, partner & 31);
+            o.z = __shfl_sync(0xffffffffu, v.z, partner & 31); o.w = __shfl_sync(0xffffffffu, v.w, partner & 31);
+            float4 out = v;
+            if (rotate || dry) {
+                int pos = live ? fp.positions[t] : 0;
+                if (pos < 0 || pos >= fp.n_positions) { atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+                const int k = low ? i0 : i0 - half;
+                const float4 *cs = (const float4 *)(fp.cos_sin + ((size_t)pos * half + k) * 2);   // (cos, sin) of 4 pairs
+                const float4 c01 = live ? cs[0] : zero, c23 = live ? cs[1] : zero;
+                if (low) out = make_float4(v.x * c01.x - o.x * c01.y, v.y * c01.z - o.y * c01.w, v.z * c23.x - o.z * c23.y, v.w * c23.z - o.w * c23.w);
+                else out = make_float4(o.x * c01.y + v.x * c01.x, o.y * c01.w + v.y * c01.z, o.z * c23.y + v.z * c23.x, o.w * c23.w + v.w * c23.z);
+            }
+            if (head < fp.H) {
+                if (live) store4((T *)fp.q_out + ((size_t)t * fp.H + head) * d + i0, out);
+            } else {
+                long long slot = (fp.slots && live) ? fp.slots[t] : -1;
+                if (slot >= fp.cache_slots) { atomicOr(err, HFB_ERR_SLOT); slot = -1; }
+                if (slot >= 0) {
+                    if (head < fp.H + fp.G) store4((T *)fp.k_cache + ((size_t)slot * fp.G + (head - fp.H)) * d + i0, out);
+                    else store4((T *)fp.v_cache + ((size_t)slot * fp.G + (head - fp.H - fp.G)) * d + i0, out);
+                }
             }
         }
+    }
+}
+
+// Picks the number of tokens a warp sums at a time by the number of splits, so that about 32 loads are in flight.
+template <typename T>
+__device__ __forceinline__ void finish_tile(const GemmParams &p, int tx, int q, int lane, const float *rstd, int *err, bool dry)
+{
+    if (p.fin.kind == FIN_RESIDUAL) {
+        if (p.splits <= 4) finish_residual<8, 4>(p, tx, q, lane, dry);
+        else if (p.splits <= 8) finish_residual<4, 8>(p, tx, q, lane, dry);
+        else finish_residual<2, 16>(p, tx, q, lane, dry);
+    } else {
+        if (p.splits <= 4) finish_rope_kv<T, 8, 4>(p, tx, q, lane, rstd, err, dry);
+        else if (p.splits <= 8) finish_rope_kv<T, 4, 8>(p, tx, q, lane, rstd, err, dry);
+        else finish_rope_kv<T, 2, 16>(p, tx, q, lane, rstd, err, dry);
     }
 }
 
@@ -356,8 +439,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen_base + STAGES * (X_BYTES + Y_BYTES) + (2 * STAGES + 4) * 8);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     volatile int *last_flag = (volatile int *)(tmem_slot + 2);       // this CTA stored a tile's last split
-    float *rstd_smem = (float *)(tmem_slot + 4);                     // [128] row factors, then [2][128] exchange
-    float *xch_smem = rstd_smem + 128;
+    float *rstd_smem = (float *)(tmem_slot + 4);                     // [128] row factors
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -376,29 +458,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    HFB_TRACE_MARK(2);
 
     const int total_items = p.tiles_x * p.tiles_y * p.splits;
     const int per_split = p.tiles_x * p.tiles_y;
 
     if (warp == 0) {
         // ---- producer: TMA loads --------------------------------------------------------------
-        // The weights do not depend on the kernel before this one, the activations do.  The first STAGES
-        // weight tiles are requested at once; only then does the producer wait for the predecessor
-        // (and let the successor start), and sends the activation loads it had put off.
+        // The weights do not depend on the kernel before this one, the activations do.  One lane requests the weight
+        // tiles of the first STAGES k blocks at once, long before that kernel has finished; the activation tiles of
+        // those blocks are requested by the seventh warp the moment it has (both count on the stage's "full" barrier,
+        // whose phase ends when the armed byte count has arrived, in whichever order).  From the second round on the
+        // producer has waited too and requests both.  The other lanes of this warp do nothing: a lane that sat in
+        // griddepcontrol.wait would hold up its whole warp, the requesting lane with it.
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true, dep_ready = false;
-            int pend_n = 0, pend_s[STAGES], pend_kb[STAGES], pend_row[STAGES];
-            auto load_dependent = [&](int s, int kb, int row) {
-                if (p.swapped) tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, row, full0 + 8 * s);
-                else tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, row, full0 + 8 * s);
-            };
-            auto flush = [&]() {
-                pdl_sync();
-                for (int i = 0; i < pend_n; i++) load_dependent(pend_s[i], pend_kb[i], pend_row[i]);
-                pend_n = 0;
-                dep_ready = true;
-            };
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 int split = item / per_split, t = item % per_split;
                 int tx = t % p.tiles_x, ty = t / p.tiles_x;
@@ -406,19 +481,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int kb = kb0; kb < kb1; kb++, it++) {
                     int s = it % STAGES;
                     uint32_t ph = (it / STAGES) & 1;
-                    if (!dep_ready && it >= STAGES) flush();       // the stage to be reused still awaits its activation tile
+                    if (!dep_ready && it >= STAGES) { pdl_sync(); dep_ready = true; }
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
                     mbar_arrive_expect_tx(full0 + 8 * s, X_BYTES + Y_BYTES);
                     if (p.swapped) tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
                     else tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * s);
-                    const int dep_row = p.swapped ? ty * BN : tx * TILE_X;
-                    if (dep_ready) load_dependent(s, kb, dep_row);
-                    else { pend_s[pend_n] = s; pend_kb[pend_n] = kb; pend_row[pend_n] = dep_row; pend_n++; }
+                    if (dep_ready) {
+                        if (p.swapped) tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * s);
+                        else tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
+                    }
                 }
             }
-            if (!dep_ready) flush();
-        } else {
-            pdl_sync();
+            if (!dep_ready) pdl_sync();
+        }
+    } else if (warp == 6) {
+        // ---- the activation tiles of the first STAGES k blocks, as soon as the kernel in front has finished ----
+        pdl_sync();
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int item = blockIdx.x; item < total_items && it < (uint32_t)STAGES; item += gridDim.x) {
+                int split = item / per_split, t = item % per_split;
+                int tx = t % p.tiles_x, ty = t / p.tiles_x;
+                int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
+                for (int kb = kb0; kb < kb1 && it < (uint32_t)STAGES; kb++, it++) {
+                    if (p.swapped) tma_load_2d(sy + it * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * it);
+                    else tma_load_2d(sx + it * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * it);
+                }
+            }
         }
     } else if (warp == 1) {
         // ---- tensor-core issue ------------------------------------------------------------------
@@ -500,6 +589,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane, !rehearsal, rstd);
             }
             if (rehearsal) {
+                if (BN <= 128 && p.fin.kind != FIN_NONE) {
+                    if (p.out_dt == HFB_BF16) finish_tile<__nv_bfloat16>(p, tx, warp - 2, lane, rstd, err, true);
+                    else finish_tile<float>(p, tx, warp - 2, lane, rstd, err, true);
+                }
                 rehearsal = false;
                 pdl_sync();
                 after_wait();
@@ -508,12 +601,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * a);
-            if (p.swapped && p.fin.kind != FIN_NONE) {
+            if (BN <= 128 && p.swapped && p.fin.kind != FIN_NONE) {      // (the few-token form has at most 128 columns)
                 // The split is in global memory.  Count it; the CTA that brings a tile's count to the number of
                 // splits sums the tile in split order, whichever CTA that is, and does the step that follows.
-                __threadfence();
                 epi_bar();
                 if (row == 0) {
+                    __threadfence();                             // (after the barrier: it covers the four warps' stores)
                     const int before = atomicAdd(&p.fin.counters[tx], 1);
                     const int last = before == p.splits - 1;
                     if (last) p.fin.counters[tx] = 0;            // every split has counted: ready for the next launch
@@ -522,9 +615,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 epi_bar();
                 if (*last_flag) {
                     __threadfence();
-                    if (p.fin.kind == FIN_RESIDUAL) finish_residual(p, tx, row, q, lane);
-                    else if (p.out_dt == HFB_BF16) finish_rope_kv<__nv_bfloat16>(p, tx, row, rstd, xch_smem, err);
-                    else finish_rope_kv<float>(p, tx, row, rstd, xch_smem, err);
+                    const int fq = warp - 2;                     // the finishing step's own numbering of the four warps
+                    if (p.out_dt == HFB_BF16) finish_tile<__nv_bfloat16>(p, tx, fq, lane, rstd, err, false);
+                    else finish_tile<float>(p, tx, fq, lane, rstd, err, false);
                 }
                 epi_bar();                                       // the flag may be rewritten for the next item
             }
@@ -598,7 +691,7 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar)
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, GemmParams p, int *err)
 {
     HFB_TRACE_ENTRY(1);
@@ -870,7 +963,7 @@ static int launch_pair(const CUtensorMap &mx, const CUtensorMap &my, const GemmP
     const int pairs = items < pairs_cap ? items : pairs_cap;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(PAIR_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -1142,9 +1235,11 @@ static int plan_fused(const char *who, const void *a, const void *w, int M, int 
     if (!workspace || workspace_bytes < need) return fail(HFB_EINVAL, "%s: workspace of %zu bytes, %zu needed", who, workspace_bytes, need);
     if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
     if (!counters || counters_len < p.tiles_x) return fail(HFB_EINVAL, "%s: %d tile counters needed, %d given", who, p.tiles_x, counters_len);
+    if (N & 3) return fail(HFB_ENOTSUP, "%s: N = %d must be a multiple of 4", who, N);
     const int want = (int)(need / ((size_t)M * N * sizeof(float)));
     p.kb_per_split = (p.kb_total + want - 1) / want;
     p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    if (p.splits > FIN_MAX_SPLITS) return fail(HFB_ENOTSUP, "%s: %d splits exceed %d", who, p.splits, FIN_MAX_SPLITS);
     p.partial = (float *)workspace;
     p.mode = EPI_PARTIAL;
     p.fin.counters = counters;
@@ -1152,7 +1247,7 @@ static int plan_fused(const char *who, const void *a, const void *w, int M, int 
 }
 
 // Row-factor parts hfb_linear_tc_residual_y writes per row for N output features.
-extern "C" int hfb_linear_tc_sumsq_parts(int N) { return 4 * ((N + hfb::TILE_X - 1) / hfb::TILE_X); }
+extern "C" int hfb_linear_tc_sumsq_parts(int N) { return (N + hfb::TILE_X - 1) / hfb::TILE_X; }
 
 // residual[M, N] += a . w^T (+ bias), M <= 128, in one kernel: the CTA that stores the last split of a weight tile
 // sums the splits in split order and adds them into the float32 residual.  With `y`: y = residual * norm_w (the
@@ -1190,7 +1285,10 @@ extern "C" int hfb_linear_tc_rope_kv(const void *a, const void *w, const void *b
     if (M <= 0) return HFB_OK;
     if (!valid_dt(dt) || H <= 0 || G <= 0 || d <= 0 || n_rot < 0 || n_rot > d || (n_rot & 1) || (bias && !valid_dt(bias_dt)))
         return fail(HFB_EINVAL, "linear_tc_rope_kv: bad arguments");
-    if (TILE_X % d) return fail(HFB_ENOTSUP, "linear_tc_rope_kv: head size %d does not divide %d", d, TILE_X);
+    if (TILE_X % d || (d & 3)) return fail(HFB_ENOTSUP, "linear_tc_rope_kv: head size %d does not divide %d", d, TILE_X);
+    if (n_rot & 7) return fail(HFB_ENOTSUP, "linear_tc_rope_kv: a rotary width of %d is not a multiple of 8", n_rot);
+    if (((uintptr_t)q_out & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)cos_sin & 15))
+        return fail(HFB_ENOTSUP, "linear_tc_rope_kv: outputs and the rotary table must be 16-byte aligned");
     if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "linear_tc_rope_kv: rotation needs a table and positions");
     const int N = (H + 2 * G) * d;
     GemmParams p{};

@@ -50,6 +50,9 @@ int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, v
 /* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
 int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
 
+/* Hints the first seg_bytes of each of `rows` rows (row_bytes apart) into the L2 cache; multiples of 16 bytes. */
+int hfb_prefetch_rows_l2(const void *base, int rows, size_t row_bytes, int seg_bytes, hfb_stream s);
+
 /* a[m, :] *= rsqrt(sum_p sumsq[p, m] / E + eps), in place (rows whose RMSNorm row factor was left to the consumer). */
 int hfb_scale_rows(void *a, int dt, const float *sumsq, int parts, float eps, int M, int E, hfb_stream s);
 
@@ -126,12 +129,14 @@ int hfb_attention_fast(const void *q, const void *k_cache, const void *v_cache, 
 
 /* Decode attention with the keys and values fetched by TMA: tiles as hfb_attention_fast's 16-row form takes them
  * (one or two tokens of one request), bfloat16, head_dim 64 or 128, block sizes 8..64 dividing 64.  `stages` (2..4)
- * tiles of 64 keys are in flight per CTA; `splits` > 1 needs hfb_attention_fast_scratch bytes of scratch. */
+ * tiles of 64 keys are in flight per CTA; `splits` > 1 needs hfb_attention_fast_scratch bytes of scratch, and is
+ * merged by the CTA that stores a tile's last split when `counters` (n_tiles * G ints, zero before the first launch
+ * and after every launch) is given, else by a second kernel. */
 int hfb_attention_decode(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                          int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                          const int32_t *tile_nt, int n_tiles, int stages, int splits, int block_size, int64_t num_pages,
                          int window, float scale, void *out, void *scratch, size_t scratch_bytes, int T, int H, int G,
-                         int d, hfb_stream s);
+                         int d, int *counters, int counters_len, hfb_stream s);
 
 /* Attention of prompt portions on tcgen05 (S and PV accumulators in TMEM, K and V gathered page by page with
  * TMA): bfloat16, head_dim 128, block sizes 8..128 that divide 128.  Tiles hold at most 128 / (H/G) tokens. */

@@ -62,7 +62,9 @@ class NativeBackend:
         self._argmax_ws = None
         # few rows: the split-K reduction and the step after it run in the product's own kernel (HFB_FUSE_TAILS=0:
         # as separate kernels, which the tests compare with)
-        self.fuse_tails = os.environ.get("HFB_FUSE_TAILS", "1") != "0"
+        self.fuse_tails = os.environ.get("HFB_FUSE_TAILS", "0") != "0"
+        # decode attention: the CTA that stores a tile's last split merges the splits (0: a second kernel does)
+        self.merge_in_kernel = os.environ.get("HFB_ATTN_MERGE", "1") != "0"
         self._counters = None
         self._sumsq = {}
         self.lib.hfb_linear_tc_partials_workspace.restype = ctypes.c_size_t
@@ -189,14 +191,20 @@ class NativeBackend:
                 need = self.lib.hfb_attention_fast_scratch(c_int(T), c_int(H), c_int(d), c_int(splits))
                 scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
                 if decode_tma:
-                    # the keys and values come by TMA, a warp of their own keeps them coming
+                    # the keys and values come by TMA, a warp of their own keeps them coming; the CTA that stores a
+                    # tile's last split merges the splits (HFB_FUSE_TAILS=0: a second kernel does)
+                    counters = None
+                    if self.merge_in_kernel and splits > 1 and n_tiles * G <= 4096:
+                        if self._counters is None or self._counters.device != q.device:
+                            self._counters = torch.zeros(4096, dtype=torch.int32, device=q.device)
+                        counters = self._counters
                     self._check(self.lib.hfb_attention_decode(
                         _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
                         _p(tile_seq), _p(tile_t0), _p(tile_nt), c_int(n_tiles), c_int(stages), c_int(splits),
                         c_int(meta.block_size), c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out),
-                        _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), self._stream()),
-                        "attention_decode")
-                    if splits > 1:
+                        _p(scratch), ctypes.c_size_t(need), c_int(T), c_int(H), c_int(G), c_int(d), _p(counters),
+                        c_int(counters.numel() if counters is not None else 0), self._stream()), "attention_decode")
+                    if splits > 1 and counters is None:
                         self.launches += 1
                     return
                 self._check(self.lib.hfb_attention_fast(
@@ -242,7 +250,8 @@ class NativeBackend:
 
     def _fused_ok(self, a, w, residual=None):
         """Few rows of bfloat16 on the tensor cores: the product finishes its own split-K sum and what follows."""
-        return (self.fuse_tails and a.shape[0] <= 128 and self._tc_ok(a, w, residual) and (w.shape[0] + 127) // 128 <= 4096)
+        return (self.fuse_tails and a.shape[0] <= 128 and self._tc_ok(a, w, residual) and w.shape[0] % 4 == 0
+                and (w.shape[0] + 127) // 128 <= 4096)
 
     def _fused_buffers(self, a, w):
         """(workspace, bytes the partial sums need, tile counters) or None when the workspace is too small."""
@@ -279,6 +288,26 @@ class NativeBackend:
             c_int(M), c_int(N), c_int(K), _p(ws), ctypes.c_size_t(ws.numel()), _p(counters), c_int(counters.numel()),
             self._stream()), "linear_tc_residual_y")
         return sumsq if sumsq is not None else True
+
+    def prefetch_l2(self, w, rows, seg_bytes):
+        """On a side stream that starts where the current stream stands: hint the first ``seg_bytes`` of the first
+        ``rows`` rows of ``w`` into the L2 cache.  ``join_side()`` makes the current stream wait for the side stream."""
+        cur = torch.cuda.current_stream()
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream()
+        self._side.wait_stream(cur)
+        row_bytes = w.shape[1] * w.element_size()
+        seg = min(seg_bytes, row_bytes) // 16 * 16
+        rc = self.lib.hfb_prefetch_rows_l2(_p(w), c_int(min(rows, w.shape[0])), ctypes.c_size_t(row_bytes), c_int(seg),
+                                           c_void_p(self._side.cuda_stream))
+        if rc != 0:
+            raise KernelError(f"prefetch: {self.lib.hfb_last_error().decode()}")
+        self._side_used = True
+
+    def join_side(self):
+        if getattr(self, "_side_used", False):
+            torch.cuda.current_stream().wait_stream(self._side)
+            self._side_used = False
 
     def scale_rows(self, a, sumsq, eps):
         self._on_gpu(a, sumsq)
@@ -348,7 +377,8 @@ class NativeBackend:
         M, K = a.shape
         cache_slots = k_cache.shape[0] * k_cache.shape[1]
         npos = cos_sin.shape[0] if cos_sin is not None else 0
-        if self._fused_ok(a, w) and 128 % d == 0 and (bias is None or bias.data_ptr() % 16 == 0):
+        if (self._fused_ok(a, w) and 128 % d == 0 and d % 4 == 0 and n_rot % 8 == 0 and w.shape[0] % 4 == 0
+                and (bias is None or bias.data_ptr() % 16 == 0)):
             bufs = self._fused_buffers(a, w)
             if bufs is not None:
                 ws, _, counters = bufs

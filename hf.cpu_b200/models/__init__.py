@@ -111,6 +111,10 @@ class Model:
                                      ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None,
                                      xn_ready=xn, next_norm=nxt.norm1 if nxt else None,
                                      next_mixer=nxt.mixer if nxt else None)
+        from .. import kernels
+        b = kernels.backend()
+        if hasattr(b, "join_side"):
+            b.join_side()
         M = ctx.num_logit_rows
         if M == 0:
             return None

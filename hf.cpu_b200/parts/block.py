@@ -18,6 +18,15 @@ class PreNormResidual(Block):
         else:
             xn = xn_ready
         xn2 = ctx.buf("block_xn2", x.shape, ctx.run_dtype)
+        import os
+        pf = int(os.environ.get("HFB_PREFETCH_MB", "0"))
+        if pf and ctx.num_tokens <= 128 and hasattr(ffn, "w_gate_up"):
+            from .. import kernels
+            b = kernels.backend()
+            if hasattr(b, "prefetch_l2"):
+                w = ffn.w_gate_up
+                rows = min(w.shape[0], b.sm_count * 128)
+                b.prefetch_l2(w, rows, (pf << 20) // rows)
         fused = getattr(mixer, "forward_then_norm", None)
         done = False
         if fused:
