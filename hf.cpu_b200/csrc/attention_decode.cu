@@ -2,9 +2,12 @@
 //
 // With one new token per request the work is a pure read of the request's keys and values, and what costs
 // is every instruction spent on moving them.  A fifth warp owns the copies: for each tile of 64 keys it looks
-// up the tile's pages and asks the TMA unit for them (one box of [block_size keys, 64 elements] per page and
-// 128-byte half of the head, 128-byte swizzle; a page the table does not map is read from beyond the cache and
-// arrives as zeros), several tiles ahead of the four warps that compute.  Those share each tile as the cp.async
+// up the tile's pages and asks the TMA unit for them, one request per page that brings the page's keys and values of
+// one head at once (a box [keys|values][128-byte piece of the head][block_size keys][64 elements] through a map of
+// rank 4, 128-byte swizzle; two requests where keys and values are not one array; a page the table does not map is
+// read from beyond the cache and arrives as zeros): a request costs the issuing thread a few hundred cycles whatever
+// its size, and at one per page and piece of keys or values that was what bounded this kernel.  The copies run
+// several tiles ahead of the four warps that compute.  Those share each tile as the cp.async
 // form does (attention_fast.cu): 16 keys per warp, the query heads of one key/value head on the 16 rows of
 // mma.sync m16n8k16, a running maximum and sum per warp, merged in warp order at the end.  Full and empty
 // mbarriers pair the two sides, so the loop has no CTA-wide barrier.  Tiles that lie wholly inside every row's
@@ -21,29 +24,32 @@ static thread_local cudaError_t g_launch_err = cudaSuccess;      // what the las
 
 namespace hfb {
 int *error_word();
-int tensor_map(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *out);
+int tensor_map_kv(const void *k, const void *v, int slots, int row_elems, int box_keys, int halves, CUtensorMap *maps, bool *single);
 
 constexpr int ADT_THREADS = 160;        // four computing warps and the copying warp
-constexpr uint32_t ADT_SUB = ABN * 128; // one 128-byte half of a tile of 64 keys
 
-// Byte offset of 16-byte chunk `c` of key row `row` in a tile the TMA unit wrote with the 128-byte swizzle.
-__device__ __forceinline__ uint32_t tma_off(int row, int c)
+// A stage holds a tile of 64 keys page by page: [page][keys | values][128-byte piece of the head][key of the page][64
+// elements], as the page copies arrive.  Byte offset, from the page's keys (or values), of 16-byte chunk `c` of the
+// page's key `kr`, written by the TMA unit with the 128-byte swizzle (every piece of a page starts on a multiple of
+// 1024 bytes: pages hold 8 keys or more).
+__device__ __forceinline__ uint32_t page_off(int kr, int c, int bs)
 {
-    return (uint32_t)(c >> 3) * ADT_SUB + (uint32_t)row * 128u + (uint32_t)(((c & 7) ^ (row & 7)) << 4);
+    return (uint32_t)(c >> 3) * (uint32_t)bs * 128u + (uint32_t)kr * 128u + (uint32_t)(((c & 7) ^ (kr & 7)) << 4);
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool ONE_MAP>
 __global__ void __launch_bounds__(ADT_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p,
                             int num_slots, int *err)
 {
     HFB_TRACE_ENTRY(3);
     constexpr int CH = D / 8, HALVES = D / 64;
-    constexpr uint32_t TILE = HALVES * ADT_SUB;          // bytes of the keys (or the values) of one tile
+    constexpr uint32_t TILE = HALVES * ABN * 128;        // bytes of the keys (or the values) of one tile
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t sk = base, sv = base + STAGES * TILE, sq = sv + STAGES * TILE;
+    const uint32_t st0 = base, sq = base + 2 * STAGES * TILE;   // stage s: keys and values of a tile, page by page
+    const uint32_t page_bytes = (uint32_t)p.block_size * HALVES * 128u;   // a page's keys (or values) of one head
     const uint32_t full0 = sq + 16 * D * 2, empty0 = full0 + 8 * STAGES;
     volatile int *abort_flag = (volatile int *)(gen + 2 * STAGES * TILE + 16 * D * 2 + 16 * STAGES);
 
@@ -106,11 +112,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 for (int pg = 0; pg < pages; pg++) {
                     const int row = __shfl_sync(0xffffffffu, my_row, t * pages + pg);
                     if (lane == 0) {
-                        const uint32_t off = (uint32_t)s * TILE + (uint32_t)pg * bs * 128u;
-#pragma unroll
-                        for (int half = 0; half < HALVES; half++) {
-                            tma_load_2d(sk + off + half * ADT_SUB, &map_k, g * D + half * 64, row, full0 + 8 * s);
-                            tma_load_2d(sv + off + half * ADT_SUB, &map_v, g * D + half * 64, row, full0 + 8 * s);
+                        const uint32_t dst = st0 + (uint32_t)s * 2 * TILE + (uint32_t)pg * 2 * page_bytes;
+                        if (ONE_MAP) {
+                            tma_load_4d(dst, &map_k, 0, row, g * HALVES, 0, full0 + 8 * s);
+                        } else {
+                            tma_load_3d(dst, &map_k, 0, row, g * HALVES, full0 + 8 * s);
+                            tma_load_3d(dst + page_bytes, &map_v, 0, row, g * HALVES, full0 + 8 * s);
                         }
                     }
                 }
@@ -130,6 +137,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         cp_async_commit();
         cp_async_wait<0>();
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        HFB_TRACE_MARK(5);
         uint32_t qf[D / 16][4];
 #pragma unroll
         for (int kk = 0; kk < D / 16; kk++)
@@ -140,17 +148,22 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int pos0 = v0 ? p.positions[t0 + tl0] : -1, pos1 = v1 ? p.positions[t0 + tl1] : -1;
         const int lo0 = p.window > 0 ? max(0, pos0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, pos1 - p.window + 1) : 0;
         const int kbase = warp * 16, mi = lane >> 3;
+        // the 8 keys whose rows this lane names to ldmatrix lie in one page (pages hold 8 keys or more)
+        const int bs = p.block_size;
+        const int krow = kbase + (mi >> 1) * 8 + (lane & 7), vrow = kbase + (mi & 1) * 8 + (lane & 7);
+        const uint32_t k_page = (uint32_t)(krow / bs) * 2 * page_bytes, v_page = (uint32_t)(vrow / bs) * 2 * page_bytes + page_bytes;
+        const int k_kr = krow % bs, v_kr = vrow % bs;
 
         for (int kt = kt_lo; kt < kt_hi; kt++) {
             const int j = kt - kt_lo, s = j % STAGES;
             if (!mbar_wait(full0 + 8 * s, (j / STAGES) & 1, abort_flag, err)) break;
-            const uint32_t ks = sk + s * TILE, vs = sv + s * TILE;
+            const uint32_t ks = st0 + s * 2 * TILE + k_page, vs = st0 + s * 2 * TILE + v_page;
             float sc[2][4];
             sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < D / 16; kk++) {
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4(ks + tma_off(kbase + (mi >> 1) * 8 + (lane & 7), kk * 2 + (mi & 1)), b0, b1, b2, b3);
+                ldsm_x4(ks + page_off(k_kr, kk * 2 + (mi & 1), bs), b0, b1, b2, b3);
                 mma_bf16(sc[0], qf[kk], b0, b1);
                 mma_bf16(sc[1], qf[kk], b2, b3);
             }
@@ -192,7 +205,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
             for (int dn = 0; dn < D / 16; dn++) {
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4_t(vs + tma_off(kbase + (mi & 1) * 8 + (lane & 7), dn * 2 + (mi >> 1)), b0, b1, b2, b3);
+                ldsm_x4_t(vs + page_off(v_kr, dn * 2 + (mi >> 1), bs), b0, b1, b2, b3);
                 mma_bf16(o[2 * dn], pf, b0, b1);
                 mma_bf16(o[2 * dn + 1], pf, b2, b3);
             }
@@ -205,6 +218,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 
     // ---- merge the four warps (they saw disjoint keys) in warp order -------------------------------------
     __syncthreads();                                      // every tile has been used: its buffers are free
+    HFB_TRACE_MARK(6);
     const bool dead = *abort_flag != 0;
     if (dead) {
         // a wait ran out: give copies that are still in flight time to land before the shared memory goes away
@@ -268,6 +282,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // attention_combine_kernel: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s.
         volatile int *last_flag = abort_flag + 1;
         __syncthreads();
+        HFB_TRACE_MARK(7);
         if (threadIdx.x == 0) {
             __threadfence();                              // (after the barrier: it covers every thread's stores)
             int *cnt = p.counters + (size_t)tile * p.G + g;
@@ -277,11 +292,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         }
         __syncthreads();
         if (!*last_flag) return;
+        if (tile == 0 && g == 0) HFB_TRACE_ANY(8);
         __threadfence();
         // What this costs is the latency of reads from the L2 cache, so they are issued many at a time.  First, per
         // row, the weight of every split: f_s = 2^(m_s - m) / sum_s' l_s' 2^(m_s' - m).
         constexpr int MAXS = 64;                          // (the host asks for no more splits than this)
         float *fs = (float *)gen;                         // [16][MAXS]; the tile buffers are free
+        const int n_elems = rows * (D / 4);               // float4 pieces of the merged rows
         if (threadIdx.x < rows) {
             const int row = threadIdx.x;
             const size_t th = (size_t)(t0 + row / r) * p.H + g * r + row % r;
@@ -308,7 +325,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             fs[(16 + row) * MAXS] = inv;
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < rows * (D / 4); e += ADT_THREADS) {
+        for (int e = threadIdx.x; e < n_elems; e += ADT_THREADS) {
             const int row = e / (D / 4), c4 = e % (D / 4);
             const size_t th = (size_t)(t0 + row / r) * p.H + g * r + row % r;
             const float4 *src = (const float4 *)(p.part_o + th * p.splits * D) + c4;
@@ -328,18 +345,19 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
             *(uint2 *)(p.out + th * D + 4 * c4) = make_uint2(*(const uint32_t *)&lo, *(const uint32_t *)&hi);
         }
+        if (tile == 0 && g == 0) HFB_TRACE_ANY(9);
     }
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool ONE_MAP>
 static int launch_decode_tma(const CUtensorMap &mk, const CUtensorMap &mv, const AttnParams &p, int num_slots, int n_tiles, cudaStream_t st)
 {
-    constexpr uint32_t TILE = (D / 64) * ADT_SUB;
+    constexpr uint32_t TILE = (D / 64) * ABN * 128;
     constexpr int smem = 1024 + 2 * STAGES * TILE + 16 * D * 2 + 16 * STAGES + 16;
     static_assert(2 * STAGES * TILE >= (4 * 16 * (D + 2) + 96) * 4 && 2 * STAGES * TILE >= 32 * 64 * 4, "the merge reuses the tile buffers");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, STAGES, ONE_MAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_decode: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -357,16 +375,16 @@ static int launch_decode_tma(const CUtensorMap &mk, const CUtensorMap &mv, const
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    g_launch_err = cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<D, STAGES>, mk, mv, p, num_slots, error_word());
+    g_launch_err = cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<D, STAGES, ONE_MAP>, mk, mv, p, num_slots, error_word());
     return check_pdl_launch(g_launch_err, "attention_decode");
 }
 
-template <int D>
+template <int D, bool ONE_MAP>
 static int launch_decode_stages(int stages, const CUtensorMap &mk, const CUtensorMap &mv, const AttnParams &p, int num_slots, int n_tiles, cudaStream_t st)
 {
-    return stages >= 4 ? launch_decode_tma<D, 4>(mk, mv, p, num_slots, n_tiles, st)
-         : stages == 3 ? launch_decode_tma<D, 3>(mk, mv, p, num_slots, n_tiles, st)
-                       : launch_decode_tma<D, 2>(mk, mv, p, num_slots, n_tiles, st);
+    return stages >= 4 ? launch_decode_tma<D, 4, ONE_MAP>(mk, mv, p, num_slots, n_tiles, st)
+         : stages == 3 ? launch_decode_tma<D, 3, ONE_MAP>(mk, mv, p, num_slots, n_tiles, st)
+                       : launch_decode_tma<D, 2, ONE_MAP>(mk, mv, p, num_slots, n_tiles, st);
 }
 
 }  // namespace hfb
@@ -395,11 +413,12 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
     if (splits < 1 || G > 65535 || splits > 65535) return fail(HFB_EINVAL, "attention_decode: bad split or group count");
     if (splits > 1 && (!scratch || scratch_bytes < (size_t)T * H * splits * (d + 2) * sizeof(float)))
         return fail(HFB_EINVAL, "attention_decode: scratch of %zu bytes is too small for %d splits", scratch_bytes, splits);
-    CUtensorMap mk, mv;
+    CUtensorMap maps[2];
+    bool one_map = false;
     int rc;
     const int slots = (int)(num_pages * block_size);
-    if ((rc = tensor_map(k_cache, slots, G * d, block_size, &mk)) != HFB_OK) return rc;
-    if ((rc = tensor_map(v_cache, slots, G * d, block_size, &mv)) != HFB_OK) return rc;
+    if ((rc = tensor_map_kv(k_cache, v_cache, slots, G * d, block_size, d / 64, maps, &one_map)) != HFB_OK) return rc;
+    const CUtensorMap &mk = maps[0], &mv = maps[one_map ? 0 : 1];
     AttnParams p;
     p.q = (const __nv_bfloat16 *)q; p.k_cache = (const __nv_bfloat16 *)k_cache; p.v_cache = (const __nv_bfloat16 *)v_cache;
     p.out = (__nv_bfloat16 *)out; p.block_table = block_table; p.positions = positions;
@@ -409,8 +428,10 @@ extern "C" int hfb_attention_decode(const void *q, const void *k_cache, const vo
     p.num_pages = num_pages; p.scale_log2 = scale * 1.4426950408889634f;
     p.counters = (splits > 1 && splits <= 64 && counters && counters_len >= n_tiles * G) ? counters : nullptr;
     cudaStream_t st = (cudaStream_t)s;
-    rc = d == 128 ? launch_decode_stages<128>(stages, mk, mv, p, slots, n_tiles, st)
-                  : launch_decode_stages<64>(stages, mk, mv, p, slots, n_tiles, st);
+    if (one_map) rc = d == 128 ? launch_decode_stages<128, true>(stages, mk, mv, p, slots, n_tiles, st)
+                               : launch_decode_stages<64, true>(stages, mk, mv, p, slots, n_tiles, st);
+    else rc = d == 128 ? launch_decode_stages<128, false>(stages, mk, mv, p, slots, n_tiles, st)
+                       : launch_decode_stages<64, false>(stages, mk, mv, p, slots, n_tiles, st);
     if (rc != HFB_OK || splits == 1 || p.counters) return rc;
     return launch_attention_combine(p, T, d, st);
 }

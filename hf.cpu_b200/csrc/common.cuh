@@ -83,13 +83,26 @@ __device__ __forceinline__ void trace_put(int kind, unsigned long long value)
         if (i < HFB_TRACE_CAP) { log[2 + 2 * i] = (unsigned)kind; log[3 + 2 * i] = value; }
     }
 }
+// (developers) the time, from thread 0 of whichever block calls it
+__device__ __forceinline__ void trace_any(int kind)
+{
+    unsigned long long *log = g_trace_ptr;
+    if (log && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        unsigned long long i = atomicAdd(log, 1ull);
+        if (i < HFB_TRACE_CAP) { log[2 + 2 * i] = (unsigned)kind; log[3 + 2 * i] = t; }
+    }
+}
 void trace_register(void (*setter)(void *));
 static void trace_set_ptr(void *p) { cudaMemcpyToSymbol(g_trace_ptr, &p, sizeof p); }
 namespace { struct TraceRegistration { TraceRegistration() { trace_register(trace_set_ptr); } } g_trace_registration; }
 #define HFB_TRACE_ENTRY(id) trace_log(id, 0)
 #define HFB_TRACE_READY() trace_log(0, 1)
 #define HFB_TRACE_MARK(k) trace_log(0, k)
+#define HFB_TRACE_ANY(k) trace_any(k)
 #else
+#define HFB_TRACE_ANY(k)
 #define HFB_TRACE_ENTRY(id)
 #define HFB_TRACE_READY()
 #define HFB_TRACE_MARK(k)

@@ -227,28 +227,6 @@ __global__ void argmax_kernel(const float *logits, int32_t *out, int V)
     if (threadIdx.x == 0) out[blockIdx.x] = si[0] < 0 ? 0 : si[0];
 }
 
-// a[m, :] *= rsqrt(sum_p sumsq[p, m] / E + eps): completes rows of an RMSNorm whose row factor was left to the consumer.
-template <typename T>
-__global__ void scale_rows_kernel(T *a, const float *sumsq, int parts, int M, int E, float eps)
-{
-    pdl_sync();
-    const int m = blockIdx.x;
-    float ss = 0.f;
-    for (int p = 0; p < parts; p++) ss += sumsq[(size_t)p * M + m];
-    const float r = 1.0f / sqrtf(ss / (float)E + eps);
-    T *row = a + (size_t)m * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) row[i] = from_f32<T>(to_f32(row[i]) * r);
-}
-
-// Asks the memory system to bring the first `seg_bytes` of each of `rows` rows into the L2 cache; nothing waits for it.
-__global__ void prefetch_rows_l2_kernel(const uint8_t *base, int rows, size_t row_bytes, int seg_bytes)
-{
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= rows) return;
-    const uint8_t *p = base + (size_t)i * row_bytes;
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(seg_bytes) : "memory");
-}
-
 }  // namespace hfb
 
 using namespace hfb;
@@ -332,22 +310,4 @@ extern "C" int hfb_argmax(const float *logits, int32_t *out, int M, int V, hfb_s
     if (V <= 0) return fail(HFB_EINVAL, "argmax: empty vocabulary");
     g_launch_err = launch_pdl(argmax_kernel, dim3(M), dim3(1024), 0, (cudaStream_t)s, logits, out, V);
     return check_pdl_launch(g_launch_err, "argmax");
-}
-
-extern "C" int hfb_scale_rows(void *a, int dt, const float *sumsq, int parts, float eps, int M, int E, hfb_stream s)
-{
-    if (M <= 0) return HFB_OK;
-    if (!valid_dt(dt) || parts < 1 || E <= 0 || !sumsq) return fail(HFB_EINVAL, "scale_rows: bad arguments");
-    if (dt == HFB_F32) g_launch_err = launch_pdl(scale_rows_kernel<float>, dim3(M), dim3(256), 0, (cudaStream_t)s, (float *)a, sumsq, parts, M, E, eps);
-    else g_launch_err = launch_pdl(scale_rows_kernel<__nv_bfloat16>, dim3(M), dim3(256), 0, (cudaStream_t)s, (__nv_bfloat16 *)a, sumsq, parts, M, E, eps);
-    return check_pdl_launch(g_launch_err, "scale_rows");
-}
-
-extern "C" int hfb_prefetch_rows_l2(const void *base, int rows, size_t row_bytes, int seg_bytes, hfb_stream s)
-{
-    if (rows <= 0 || seg_bytes <= 0) return HFB_OK;
-    if (((uintptr_t)base & 15) || (row_bytes & 15) || (seg_bytes & 15) || (size_t)seg_bytes > row_bytes)
-        return fail(HFB_EINVAL, "prefetch_rows_l2: addresses and sizes must be multiples of 16 bytes");
-    prefetch_rows_l2_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)s>>>((const uint8_t *)base, rows, row_bytes, seg_bytes);
-    return check_launch("prefetch_rows_l2");
 }

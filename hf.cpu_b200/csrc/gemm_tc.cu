@@ -43,28 +43,6 @@ constexpr int PAIR_THREADS = 192;            // (the pair kernel has no such war
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
 
-enum { FIN_NONE = 0, FIN_RESIDUAL = 1, FIN_ROPE_KV = 2 };
-
-// What the CTA that stores the last split of a weight tile does with the tile's sum (few-token form only): the
-// reduction of the split-K partial sums and the memory-bound step that follows it, without another kernel.
-//   FIN_RESIDUAL: residual[t, n] += sum (+ bias); y[t, n] = residual * norm_w[n] (the next RMSNorm without its row
-//     factor) and, per row and quarter of the tile, the sum of squares of the new residual in sumsq[tile * 4 + q, t]:
-//     whoever consumes y multiplies by rsqrt(sum of the parts / N + eps) per row.
-//   FIN_ROPE_KV: the tile holds whole heads of the q|k|v row (128 % d == 0): + bias, rotary encoding, q to q_out,
-//     k and v into the paged cache, as reduce_rope_kv_kernel does.
-struct FinishParams {
-    int kind;
-    int *counters;                     // one per weight tile; zero before the launch, zero again after it
-    float *residual; const void *norm_w; int norm_w_dt; void *y; int y_dt; float *sumsq;
-    const float *cos_sin; int n_rot, n_positions; const int32_t *positions, *slots;
-    void *q_out, *k_cache, *v_cache; long long cache_slots; int H, G, d;
-};
-
-// The activations are the rows of an RMSNorm still to be multiplied by their row factor: sumsq[parts, M] holds
-// partial sums of squares per row, summed in order here; the factor rsqrt(sum / width + eps) is applied to the
-// accumulators (a product is linear in its rows).  sumsq == null: the activations are complete.
-struct RowScale { const float *sumsq; int parts; float eps; int width; };
-
 struct GemmParams {
     int M, N, K;                       // logical sizes: tokens, output features, inner
     int swapped;                       // X = weights, Y = activations
@@ -74,8 +52,6 @@ struct GemmParams {
     const void *bias; int bias_dt;     // [N] or null
     int mode;
     float *partial;                    // [splits, M, N] when mode == EPI_PARTIAL
-    FinishParams fin;                  // few-token form with partial sums only
-    RowScale scale;                    // few-token form only
 };
 
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -91,8 +67,6 @@ __host__ __device__ constexpr uint32_t instr_desc(int n)
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_X >> 4) << 24);
 }
 
-constexpr uint32_t FIN_SMEM_BYTES = 128 * 4;                 // row factors of up to 128 tokens
-
 template <int BN> constexpr int tmem_cols()
 {
     int need = 2 * BN, c = 32;
@@ -102,23 +76,17 @@ template <int BN> constexpr int tmem_cols()
 
 template <int BN, int STAGES> constexpr uint32_t gemm_smem_bytes()
 {
-    return 1024 + STAGES * (X_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + FIN_SMEM_BYTES;
+    return 1024 + STAGES * (X_BYTES + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16;
 }
 
 // One chunk of 16 accumulator columns of one row: v[i] is element (xr, y0 + i) of X . Y^T.
 // `live` false: the same instructions, nothing stored (the few-token form runs its epilogue once this way while the
 // first weights are on their way, so that its code is in the instruction cache when the first tile is done: fetched
 // at that moment it waits behind the weight stream, several microseconds for a 64-token tile).
-__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t *v, int xr, int y0, int split, int lane,
-                                               bool live = true, const float *rstd = nullptr)
+__device__ __forceinline__ void epilogue_chunk(const GemmParams &p, const uint32_t *v, int xr, int y0, int split, int lane,
+                                               bool live = true)
 {
     if (!live && !p.swapped) return;
-    if (rstd && p.mode != EPI_PARTIAL) {
-        // the tokens' row factors (all lanes read the same words of shared memory); partial sums are scaled when
-        // they are summed
-#pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * rstd[(y0 + i) & 127]);
-    }
     if (p.swapped && p.mode == EPI_SWIGLU) {
         // rows alternate gate, up: even lanes hold gate_i, the next lane holds up_i; out is [M, N/2].  The two lanes
         // of a pair exchange their values and share the work: of every two tokens the even lane finishes the first,
@@ -259,169 +227,6 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams &p, uint32_t *v,
     }
 }
 
-// ---- finishing a weight tile in the CTA that stored its last split ----------------------------------------
-// The four epilogue warps (128 threads) meet on a named barrier of their own.
-__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
-
-// The finishing work is a read of splits x tokens x 128 floats from the L2 cache by one CTA: what it costs is
-// latency, so every thread keeps many 16-byte loads in flight.  A warp takes every fourth token, a lane four
-// consecutive features of the tile; TB tokens are summed at a time, their loads of up to SMAX splits issued together
-// (TB * SMAX = 32 loads of 16 bytes per thread).  Loads go past the L1 cache (__ldcg), which may hold lines of an
-// earlier launch's partial sums at the same addresses.
-constexpr int FIN_MAX_SPLITS = 16;
-
-//
-// `dry`: the same instructions with every load and store switched off.  The few-token form runs its finishing step
-// once this way before it waits for the kernel in front (as it does with its epilogue), so that the code is in the
-// instruction cache when a tile's last split arrives: fetched at that moment it would wait, line after line, behind
-// the weight streams of the CTAs that are still running.
-template <int TB, int SMAX>
-__device__ __forceinline__ void sum_splits4(const GemmParams &p, int t0, int n0, float4 (&acc)[TB], bool dry)
-{
-    const size_t MN = (size_t)p.M * p.N;
-    float4 v[TB][SMAX];
-#pragma unroll
-    for (int j = 0; j < TB; j++) {
-        const int t = t0 + 4 * j;
-#pragma unroll
-        for (int s = 0; s < SMAX; s++)
-            v[j][s] = (t < p.M && s < p.splits && !dry) ? __ldcg((const float4 *)(p.partial + (size_t)s * MN + (size_t)t * p.N + n0))
-                                                : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-#pragma unroll
-    for (int j = 0; j < TB; j++) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int s = 0; s < SMAX; s++) { a.x += v[j][s].x; a.y += v[j][s].y; a.z += v[j][s].z; a.w += v[j][s].w; }   // split order
-        acc[j] = a;
-    }
-}
-
-__device__ __forceinline__ float4 load4_any(const void *p, int dt, size_t i)
-{
-    if (dt == HFB_F32) return *(const float4 *)((const float *)p + i);
-    const uint2 raw = *(const uint2 *)((const __nv_bfloat16 *)p + i);
-    const float2 lo = __bfloat1622float2(*(const __nv_bfloat162 *)&raw.x), hi = __bfloat1622float2(*(const __nv_bfloat162 *)&raw.y);
-    return make_float4(lo.x, lo.y, hi.x, hi.y);
-}
-
-template <typename T> __device__ __forceinline__ void store4(T *dst, float4 v);
-template <> __device__ __forceinline__ void store4<float>(float *dst, float4 v) { *(float4 *)dst = v; }
-template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16 *dst, float4 v)
-{
-    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-    *(uint2 *)dst = make_uint2(*(const uint32_t *)&lo, *(const uint32_t *)&hi);
-}
-
-// q = this warp among the four: it takes tokens q, q + 4, ...; the lane takes features 4 * lane .. 4 * lane + 3.
-template <int TB, int SMAX>
-__device__ __forceinline__ void finish_residual(const GemmParams &p, int tx, int q, int lane, bool dry)
-{
-    const FinishParams &fp = p.fin;
-    const int n0 = tx * TILE_X + 4 * lane;
-    const bool live = n0 < p.N && !dry;                   // (N is a multiple of 4: a lane's four features are in or out)
-    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 b = (live && p.bias) ? load4_any(p.bias, p.bias_dt, n0) : zero;
-    const float4 w = (live && fp.y) ? load4_any(fp.norm_w, fp.norm_w_dt, n0) : zero;
-    for (int t0 = q; t0 < p.M; t0 += 4 * TB) {
-        float4 acc[TB], res[TB];
-#pragma unroll
-        for (int j = 0; j < TB; j++) {
-            const int t = t0 + 4 * j;
-            res[j] = (live && t < p.M) ? __ldcg((const float4 *)(fp.residual + (size_t)t * p.N + n0)) : zero;
-        }
-        sum_splits4<TB, SMAX>(p, t0, n0, acc, !live);
-#pragma unroll
-        for (int j = 0; j < TB; j++) {
-            const int t = t0 + 4 * j;
-            if (t >= p.M) break;
-            float4 v = zero;
-            if (live) {
-                v = make_float4((acc[j].x + b.x) + res[j].x, (acc[j].y + b.y) + res[j].y, (acc[j].z + b.z) + res[j].z,
-                                (acc[j].w + b.w) + res[j].w);
-                *(float4 *)(fp.residual + (size_t)t * p.N + n0) = v;
-                if (fp.y) {
-                    const float4 yv = make_float4(v.x * w.x, v.y * w.y, v.z * w.z, v.w * w.w);
-                    if (fp.y_dt == HFB_BF16) store4((__nv_bfloat16 *)fp.y + (size_t)t * p.N + n0, yv);
-                    else store4((float *)fp.y + (size_t)t * p.N + n0, yv);
-                }
-            }
-            if (fp.sumsq) {
-                const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-                if (lane == 0 && !dry) fp.sumsq[(size_t)tx * p.M + t] = ss;
-            }
-        }
-    }
-}
-
-// The tile holds whole heads (128 % d == 0) and a lane's four features lie in one half of a rotation pair (n_rot is a
-// multiple of 8): the partner values are four lanes' worth away, fetched with a shuffle.
-template <typename T, int TB, int SMAX>
-__device__ __forceinline__ void finish_rope_kv(const GemmParams &p, int tx, int q, int lane, const float *rstd, int *err, bool dry)
-{
-    const FinishParams &fp = p.fin;
-    const int n0 = tx * TILE_X + 4 * lane, d = fp.d, half = fp.n_rot >> 1;
-    const bool live = n0 < p.N && !dry;
-    const int head = n0 / d, i0 = n0 - head * d;
-    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float4 b = (live && p.bias) ? load4_any(p.bias, p.bias_dt, n0) : zero;
-    const bool rotate = live && head < fp.H + fp.G && i0 < fp.n_rot;
-    const bool low = i0 < half;                           // this lane holds the first elements of its pairs
-    const int partner = low ? lane + (half >> 2) : lane - (half >> 2);
-    for (int t0 = q; t0 < p.M; t0 += 4 * TB) {
-        float4 acc[TB];
-        sum_splits4<TB, SMAX>(p, t0, n0, acc, !live);
-#pragma unroll
-        for (int j = 0; j < TB; j++) {
-            const int t = t0 + 4 * j;
-            if (t >= p.M) break;                          // (the same for the whole warp)
-            float4 v = acc[j];
-            if (rstd) { const float r = rstd[t & 127]; v.x *= r; v.y *= r; v.z *= r; v.w *= r; }
-            // the separate kernels round q|k|v to the run type before rotating; keep the same values
-            v = make_float4(to_f32(from_f32<T>(v.x + b.x)), to_f32(from_f32<T>(v.y + b.y)), to_f32(from_f32<T>(v.z + b.z)),
-                            to_f32(from_f32<T>(v.w + b.w)));
-            float4 o;
-            o.x = __shfl_sync(0xffffffffu, v.x, partner & 31); o.y = __shfl_sync(0xffffffffu, v.y, partner & 31);
-            o.z = __shfl_sync(0xffffffffu, v.z, partner & 31); o.w = __shfl_sync(0xffffffffu, v.w, partner & 31);
-            float4 out = v;
-            if (rotate || dry) {
-                int pos = live ? fp.positions[t] : 0;
-                if (pos < 0 || pos >= fp.n_positions) { atomicOr(err, HFB_ERR_POSITION); pos = 0; }
-                const int k = low ? i0 : i0 - half;
-                const float4 *cs = (const float4 *)(fp.cos_sin + ((size_t)pos * half + k) * 2);   // (cos, sin) of 4 pairs
-                const float4 c01 = live ? cs[0] : zero, c23 = live ? cs[1] : zero;
-                if (low) out = make_float4(v.x * c01.x - o.x * c01.y, v.y * c01.z - o.y * c01.w, v.z * c23.x - o.z * c23.y, v.w * c23.z - o.w * c23.w);
-                else out = make_float4(o.x * c01.y + v.x * c01.x, o.y * c01.w + v.y * c01.z, o.z * c23.y + v.z * c23.x, o.w * c23.w + v.w * c23.z);
-            }
-            if (head < fp.H) {
-                if (live) store4((T *)fp.q_out + ((size_t)t * fp.H + head) * d + i0, out);
-            } else {
-                long long slot = (fp.slots && live) ? fp.slots[t] : -1;
-                if (slot >= fp.cache_slots) { atomicOr(err, HFB_ERR_SLOT); slot = -1; }
-                if (slot >= 0) {
-                    if (head < fp.H + fp.G) store4((T *)fp.k_cache + ((size_t)slot * fp.G + (head - fp.H)) * d + i0, out);
-                    else store4((T *)fp.v_cache + ((size_t)slot * fp.G + (head - fp.H - fp.G)) * d + i0, out);
-                }
-            }
-        }
-    }
-}
-
-// Picks the number of tokens a warp sums at a time by the number of splits, so that about 32 loads are in flight.
-template <typename T>
-__device__ __forceinline__ void finish_tile(const GemmParams &p, int tx, int q, int lane, const float *rstd, int *err, bool dry)
-{
-    if (p.fin.kind == FIN_RESIDUAL) {
-        if (p.splits <= 4) finish_residual<8, 4>(p, tx, q, lane, dry);
-        else if (p.splits <= 8) finish_residual<4, 8>(p, tx, q, lane, dry);
-        else finish_residual<2, 16>(p, tx, q, lane, dry);
-    } else {
-        if (p.splits <= 4) finish_rope_kv<T, 8, 4>(p, tx, q, lane, rstd, err, dry);
-        else if (p.splits <= 8) finish_rope_kv<T, 4, 8>(p, tx, q, lane, rstd, err, dry);
-        else finish_rope_kv<T, 2, 16>(p, tx, q, lane, rstd, err, dry);
-    }
-}
-
 // ---- the kernel ---------------------------------------------------------------------------------
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -438,8 +243,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
     volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen_base + STAGES * (X_BYTES + Y_BYTES) + (2 * STAGES + 4) * 8);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
-    volatile int *last_flag = (volatile int *)(tmem_slot + 2);       // this CTA stored a tile's last split
-    float *rstd_smem = (float *)(tmem_slot + 4);                     // [128] row factors
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
@@ -550,23 +353,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int row = q * 32 + lane;
         uint32_t tile_it = 0;
         bool ok = true;
-        const float *rstd = (p.swapped && p.scale.sumsq) ? rstd_smem : nullptr;
         // With few tokens the first turn of this loop is a rehearsal: it reads whatever the accumulator holds and
         // stores nothing, before the kernel in front is known to have finished (see epilogue_chunk).
         bool rehearsal = p.swapped != 0;
-        auto after_wait = [&]() {
-            // what comes from the kernel in front: the rows' sums of squares.  Thread t sums the parts of token t in
-            // order and keeps the row factor where the four warps find it.
-            if (rstd) {
-                if (row < p.M) {
-                    float ss = 0.f;
-                    for (int i = 0; i < p.scale.parts; i++) ss += __ldcg(p.scale.sumsq + (size_t)i * p.M + row);
-                    rstd_smem[row] = 1.0f / sqrtf(ss / (float)p.scale.width + p.scale.eps);
-                }
-                epi_bar();
-            }
-        };
-        if (!rehearsal) { pdl_sync(); after_wait(); } // nothing is written before the kernel in front has finished
+        if (!rehearsal) pdl_sync();                   // nothing is written before the kernel in front has finished
         for (int item = blockIdx.x; item < total_items && ok;) {
             int split = item / per_split, t = item % per_split;
             int tx = t % p.tiles_x, ty = t / p.tiles_x;
@@ -585,42 +375,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tmem_ld16(taddr + c0, v);
                 if (two) tmem_ld16(taddr + c0 + 16, v + (BN >= 32 ? 16 : 0));
                 tmem_wait_ld();
-                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane, !rehearsal, rstd);
-                if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane, !rehearsal, rstd);
+                epilogue_chunk(p, v, xr, ty * BN + c0, split, lane, !rehearsal);
+                if (two) epilogue_chunk(p, v + (BN >= 32 ? 16 : 0), xr, ty * BN + c0 + 16, split, lane, !rehearsal);
             }
             if (rehearsal) {
-                if (BN <= 128 && p.fin.kind != FIN_NONE) {
-                    if (p.out_dt == HFB_BF16) finish_tile<__nv_bfloat16>(p, tx, warp - 2, lane, rstd, err, true);
-                    else finish_tile<float>(p, tx, warp - 2, lane, rstd, err, true);
-                }
                 rehearsal = false;
                 pdl_sync();
-                after_wait();
                 continue;
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * a);
-            if (BN <= 128 && p.swapped && p.fin.kind != FIN_NONE) {      // (the few-token form has at most 128 columns)
-                // The split is in global memory.  Count it; the CTA that brings a tile's count to the number of
-                // splits sums the tile in split order, whichever CTA that is, and does the step that follows.
-                epi_bar();
-                if (row == 0) {
-                    __threadfence();                             // (after the barrier: it covers the four warps' stores)
-                    const int before = atomicAdd(&p.fin.counters[tx], 1);
-                    const int last = before == p.splits - 1;
-                    if (last) p.fin.counters[tx] = 0;            // every split has counted: ready for the next launch
-                    *last_flag = last;
-                }
-                epi_bar();
-                if (*last_flag) {
-                    __threadfence();
-                    const int fq = warp - 2;                     // the finishing step's own numbering of the four warps
-                    if (p.out_dt == HFB_BF16) finish_tile<__nv_bfloat16>(p, tx, fq, lane, rstd, err, false);
-                    else finish_tile<float>(p, tx, fq, lane, rstd, err, false);
-                }
-                epi_bar();                                       // the flag may be rewritten for the next item
-            }
             item += gridDim.x;
             tile_it++;
         }
@@ -902,6 +667,47 @@ int tensor_map(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *o
 }
 
 // Index of the current device (0 where it cannot be told), for what is remembered per device.
+// Maps over a paged key/value cache [slots, row_elems] of bfloat16 for copies of whole pages: a box holds `box_keys`
+// consecutive slots of the `halves` 128-byte pieces of one head ([piece][key][64 elements] in shared memory, 128-byte
+// swizzle).  Where the values lie a multiple of 16 bytes above the keys, ONE map of rank 4 covers both (box
+// [keys|values][piece][key][64], *single = true, written to maps[0]); else maps[0] covers the keys and maps[1] the values
+// (rank 3).  Coordinates: (0, slot, head * halves [, 0]).
+int tensor_map_kv(const void *k, const void *v, int slots, int row_elems, int box_keys, int halves, CUtensorMap *maps, bool *single)
+{
+    struct Key {
+        const void *k, *v; int slots, row_elems, box_keys, halves;
+        bool operator==(const Key &o) const { return k == o.k && v == o.v && slots == o.slots && row_elems == o.row_elems && box_keys == o.box_keys && halves == o.halves; }
+    };
+    struct Val { CUtensorMap m[2]; bool single; };
+    struct Hash { size_t operator()(const Key &x) const { return ((size_t)x.k * 1000003u ^ (size_t)x.v) * 1000003u ^ (size_t)x.slots * 31u ^ (size_t)x.box_keys; } };
+    static std::unordered_map<Key, Val, Hash> cache;
+    static std::mutex mu;
+    Key key{k, v, slots, row_elems, box_keys, halves};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { maps[0] = it->second.m[0]; maps[1] = it->second.m[1]; *single = it->second.single; return HFB_OK; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fail(HFB_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const long long gap = (const char *)v - (const char *)k;
+    Val val{};
+    val.single = gap > 0 && (gap & 15) == 0 && gap < (1ll << 40);
+    cuuint64_t dims[4] = {64, (cuuint64_t)slots, (cuuint64_t)(row_elems / 64), 2};
+    cuuint64_t strides[3] = {(cuuint64_t)row_elems * 2, 128, (cuuint64_t)(val.single ? gap : 0)};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_keys, (cuuint32_t)halves, 2};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    const int rank = val.single ? 4 : 3;
+    for (int i = 0; i < (val.single ? 1 : 2); i++) {
+        CUresult r = fn(&val.m[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void *>(i ? v : k), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(HFB_ECUDA, "cuTensorMapEncodeTiled (key/value pages) failed with %d", (int)r);
+    }
+    if (cache.size() > 4096) cache.clear();
+    cache[key] = val;
+    maps[0] = val.m[0]; maps[1] = val.m[1]; *single = val.single;
+    return HFB_OK;
+}
+
 static int current_device()
 {
     int dev = 0;
@@ -1157,34 +963,18 @@ extern "C" int hfb_linear_tc(const void *a, const void *w, const void *bias, int
 
 // h[M, N/2] = silu(g) * u where row 2i of w holds gate feature i and row 2i+1 up feature i: the activation runs in
 // the product's epilogue, from the float32 accumulators.
-static int linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, const hfb::RowScale &scale,
-                            hfb_stream s)
+extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s)
 {
     if (M <= 0 || N <= 0) return HFB_OK;
     int rc = check_tc_args("linear_tc_swiglu", a, w, out, M, N, K);
     if (rc != HFB_OK) return rc;
     if ((N & 1) || !valid_dt(out_dt)) return fail(HFB_EINVAL, "linear_tc_swiglu: N must be even (gate and up rows alternate)");
-    if (scale.sumsq && M > 128) return fail(HFB_ENOTSUP, "linear_tc_swiglu: row factors are applied with at most 128 rows (got %d)", M);
     GemmParams p{};
     CUtensorMap mx, my;
     int bn;
     if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
     p.out = out; p.out_dt = out_dt; p.bias = nullptr; p.mode = EPI_SWIGLU;
-    p.scale = scale;
     return launch_bn(bn, mx, my, p, (cudaStream_t)s);
-}
-
-extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s)
-{
-    return linear_tc_swiglu(a, w, out, out_dt, M, N, K, hfb::RowScale{}, s);
-}
-
-// The same where the rows of `a` still lack their RMSNorm row factor (see hfb_linear_tc_residual_y): M <= 128.
-extern "C" int hfb_linear_tc_swiglu_scaled(const void *a, const void *w, void *out, int out_dt, int M, int N, int K,
-                                           const float *sumsq, int parts, float eps, hfb_stream s)
-{
-    if (!sumsq || parts < 1) return fail(HFB_EINVAL, "linear_tc_swiglu_scaled: no sums of squares");
-    return linear_tc_swiglu(a, w, out, out_dt, M, N, K, hfb::RowScale{sumsq, parts, eps, K}, s);
 }
 
 // Only the split-K partial sums: partial[s, M, N] float32 for s < *splits, in `workspace`
@@ -1218,89 +1008,6 @@ extern "C" int hfb_linear_tc_partials(const void *a, const void *w, int M, int N
     p.partial = (float *)workspace;
     p.mode = EPI_PARTIAL;
     *splits = p.splits;
-    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
-}
-
-// ---- few tokens: the product, its split-K reduction and the step after it in one kernel ---------------------
-// Sets up the few-token product with partial sums in `workspace` (hfb_linear_tc_partials_workspace bytes) and checks
-// the tile counters.
-static int plan_fused(const char *who, const void *a, const void *w, int M, int N, int K, void *workspace, size_t workspace_bytes,
-                      int *counters, int counters_len, hfb::GemmParams &p, int &bn, CUtensorMap &mx, CUtensorMap &my)
-{
-    using namespace hfb;
-    if (M > 128) return fail(HFB_ENOTSUP, "%s: at most 128 rows (got %d)", who, M);
-    int rc = check_tc_args(who, a, w, workspace, M, N, K);
-    if (rc != HFB_OK) return rc;
-    const size_t need = hfb_linear_tc_partials_workspace(M, N, K);
-    if (!workspace || workspace_bytes < need) return fail(HFB_EINVAL, "%s: workspace of %zu bytes, %zu needed", who, workspace_bytes, need);
-    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
-    if (!counters || counters_len < p.tiles_x) return fail(HFB_EINVAL, "%s: %d tile counters needed, %d given", who, p.tiles_x, counters_len);
-    if (N & 3) return fail(HFB_ENOTSUP, "%s: N = %d must be a multiple of 4", who, N);
-    const int want = (int)(need / ((size_t)M * N * sizeof(float)));
-    p.kb_per_split = (p.kb_total + want - 1) / want;
-    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
-    if (p.splits > FIN_MAX_SPLITS) return fail(HFB_ENOTSUP, "%s: %d splits exceed %d", who, p.splits, FIN_MAX_SPLITS);
-    p.partial = (float *)workspace;
-    p.mode = EPI_PARTIAL;
-    p.fin.counters = counters;
-    return HFB_OK;
-}
-
-// Row-factor parts hfb_linear_tc_residual_y writes per row for N output features.
-extern "C" int hfb_linear_tc_sumsq_parts(int N) { return (N + hfb::TILE_X - 1) / hfb::TILE_X; }
-
-// residual[M, N] += a . w^T (+ bias), M <= 128, in one kernel: the CTA that stores the last split of a weight tile
-// sums the splits in split order and adds them into the float32 residual.  With `y`: y = residual * norm_w (the
-// next RMSNorm without its row factor) and sumsq[hfb_linear_tc_sumsq_parts(N), M] = partial sums of squares of the
-// new residual rows; the row factor is rsqrt(sum over the parts / N + eps), which hfb_linear_tc_swiglu_scaled and
-// hfb_linear_tc_rope_kv apply.  `counters`: at least ceil(N / 128) ints, zero before the first launch (every launch
-// leaves them zero).
-extern "C" int hfb_linear_tc_residual_y(const void *a, const void *w, const void *bias, int bias_dt, float *residual,
-                                        const void *norm_w, int norm_w_dt, void *y, int y_dt, float *sumsq, int M, int N, int K,
-                                        void *workspace, size_t workspace_bytes, int *counters, int counters_len, hfb_stream s)
-{
-    if (M <= 0 || N <= 0) return HFB_OK;
-    if ((bias && !valid_dt(bias_dt)) || (y && (!valid_dt(y_dt) || !valid_dt(norm_w_dt) || !norm_w || !sumsq)))
-        return fail(HFB_EINVAL, "linear_tc_residual_y: bad arguments");
-    GemmParams p{};
-    CUtensorMap mx, my;
-    int bn, rc;
-    if ((rc = plan_fused("linear_tc_residual_y", a, w, M, N, K, workspace, workspace_bytes, counters, counters_len, p, bn, mx, my)) != HFB_OK) return rc;
-    p.bias = bias; p.bias_dt = bias_dt; p.out_dt = HFB_F32;
-    p.fin.kind = FIN_RESIDUAL;
-    p.fin.residual = residual; p.fin.norm_w = norm_w; p.fin.norm_w_dt = norm_w_dt; p.fin.y = y; p.fin.y_dt = y_dt;
-    p.fin.sumsq = y ? sumsq : nullptr;
-    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
-}
-
-// q|k|v = a . w^T (scaled by the rows' factors when `in_sumsq` is given) + bias, rotary encoding of q and k, q to q_out
-// [M, H*d], k and v into the paged cache at `slots` (null: q only), M <= 128, in one kernel; head sizes that divide
-// 128.  Element type `dt` of q_out and the cache.  Same arithmetic as hfb_reduce_rope_kv.
-extern "C" int hfb_linear_tc_rope_kv(const void *a, const void *w, const void *bias, int bias_dt, const float *in_sumsq, int in_parts,
-                                     float in_eps, const float *cos_sin, int n_rot, int n_positions, const int32_t *positions,
-                                     const int32_t *slots, void *q_out, void *k_cache, void *v_cache, int64_t cache_slots, int dt,
-                                     int M, int H, int G, int d, int K, void *workspace, size_t workspace_bytes, int *counters,
-                                     int counters_len, hfb_stream s)
-{
-    if (M <= 0) return HFB_OK;
-    if (!valid_dt(dt) || H <= 0 || G <= 0 || d <= 0 || n_rot < 0 || n_rot > d || (n_rot & 1) || (bias && !valid_dt(bias_dt)))
-        return fail(HFB_EINVAL, "linear_tc_rope_kv: bad arguments");
-    if (TILE_X % d || (d & 3)) return fail(HFB_ENOTSUP, "linear_tc_rope_kv: head size %d does not divide %d", d, TILE_X);
-    if (n_rot & 7) return fail(HFB_ENOTSUP, "linear_tc_rope_kv: a rotary width of %d is not a multiple of 8", n_rot);
-    if (((uintptr_t)q_out & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)cos_sin & 15))
-        return fail(HFB_ENOTSUP, "linear_tc_rope_kv: outputs and the rotary table must be 16-byte aligned");
-    if (n_rot > 0 && (!cos_sin || !positions)) return fail(HFB_EINVAL, "linear_tc_rope_kv: rotation needs a table and positions");
-    const int N = (H + 2 * G) * d;
-    GemmParams p{};
-    CUtensorMap mx, my;
-    int bn, rc;
-    if ((rc = plan_fused("linear_tc_rope_kv", a, w, M, N, K, workspace, workspace_bytes, counters, counters_len, p, bn, mx, my)) != HFB_OK) return rc;
-    p.bias = bias; p.bias_dt = bias_dt; p.out_dt = dt;
-    if (in_sumsq) p.scale = RowScale{in_sumsq, in_parts, in_eps, K};
-    p.fin.kind = FIN_ROPE_KV;
-    p.fin.cos_sin = cos_sin; p.fin.n_rot = n_rot; p.fin.n_positions = n_positions; p.fin.positions = positions; p.fin.slots = slots;
-    p.fin.q_out = q_out; p.fin.k_cache = k_cache; p.fin.v_cache = v_cache; p.fin.cache_slots = cache_slots;
-    p.fin.H = H; p.fin.G = G; p.fin.d = d;
     return launch_bn(bn, mx, my, p, (cudaStream_t)s);
 }
 

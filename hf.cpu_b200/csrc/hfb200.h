@@ -50,34 +50,6 @@ int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, v
 /* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
 int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
 
-/* Hints the first seg_bytes of each of `rows` rows (row_bytes apart) into the L2 cache; multiples of 16 bytes. */
-int hfb_prefetch_rows_l2(const void *base, int rows, size_t row_bytes, int seg_bytes, hfb_stream s);
-
-/* a[m, :] *= rsqrt(sum_p sumsq[p, m] / E + eps), in place (rows whose RMSNorm row factor was left to the consumer). */
-int hfb_scale_rows(void *a, int dt, const float *sumsq, int parts, float eps, int M, int E, hfb_stream s);
-
-/* Few rows (M <= 128): a product, its split-K reduction and the memory-bound step after it as ONE kernel.  The
- * CTA that stores the last split of a weight tile sums the tile's splits (in split order, whichever CTA it is) and
- * finishes it.  `workspace`: hfb_linear_tc_partials_workspace(M, N, K) bytes; `counters`: ceil(N / 128) ints that
- * are zero before the first launch (each launch leaves them zero).
- *  - hfb_linear_tc_residual_y: residual += a . w^T (+ bias); with y != null also y = residual * norm_w and
- *    sumsq[hfb_linear_tc_sumsq_parts(N), M] = partial sums of squares of the new rows, so that the consumer of y can
- *    apply the RMSNorm's row factor rsqrt(sum of the parts / N + eps) itself;
- *  - hfb_linear_tc_swiglu_scaled: hfb_linear_tc_swiglu on such rows (factor applied to the accumulators);
- *  - hfb_linear_tc_rope_kv: q|k|v = a . w^T (on such rows when in_sumsq != null) + bias, rotary encoding, q to q_out,
- *    k and v into the paged cache; head sizes that divide 128. */
-int hfb_linear_tc_sumsq_parts(int N);
-int hfb_linear_tc_residual_y(const void *a, const void *w, const void *bias, int bias_dt, float *residual,
-                             const void *norm_w, int norm_w_dt, void *y, int y_dt, float *sumsq, int M, int N, int K,
-                             void *workspace, size_t workspace_bytes, int *counters, int counters_len, hfb_stream s);
-int hfb_linear_tc_swiglu_scaled(const void *a, const void *w, void *out, int out_dt, int M, int N, int K,
-                                const float *sumsq, int parts, float eps, hfb_stream s);
-int hfb_linear_tc_rope_kv(const void *a, const void *w, const void *bias, int bias_dt, const float *in_sumsq, int in_parts,
-                          float in_eps, const float *cos_sin, int n_rot, int n_positions, const int32_t *positions,
-                          const int32_t *slots, void *q_out, void *k_cache, void *v_cache, int64_t cache_slots, int dt,
-                          int M, int H, int G, int d, int K, void *workspace, size_t workspace_bytes, int *counters,
-                          int counters_len, hfb_stream s);
-
 /* Only the split-K partial sums partial[*splits, M, N] (float32) of a product, for a fused reduction to finish;
  * `workspace` must hold hfb_linear_tc_partials_workspace bytes.  Above 128 rows that size is 0 for a product that
  * would not be split, and this entry refuses it (HFB_ENOTSUP). */

@@ -176,53 +176,30 @@ def swiglu(gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> No
     backend().swiglu(gu, out, bool(interleaved))
 
 
-def _check_row_scale(a, row_scale) -> None:
-    if row_scale is not None:
-        sumsq, eps = row_scale
-        _need(sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == a.shape[0] and eps >= 0,
-              "row scale: partial sums of squares must be float32 [parts, M]")
-
-
-def linear_swiglu(a: torch.Tensor, w: torch.Tensor, gu_buf: torch.Tensor, out: torch.Tensor, row_scale=None) -> None:
+def linear_swiglu(a: torch.Tensor, w: torch.Tensor, gu_buf: torch.Tensor, out: torch.Tensor) -> None:
     """out = silu(g) * u where [g0, u0, g1, u1, ...] = a @ w.T (rows of ``w`` alternate gate, up).  ``gu_buf``
-    [M, 2F] is scratch for the unfused form.  ``row_scale`` = (sumsq [parts, M], eps): the rows of ``a`` still lack
-    the factor rsqrt(sum of the parts / K + eps), see :func:`linear_residual_norm`."""
+    [M, 2F] is scratch for the unfused form."""
     _need(a.shape[1] == w.shape[1] and w.shape[0] == 2 * out.shape[1] and out.shape[0] == a.shape[0],
           "linear_swiglu: shape mismatch")
     _need(gu_buf.shape == (a.shape[0], w.shape[0]), "linear_swiglu: scratch must be [M, 2F]")
-    _check_row_scale(a, row_scale)
-    backend().linear_swiglu(a, w, gu_buf, out, row_scale)
+    backend().linear_swiglu(a, w, gu_buf, out)
 
 
-def linear_residual_norm(a, w, bias, residual, norm_w, eps, xn_out, defer: bool = False):
-    """residual += a @ w.T (+ bias); then, if ``xn_out`` is given, xn_out = rmsnorm(residual) * norm_w.
-
-    With ``defer`` the backend may leave the norm's row factor to whoever consumes ``xn_out``: it then writes
-    xn_out = residual * norm_w and returns float32 partial sums of squares of the new residual rows, [parts, M]; the
-    consumer passes (that, eps) as ``row_scale``.  Returns None when ``xn_out`` is complete."""
+def linear_residual_norm(a, w, bias, residual, norm_w, eps, xn_out) -> None:
+    """residual += a @ w.T (+ bias); then, if ``xn_out`` is given, xn_out = rmsnorm(residual) * norm_w."""
     _need(a.shape[1] == w.shape[1] and residual.shape == (a.shape[0], w.shape[0]) and residual.dtype == torch.float32,
           "linear_residual_norm: shape mismatch")
     _need(xn_out is None or (xn_out.shape == residual.shape and norm_w.shape == (w.shape[0],)),
           "linear_residual_norm: norm shape mismatch")
-    return backend().linear_residual_norm(a, w, bias, residual, norm_w, float(eps), xn_out, bool(defer) and xn_out is not None)
+    backend().linear_residual_norm(a, w, bias, residual, norm_w, float(eps), xn_out)
 
 
-def linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d,
-                   row_scale=None) -> None:
-    """q|k|v = a @ w.T + bias, then :func:`rope_kv_write`; ``qkv_buf`` [T, (H+2G)d] is scratch for the unfused form.
-    ``row_scale`` as in :func:`linear_swiglu`."""
+def linear_rope_kv(a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d) -> None:
+    """q|k|v = a @ w.T + bias, then :func:`rope_kv_write`; ``qkv_buf`` [T, (H+2G)d] is scratch for the unfused form."""
     _need(w.shape[0] == (H + 2 * G) * d and q_out.shape == (a.shape[0], H * d), "linear_rope_kv: shape mismatch")
     _need(k_cache.shape[2:] == (G, d) and v_cache.shape == k_cache.shape and k_cache.dtype == q_out.dtype,
           "linear_rope_kv: cache geometry mismatch")
-    _check_row_scale(a, row_scale)
-    backend().linear_rope_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache, H, G, d,
-                             row_scale)
-
-
-def scale_rows(a: torch.Tensor, row_scale) -> None:
-    """a[m, :] *= rsqrt(sum of the parts of row m / K + eps), in place: completes rows whose factor was deferred."""
-    _check_row_scale(a, row_scale)
-    backend().scale_rows(a, row_scale[0], float(row_scale[1]))
+    backend().linear_rope_kv(a, w, bias, qkv_buf, cos_sin, int(n_rot), positions, slots, q_out, k_cache, v_cache, H, G, d)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

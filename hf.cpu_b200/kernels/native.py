@@ -60,13 +60,9 @@ class NativeBackend:
         self.gemm = os.environ.get("HFB_GEMM", "tc")
         self._ws = None
         self._argmax_ws = None
-        # few rows: the split-K reduction and the step after it run in the product's own kernel (HFB_FUSE_TAILS=0:
-        # as separate kernels, which the tests compare with)
-        self.fuse_tails = os.environ.get("HFB_FUSE_TAILS", "0") != "0"
-        # decode attention: the CTA that stores a tile's last split merges the splits (0: a second kernel does)
-        self.merge_in_kernel = os.environ.get("HFB_ATTN_MERGE", "1") != "0"
+        # decode attention: the CTA that stores a tile's last split merges the splits (False: a second kernel does)
+        self.merge_in_kernel = True
         self._counters = None
-        self._sumsq = {}
         self.lib.hfb_linear_tc_partials_workspace.restype = ctypes.c_size_t
         self.lib.hfb_argmax2_scratch.restype = ctypes.c_size_t
         self.path = path
@@ -103,8 +99,6 @@ class NativeBackend:
         self._on_gpu(a, w, bias, out)
         M, K = a.shape
         N = w.shape[0]
-        if accumulate and self._fused_ok(a, w, out) and self._residual_y(a, w, bias, out, None, 0.0, None):
-            return
         if (self.gemm == "tc" and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
                 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
                 and (bias is None or bias.data_ptr() % 16 == 0)):
@@ -248,73 +242,6 @@ class NativeBackend:
             self._ws = torch.empty(64 << 20, dtype=torch.uint8, device=device)     # split-K partials never need more
         return self._ws
 
-    def _fused_ok(self, a, w, residual=None):
-        """Few rows of bfloat16 on the tensor cores: the product finishes its own split-K sum and what follows."""
-        return (self.fuse_tails and a.shape[0] <= 128 and self._tc_ok(a, w, residual) and w.shape[0] % 4 == 0
-                and (w.shape[0] + 127) // 128 <= 4096)
-
-    def _fused_buffers(self, a, w):
-        """(workspace, bytes the partial sums need, tile counters) or None when the workspace is too small."""
-        M, K = a.shape
-        ws = self._workspace(a.device)
-        need = self.lib.hfb_linear_tc_partials_workspace(c_int(M), c_int(w.shape[0]), c_int(K))
-        if need == 0 or need > ws.numel():
-            return None
-        if self._counters is None or self._counters.device != a.device:
-            self._counters = torch.zeros(4096, dtype=torch.int32, device=a.device)
-        return ws, need, self._counters
-
-    def _residual_y(self, a, w, bias, residual, norm_w, eps, y):
-        """residual += a @ w.T (+ bias) in one kernel; with ``y`` also y = residual * norm_w and the rows' partial sums
-        of squares, which are returned.  False when the sizes do not allow it."""
-        bufs = self._fused_buffers(a, w)
-        if bufs is None or (bias is not None and bias.data_ptr() % 16):
-            return False
-        ws, _, counters = bufs
-        M, K = a.shape
-        N = w.shape[0]
-        sumsq = None
-        if y is not None:
-            parts = self.lib.hfb_linear_tc_sumsq_parts(c_int(N))
-            key = (y.data_ptr(), parts, M)
-            sumsq = self._sumsq.get(key)
-            if sumsq is None:
-                if len(self._sumsq) > 256:
-                    self._sumsq.clear()
-                sumsq = self._sumsq[key] = torch.empty((parts, M), dtype=torch.float32, device=a.device)
-        self._check(self.lib.hfb_linear_tc_residual_y(
-            _p(a), _p(w), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(residual), _p(norm_w),
-            c_int(_dt(norm_w) if norm_w is not None else 0), _p(y), c_int(_dt(y) if y is not None else 0), _p(sumsq),
-            c_int(M), c_int(N), c_int(K), _p(ws), ctypes.c_size_t(ws.numel()), _p(counters), c_int(counters.numel()),
-            self._stream()), "linear_tc_residual_y")
-        return sumsq if sumsq is not None else True
-
-    def prefetch_l2(self, w, rows, seg_bytes):
-        """On a side stream that starts where the current stream stands: hint the first ``seg_bytes`` of the first
-        ``rows`` rows of ``w`` into the L2 cache.  ``join_side()`` makes the current stream wait for the side stream."""
-        cur = torch.cuda.current_stream()
-        if getattr(self, "_side", None) is None:
-            self._side = torch.cuda.Stream()
-        self._side.wait_stream(cur)
-        row_bytes = w.shape[1] * w.element_size()
-        seg = min(seg_bytes, row_bytes) // 16 * 16
-        rc = self.lib.hfb_prefetch_rows_l2(_p(w), c_int(min(rows, w.shape[0])), ctypes.c_size_t(row_bytes), c_int(seg),
-                                           c_void_p(self._side.cuda_stream))
-        if rc != 0:
-            raise KernelError(f"prefetch: {self.lib.hfb_last_error().decode()}")
-        self._side_used = True
-
-    def join_side(self):
-        if getattr(self, "_side_used", False):
-            torch.cuda.current_stream().wait_stream(self._side)
-            self._side_used = False
-
-    def scale_rows(self, a, sumsq, eps):
-        self._on_gpu(a, sumsq)
-        M, E = a.shape
-        self._check(self.lib.hfb_scale_rows(_p(a), c_int(_dt(a)), _p(sumsq), c_int(sumsq.shape[0]), c_float(eps), c_int(M),
-                                            c_int(E), self._stream()), "scale_rows")
-
     def _partials(self, a, w):
         """Split-K partial sums of a @ w.T in the workspace; returns (workspace, splits)."""
         M, K = a.shape
@@ -329,69 +256,36 @@ class NativeBackend:
                     "linear_tc_partials")
         return ws, splits.value
 
-    def linear_swiglu(self, a, w, gu_buf, out, row_scale=None):
+    def linear_swiglu(self, a, w, gu_buf, out):
         self._on_gpu(a, w, out)
         M, K = a.shape
         N = w.shape[0]
         if self._tc_ok(a, w, out):
-            if row_scale is not None and M <= 128:
-                sumsq, eps = row_scale
-                self._check(self.lib.hfb_linear_tc_swiglu_scaled(_p(a), _p(w), _p(out), c_int(_dt(out)), c_int(M), c_int(N),
-                                                                 c_int(K), _p(sumsq), c_int(sumsq.shape[0]), c_float(eps),
-                                                                 self._stream()), "linear_tc_swiglu_scaled")
-                return
-            if row_scale is not None:
-                self.scale_rows(a, *row_scale)
             self._check(self.lib.hfb_linear_tc_swiglu(_p(a), _p(w), _p(out), c_int(_dt(out)), c_int(M), c_int(N), c_int(K),
                                                       self._stream()), "linear_tc_swiglu")
             return
-        if row_scale is not None:
-            self.scale_rows(a, *row_scale)
         self.linear(a, w, None, gu_buf, False)
         self.swiglu(gu_buf, out, True)
 
-    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out, defer=False):
+    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out):
         self._on_gpu(a, w, bias, residual, norm_w, xn_out)
         M, K = a.shape
         N = w.shape[0]
-        if self._fused_ok(a, w, residual) and (xn_out is None or (defer and xn_out.dtype == torch.bfloat16 and N % 8 == 0)):
-            done = self._residual_y(a, w, bias, residual, norm_w, eps, xn_out)
-            if done is not False:
-                return None if done is True else done
         part = self._partials(a, w) if self._tc_ok(a, w) else None
         if part is None:
             self.linear(a, w, bias, residual, True)
             if xn_out is not None:
                 self.rmsnorm(residual, norm_w, eps, xn_out, None)
-            return None
+            return
         ws, splits = part
         self._check(self.lib.hfb_reduce_residual_norm(
             _p(ws), c_int(splits), c_int(M), c_int(N), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(residual),
             _p(norm_w), c_int(_dt(norm_w) if norm_w is not None else 0), c_float(eps), _p(xn_out),
             c_int(_dt(xn_out) if xn_out is not None else 0), self._stream()), "reduce_residual_norm")
-        return None
 
-    def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d,
-                       row_scale=None):
+    def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
         self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
         M, K = a.shape
-        cache_slots = k_cache.shape[0] * k_cache.shape[1]
-        npos = cos_sin.shape[0] if cos_sin is not None else 0
-        if (self._fused_ok(a, w) and 128 % d == 0 and d % 4 == 0 and n_rot % 8 == 0 and w.shape[0] % 4 == 0
-                and (bias is None or bias.data_ptr() % 16 == 0)):
-            bufs = self._fused_buffers(a, w)
-            if bufs is not None:
-                ws, _, counters = bufs
-                sumsq, eps = row_scale if row_scale is not None else (None, 0.0)
-                self._check(self.lib.hfb_linear_tc_rope_kv(
-                    _p(a), _p(w), _p(bias), c_int(_dt(bias) if bias is not None else 0), _p(sumsq),
-                    c_int(sumsq.shape[0] if sumsq is not None else 0), c_float(eps), _p(cos_sin), c_int(n_rot), c_int(npos),
-                    _p(positions), _p(slots), _p(q_out), _p(k_cache), _p(v_cache), c_int64(cache_slots), c_int(_dt(q_out)),
-                    c_int(M), c_int(H), c_int(G), c_int(d), c_int(K), _p(ws), ctypes.c_size_t(ws.numel()), _p(counters),
-                    c_int(counters.numel()), self._stream()), "linear_tc_rope_kv")
-                return
-        if row_scale is not None:
-            self.scale_rows(a, *row_scale)
         part = self._partials(a, w) if self._tc_ok(a, w) else None
         if part is None:
             self.linear(a, w, bias, qkv_buf, False)

@@ -106,15 +106,10 @@ class Model:
         for i, e in enumerate(schedule):
             layer = self.layers[e.layer]
             owner = i if e.cache_of is None else e.cache_of
-            nxt = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+            next_norm = self.layers[schedule[i + 1].layer].norm1 if i + 1 < len(schedule) else None
             xn = layer.block.forward(ctx, x, layer.norm1, layer.mixer, layer.norm2, layer.ffn,
                                      ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None,
-                                     xn_ready=xn, next_norm=nxt.norm1 if nxt else None,
-                                     next_mixer=nxt.mixer if nxt else None)
-        from .. import kernels
-        b = kernels.backend()
-        if hasattr(b, "join_side"):
-            b.join_side()
+                                     xn_ready=xn, next_norm=next_norm)
         M = ctx.num_logit_rows
         if M == 0:
             return None

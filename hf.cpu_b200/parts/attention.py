@@ -16,12 +16,11 @@ import torch
 from .. import kernels
 from ..config.base import UnsupportedError
 from ..weights.loader import TensorSpec, fused_rows
-from .base import CacheSpec, Mixer, ScaledRows, register_part
+from .base import CacheSpec, Mixer, register_part
 
 
 class PagedAttention(Mixer):
     graph_safe = True
-    takes_row_scale = True          # the q|k|v product applies an RMSNorm's row factor to its accumulators
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, out_bias: bool, window: int, position, prefix: str,
@@ -94,7 +93,6 @@ class PagedAttention(Mixer):
         return 2.0 * T * (self.w_qkv.numel() + self.w_o.numel()) + 4.0 * self.QD * seen
 
     def _attend(self, ctx, xn, cache, write_cache):
-        xn, row_scale = ScaledRows.unpack(xn)
         T = xn.shape[0]
         qkv = ctx.buf("attn_qkv", (T, self.QD + 2 * self.KD), xn.dtype)
         q = ctx.buf("attn_q", (T, self.QD), xn.dtype)
@@ -103,8 +101,7 @@ class PagedAttention(Mixer):
         n_rot = self.rotary.n_rot if self.rotary is not None else 0
         with kernels.phase("qkv"):
             kernels.linear_rope_kv(xn, self.w_qkv, self.b_qkv, qkv, cos_sin, n_rot, ctx.positions,
-                                   meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d,
-                                   row_scale=row_scale)
+                                   meta.slots if write_cache else None, q, cache.k, cache.v, self.H, self.G, self.d)
         att = ctx.buf("attn_out", (T, self.QD), xn.dtype)
         with kernels.phase("attn"):
             kernels.paged_attention(q, cache.k, cache.v, meta, ctx, self.H, self.G, self.d,
@@ -116,15 +113,15 @@ class PagedAttention(Mixer):
         with kernels.phase("wo"):
             kernels.linear(att, self.w_o, self.b_o, residual, accumulate=True)
 
-    def forward_then_norm(self, ctx, xn, residual, cache, state, write_cache, norm, out, defer=False):
+    def forward_then_norm(self, ctx, xn, residual, cache, state, write_cache, norm, out):
         args = norm.fused_args()
         if args is None:
             self.forward(ctx, xn, residual, cache, state, write_cache)
             return False
         att = self._attend(ctx, xn, cache, write_cache)
         with kernels.phase("wo"):
-            sumsq = kernels.linear_residual_norm(att, self.w_o, self.b_o, residual, args[0], args[1], out, defer=defer)
-        return True if sumsq is None else ScaledRows(out, sumsq, args[1])
+            kernels.linear_residual_norm(att, self.w_o, self.b_o, residual, args[0], args[1], out)
+        return True
 
 
 register_part("mixer", "paged_attention", PagedAttention)

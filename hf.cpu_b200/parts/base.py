@@ -58,24 +58,6 @@ class StateSpec:
     dtype: torch.dtype = torch.float32
 
 
-class ScaledRows:
-    """Rows of an RMSNorm that still lack their row factor: ``tensor`` [T, E] holds ``x * w``, ``sumsq`` [parts, T]
-    float32 partial sums of ``x^2`` per row (to be added in order), and the rows are to be multiplied by
-    ``rsqrt(sum / E + eps)``.  A product is linear in its rows, so the part that consumes them can apply the factor to
-    its accumulators.  Only parts that declare ``takes_row_scale = True`` are ever handed one."""
-    __slots__ = ("tensor", "sumsq", "eps")
-
-    def __init__(self, tensor: torch.Tensor, sumsq: torch.Tensor, eps: float):
-        self.tensor, self.sumsq, self.eps = tensor, sumsq, float(eps)
-
-    @staticmethod
-    def unpack(xn):
-        """(tensor, (sumsq, eps) or None) of a plain tensor or a ScaledRows."""
-        if isinstance(xn, ScaledRows):
-            return xn.tensor, (xn.sumsq, xn.eps)
-        return xn, None
-
-
 class Part:
     # True when forward() only launches kernels on tensors at stable addresses and reads nothing of the step
     # on the host, so that a decode step may be captured once as a CUDA graph and replayed
@@ -141,10 +123,8 @@ class Mixer(Part):
         the entry reads another entry's cache."""
         raise NotImplementedError
 
-    # Optional: ``forward_then_norm(ctx, xn, residual, cache, state, write_cache, norm, out, defer=False)`` does the
-    # same and, if it returns True, has also written ``out = norm(residual)`` (the block then skips that norm); with
-    # ``defer`` it may return a :class:`ScaledRows` over ``out`` instead, leaving the row factor to the consumer.
-    # Optional: ``takes_row_scale = True``: ``xn`` may be a :class:`ScaledRows`.
+    # Optional: ``forward_then_norm(ctx, xn, residual, cache, state, write_cache, norm, out) -> bool`` does the same
+    # and, if it returns True, has also written ``out = norm(residual)`` (the block then skips that norm).
 
 
 class FeedForward(Part):
@@ -152,15 +132,14 @@ class FeedForward(Part):
         """Token-wise transform of ``xn`` added into the float32 ``residual``."""
         raise NotImplementedError
 
-    # Optional: ``forward_then_norm(ctx, xn, residual, norm, out, defer=False)`` and ``takes_row_scale``, as for mixers.
+    # Optional: ``forward_then_norm(ctx, xn, residual, norm, out) -> bool``, as for mixers.
 
 
 class Block(Part):
     def forward(self, ctx, x: torch.Tensor, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward,
-                cache, state, write_cache: bool, xn_ready=None, next_norm: Optional[Norm] = None,
-                next_mixer: Optional[Mixer] = None):
+                cache, state, write_cache: bool, xn_ready: Optional[torch.Tensor] = None,
+                next_norm: Optional[Norm] = None) -> Optional[torch.Tensor]:
         """Run one layer on the float32 residual stream ``x`` in place.  ``xn_ready`` is ``norm1(x)`` if the
         previous block already computed it.  If ``next_norm`` is given the block may return ``next_norm(x)`` of
-        its result (computed in the tail of its last product), as a tensor, or as a :class:`ScaledRows` when
-        ``next_mixer`` (which will consume it) takes those; returning None leaves that norm to the next block."""
+        its result (computed in the tail of its last product); returning None leaves that norm to the next block."""
         raise NotImplementedError

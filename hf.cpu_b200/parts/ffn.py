@@ -8,12 +8,11 @@ import torch
 
 from .. import kernels
 from ..weights.loader import TensorSpec, fused_rows
-from .base import FeedForward, ScaledRows, register_part
+from .base import FeedForward, register_part
 
 
 class SwiGlu(FeedForward):
     graph_safe = True
-    takes_row_scale = True          # the gate|up product applies an RMSNorm's row factor to its accumulators
 
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str, names=None, **_):
         self.E, self.F = int(hidden_size), int(intermediate_size)
@@ -38,12 +37,11 @@ class SwiGlu(FeedForward):
         return 2.0 * rows * (self.w_gate_up.numel() + self.w_down.numel())
 
     def _hidden(self, ctx, xn):
-        xn, row_scale = ScaledRows.unpack(xn)
         T = xn.shape[0]
         gu = ctx.buf("ffn_gate_up", (T, 2 * self.F), xn.dtype)
         h = ctx.buf("ffn_h", (T, self.F), xn.dtype)
         with kernels.phase("gate_up"):
-            kernels.linear_swiglu(xn, self.w_gate_up, gu, h, row_scale=row_scale)
+            kernels.linear_swiglu(xn, self.w_gate_up, gu, h)
         return h
 
     def forward(self, ctx, xn, residual):
@@ -51,15 +49,15 @@ class SwiGlu(FeedForward):
         with kernels.phase("down"):
             kernels.linear(h, self.w_down, None, residual, accumulate=True)
 
-    def forward_then_norm(self, ctx, xn, residual, norm, out, defer=False):
+    def forward_then_norm(self, ctx, xn, residual, norm, out):
         args = norm.fused_args()
         if args is None:
             self.forward(ctx, xn, residual)
             return False
         h = self._hidden(ctx, xn)
         with kernels.phase("down"):
-            sumsq = kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out, defer=defer)
-        return True if sumsq is None else ScaledRows(out, sumsq, args[1])
+            kernels.linear_residual_norm(h, self.w_down, None, residual, args[0], args[1], out)
+        return True
 
 
 register_part("ffn", "swiglu", SwiGlu)

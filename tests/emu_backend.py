@@ -80,29 +80,16 @@ class EmuBackend:
             g, u = gu[:, :F].float(), gu[:, F:].float()
         out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
 
-    @staticmethod
-    def _scaled(a, row_scale):
-        if row_scale is None:
-            return a
-        sumsq, eps = row_scale
-        return a.float() * (1.0 / torch.sqrt(sumsq.sum(0) / a.shape[1] + eps))[:, None]
-
-    def scale_rows(self, a, sumsq, eps):
-        a.copy_(self._scaled(a, (sumsq, eps)).to(a.dtype))
-
-    def linear_swiglu(self, a, w, gu_buf, out, row_scale=None):
-        self.linear(self._scaled(a, row_scale), w, None, gu_buf, False)
+    def linear_swiglu(self, a, w, gu_buf, out):
+        self.linear(a, w, None, gu_buf, False)
         self.swiglu(gu_buf, out, True)
 
-    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out, defer=False):
+    def linear_residual_norm(self, a, w, bias, residual, norm_w, eps, xn_out):
         self.linear(a, w, bias, residual, True)
         if xn_out is not None:
             self.rmsnorm(residual, norm_w, eps, xn_out, None)
-        return None
 
-    def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d,
-                       row_scale=None):
-        a = self._scaled(a, row_scale)
+    def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
         self.linear(a, w, bias, qkv_buf, False)
         self.rope_kv_write(qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d)
 

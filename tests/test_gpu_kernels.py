@@ -452,3 +452,30 @@ def test_attention_long_context_far_keys(lens_q, both_tc_forms):
         assert rel(row, ref.view(-1, H, d)[t].float()) < TOL["bfloat16"]
     from hfcpu_b200 import kernels
     kernels.check_device_errors()
+
+
+@pytest.mark.parametrize("geom", [(28, 4, 128, 16), (14, 2, 64, 16), (8, 2, 128, 32), (16, 1, 64, 8)])
+def test_decode_attention_merges_its_own_splits(geom):
+    """The decode kernel with the keys split over CTAs: merged by the CTA that stores a tile's last split, it gives
+    what the separate merge kernel gives, in one launch, and leaves its counters at zero."""
+    from hfcpu_b200 import kernels
+    H, G, d, bs = geom
+    b = kernels.backend()
+    for lens_kv in ([1, 64, 65, 1000, 2311], [2048] * 8, [700]):
+        lens_q = [1] * len(lens_kv)
+        for window in (0, 300):
+            case = _with_tiles(_attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window), lens_q, lens_kv, H, G)
+            ref = _run_attention(EmuBackend(), case, H, G, d, window)
+            before = b.launches
+            out = _run_attention(native(), case, H, G, d, window)
+            assert b.launches - before == 1, "one kernel, no separate merge"
+            again = _run_attention(native(), case, H, G, d, window)
+            b.merge_in_kernel = False
+            try:
+                apart = _run_attention(native(), case, H, G, d, window)
+            finally:
+                b.merge_in_kernel = True
+            assert torch.equal(out, again) and rel(out.float(), ref.float()) < 3e-2
+            assert rel(out.float(), apart.float()) < 1e-2
+            assert int(b._counters.abs().sum()) == 0
+    kernels.check_device_errors()
