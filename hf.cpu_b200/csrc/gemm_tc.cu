@@ -490,16 +490,26 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     cluster_barrier();                                       // both CTAs' barriers exist before either is signalled
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_sync();
 
     const int pairs = gridDim.x >> 1, pair = blockIdx.x >> 1;
     const int per_split = p.tiles_x * p.tiles_y;             // tiles_x counts tiles of 256 tokens here
     const int total_items = per_split * p.splits;
 
     if (warp == 0) {
+        // The weights do not depend on the kernel before this one: their tiles of the first STAGES k blocks are
+        // requested before the wait for it, the activation tiles of those blocks right after.  (The other lanes of
+        // the warp do not wait: a lane in griddepcontrol.wait would hold up the requesting lane with it.)
         if (lane == 0) {
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = true, dep_ready = false;
+            int pend_n = 0, pend_kb[STAGES], pend_row[STAGES];
+            auto flush = [&]() {
+                pdl_sync();
+                for (int i = 0; i < pend_n; i++)
+                    tma_load_2d_pair(sx + i * X_BYTES, &map_x, pend_kb[i] * BK, pend_row[i], map_to_rank(full0 + 8 * i, 0));
+                pend_n = 0;
+                dep_ready = true;
+            };
             for (int item = pair; item < total_items && ok; item += pairs) {
                 const int split = item / per_split, t = item % per_split;
                 const int tx = t % p.tiles_x, ty = t / p.tiles_x;
@@ -507,13 +517,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
+                    if (!dep_ready && it >= STAGES) flush();
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
                     if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * (X_BYTES + Y_BYTES));
                     const uint32_t full_leader = map_to_rank(full0 + 8 * s, 0);
-                    tma_load_2d_pair(sx + s * X_BYTES, &map_x, kb * BK, tx * 256 + (int)rank * TILE_X, full_leader);
                     tma_load_2d_pair(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN + (int)rank * (BN / 2), full_leader);
+                    const int row = tx * 256 + (int)rank * TILE_X;
+                    if (dep_ready) tma_load_2d_pair(sx + s * X_BYTES, &map_x, kb * BK, row, full_leader);
+                    else { pend_kb[pend_n] = kb; pend_row[pend_n] = row; pend_n++; }       // (stage pend_n: the first round)
                 }
             }
+            if (!dep_ready) flush();
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
@@ -552,6 +566,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         const int row = q * 32 + lane;
         uint32_t tile_it = 0;
         bool ok = true;
+        pdl_sync();                                          // nothing is written before the kernel in front has finished
         for (int item = pair; item < total_items && ok; item += pairs, tile_it++) {
             const int split = item / per_split, t = item % per_split;
             const int tx = t % p.tiles_x, ty = t / p.tiles_x;
