@@ -211,6 +211,36 @@ def time_decode(engine, batch, steps, warmup, vocab, seed, sampler=None):
     return ms, ctx_mid, launches
 
 
+def print_timeline(args, engine, vocab):
+    """One decode step of the batch (after seven warm ones), or one prompt of PROMPT tokens, kernel by kernel."""
+    import torch
+    from hfcpu_b200 import StepEntry, kernels
+    from hfcpu_b200.kernels import timeline
+    if args.timeline == "decode":
+        tag = "tl"
+        toks = prefill_requests(engine, synthetic_prompts(args.batch, PROMPT, vocab, 1), tag)
+        out = torch.empty(args.batch, dtype=torch.int32, device=engine.device)
+        for s in range(8):
+            if s == 7:
+                torch.cuda.synchronize()
+                timeline.start()
+            logits = engine.step([StepEntry((tag, b), [toks[b]], [0]) for b in range(args.batch)])
+            kernels.argmax(logits, out)
+            toks = out.tolist()
+    else:
+        for i, ids in enumerate(synthetic_prompts(3, PROMPT, vocab, 5)):
+            engine.add_request(("tl", i))
+            if i == 2:
+                torch.cuda.synchronize()
+                timeline.start()
+            engine.step([StepEntry(("tl", i), ids, [PROMPT - 1])])
+            torch.cuda.synchronize()
+            engine.finish_request(("tl", i))
+    records = timeline.take()
+    print(timeline.format_marks(records) if args.marks else timeline.format_rows(timeline.kernels(records)))
+    return 0
+
+
 def main():
     global PROMPT, CTX_MAX
     ap = argparse.ArgumentParser()
@@ -222,6 +252,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt length (the record uses 2,048; others are for profiling)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
+    ap.add_argument("--timeline", choices=["decode", "prefill"], help="print the kernel timeline of one step instead of the "
+                    "record (needs a library built with HFB_NVCC_EXTRA=-DHFB_TRACE; see hfcpu_b200/kernels/timeline.py)")
+    ap.add_argument("--marks", action="store_true", help="with --timeline: every logged mark, not one row per kernel")
     ap.add_argument("--ref-layers", type=int, default=4, help="layers the reference arm runs (it is a CPU program)")
     ap.add_argument("--ref-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = ap.parse_args()
@@ -255,6 +288,8 @@ def main():
     pages = max_b * ((PROMPT + warmup + args.steps + 64 + BLOCK - 1) // BLOCK + 1)
     engine = hfcpu_b200.Engine(model, block_size=BLOCK, num_pages=pages, max_requests=max_b, ctx_max=CTX_MAX)
     pk, pk_src = measure.load_peaks(ROOT)
+    if args.timeline:
+        return print_timeline(args, engine, V)
 
     # ---- prefill: one prompt of 2,048 tokens, eight times over; the median of the last six ----------------
     pre_ms = []
