@@ -11,9 +11,10 @@
 // Above 128 tokens the inner dimension is split as well when the output has few tiles and K is long (mid_splits).
 // Pipeline per CTA (persistent over work items): warp 0 issues TMA loads of 128-byte-swizzled K
 // blocks into a ring of shared-memory stages (the weights of the first round before the kernel in front has finished,
-// warp 6 the activations of that round as soon as it has); warp 1 issues tcgen05.mma from shared memory into one
-// of two TMEM accumulators and commits to the stage's "empty" barrier; warps 2..5 read a finished
-// accumulator with tcgen05.ld, apply the epilogue and store, while the next tile's products run.
+// warp 10 the activations of that round as soon as it has); warp 1 issues tcgen05.mma from shared memory into one
+// of two TMEM accumulators and commits to the stage's "empty" barrier; warps 2..9 read a finished
+// accumulator with tcgen05.ld (two warps per quarter of its lanes, half of the columns each), apply the epilogue and
+// store, while the next tile's products run.
 // Every barrier wait has a time limit: on expiry the kernel raises HFB_ERR_WAIT in the device error
 // word, lets its copies land, frees its TMEM and returns.
 //
@@ -38,7 +39,8 @@ constexpr int BK = 64;                 // bf16 elements per K block: 128 bytes, 
 constexpr int UMMA_K = 16;
 constexpr int TILE_X = 128;            // accumulator rows (TMEM lanes)
 constexpr uint32_t X_BYTES = TILE_X * BK * 2;
-constexpr int GEMM_THREADS = 224;            // TMA warp, MMA warp, four epilogue warps, the warp for the first activation tiles
+constexpr int GEMM_THREADS = 352;            // TMA warp, MMA warp, eight epilogue warps, the warp for the first activation tiles
+constexpr int HELPER_WARP = 10;
 constexpr int PAIR_THREADS = 192;            // (the pair kernel has no such warp)
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
@@ -247,7 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 8); }       // eight epilogue warps
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -270,7 +272,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // ---- producer: TMA loads --------------------------------------------------------------
         // The weights do not depend on the kernel before this one, the activations do.  One lane requests the weight
         // tiles of the first STAGES k blocks at once, long before that kernel has finished; the activation tiles of
-        // those blocks are requested by the seventh warp the moment it has (both count on the stage's "full" barrier,
+        // those blocks are requested by the last warp the moment it has (both count on the stage's "full" barrier,
         // whose phase ends when the armed byte count has arrived, in whichever order).  From the second round on the
         // producer has waited too and requests both.  The other lanes of this warp do nothing: a lane that sat in
         // griddepcontrol.wait would hold up its whole warp, the requesting lane with it.
@@ -297,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
             if (!dep_ready) pdl_sync();
         }
-    } else if (warp == 6) {
+    } else if (warp == HELPER_WARP) {
         // ---- the activation tiles of the first STAGES k blocks, as soon as the kernel in front has finished ----
         pdl_sync();
         if (lane == 0) {
@@ -349,8 +351,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else {
         // ---- epilogue: TMEM -> registers -> global ------------------------------------------------
+        // Warps 2..5 and 6..9: two warps for each quarter of the TMEM lanes (a warp may read the quarter its index
+        // names), each with half of the accumulator's columns, so that a tile's last, exposed epilogue takes half the time.
         const int q = warp & 3;                       // the TMEM lane quarter this warp may read
         const int row = q * 32 + lane;
+        constexpr int C_STEP = BN >= 32 ? 32 : 16;
+        constexpr int C_SPLIT = BN >= 64 ? ((BN / 32 + 1) / 2) * 32 : BN;
+        const int c_lo = warp >= 6 ? C_SPLIT : 0, c_hi = warp >= 6 ? BN : C_SPLIT;
         uint32_t tile_it = 0;
         bool ok = true;
         // With few tokens the first turn of this loop is a rehearsal: it reads whatever the accumulator holds and
@@ -369,9 +376,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
             const int xr = tx * TILE_X + row;         // row of X this thread holds
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += (BN >= 32 ? 32 : 16)) {
-                uint32_t v[BN >= 32 ? 32 : 16];
-                const bool two = BN >= 32 && c0 + 16 < BN;       // widths such as 208 end on a single chunk
+            for (int c0 = c_lo; c0 < c_hi; c0 += C_STEP) {
+                uint32_t v[C_STEP];
+                const bool two = BN >= 32 && c0 + 16 < c_hi;     // widths such as 208 end on a single chunk
                 tmem_ld16(taddr + c0, v);
                 if (two) tmem_ld16(taddr + c0 + 16, v + (BN >= 32 ? 16 : 0));
                 tmem_wait_ld();
