@@ -255,7 +255,7 @@ def main():
     ap.add_argument("--timeline", choices=["decode", "prefill"], help="print the kernel timeline of one step instead of the "
                     "record (needs a library built with HFB_NVCC_EXTRA=-DHFB_TRACE; see hfcpu_b200/kernels/timeline.py)")
     ap.add_argument("--marks", action="store_true", help="with --timeline: every logged mark, not one row per kernel")
-    ap.add_argument("--ref-layers", type=int, default=4, help="layers the reference arm runs (it is a CPU program)")
+    ap.add_argument("--ref-layers", type=int, default=28, help="layers the reference arm runs (it is a CPU program)")
     ap.add_argument("--ref-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = ap.parse_args()
     if args.prompt != PROMPT:

@@ -1,4 +1,4 @@
-// Temperature sampling with top-k, min-p and top-p on the device, one block per row of logits.
+// Temperature sampling with top-k, min-p and top-p on the device: a thread-block cluster of eight CTAs per row of logits.
 //
 // Order of operations as the reference's sampler (src/sample.c:66-116): candidates in the order
 // (logit descending, id ascending); cut to top-k; p = exp((l - max)/temp) / sum; min-p keeps

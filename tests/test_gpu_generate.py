@@ -39,12 +39,33 @@ def test_sampled_generation_survives_preemption(tiny_folders):
     assert [c[0].tokens for c in roomy] == [c[0].tokens for c in tight]
 
 
-def test_bfloat16_generation_runs(tiny_folders):
+def test_bfloat16_generation_follows_plain(tiny_folders):
+    """Greedy generation in bfloat16 through the entry point gives the plain implementation's tokens (evaluated on the
+    same bfloat16-stored weights) up to the first position where the plain logits hold a near-tie; sampled requests
+    beside them run to their limit and are the same from run to run."""
     import hfcpu_b200
-    sess = hfcpu_b200.Session(tiny_folders["B16"], dtype="bfloat16", kv_block=8, kv_pages=128, max_seqs=4)
-    prompts = list(make_requests("B", [19, 130], seed=2).values())
-    out = sess.generate(prompts, temp=0.7, seed=1, max_tokens=16, n=2)
-    assert all(len(c.tokens) == 16 and c.stop == "length" for comps in out for c in comps)
+    folder = tiny_folders["B16"]
+    prompts = list(make_requests("B", [19, 130, 64], seed=2).values())
+    sess = hfcpu_b200.Session(folder, dtype="bfloat16", kv_block=8, kv_pages=128, max_seqs=4)
+    out = sess.generate(prompts, temp=0, max_tokens=16)
+    cfg, W = plain.read_folder(folder)
+    exact = 0
+    for p, comps in zip(prompts, out):
+        got, want = comps[0].tokens, plain.greedy(cfg, W, p, 16)
+        assert len(got) == 16 and comps[0].stop == "length"
+        if got == want:
+            exact += 1
+            continue
+        i = next(k for k in range(16) if got[k] != want[k])
+        row = plain.forward(cfg, W, p + want[:i])[-1]
+        gap = float(row[want[i]] - row[got[i]]) / float(row.abs().max())
+        assert 0 <= gap < 3e-2, f"token {i}: plain prefers {want[i]} over {got[i]} by {gap:.3g} of the logits' range"
+    assert exact >= 1
+    a = sess.generate(prompts[:2], temp=0.7, seed=1, max_tokens=16, n=2)
+    b = hfcpu_b200.Session(folder, dtype="bfloat16", kv_block=8, kv_pages=128, max_seqs=4).generate(
+        prompts[:2], temp=0.7, seed=1, max_tokens=16, n=2)
+    assert all(len(c.tokens) == 16 and c.stop == "length" for comps in a for c in comps)
+    assert [[c.tokens for c in comps] for comps in a] == [[c.tokens for c in comps] for comps in b]
 
 
 def test_command_line_generate(tiny_folders):

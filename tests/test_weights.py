@@ -230,3 +230,19 @@ def test_tensors_are_made_one_at_a_time_and_shared_ones_once(tmp_path, emu):
     assert torch.equal(att.w_qkv, torch.cat([src[p + f"self_attn.{x}_proj.weight"] for x in "qkv"]))
     g, u = src[p + "mlp.gate_proj.weight"], src[p + "mlp.up_proj.weight"]
     assert torch.equal(model.layers[0].ffn.w_gate_up, torch.stack([g, u], 1).reshape(352, 64))
+
+
+def test_tensor_core_product_refuses_a_misaligned_bias_before_launching():
+    """The many-token epilogue reads the bias sixteen bytes at a time: a bias (or operand) that is not 16-byte aligned is
+    answered HFB_ENOTSUP from the argument check, before anything touches a GPU (none is needed for this test)."""
+    import ctypes
+    from ctypes import c_int, c_size_t, c_void_p
+    from hfcpu_b200.kernels import build
+    lib = ctypes.CDLL(build.build())
+    lib.hfb_last_error.restype = ctypes.c_char_p
+    args = lambda bias, a=4096: (c_void_p(a), c_void_p(8192), c_void_p(bias), c_int(1), c_void_p(16384), c_int(1), c_int(0),
+                                 c_int(256), c_int(64), c_int(64), c_void_p(0), c_size_t(0), c_void_p(0))
+    for bias in (2, 4, 8):
+        assert lib.hfb_linear_tc(*args(bias)) == 2 and b"aligned" in lib.hfb_last_error()
+        assert lib.hfb_linear_tc_noalloc(*args(bias)[:10], c_void_p(0)) == 2
+    assert lib.hfb_linear_tc(*args(32, a=4098)) == 2
