@@ -94,6 +94,17 @@ __device__ __forceinline__ void trace_any(int kind)
         if (i < HFB_TRACE_CAP) { log[2 + 2 * i] = (unsigned)kind; log[3 + 2 * i] = t; }
     }
 }
+// (developers) "ready" from the calling thread of block 0, for kernels whose thread 0 does not wait for the predecessor
+__device__ __forceinline__ void trace_ready_here()
+{
+    unsigned long long *log = g_trace_ptr;
+    if (log && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        unsigned long long i = atomicAdd(log, 1ull);
+        if (i < HFB_TRACE_CAP) { log[2 + 2 * i] = 1ull; log[3 + 2 * i] = t; }
+    }
+}
 void trace_register(void (*setter)(void *));
 static void trace_set_ptr(void *p) { cudaMemcpyToSymbol(g_trace_ptr, &p, sizeof p); }
 namespace { struct TraceRegistration { TraceRegistration() { trace_register(trace_set_ptr); } } g_trace_registration; }
@@ -101,7 +112,9 @@ namespace { struct TraceRegistration { TraceRegistration() { trace_register(trac
 #define HFB_TRACE_READY() trace_log(0, 1)
 #define HFB_TRACE_MARK(k) trace_log(0, k)
 #define HFB_TRACE_ANY(k) trace_any(k)
+#define HFB_TRACE_READY_HERE() trace_ready_here()
 #else
+#define HFB_TRACE_READY_HERE()
 #define HFB_TRACE_ANY(k)
 #define HFB_TRACE_ENTRY(id)
 #define HFB_TRACE_READY()

@@ -97,6 +97,50 @@ __global__ void rmsnorm_vec_kernel(const float *x, const TW *w, float eps, TO *o
     }
 }
 
+// The same for rows of up to 256 * 4 * PER values: a thread keeps its part of the row in registers between the sum of
+// squares and the scaling, so the row is read once and all of a thread's reads are under way together.
+template <typename TW, typename TO, int PER>
+__global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const float *x, const TW *w, float eps, TO *out, const int32_t *rows, int E)
+{
+    HFB_TRACE_ENTRY(6);
+    pdl_sync();
+    const int m = blockIdx.x;
+    const float4 *xr = (const float4 *)(x + (size_t)(rows ? rows[m] : m) * E);
+    const int E4 = E >> 2;
+    float4 v[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * 256;
+        v[j] = i < E4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < PER; j++) ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    __shared__ float part[8];
+    ss = warp_sum(ss);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += part[i];              // (every thread adds the eight sums in the same order)
+    const float r = 1.0f / sqrtf(total / (float)E + eps);
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < E4) {
+            const float w0 = to_f32(w[4 * i]), w1 = to_f32(w[4 * i + 1]), w2 = to_f32(w[4 * i + 2]), w3 = to_f32(w[4 * i + 3]);
+            const float y0 = (v[j].x * r) * w0, y1 = (v[j].y * r) * w1, y2 = (v[j].z * r) * w2, y3 = (v[j].w * r) * w3;
+            TO *o = out + (size_t)m * E + 4 * i;
+            if (sizeof(TO) == 4) *(float4 *)o = make_float4(y0, y1, y2, y3);
+            else {
+                __nv_bfloat162 a = __floats2bfloat162_rn(y0, y1), b = __floats2bfloat162_rn(y2, y3);
+                *(uint2 *)o = make_uint2(*(uint32_t *)&a, *(uint32_t *)&b);
+            }
+        }
+    }
+}
+
 // ---- rotary + cache write (src/model.c:587-601, :468-493) -------------------------------------
 // One block per (token, head of the fused q|k|v row).  Pairs (i, i + n_rot/2) rotate; the rest copies.
 template <typename T>
@@ -247,7 +291,14 @@ extern "C" int hfb_rmsnorm(const float *x, const void *w, int w_dt, float eps, v
     int threads = E >= 2048 ? 512 : (E >= 512 ? 256 : 128);
     cudaStream_t st = (cudaStream_t)s;
     const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)w & 15) == 0;
-    if ((E & 3) == 0 && aligned) {
+    if ((E & 3) == 0 && aligned && w_dt == HFB_BF16 && out_dt == HFB_BF16 && E <= 8192 && M >= 64) {
+        // many rows of the serving types: the row stays in registers
+        const __nv_bfloat16 *wb = (const __nv_bfloat16 *)w;
+        __nv_bfloat16 *ob = (__nv_bfloat16 *)out;
+        if (E <= 2048) g_launch_err = launch_pdl(rmsnorm_reg_kernel<__nv_bfloat16, __nv_bfloat16, 2>, dim3(M), dim3(256), 0, st, x, wb, eps, ob, rows, E);
+        else if (E <= 4096) g_launch_err = launch_pdl(rmsnorm_reg_kernel<__nv_bfloat16, __nv_bfloat16, 4>, dim3(M), dim3(256), 0, st, x, wb, eps, ob, rows, E);
+        else g_launch_err = launch_pdl(rmsnorm_reg_kernel<__nv_bfloat16, __nv_bfloat16, 8>, dim3(M), dim3(256), 0, st, x, wb, eps, ob, rows, E);
+    } else if ((E & 3) == 0 && aligned) {
         if (w_dt == HFB_F32 && out_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<float, float>, dim3(M), dim3(threads), 0, st, x, (const float *)w, eps, (float *)out, rows, E);
         else if (w_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<float, __nv_bfloat16>, dim3(M), dim3(threads), 0, st, x, (const float *)w, eps, (__nv_bfloat16 *)out, rows, E);
         else if (out_dt == HFB_F32) g_launch_err = launch_pdl(rmsnorm_vec_kernel<__nv_bfloat16, float>, dim3(M), dim3(threads), 0, st, x, (const __nv_bfloat16 *)w, eps, (float *)out, rows, E);

@@ -39,9 +39,10 @@ constexpr int BK = 64;                 // bf16 elements per K block: 128 bytes, 
 constexpr int UMMA_K = 16;
 constexpr int TILE_X = 128;            // accumulator rows (TMEM lanes)
 constexpr uint32_t X_BYTES = TILE_X * BK * 2;
-constexpr int GEMM_THREADS = 352;            // TMA warp, MMA warp, eight epilogue warps, the warp for the first activation tiles
+constexpr int GEMM_THREADS = 352;            // weight-tile warp, MMA warp, eight epilogue warps, activation-tile warp
 constexpr int HELPER_WARP = 10;
-constexpr int PAIR_THREADS = 192;            // (the pair kernel has no such warp)
+constexpr int PAIR_THREADS = 224;            // pair kernel: weight-tile warp, MMA warp, four epilogue warps, activation-tile warp
+constexpr int PAIR_ACT_WARP = 6;
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
 
@@ -268,17 +269,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int total_items = p.tiles_x * p.tiles_y * p.splits;
     const int per_split = p.tiles_x * p.tiles_y;
 
-    if (warp == 0) {
-        // ---- producer: TMA loads --------------------------------------------------------------
-        // The weights do not depend on the kernel before this one, the activations do.  One lane requests the weight
-        // tiles of the first STAGES k blocks at once, long before that kernel has finished; the activation tiles of
-        // those blocks are requested by the last warp the moment it has (both count on the stage's "full" barrier,
-        // whose phase ends when the armed byte count has arrived, in whichever order).  From the second round on the
-        // producer has waited too and requests both.  The other lanes of this warp do nothing: a lane that sat in
-        // griddepcontrol.wait would hold up its whole warp, the requesting lane with it.
+    if (warp == 0 || warp == HELPER_WARP) {
+        // ---- two requesting threads, one per operand -------------------------------------------------------------
+        // The weights do not depend on the kernel before this one, the activations do.  Lane 0 of warp 0 arms each
+        // stage's "full" barrier and asks for its weight tile, without ever waiting for that kernel: the first STAGES
+        // tiles are under way long before it has finished.  Lane 0 of the last warp waits for it and asks for the
+        // activation tiles (both copies count on the stage's barrier, whose phase ends when the armed bytes have
+        // arrived, in whichever order).  The other lanes of both warps do nothing: a lane in griddepcontrol.wait
+        // would hold up its whole warp.
+        const bool weights = warp == 0;
         if (lane == 0) {
+            if (!weights) { pdl_sync(); HFB_TRACE_READY_HERE(); }
             uint32_t it = 0;
-            bool ok = true, dep_ready = false;
+            bool ok = true;
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 int split = item / per_split, t = item % per_split;
                 int tx = t % p.tiles_x, ty = t / p.tiles_x;
@@ -286,31 +289,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 for (int kb = kb0; kb < kb1; kb++, it++) {
                     int s = it % STAGES;
                     uint32_t ph = (it / STAGES) & 1;
-                    if (!dep_ready && it >= STAGES) { pdl_sync(); dep_ready = true; }
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
-                    mbar_arrive_expect_tx(full0 + 8 * s, X_BYTES + Y_BYTES);
-                    if (p.swapped) tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
+                    if (weights) mbar_arrive_expect_tx(full0 + 8 * s, X_BYTES + Y_BYTES);
+                    if (weights == (p.swapped != 0)) tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
                     else tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * s);
-                    if (dep_ready) {
-                        if (p.swapped) tma_load_2d(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * s);
-                        else tma_load_2d(sx + s * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * s);
-                    }
-                }
-            }
-            if (!dep_ready) pdl_sync();
-        }
-    } else if (warp == HELPER_WARP) {
-        // ---- the activation tiles of the first STAGES k blocks, as soon as the kernel in front has finished ----
-        pdl_sync();
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int item = blockIdx.x; item < total_items && it < (uint32_t)STAGES; item += gridDim.x) {
-                int split = item / per_split, t = item % per_split;
-                int tx = t % p.tiles_x, ty = t / p.tiles_x;
-                int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.kb_total);
-                for (int kb = kb0; kb < kb1 && it < (uint32_t)STAGES; kb++, it++) {
-                    if (p.swapped) tma_load_2d(sy + it * Y_BYTES, &map_y, kb * BK, ty * BN, full0 + 8 * it);
-                    else tma_load_2d(sx + it * X_BYTES, &map_x, kb * BK, tx * TILE_X, full0 + 8 * it);
                 }
             }
         }
@@ -502,21 +484,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int per_split = p.tiles_x * p.tiles_y;             // tiles_x counts tiles of 256 tokens here
     const int total_items = per_split * p.splits;
 
-    if (warp == 0) {
-        // The weights do not depend on the kernel before this one: their tiles of the first STAGES k blocks are
-        // requested before the wait for it, the activation tiles of those blocks right after.  (The other lanes of
-        // the warp do not wait: a lane in griddepcontrol.wait would hold up the requesting lane with it.)
+    if (warp == 0 || warp == PAIR_ACT_WARP) {
+        // Two requesting threads, one per operand.  Lane 0 of warp 0 asks for this CTA's half of the weight tile and
+        // arms the stage's barrier; it never waits for the kernel in front, on which the weights do not depend, so the
+        // first STAGES tiles are under way long before that kernel ends.  Lane 0 of the last warp waits for it and
+        // then asks for the activation tiles.  Both copies count on the leader's "full" barrier, whose phase ends
+        // when the armed bytes have arrived, in whichever order.  (The other lanes of these warps do nothing: a lane
+        // in griddepcontrol.wait would hold up its whole warp.)
+        const bool weights = warp == 0;
         if (lane == 0) {
+            if (!weights) { pdl_sync(); HFB_TRACE_READY_HERE(); }
             uint32_t it = 0;
-            bool ok = true, dep_ready = false;
-            int pend_n = 0, pend_kb[STAGES], pend_row[STAGES];
-            auto flush = [&]() {
-                pdl_sync();
-                for (int i = 0; i < pend_n; i++)
-                    tma_load_2d_pair(sx + i * X_BYTES, &map_x, pend_kb[i] * BK, pend_row[i], map_to_rank(full0 + 8 * i, 0));
-                pend_n = 0;
-                dep_ready = true;
-            };
+            bool ok = true;
             for (int item = pair; item < total_items && ok; item += pairs) {
                 const int split = item / per_split, t = item % per_split;
                 const int tx = t % p.tiles_x, ty = t / p.tiles_x;
@@ -524,17 +503,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!dep_ready && it >= STAGES) flush();
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, err)) { ok = false; break; }
-                    if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * (X_BYTES + Y_BYTES));
                     const uint32_t full_leader = map_to_rank(full0 + 8 * s, 0);
-                    tma_load_2d_pair(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN + (int)rank * (BN / 2), full_leader);
-                    const int row = tx * 256 + (int)rank * TILE_X;
-                    if (dep_ready) tma_load_2d_pair(sx + s * X_BYTES, &map_x, kb * BK, row, full_leader);
-                    else { pend_kb[pend_n] = kb; pend_row[pend_n] = row; pend_n++; }       // (stage pend_n: the first round)
+                    if (weights) {
+                        if (rank == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * (X_BYTES + Y_BYTES));
+                        tma_load_2d_pair(sy + s * Y_BYTES, &map_y, kb * BK, ty * BN + (int)rank * (BN / 2), full_leader);
+                    } else {
+                        tma_load_2d_pair(sx + s * X_BYTES, &map_x, kb * BK, tx * 256 + (int)rank * TILE_X, full_leader);
+                    }
                 }
             }
-            if (!dep_ready) flush();
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {

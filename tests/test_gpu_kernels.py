@@ -66,6 +66,21 @@ def test_rmsnorm(dtype, E):
         assert rel(out.float(), ref.float()) < (1e-6 if dtype == "float32" else 1e-2)
 
 
+@pytest.mark.parametrize("E", [64, 1000, 3584, 5000, 8192, 8200])
+def test_rmsnorm_many_rows(E):
+    """From 64 rows on the bfloat16 form keeps a row in registers (up to 8,192 values): against float64."""
+    x = rnd(200, E, scale=3.0)
+    w = rnd(E, dtype=torch.bfloat16) + 1
+    rows = torch.arange(199, 99, -1, device=DEV, dtype=torch.int32)
+    for r in (None, rows):
+        src = x if r is None else x[r.long()]
+        out = torch.empty(src.shape[0], E, device=DEV, dtype=torch.bfloat16)
+        native().rmsnorm(x, w, 1e-6, out, r)
+        want = src.double() / torch.sqrt((src.double() ** 2).mean(-1, keepdim=True) + 1e-6) * w.double()
+        assert rel(out.double(), want) < 5e-3
+        assert torch.equal(out, want.float().to(torch.bfloat16)) or float((out.float() - want.float()).abs().max()) <= float(want.abs().max()) * 2 ** -7
+
+
 @pytest.mark.parametrize("shape", [(1, 50, 70), (5, 130, 64), (67, 1000, 192), (130, 96, 333), (300, 257, 1030)])
 @pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -236,7 +251,9 @@ TC_SHAPES = [(1, 128, 64), (1, 3584, 3584), (8, 4608, 3584), (8, 3584, 18944), (
              # from 256 rows on, pairs of CTAs share tiles of 256 rows (cta_group::2): edges of the pair's halves
              (256, 96, 64), (257, 136, 192), (384, 1000, 72), (511, 3000, 320), (1024, 208, 128), (640, 37888 // 8, 256),
              # a few hundred rows, few output tiles and a long inner dimension: split over K (one CTA, and pairs; ragged K)
-             (192, 512, 4096), (300, 256, 4168), (384, 520, 1096), (512, 3584, 18944)]
+             (192, 512, 4096), (300, 256, 4168), (384, 520, 1096), (512, 3584, 18944),
+             # the o product at 2,048 tokens; ragged in every dimension with pairs
+             (2048, 3584, 3584), (1100, 2000, 640), (768, 3000, 1096)]
 
 
 @pytest.mark.parametrize("shape", TC_SHAPES)
