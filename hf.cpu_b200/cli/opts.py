@@ -50,7 +50,8 @@ OPTIONS: List[Opt] = [
     Opt("ctx-step", SIZE, SESSION, 1024, "context growth increment in tokens", note="ignored"),
     Opt("ctx-max", SIZE, SESSION, 32768, "maximum context tokens"),
     Opt("max-record", SIZE, SESSION, 64 << 20, "largest accepted prompt or request line"),
-    Opt("batch", INT, SESSION, 64, "prefill tokens per step", 1, 4096),
+    Opt("batch", INT, SESSION, 0, "prefill tokens per step at most, 0 = as many as --max-batched-tokens allows (the "
+        "reference's default of 64 is a CPU's step; here a step of 64 tokens costs a prompt seven times the time)", 0, 4096),
     Opt("log-level", ENUM, SESSION, "info", "error | warn | info | debug", choices=("error", "warn", "info", "debug")),
     # engine options (no counterpart in the reference)
     Opt("dtype", ENUM, SESSION, "bf16", "bf16 | fp32 (fp32 = the whole model in true 32-bit)",

@@ -182,6 +182,10 @@ class NativeBackend:
                     hint = getattr(ctx, "decode_split_hint", max(1, ((ctx.max_kv_len + 63) // 64) // 2))
                     splits = max(1, min(self.decode_ctas_per_sm * self.sm_count // max(1, n_tiles * G), hint))
                     stages = self.decode_stages
+                else:
+                    # short portions over a long context (the end of a prompt, a prompt behind a shared prefix): few
+                    # tiles would each walk all the keys alone; their keys are split too, 256 to a CTA at least
+                    splits = max(1, min(2 * self.sm_count // max(1, n_tiles * G), ((ctx.max_kv_len + 63) // 64) // 4, 64))
                 need = self.lib.hfb_attention_fast_scratch(c_int(T), c_int(H), c_int(d), c_int(splits))
                 scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
                 if decode_tma:

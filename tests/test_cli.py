@@ -14,7 +14,7 @@ def test_option_forms_and_ranges():
     from hfcpu_b200.cli import opts as O
     d = O.defaults()
     assert d["temp"] == 0.8 and d["top_k"] == 40 and d["top_p"] == 0.95 and d["min_p"] == 0.05
-    assert d["max_tokens"] == 512 and d["batch"] == 64 and d["ctx_max"] == 32768 and d["record_sep"] == 0x1E
+    assert d["max_tokens"] == 512 and d["batch"] == 0 and d["ctx_max"] == 32768 and d["record_sep"] == 0x1E
     o = O.apply(d, ["--temp", "0.5", "--top-k=7", "--no-profile", "--profile", "--ctx-max", "4K", "--record-sep", "US"])
     assert o["temp"] == 0.5 and o["top_k"] == 7 and o["profile"] is True and o["ctx_max"] == 4096 and o["record_sep"] == 0x1F
     assert O.apply(d, ["--profile=false"])["profile"] is False

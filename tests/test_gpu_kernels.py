@@ -471,6 +471,26 @@ def test_attention_long_context_far_keys(lens_q, both_tc_forms):
     kernels.check_device_errors()
 
 
+@pytest.mark.parametrize("geom", [(28, 4, 128, 16), (14, 2, 64, 16), (40, 8, 128, 32), (6, 3, 64, 8)])
+def test_attention_short_portions_over_long_context(geom):
+    """Portions of 2 to 63 tokens behind thousands of cached keys (the end of a prompt, a prompt behind a shared
+    prefix) beside single tokens: their keys are split over CTAs and merged; one key far back made to stand out."""
+    from hfcpu_b200 import kernels
+    H, G, d, bs = geom
+    b = kernels.backend()
+    for lens_q, lens_kv in (([9], [3000]), ([2, 33, 1], [9000, 1500, 700]), ([63], [8200])):
+        for window, key_pos in ((0, 5), (0, lens_kv[0] - lens_q[0]), (300, lens_kv[0] - lens_q[0] - 250)):
+            case = _attention_case("bfloat16", H, G, d, bs, lens_q, lens_kv, window, spike=(0, key_pos, lens_q[0] - 1), seed=key_pos)
+            case = _with_tiles(case, lens_q, lens_kv, H, G)
+            before = b.launches
+            out = _run_attention(native(), case, H, G, d, window)
+            assert b.launches - before == 2, "the keys were split (attention and merge)"
+            ref = _run_attention(EmuBackend(), case, H, G, d, window)
+            assert rel(out.float(), ref.float()) < TOL["bfloat16"], (lens_q, window, key_pos)
+            assert torch.equal(out, _run_attention(native(), case, H, G, d, window)), "two calls differ"
+    kernels.check_device_errors()
+
+
 @pytest.mark.parametrize("geom", [(28, 4, 128, 16), (14, 2, 64, 16), (8, 2, 128, 32), (16, 1, 64, 8)])
 def test_decode_attention_merges_its_own_splits(geom):
     """The decode kernel with the keys split over CTAs: merged by the CTA that stores a tile's last split, it gives
