@@ -355,11 +355,11 @@ static int launch_decode_tma(const CUtensorMap &mk, const CUtensorMap &mv, const
     constexpr uint32_t TILE = (D / 64) * ABN * 128;
     constexpr int smem = 1024 + 2 * STAGES * TILE + 16 * D * 2 + 16 * STAGES + 16;
     static_assert(2 * STAGES * TILE >= (4 * 16 * (D + 2) + 96) * 4 && 2 * STAGES * TILE >= 32 * 64 * 4, "the merge reuses the tile buffers");
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};                 // (the opt-in is a property of the function on one device)
+    if (!configured[current_device()]) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, STAGES, ONE_MAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_decode: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        configured[current_device()] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles, p.G, p.splits);

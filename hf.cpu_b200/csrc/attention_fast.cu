@@ -249,11 +249,11 @@ template <int D, int WARPS, int STAGES>
 static int launch_attention(const AttnParams &p, int n_tiles, cudaStream_t st)
 {
     constexpr int smem = (16 * WARPS + 2 * STAGES * ABN) * D * 2;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};                 // (the opt-in is a property of the function on one device)
+    if (!configured[current_device()]) {
         cudaError_t e = cudaFuncSetAttribute(attention_fast_kernel<D, WARPS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "attention: cannot opt in to %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        configured[current_device()] = true;
     }
     dim3 grid(n_tiles, p.G, p.splits);
     g_launch_err = launch_pdl(attention_fast_kernel<D, WARPS, STAGES>, dim3(grid), dim3(WARPS * 32), smem, st, p, error_word());

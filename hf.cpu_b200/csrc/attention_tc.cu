@@ -202,19 +202,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             uint32_t sv[64];
             tmem_ld16(tS, sv); tmem_ld16(tS + 16, sv + 16); tmem_ld16(tS + 32, sv + 32); tmem_ld16(tS + 48, sv + 48);
             tmem_wait_ld();
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // (four chains: see attention_tc2.cu)
             if (all_visible) {
 #pragma unroll
-                for (int i = 0; i < 64; i++) mx = fmaxf(mx, __uint_as_float(sv[i]));
+                for (int i = 0; i < 64; i++) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
             } else {
 #pragma unroll
                 for (int i = 0; i < 64; i++) {
                     const int key = key0 + i;
                     const bool see = valid && key >= lo && key <= pos;
                     if (!see) sv[i] = 0xff800000u;                  // -inf: contributes neither to the maximum nor to the sum
-                    mx = fmaxf(mx, __uint_as_float(sv[i]));
+                    mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[i]));
                 }
             }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float *xm = xchg + (j & 1) * 256;
             xm[half * 128 + row] = mx;
             __syncwarp();
@@ -225,16 +226,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const float bs = m_new == -INFINITY ? 0.f : m_new;
             const float corr = ex2(m - bs);                        // 2^-inf = 0 for the first tile
             m = m_new;
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];
 #pragma unroll
             for (int i = 0; i < 64; i += 2) {
                 float a = ex2(__uint_as_float(sv[i]) * p.scale_log2 - bs), b = ex2(__uint_as_float(sv[i + 1]) * p.scale_log2 - bs);
                 __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                 const uint32_t hb = *(uint32_t *)&h;                // the sum runs over the rounded values the product uses:
-                sum += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
+                sum4[(i >> 1) & 3] += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
                 pk[i >> 1] = hb;
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 #pragma unroll
             for (int q = 0; q < 8; q++)
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sP + sw_off(row, half * 8 + q)), "r"(pk[4 * q]),
@@ -321,11 +323,11 @@ extern "C" int hfb_attention_tc(const void *q, const void *k_cache, const void *
     p.max_blocks = max_blocks; p.block_size = block_size; p.window = window; p.H = H; p.G = G; p.num_slots = slots;
     p.scale_log2 = scale * 1.4426950408889634f;
     constexpr uint32_t smem = 1024 + 4 * SUB + 4 * KV_STAGE + 128 + 768 * 4;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};                 // (the opt-in is a property of the function on one device)
+    if (!configured[current_device()]) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_tc: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        configured[current_device()] = true;
     }
     g_launch_err = launch_pdl(attention_tc_kernel, dim3(n_tiles, G), dim3(ATC_THREADS), smem, (cudaStream_t)s, mk, mv, p, error_word());
     return check_pdl_launch(g_launch_err, "attention_tc");

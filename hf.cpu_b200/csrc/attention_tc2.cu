@@ -288,22 +288,25 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s_free + 8 * i);         // the tensor core may write the next scores
-                float mx = -INFINITY;
+                // (the maximum and the sum each run in four independent chains: with two warps per scheduler a chain of
+                // 128 dependent operations is not hidden by the other warp)
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 // rows beyond the tile's tokens (their queries are zeros, nothing of them is written) go with the
                 // rows that see every key, so that their warp is not split over both branches
                 const bool all_visible = !valid || (key0 + U_KEYS - 1 <= pos && key0 >= lo);
                 if (all_visible) {
 #pragma unroll
-                    for (int c = 0; c < 128; c++) mx = fmaxf(mx, __uint_as_float(sv[c]));
+                    for (int c = 0; c < 128; c++) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
                 } else {
 #pragma unroll
                     for (int c = 0; c < 128; c++) {
                         const int key = key0 + c;
                         const bool see = valid && key >= lo && key <= pos;
                         if (!see) sv[c] = 0xff800000u;              // -inf: contributes neither to the maximum nor to the sum
-                        mx = fmaxf(mx, __uint_as_float(sv[c]));
+                        mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
                     }
                 }
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 mx *= p.scale_log2;                                  // scale > 0 commutes with the maximum
                 // raise the reference only when the row's maximum has outgrown it by 2^TAU (or there was none yet)
                 float corr = 1.f;
@@ -312,16 +315,17 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                     m_ref = mx;
                 }
                 const float bs = m_ref == -INFINITY ? 0.f : m_ref;
-                float sum = 0.f;
+                float sum4[4] = {0.f, 0.f, 0.f, 0.f};
                 uint32_t pk[64];
 #pragma unroll
                 for (int c = 0; c < 128; c += 2) {
                     const float a = u_ex2(__uint_as_float(sv[c]) * p.scale_log2 - bs), b = u_ex2(__uint_as_float(sv[c + 1]) * p.scale_log2 - bs);
                     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
                     const uint32_t hb = *(uint32_t *)&h;            // the sum runs over the rounded values the product uses:
-                    sum += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
+                    sum4[(c >> 1) & 3] += __uint_as_float(hb << 16) + __uint_as_float(hb & 0xffff0000u);   // widened by bit moves, not conversions
                     pk[c >> 1] = hb;
                 }
+                const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                 l = l * corr + sum;
                 if (j > 0) {
                     // P of the step before has been used, and O holds everything up to it
@@ -356,16 +360,21 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
                 uint4 *dst = (uint4 *)(p.out + th);
 #pragma unroll 1
-                for (int c = 0; c < 8; c++) {
-                    uint32_t ov[16];
-                    tmem_ld16(tO + 16 * c, ov);                       // all lanes of the warp take part, valid row or not
+                for (int c = 0; c < 8; c += 4) {                      // four reads of 16 columns under way together
+                    uint32_t ov[64];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) tmem_ld16(tO + 16 * (c + u), ov + 16 * u);   // all lanes take part, valid row or not
                     tmem_wait_ld();
                     if (valid) {
-                        __nv_bfloat162 h[8];
 #pragma unroll
-                        for (int e = 0; e < 8; e++) h[e] = __floats2bfloat162_rn(__uint_as_float(ov[2 * e]) * inv, __uint_as_float(ov[2 * e + 1]) * inv);
-                        dst[2 * c] = *(uint4 *)&h[0];
-                        dst[2 * c + 1] = *(uint4 *)&h[4];
+                        for (int u = 0; u < 4; u++) {
+                            __nv_bfloat162 h[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++)
+                                h[e] = __floats2bfloat162_rn(__uint_as_float(ov[16 * u + 2 * e]) * inv, __uint_as_float(ov[16 * u + 2 * e + 1]) * inv);
+                            dst[2 * (c + u)] = *(uint4 *)&h[0];
+                            dst[2 * (c + u) + 1] = *(uint4 *)&h[4];
+                        }
                     }
                 }
                 tc_fence_before();
@@ -420,11 +429,11 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
     p.n_tiles = n_tiles;
     p.scale_log2 = scale * 1.4426950408889634f;
     constexpr uint32_t smem = 1024 + 7 * U_TILE + 160;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};                 // (the opt-in is a property of the function on one device)
+    if (!configured[current_device()]) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_tc2: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured = true;
+        configured[current_device()] = true;
     }
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);

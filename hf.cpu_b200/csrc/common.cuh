@@ -124,6 +124,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_sync() { pdl_wait(); pdl_trigger(); }
 
+// Index of the current device (0 where it cannot be told), for what is remembered per device.
+inline int current_device()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    return dev;
+}
+
 bool pdl_enabled();          // HFB_PDL != 0
 
 template <typename... KArgs, typename... Args>

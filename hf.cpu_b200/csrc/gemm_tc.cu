@@ -708,13 +708,6 @@ int tensor_map_kv(const void *k, const void *v, int slots, int row_elems, int bo
     return HFB_OK;
 }
 
-static int current_device()
-{
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-    return dev;
-}
-
 static int sm_count()
 {
     static int n[64] = {0};
