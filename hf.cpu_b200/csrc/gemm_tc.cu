@@ -557,7 +557,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const int tx = t % p.tiles_x, ty = t / p.tiles_x;
             const int a = tile_it & 1;
             const uint32_t aph = (tile_it >> 1) & 1;
-            if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag, err)) { ok = false; break; }
+            if (!mbar_wait_long(tfull0 + 8 * a, aph, abort_flag, err)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
             const int xr = tx * 256 + (int)rank * TILE_X + row;

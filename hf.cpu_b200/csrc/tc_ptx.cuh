@@ -56,6 +56,31 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// The same for a wait that is expected to last many microseconds (an epilogue warp waiting for its tile): the thread
+// sleeps between polls, so that it does not spend issue slots and power the tensor cores could use.
+__device__ __forceinline__ bool mbar_wait_long(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err)
+{
+    unsigned long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if (*abort_flag) return false;
+        __nanosleep(256);
+        if ((spin & 63) == 63) {
+            unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicOr(err, HFB_ERR_WAIT);
+                return false;
+            }
+        }
+    }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
 {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
