@@ -124,6 +124,15 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_sync() { pdl_wait(); pdl_trigger(); }
 
+// One rotation pair (src/model.c:587-601): products and sums each rounded to float32 on their own, so that every kernel
+// that rotates gives the same bits (the compiler is free to contract a * c - b * s into a fused multiply-add in one
+// place and not in another).
+__device__ __forceinline__ void rope_pair(float a, float b, float c, float s, float &lo, float &hi)
+{
+    lo = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+    hi = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+}
+
 // Index of the current device (0 where it cannot be told), for what is remembered per device.
 inline int current_device()
 {

@@ -173,8 +173,10 @@ __global__ void rope_kv_write_kernel(const T *qkv, const float *cos_sin, int n_r
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
             float c = cs[2 * i], s = cs[2 * i + 1];
             float a = to_f32(src[i]), b = to_f32(src[i + half]);
-            dst[i] = from_f32<T>(a * c - b * s);
-            dst[i + half] = from_f32<T>(a * s + b * c);
+            float lo, hi;
+            rope_pair(a, b, c, s, lo, hi);
+            dst[i] = from_f32<T>(lo);
+            dst[i + half] = from_f32<T>(hi);
         }
         for (int i = n_rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
     } else {
@@ -219,8 +221,10 @@ __global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int
             for (int i = 0; i < VEC; i++) {
                 float c = csv[2 * i], sn = csv[2 * i + 1];
                 float x = to_f32(a.e[i]), y = to_f32(b.e[i]);
-                ra.e[i] = from_f32<T>(x * c - y * sn);
-                rb.e[i] = from_f32<T>(x * sn + y * c);
+                float lo, hi;
+                rope_pair(x, y, c, sn, lo, hi);
+                ra.e[i] = from_f32<T>(lo);
+                rb.e[i] = from_f32<T>(hi);
             }
             *(Pack *)(dst + e0) = ra;
             *(Pack *)(dst + e0 + half) = rb;

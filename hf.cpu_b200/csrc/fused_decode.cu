@@ -185,8 +185,10 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
             float a = value(i), b = value(i + half);
             // the separate kernels round q|k|v to the run type before rotating; keep the same values
             a = to_f32(from_f32<T>(a)); b = to_f32(from_f32<T>(b));
-            dst[i] = from_f32<T>(a * c - b * s);
-            dst[i + half] = from_f32<T>(a * s + b * c);
+            float lo, hi;
+            rope_pair(a, b, c, s, lo, hi);
+            dst[i] = from_f32<T>(lo);
+            dst[i + half] = from_f32<T>(hi);
         }
         for (int i = n_rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>(value(i));
     } else {

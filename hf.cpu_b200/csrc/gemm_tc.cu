@@ -44,7 +44,7 @@ constexpr int HELPER_WARP = 10;
 constexpr int PAIR_THREADS = 224;            // pair kernel: weight-tile warp, MMA warp, four epilogue warps, activation-tile warp
 constexpr int PAIR_ACT_WARP = 6;
 
-enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3 };
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_PARTIAL = 2, EPI_SWIGLU = 3, EPI_ROPE_KV = 4 };
 
 struct GemmParams {
     int M, N, K;                       // logical sizes: tokens, output features, inner
@@ -55,6 +55,14 @@ struct GemmParams {
     const void *bias; int bias_dt;     // [N] or null
     int mode;
     float *partial;                    // [splits, M, N] when mode == EPI_PARTIAL
+    // mode == EPI_ROPE_KV (pair kernel, tiles of whole heads): the output is the q|k|v row of a token; bias, rounding
+    // to bfloat16, rotation of the query and key heads by the token's position, queries to q_out, keys and values to
+    // the token's cache slot
+    const float *cos_sin;              // [n_positions, d / 2, 2]
+    const int32_t *positions, *slots;  // per token; slots may be null (nothing is cached)
+    __nv_bfloat16 *q_out, *k_cache, *v_cache;
+    long long cache_slots;
+    int n_positions, H, G, d;
 };
 
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -444,6 +452,56 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar)
                  ::"r"(bar), "h"((unsigned short)3) : "memory");
 }
 
+// The q|k|v epilogue of one head of one token (see GemmParams): `lo` and `hi` are 32 accumulator columns each, of the
+// head's first half from j0 on and of its second half from j0 on; the rotation pairs column i with column i + d/2.
+__device__ __forceinline__ void rope_kv_piece(const GemmParams &p, const uint32_t *lo, const uint32_t *hi, int col, int j0,
+                                              const float *cs, bool rotate, __nv_bfloat16 *dst)
+{
+    const int half = p.d >> 1;
+    float bl[32], bh[32];
+    if (p.bias) {
+        const uint4 *b0 = (const uint4 *)((const __nv_bfloat16 *)p.bias + col + j0), *b1 = (const uint4 *)((const __nv_bfloat16 *)p.bias + col + half + j0);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint4 x = b0[q], y = b1[q];
+            const __nv_bfloat162 *hx = (const __nv_bfloat162 *)&x, *hy = (const __nv_bfloat162 *)&y;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float2 fx = __bfloat1622float2(hx[e]), fy = __bfloat1622float2(hy[e]);
+                bl[8 * q + 2 * e] = fx.x; bl[8 * q + 2 * e + 1] = fx.y; bh[8 * q + 2 * e] = fy.x; bh[8 * q + 2 * e + 1] = fy.y;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; i++) bl[i] = bh[i] = 0.f;
+    }
+    __align__(16) __nv_bfloat16 ol[32], oh[32];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+        // the separate kernels round q|k|v to bfloat16 before they rotate; the same values here
+        const float a0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[i]) + bl[i]));
+        const float a1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(lo[i + 1]) + bl[i + 1]));
+        const float b0 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[i]) + bh[i]));
+        const float b1 = __bfloat162float(__float2bfloat16_rn(__uint_as_float(hi[i + 1]) + bh[i + 1]));
+        if (rotate) {
+            const float4 c = *(const float4 *)(cs + 2 * (j0 + i));           // cos, sin of pair j0 + i and of the next
+            float l0, h0, l1, h1;
+            rope_pair(a0, b0, c.x, c.y, l0, h0);
+            rope_pair(a1, b1, c.z, c.w, l1, h1);
+            ol[i] = __float2bfloat16_rn(l0); oh[i] = __float2bfloat16_rn(h0);
+            ol[i + 1] = __float2bfloat16_rn(l1); oh[i + 1] = __float2bfloat16_rn(h1);
+        } else {
+            ol[i] = __float2bfloat16_rn(a0); oh[i] = __float2bfloat16_rn(b0);
+            ol[i + 1] = __float2bfloat16_rn(a1); oh[i + 1] = __float2bfloat16_rn(b1);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        *(uint4 *)(dst + j0 + 8 * q) = *(const uint4 *)(ol + 8 * q);
+        *(uint4 *)(dst + half + j0 + 8 * q) = *(const uint4 *)(oh + 8 * q);
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, GemmParams p, int *err)
@@ -561,6 +619,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + a * BN;
             const int xr = tx * 256 + (int)rank * TILE_X + row;
+            if ((BN == 256 || BN == 128) && p.mode == EPI_ROPE_KV) {
+                // the tile holds whole heads of the q|k|v rows of 128 tokens per CTA; a thread has one token
+                const bool row_ok = xr < p.M;
+                const int half = p.d >> 1;
+                int pos = row_ok ? p.positions[xr] : 0;
+                if (pos < 0 || pos >= p.n_positions) { atomicOr(err, HFB_ERR_POSITION); pos = 0; }
+                long long slot = (row_ok && p.slots) ? p.slots[xr] : -1;
+                if (slot >= p.cache_slots) { atomicOr(err, HFB_ERR_SLOT); slot = -1; }
+                const float *cs = p.cos_sin + (size_t)pos * half * 2;
+#pragma unroll 1
+                for (int h0 = 0; h0 < BN; h0 += p.d) {
+                    const int col = ty * BN + h0, head = col / p.d;
+                    if (col >= p.N) break;                   // (the same for every thread)
+                    __nv_bfloat16 *dst = nullptr;
+                    if (row_ok) {
+                        if (head < p.H) dst = p.q_out + ((size_t)xr * p.H + head) * p.d;
+                        else if (slot >= 0) dst = (head < p.H + p.G ? p.k_cache + ((size_t)slot * p.G + (head - p.H)) * p.d
+                                                                      : p.v_cache + ((size_t)slot * p.G + (head - p.H - p.G)) * p.d);
+                    }
+#pragma unroll 1
+                    for (int j0 = 0; j0 < half; j0 += 32) {
+                        uint32_t lo[32], hi[32];
+                        tmem_ld16(taddr + h0 + j0, lo); tmem_ld16(taddr + h0 + j0 + 16, lo + 16);
+                        tmem_ld16(taddr + h0 + half + j0, hi); tmem_ld16(taddr + h0 + half + j0 + 16, hi + 16);
+                        tmem_wait_ld();
+                        if (dst) rope_kv_piece(p, lo, hi, col, j0, cs, head < p.H + p.G, dst);
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t v[32];
@@ -818,7 +905,7 @@ static int mid_splits(int M, int N, int K)
 // Common set-up of the product's tiling: fills p (sizes, tiles, maps) for `bn`.  `splits` > 1 (more than 128 tokens
 // only; see mid_splits) asks for that many slices of the inner dimension; the caller then sets the partial-sum mode.
 static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb::GemmParams &p, int &bn, CUtensorMap &mx, CUtensorMap &my,
-                         int splits = 1)
+                         int splits = 1, int force_bn = 0)
 {
     using namespace hfb;
     p.M = M; p.N = N; p.K = K;
@@ -844,12 +931,16 @@ static int plan_and_maps(const void *a, const void *w, int M, int N, int K, hfb:
         if (splits > 1) {
             p.kb_per_split = (p.kb_total + splits - 1) / splits;
             p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+        } else if (force_bn) {
+            bn = force_bn;
         } else {
             const int widths[6] = {256, 240, 224, 208, 192, 128};
             long best = -1;
             for (int i = 0; i < 6; i++) {
                 long tiles = (long)p.tiles_x * ((N + widths[i] - 1) / widths[i]);
-                long cost = (tiles + units - 1) / units * widths[i];
+                // a k block of a pair's tile takes about 265 ns + 0.6 ns per column (measured at 128..256 columns: a
+                // narrow tile is hardly cheaper than a wide one); on one CTA its time goes with the width
+                long cost = (tiles + units - 1) / units * (p.pair ? 424 + widths[i] : widths[i]);
                 if (best < 0 || cost < best) { best = cost; bn = widths[i]; }
             }
         }
@@ -967,6 +1058,38 @@ extern "C" int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int
     int bn;
     if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my)) != HFB_OK) return rc;
     p.out = out; p.out_dt = out_dt; p.bias = nullptr; p.mode = EPI_SWIGLU;
+    return launch_bn(bn, mx, my, p, (cudaStream_t)s);
+}
+
+// q|k|v of many tokens (256 and more: the pair kernel) with the rest of the step in the product's epilogue: bias,
+// rounding to bfloat16, rotation of the query and key heads by cos_sin [n_positions, d / 2, 2] at the tokens'
+// positions, queries to q_out [M, H d], keys and values to cache slot slots[t] (null: nothing is cached).  bfloat16
+// bias and outputs, head sizes 64 and 128, the whole head rotated.  HFB_ENOTSUP, with nothing launched, where the
+// sizes are not these: the caller then runs the product and hfb_rope_kv_write.
+extern "C" int hfb_linear_tc_rope_kv(const void *a, const void *w, const void *bias, const float *cos_sin, int n_positions,
+                                     const int32_t *positions, const int32_t *slots, void *q_out, void *k_cache, void *v_cache,
+                                     int64_t cache_slots, int M, int K, int H, int G, int d, hfb_stream s)
+{
+    if (M <= 0) return HFB_OK;
+    if (!takes_pairs(M) || (d != 64 && d != 128) || H <= 0 || G <= 0 || !cos_sin || !positions || n_positions <= 0)
+        return fail(HFB_ENOTSUP, "linear_tc_rope_kv: takes 256 tokens and more, head sizes 64 and 128, a rotation table");
+    const int N = (H + 2 * G) * d;
+    int rc = check_tc_args("linear_tc_rope_kv", a, w, q_out, M, N, K, bias);
+    if (rc != HFB_OK) return rc;
+    if (((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)cos_sin & 15))
+        return fail(HFB_ENOTSUP, "linear_tc_rope_kv: cache and table must be 16-byte aligned");
+    GemmParams p{};
+    CUtensorMap mx, my;
+    int bn;
+    // tiles of whole heads: 256 columns, or 128 where that leaves fewer rounds over the pairs
+    const int units = sm_count() / 2, tiles_x = (M + 255) / 256;
+    const long r256 = ((long)tiles_x * ((N + 255) / 256) + units - 1) / units * (424 + 256);
+    const long r128 = ((long)tiles_x * ((N + 127) / 128) + units - 1) / units * (424 + 128);
+    if ((rc = plan_and_maps(a, w, M, N, K, p, bn, mx, my, 1, r128 < r256 ? 128 : 256)) != HFB_OK) return rc;
+    p.out = q_out; p.out_dt = HFB_BF16; p.bias = bias; p.bias_dt = HFB_BF16; p.mode = EPI_ROPE_KV;
+    p.cos_sin = cos_sin; p.positions = positions; p.slots = slots; p.n_positions = n_positions;
+    p.q_out = (__nv_bfloat16 *)q_out; p.k_cache = (__nv_bfloat16 *)k_cache; p.v_cache = (__nv_bfloat16 *)v_cache;
+    p.cache_slots = cache_slots; p.H = H; p.G = G; p.d = d;
     return launch_bn(bn, mx, my, p, (cudaStream_t)s);
 }
 

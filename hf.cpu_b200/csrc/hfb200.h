@@ -50,6 +50,14 @@ int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, v
 /* The product with a SwiGLU epilogue: w holds gate row i at 2i and up row i at 2i+1; out[M, N/2]. */
 int hfb_linear_tc_swiglu(const void *a, const void *w, void *out, int out_dt, int M, int N, int K, hfb_stream s);
 
+/* q|k|v of 256 tokens and more with the rest of the step in the product's epilogue: bias, rounding to bfloat16,
+ * rotation of the query and key heads by cos_sin [n_positions, d / 2, 2] at the tokens' positions, queries to q_out
+ * [M, H d], keys and values to cache slot slots[t] (null: nothing is cached).  bfloat16 throughout, head sizes 64 and
+ * 128, the whole head rotated.  HFB_ENOTSUP, with nothing launched, for other sizes. */
+int hfb_linear_tc_rope_kv(const void *a, const void *w, const void *bias, const float *cos_sin, int n_positions,
+                          const int32_t *positions, const int32_t *slots, void *q_out, void *k_cache, void *v_cache,
+                          int64_t cache_slots, int M, int K, int H, int G, int d, hfb_stream s);
+
 /* Only the split-K partial sums partial[*splits, M, N] (float32) of a product, for a fused reduction to finish;
  * `workspace` must hold hfb_linear_tc_partials_workspace bytes.  Above 128 rows that size is 0 for a product that
  * would not be split, and this entry refuses it (HFB_ENOTSUP). */

@@ -13,6 +13,8 @@ import torch
 
 from . import build as _build
 
+HFB_ENOTSUP = 2          # status of csrc/hfb200.h: not a case for this kernel, nothing was launched
+
 
 class KernelError(RuntimeError):
     pass
@@ -62,6 +64,7 @@ class NativeBackend:
         self._argmax_ws = None
         # decode attention: the CTA that stores a tile's last split merges the splits (False: a second kernel does)
         self.merge_in_kernel = True
+        self.rope_in_epilogue = os.environ.get("HFB_ROPE_EPILOGUE", "1") != "0"     # prompts: q|k|v product rotates and writes the cache
         self._counters = None
         self.lib.hfb_linear_tc_partials_workspace.restype = ctypes.c_size_t
         self.lib.hfb_argmax2_scratch.restype = ctypes.c_size_t
@@ -290,6 +293,17 @@ class NativeBackend:
     def linear_rope_kv(self, a, w, bias, qkv_buf, cos_sin, n_rot, positions, slots, q_out, k_cache, v_cache, H, G, d):
         self._on_gpu(a, w, bias, cos_sin, positions, slots, q_out, k_cache, v_cache)
         M, K = a.shape
+        if (self.rope_in_epilogue and M >= 256 and self._tc_ok(a, w, q_out) and q_out.dtype == torch.bfloat16
+                and k_cache.dtype == torch.bfloat16 and d in (64, 128) and n_rot == d and cos_sin is not None
+                and (bias is None or (bias.dtype == torch.bfloat16 and bias.data_ptr() % 16 == 0))):
+            # many tokens: rotation and the cache write run in the product's epilogue
+            rc = self.lib.hfb_linear_tc_rope_kv(
+                _p(a), _p(w), _p(bias), _p(cos_sin), c_int(cos_sin.shape[0]), _p(positions), _p(slots), _p(q_out),
+                _p(k_cache), _p(v_cache), c_int64(k_cache.shape[0] * k_cache.shape[1]), c_int(M), c_int(K), c_int(H),
+                c_int(G), c_int(d), self._stream())
+            if rc != HFB_ENOTSUP:
+                self._check(rc, "linear_tc_rope_kv")
+                return
         part = self._partials(a, w) if self._tc_ok(a, w) else None
         if part is None:
             self.linear(a, w, bias, qkv_buf, False)

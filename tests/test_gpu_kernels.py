@@ -399,8 +399,12 @@ def test_linear_residual_norm_fused(shape, with_norm):
 
 
 @pytest.mark.parametrize("geom", [(28, 4, 128, 3584, 8), (6, 3, 32, 192, 5), (4, 2, 16, 64, 1), (8, 8, 64, 512, 130), (5, 1, 48, 100, 3),
-                                  (28, 4, 128, 3584, 512), (4, 2, 64, 4096, 200)])
+                                  (28, 4, 128, 3584, 512), (4, 2, 64, 4096, 200),
+                                  # 256 tokens and more: rotation and cache write in the epilogue of the pair kernel (tiles of
+                                  # whole heads; a last tile half outside the row; ragged token counts; head size 64)
+                                  (28, 4, 128, 3584, 2048), (6, 2, 128, 256, 257), (14, 2, 64, 896, 300), (5, 5, 64, 136, 640)])
 def test_linear_rope_kv_fused(geom):
+    from hfcpu_b200 import kernels
     H, G, d, K, T = geom
     N = (H + 2 * G) * d
     a, w, bias = rnd(T, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, scale=0.1), rnd(N, dtype=torch.bfloat16)
@@ -409,16 +413,27 @@ def test_linear_rope_kv_fused(geom):
     cos_sin = torch.stack([ang.cos(), ang.sin()], -1).float().contiguous()
     positions = torch.randint(0, P, (T,), device=DEV, dtype=torch.int32)
     slots = torch.randperm(pages * bs, device=DEV)[:T].int()
+    slots[::7] = -1                                      # tokens that are not cached
     outs = []
-    for impl in (native(), EmuBackend()):
+    b = kernels.backend()
+    for impl, in_epilogue in ((native(), True), (native(), False), (EmuBackend(), False)):
         qkv = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
         q = torch.zeros(T, H * d, device=DEV, dtype=torch.bfloat16)
         kc = torch.zeros(pages, bs, G, d, device=DEV, dtype=torch.bfloat16)
         vc = torch.zeros_like(kc)
-        impl.linear_rope_kv(a, w, bias, qkv, cos_sin, d, positions, slots, q, kc, vc, H, G, d)
+        b.rope_in_epilogue = in_epilogue
+        before = b.launches
+        try:
+            impl.linear_rope_kv(a, w, bias, qkv, cos_sin, d, positions, slots, q, kc, vc, H, G, d)
+        finally:
+            b.rope_in_epilogue = True
+        if impl is native() and T >= 256 and d in (64, 128):
+            assert b.launches - before == (1 if in_epilogue else 2)
         outs.append((q, kc, vc))
-    for x, y in zip(*outs):
-        assert rel(x.float(), y.float()) < 1.5e-2
+    for x, y, z in zip(*outs):
+        assert torch.equal(x, y), "the product's epilogue and the separate kernel differ"
+        assert rel(x.float(), z.float()) < 1.5e-2
+    kernels.check_device_errors()
 
 
 @pytest.mark.parametrize("geom", [(28, 4, 128, 16), (4, 4, 128, 8), (16, 1, 128, 128), (5, 5, 128, 32)])
