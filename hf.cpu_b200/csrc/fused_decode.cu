@@ -197,7 +197,16 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
 }
 
 // arg-max in two passes so that many blocks share a row: (value, index) per chunk, then the best chunk.
-__global__ void argmax_chunks_kernel(const float *logits, int V, int chunk, float *best_v, int32_t *best_i)
+// (value, index) pairs: the larger value wins, the smaller index among equals; an index below 0 is "none yet"
+__device__ __forceinline__ void argmax_take(float &best, int &bi, float v, int i)
+{
+    if (i >= 0 && (bi < 0 || v > best || (v == best && i < bi))) { best = v; bi = i; }
+}
+
+// A chunk of 4,096 logits per block of 256 threads: where the rows allow 16-byte reads a thread's four reads are under
+// way together (what this kernel costs is latency, not bytes); warps reduce by shuffles, the eight warps through
+// shared memory once.
+__global__ void __launch_bounds__(256) argmax_chunks_kernel(const float *logits, int V, int chunk, float *best_v, int32_t *best_i)
 {
     HFB_TRACE_ENTRY(9);
     pdl_sync();
@@ -206,23 +215,39 @@ __global__ void argmax_chunks_kernel(const float *logits, int V, int chunk, floa
     const int lo = c * chunk, hi = min(V, lo + chunk);
     float best = 0.f;
     int bi = -1;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        float v = p[i];
-        if (bi < 0 || v > best) { best = v; bi = i; }
-    }
-    __shared__ float sv[256];
-    __shared__ int si[256];
-    sv[threadIdx.x] = best; si[threadIdx.x] = bi;
-    __syncthreads();
-    for (int o = blockDim.x >> 1; o > 0; o >>= 1) {
-        if (threadIdx.x < o) {
-            float v2 = sv[threadIdx.x + o], v1 = sv[threadIdx.x];
-            int i2 = si[threadIdx.x + o], i1 = si[threadIdx.x];
-            if (i2 >= 0 && (i1 < 0 || v2 > v1 || (v2 == v1 && i2 < i1))) { sv[threadIdx.x] = v2; si[threadIdx.x] = i2; }
+    if ((V & 3) == 0 && (chunk & 3) == 0 && (((uintptr_t)logits) & 15) == 0 && chunk == 4096) {
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i = lo + 4 * ((int)threadIdx.x + 256 * j);
+            v[j] = i < hi ? *(const float4 *)(p + i) : make_float4(0.f, 0.f, 0.f, 0.f);      // (hi is a multiple of 4 too)
         }
-        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i = lo + 4 * ((int)threadIdx.x + 256 * j);
+            if (i < hi) {
+                argmax_take(best, bi, v[j].x, i); argmax_take(best, bi, v[j].y, i + 1);
+                argmax_take(best, bi, v[j].z, i + 2); argmax_take(best, bi, v[j].w, i + 3);
+            }
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) argmax_take(best, bi, p[i], i);
     }
-    if (threadIdx.x == 0) { best_v[(size_t)row * gridDim.x + c] = sv[0]; best_i[(size_t)row * gridDim.x + c] = si[0]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v2 = __shfl_xor_sync(0xffffffffu, best, o);
+        const int i2 = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_take(best, bi, v2, i2);
+    }
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++) argmax_take(best, bi, sv[w], si[w]);
+        best_v[(size_t)row * gridDim.x + c] = best; best_i[(size_t)row * gridDim.x + c] = bi;
+    }
 }
 
 __global__ void argmax_final_kernel(const float *best_v, const int32_t *best_i, int chunks, int32_t *out)

@@ -88,6 +88,7 @@ class StepContext:
         self.run_dtype = engine.model.run_dtype
         self.device = engine.device
         self.num_tokens = self.num_seqs = self.num_logit_rows = 0
+        self.logits_for_all = False
         self.max_q_len = self.max_kv_len = 0
         self.token_ids = self.positions = self.token_seq = None
         self.cu_tokens = self.kv_lens = self.seq_slots = self.logit_rows = None
@@ -318,6 +319,7 @@ class Engine:
         for key, arrs in extras:
             ctx._arrays[key] = {n: take(len(v)) for n, v in arrs.items()}
         ctx.num_tokens, ctx.num_seqs, ctx.num_logit_rows = T, S, M
+        ctx.logits_for_all = rows == list(range(T))      # every token's logits, in order: the last block may run the final norm
         ctx.h_cu_tokens, ctx.h_kv_lens, ctx.h_seq_slots = cu, kv_lens, seq_slots
         ctx.max_q_len = max_q
         ctx.max_kv_len = max(kv_lens)

@@ -106,15 +106,21 @@ class Model:
         for i, e in enumerate(schedule):
             layer = self.layers[e.layer]
             owner = i if e.cache_of is None else e.cache_of
-            next_norm = self.layers[schedule[i + 1].layer].norm1 if i + 1 < len(schedule) else None
+            # the norm that follows this block: the next block's first, or, after the last block of a step whose
+            # tokens all want their logits (a step of single tokens), the final norm
+            if i + 1 < len(schedule):
+                next_norm = self.layers[schedule[i + 1].layer].norm1
+            else:
+                next_norm = self.final_norm if getattr(ctx, "logits_for_all", False) else None
             xn = layer.block.forward(ctx, x, layer.norm1, layer.mixer, layer.norm2, layer.ffn,
                                      ctx.entry_cache(owner), ctx.entry_state(i), e.cache_of is None,
                                      xn_ready=xn, next_norm=next_norm)
         M = ctx.num_logit_rows
         if M == 0:
             return None
-        xn = ctx.buf("head_xn", (M, self.plan.hidden_size), self.run_dtype)
-        self.final_norm.forward(x, xn, rows=ctx.logit_rows)
+        if xn is None or not schedule:
+            xn = ctx.buf("head_xn", (M, self.plan.hidden_size), self.run_dtype)
+            self.final_norm.forward(x, xn, rows=ctx.logit_rows)
         logits = ctx.buf("logits", (M, self.plan.vocab_size), torch.float32)
         self.head.forward(xn, logits)
         return logits

@@ -226,15 +226,20 @@ def test_swiglu(dtype):
         assert rel(out.float(), ref.float()) < (1e-6 if dtype == "float32" else 1e-2)
 
 
-def test_argmax_lowest_index_wins():
-    logits = rnd(9, 151937)
-    logits[2, 70000] = logits[2, 140000] = 50.0
+@pytest.mark.parametrize("V", [151937, 152064, 4096, 4100, 37])
+def test_argmax_lowest_index_wins(V):
+    """Rows that allow 16-byte reads (a vocabulary that is a multiple of 4) and rows that do not; ties within a
+    16-byte piece, across warps, across chunks; a row of equal values; the maximum in the last, short chunk."""
+    logits = rnd(9, V)
+    logits[2, V // 2] = logits[2, V - 7] = 50.0
     logits[3, 5] = logits[3, 4] = 60.0
     logits[4] = 1.0
+    logits[5, V - 1] = 70.0
+    logits[6, 33] = logits[6, 32] = logits[6, 31] = 55.0
     out = torch.empty(9, device=DEV, dtype=torch.int32)
     native().argmax(logits, out)
     assert out.tolist() == torch.argmax(logits, -1).tolist()
-    assert out[2] == 70000 and out[3] == 4 and out[4] == 0
+    assert out[2] == V // 2 and out[3] == 4 and out[4] == 0 and out[5] == V - 1 and out[6] == 31
 
 
 def test_refuses_unsupported_head_dim():
