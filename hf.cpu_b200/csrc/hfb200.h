@@ -42,7 +42,10 @@ int hfb_linear_plain(const void *a, int a_dt, const void *w, int w_dt, const voi
  * and the operands 16-byte aligned, else HFB_ENOTSUP.  Where there are fewer output tiles than SMs (few rows; or a
  * few hundred rows, few output features and a long K) the kernel may split K over more CTAs and sum float32
  * partials kept in `workspace`; hfb_linear_tc_workspace gives the bytes that takes (0 = none); with a smaller or
- * null workspace it runs unsplit. */
+ * null workspace it runs unsplit.  The kernels are launched so that they may start while the kernel in front of them
+ * on the stream still runs (programmatic dependent launch), and they read `w`, the weights, before they wait for
+ * that kernel: `w` must be complete before the kernel in front is launched (weights are; an operand that the
+ * kernel in front computes belongs in `a`).  HFB_PDL=0 in the environment turns the early start off. */
 size_t hfb_linear_tc_workspace(int M, int N, int K);
 int hfb_linear_tc(const void *a, const void *w, const void *bias, int bias_dt, void *out, int out_dt,
                   int accumulate, int M, int N, int K, void *workspace, size_t workspace_bytes, hfb_stream s);

@@ -31,6 +31,8 @@
  *    start at zero: each split overwrites its whole [M, N] slice before the reduction reads it.  For the
  *    same reason two calls whose kernels may run at the same time on one GPU (different streams, or several
  *    host threads) race on the array: keep calls on one stream, or order them yourself.
+ *  - As with hfb_linear_tc, the kernel may start while the kernel in front of it on the stream still runs and
+ *    reads `w` before it waits for that kernel: `w` must be complete before the kernel in front is launched.
  */
 #ifndef HFB200_NOALLOC_H
 #define HFB200_NOALLOC_H
