@@ -154,6 +154,73 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+# The other two sized workloads the benchmark description names, through the Python entry point (scheduler, chunked
+# prompts beside decodes, sampling): `--workload c3` and `--workload c4`.
+WORKLOADS = {
+    "c3": dict(name="Qwen2.5-0.5B layer sizes: 32 requests, prompts uniform in [1, 1024], 128 new tokens each, 256-token "
+                    "prompt portions beside decodes, temperature 0.7",
+               cfg=dict(num_hidden_layers=24, hidden_size=896, num_attention_heads=14, num_key_value_heads=2,
+                        intermediate_size=4864, vocab_size=151936, tie_word_embeddings=True, rms_norm_eps=1e-6),
+               requests=32, prompt=(1, 1024), new=128, chunk=256, ctx_max=2048, temp=0.7),
+    "c4": dict(name="Qwen2.5-32B layer sizes: 16 requests, 4,096-token prompts, 128 new tokens each, greedy, 8,192 max context",
+               cfg=dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8,
+                        intermediate_size=27648, vocab_size=152064, tie_word_embeddings=False, rms_norm_eps=1e-5),
+               requests=16, prompt=(4096, 4096), new=128, chunk=2048, ctx_max=8192, temp=0.0),
+}
+
+
+def run_workload(args):
+    """One of WORKLOADS end to end through Session.generate, host ids in and out: one JSON line with the wall-clock
+    time, the tokens a second over the whole run, and over the stretch after every request has its first token."""
+    import torch
+    import hfcpu_b200
+    from hfcpu_b200.config import config_from_dict
+    w = WORKLOADS[args.workload]
+    cfg_d = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", max_position_embeddings=32768, rope_theta=1e6,
+                 use_sliding_window=False, hidden_act="silu", **w["cfg"])
+    layers_full = cfg_d["num_hidden_layers"]
+    if args.layers:
+        cfg_d["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(cfg_d)
+    torch.cuda.set_device(0)
+    model = hfcpu_b200.random_model(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
+    g = torch.Generator().manual_seed(11)
+    lens = torch.randint(w["prompt"][0], w["prompt"][1] + 1, (w["requests"],), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    sess = hfcpu_b200.Session(model, kv_block=BLOCK, max_seqs=w["requests"], ctx_max=w["ctx_max"],
+                              kv_pages=w["requests"] * (w["ctx_max"] // BLOCK + 1), max_batched_tokens=max(w["chunk"], w["requests"]),
+                              batch=w["chunk"])
+    runs = []
+    for rep in range(2):                                     # the first run warms up (graphs, buffers); the second is the record
+        first, stamps = {}, []
+
+        def on_event(ev):
+            if hasattr(ev, "token"):
+                now = time.perf_counter()
+                first.setdefault(ev.req, now)
+                stamps.append(now)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = sess.generate(prompts, temp=w["temp"], seed=5, max_tokens=w["new"], eos_ids=[], on_event=on_event, prefix_cache=False)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        new = sum(len(c[0].tokens) for c in out)
+        t_all_first = max(first.values())
+        after = sum(1 for t in stamps if t > t_all_first)
+        runs.append(dict(seconds=round(t1 - t0, 4), new_tokens=new, prompt_tokens=sum(lens),
+                         tokens_per_s=round((sum(lens) + new) / (t1 - t0), 1), new_tokens_per_s=round(new / (t1 - t0), 1),
+                         seconds_to_all_first_tokens=round(t_all_first - t0, 4),
+                         decode_tokens_per_s=round(after / max(t1 - t_all_first, 1e-9), 1)))
+    from hfcpu_b200 import kernels
+    kernels.check_device_errors()
+    print(json.dumps({"workload": args.workload, "name": w["name"], "impl": "engine", "dtype": "bf16",
+                      "data": "synthetic (seeded uniform token ids, random-init weights)",
+                      "config": {"layers": cfg.num_hidden_layers, "layers_full": layers_full, "requests": w["requests"],
+                                 "chunk": w["chunk"], "ctx_max": w["ctx_max"], "temp": w["temp"], "kv_block": BLOCK},
+                      **runs[-1], "first_run_seconds": runs[0]["seconds"]}))
+    return 0
+
+
 def synthetic_prompts(batch, n, vocab, seed):
     import torch
     g = torch.Generator().manual_seed(seed)
@@ -255,6 +322,8 @@ def main():
     ap.add_argument("--timeline", choices=["decode", "prefill"], help="print the kernel timeline of one step instead of the "
                     "record (needs a library built with HFB_NVCC_EXTRA=-DHFB_TRACE; see hfcpu_b200/kernels/timeline.py)")
     ap.add_argument("--marks", action="store_true", help="with --timeline: every logged mark, not one row per kernel")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), help="run one of the other sized workloads end to end through "
+                    "Session.generate instead of the record (c3: 0.5B sizes, mixed chunked prompts and decodes; c4: 32B sizes)")
     ap.add_argument("--ref-layers", type=int, default=28, help="layers the reference arm runs (it is a CPU program)")
     ap.add_argument("--ref-timeout", type=int, default=1500, help="seconds the reference arm may take")
     args = ap.parse_args()
@@ -267,6 +336,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload:
+        return run_workload(args)
     warmup = max(args.warmup, 3)
 
     import torch
