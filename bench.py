@@ -28,6 +28,8 @@ QWEN25_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hid
                  max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False,
                  use_sliding_window=False, hidden_act="silu")
 PROMPT, CTX_MAX, BLOCK = 2048, 4096, 16
+SETTLE_S = 0.5             # pause between the prompts' prefill and the decode steps that are timed
+E2E_LEAD = 160             # decode steps of the end-to-end run before its timed ones (about half a second)
 REF_DIR = os.path.join(ROOT, "baseline", "_ref", "hf.cpu")     # a copy of the reference's source tree, built by make
 
 
@@ -258,6 +260,10 @@ def time_decode(engine, batch, steps, warmup, vocab, seed, sampler=None):
         kernels.argmax(logits, prev)
         n_done += 1
 
+    # The prompts' prefill leaves the GPU at the clocks of its power cap for some hundred milliseconds; the numbers
+    # here are those of decoding, so the GPU gets half a second to come back before the warm-up steps.
+    torch.cuda.synchronize()
+    time.sleep(SETTLE_S)
     for _ in range(warmup):
         one_step()
     torch.cuda.synchronize()
@@ -356,17 +362,23 @@ def main():
     kernels.backend()
     model = hfcpu_b200.random_model(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
     max_b = max(64, args.batch)
-    pages = max_b * ((PROMPT + warmup + args.steps + 64 + BLOCK - 1) // BLOCK + 1)
+    pages = max_b * ((PROMPT + max(warmup, E2E_LEAD) + args.steps + 64 + BLOCK - 1) // BLOCK + 1)
     engine = hfcpu_b200.Engine(model, block_size=BLOCK, num_pages=pages, max_requests=max_b, ctx_max=CTX_MAX)
     pk, pk_src = measure.load_peaks(ROOT)
     if args.timeline:
         return print_timeline(args, engine, V)
 
-    # ---- prefill: one prompt of 2,048 tokens, eight times over; the median of the last six ----------------
+    # ---- prefill: one prompt of 2,048 tokens, eight times over ----------------------------------------------
+    # The first two warm up.  The next three are each timed alone, after a pause, as the peak they are set against
+    # was (a burst: the best of ten products); the last three run back to back, under the power cap, as a peak
+    # measured over seconds would be.  `ms` and `frac` are the median of the three alone; `back_to_back_ms` is
+    # reported beside them.
     pre_ms = []
     for i, ids in enumerate(synthetic_prompts(8, PROMPT, V, seed=100)):
         engine.add_request(("pre", i))
         torch.cuda.synchronize()
+        if 2 <= i <= 5:
+            time.sleep(SETTLE_S)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         engine.step([StepEntry(("pre", i), ids, [PROMPT - 1])])
@@ -375,12 +387,14 @@ def main():
         pre_ms.append(e0.elapsed_time(e1))
         engine.finish_request(("pre", i))
     kernels.check_device_errors()
-    pre = statistics.median(pre_ms[2:])
+    pre = statistics.median(pre_ms[2:5])
     L, E, F = cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size
     flops = measure.step_flops(model, [PROMPT], [PROMPT], 1)
     prefill = {"value": round(PROMPT / pre * 1e3, 1), "tokens": PROMPT, "ms": round(pre, 3),
                "frac": round(flops / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflop": round(flops / 1e12, 2),
-               "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src, "best_ms": round(min(pre_ms[2:]), 3)}
+               "peak_tflops": pk["bf16_tflops"], "peak_source": pk_src, "best_ms": round(min(pre_ms[2:]), 3),
+               "back_to_back_ms": round(statistics.median(pre_ms[5:]), 3),
+               "timing": "median of three prompts each timed alone after a pause; back_to_back_ms: three in a row"}
 
     # ---- decode: the default batch, timed with clocks sampled ------------------------------------------
     sampler = ClockSampler()
@@ -408,10 +422,13 @@ def main():
                                   max_batched_tokens=args.batch * PROMPT)
         prompts = synthetic_prompts(args.batch, PROMPT, V, seed=7)
         stamps = []
-        sess.generate(prompts, temp=0, max_tokens=warmup + args.steps + 1,
+        # One call prefills and decodes, so the first decode steps run at the clocks the prefill's power cap left:
+        # the call decodes E2E_LEAD steps beyond the warm-up first, and its last K steps are the timed ones.
+        lead = max(warmup, E2E_LEAD)
+        sess.generate(prompts, temp=0, max_tokens=lead + args.steps + 1, eos_ids=[],
                       on_event=lambda ev: stamps.append(time.perf_counter()) if hasattr(ev, "token") else None)
         # token events arrive batch by batch; time the last K decode steps
-        t_first = stamps[args.batch * (warmup + 1) - 1]
+        t_first = stamps[args.batch * (lead + 1) - 1]
         t_last = stamps[-1]
         e2e_value = args.batch * args.steps / (t_last - t_first)
         meta_ints = 3 * args.batch + (args.batch + 1) + 3 * args.batch + args.batch * (1 + (CTX_MAX // BLOCK // 2))
