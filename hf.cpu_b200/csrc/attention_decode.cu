@@ -299,6 +299,40 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         constexpr int MAXS = 64;                          // (the host asks for no more splits than this)
         float *fs = (float *)gen;                         // [16][MAXS]; the tile buffers are free
         const int n_elems = rows * (D / 4);               // float4 pieces of the merged rows
+        if (p.splits <= 16) {
+            // Up to sixteen splits: every thread reads the splits' maxima and sums of its row itself, beside its piece
+            // of their outputs, all at once: one trip to L2 instead of two with a barrier between them (batch 8: 1.2 %
+            // of the step, batch 1: 2 %).  The same arithmetic in the same order as below.
+            for (int e = threadIdx.x; e < n_elems; e += ADT_THREADS) {
+                const int row = e / (D / 4), c4 = e % (D / 4);
+                const size_t th = (size_t)(t0 + row / r) * p.H + g * r + row % r;
+                const float2 *ml = (const float2 *)(p.part_ml + th * p.splits * 2);
+                const float4 *src = (const float4 *)(p.part_o + th * p.splits * D) + c4;
+                float2 w[16];
+                float4 v[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    w[i] = i < p.splits ? __ldcg(ml + i) : make_float2(-INFINITY, 0.f);
+                    v[i] = i < p.splits ? __ldcg(src + (size_t)i * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+                float m = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 16; i++) m = fmaxf(m, w[i].x);
+                float denom = 0.f;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 16; i++) {                 // in split order
+                    const float f = (i >= p.splits || w[i].x == -INFINITY) ? 0.f : exp2f(w[i].x - m);
+                    if (i < p.splits) denom += w[i].y * f;
+                    acc.x += v[i].x * f; acc.y += v[i].y * f; acc.z += v[i].z * f; acc.w += v[i].w * f;
+                }
+                const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+                *(uint2 *)(p.out + th * D + 4 * c4) = make_uint2(*(const uint32_t *)&lo, *(const uint32_t *)&hi);
+            }
+            if (tile == 0 && g == 0) HFB_TRACE_ANY(9);
+            return;
+        }
         if (threadIdx.x < rows) {
             const int row = threadIdx.x;
             const size_t th = (size_t)(t0 + row / r) * p.H + g * r + row % r;
