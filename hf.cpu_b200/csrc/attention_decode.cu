@@ -229,7 +229,6 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
     float *mo = (float *)gen;                             // [4][16][D]
     float *mml = mo + 4 * 16 * D;                         // [4][16][2]
-    float *fac = mml + 4 * 16 * 2;                        // [16][4] weights of the warps, then [16] maxima and [16] sums
     if (warp < 4) {
 #pragma unroll
         for (int i = 0; i < D / 8; i++) {
@@ -244,36 +243,32 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
     __syncthreads();
     const int rows = nt * r;
-    if (threadIdx.x < rows) {
-        const int row = threadIdx.x;
+    // Every thread works out the four warps' weights of its row itself (four exponentials) instead of waiting at a
+    // barrier for sixteen threads to do it: a piece of four columns per thread and turn.
+    for (int idx = threadIdx.x; idx < rows * (D / 4); idx += ADT_THREADS) {
+        const int row = idx / (D / 4), c4 = idx % (D / 4);
         float m = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; w++) m = fmaxf(m, mml[(w * 16 + row) * 2]);
         float denom = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int w = 0; w < 4; w++) {
+        for (int w = 0; w < 4; w++) {                     // in warp order
             const float mw = mml[(w * 16 + row) * 2];
             const float f = mw == -INFINITY ? 0.f : fast_exp2(mw - m);
-            fac[row * 4 + w] = f;
             denom += mml[(w * 16 + row) * 2 + 1] * f;
+            const float4 v = *(const float4 *)(mo + ((size_t)w * 16 + row) * D + 4 * c4);
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
         }
-        fac[64 + row] = m;
-        fac[80 + row] = denom;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < rows * D; idx += ADT_THREADS) {
-        const int row = idx / D, col = idx % D;
-        float acc = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; w++) acc += mo[((size_t)w * 16 + row) * D + col] * fac[row * 4 + w];
-        const float denom = fac[80 + row];
         const int tok = t0 + row / r, head = g * r + row % r;
         const size_t th = (size_t)tok * p.H + head;
         if (p.splits > 1) {
-            p.part_o[(th * p.splits + split) * D + col] = acc;
-            if (col == 0) *(float2 *)(p.part_ml + (th * p.splits + split) * 2) = make_float2(fac[64 + row], denom);
+            *(float4 *)(p.part_o + (th * p.splits + split) * D + 4 * c4) = acc;
+            if (c4 == 0) *(float2 *)(p.part_ml + (th * p.splits + split) * 2) = make_float2(m, denom);
         } else {
-            p.out[th * D + col] = __float2bfloat16_rn(denom > 0.f ? acc / denom : 0.f);
+            const float inv = denom > 0.f ? 1.0f / denom : 0.f;       // (as the merge of key splits normalises)
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+            *(uint2 *)(p.out + th * D + 4 * c4) = make_uint2(*(const uint32_t *)&lo, *(const uint32_t *)&hi);
         }
     }
     if (p.splits > 1 && p.counters) {
