@@ -1,4 +1,4 @@
-// Attention over the paged cache for long prompt portions on tcgen05, two query tiles per CTA (head_dim 128, bf16).
+// Attention over the paged cache for long prompt portions on tcgen05, two query tiles per CTA (head_dim 64 or 128, bf16).
 //
 // The arithmetic is that of attention_tc.cu (src/model.c:499-528 of the reference: scores = q.k * scale, causal
 // and window masks by absolute position, float32 softmax, weighted values).  What differs is how the softmax and
@@ -12,7 +12,8 @@
 //     by more than 2^8 since it was set (weights stay below 2^8, well inside bfloat16's and float32's range; sum
 //     and output carry the same factor, which cancels in the end); only then is O rescaled in TMEM
 //     (tcgen05.ld, multiply, tcgen05.st), by the row's own thread, between two products into it.
-// TMEM: S0, S1, O0, O1, 128 columns each.  Shared memory: Q0, Q1, P0, P1, one K tile and two V tiles (32 KB each):
+// TMEM: S0, S1 (128 columns each), O0, O1 (head_dim columns each).  Shared memory: Q0, Q1, P0, P1 (32 KB each), one K tile
+// and two V tiles (128 keys of head_dim elements: 16 or 32 KB):
 // K is free again once both S products of a step are done, early in the step, and is refilled while the softmax
 // runs; V is in use until the step's last product, so the next one is fetched into the other buffer meanwhile.
 // Every barrier wait is bounded (HFB_ERR_WAIT, TMEM freed; tc_ptx.cuh).
@@ -27,9 +28,9 @@ namespace hfb {
 int *error_word();
 int tensor_map(const void *ptr, int rows, int cols, int box_rows, CUtensorMap *out);
 
-constexpr int U_ROWS = 128, U_KEYS = 128, U_D = 128;
+constexpr int U_ROWS = 128, U_KEYS = 128;
 constexpr uint32_t U_SUB = 128 * 64 * 2;            // one swizzled sub-tile: 128 rows of 64 bf16
-constexpr uint32_t U_TILE = 2 * U_SUB;              // a [128 x 128] bf16 operand: two sub-tiles
+constexpr uint32_t U_TILE = 2 * U_SUB;              // a [128 x 128] bf16 operand (P; Q, K, V at head_dim 128): two sub-tiles
 constexpr int U_THREADS = 320;                     // TMA warp, MMA warp, four softmax warps per query tile
 constexpr int U_TMEM_COLS = 512;
 constexpr float U_TAU = 8.0f;                       // log2 of how far a row's maximum may outgrow its reference
@@ -65,6 +66,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *v)
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+template <int D>
 __global__ void __launch_bounds__(U_THREADS, 1)
 attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnTc2Params p, int *err)
 {
@@ -72,13 +74,15 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t sQ = base, sP = base + 2 * U_TILE, sK = base + 4 * U_TILE, sV = base + 5 * U_TILE;
-    const uint32_t bars = base + 7 * U_TILE;         // V has two stages: sV, sV + U_TILE
+    constexpr uint32_t HT = (D / 64) * U_SUB;        // a [128 x D] bf16 operand: Q, K or V
+    constexpr uint32_t U_BARS = 2 * U_TILE + 5 * HT; // bytes of the tiles in front of the barriers
+    const uint32_t sQ = base, sK = base + 2 * HT, sV = base + 3 * HT, sP = base + 5 * HT;
+    const uint32_t bars = base + U_BARS;             // V has two stages: sV, sV + HT
     // per query tile i: q_ready + 8i, s_full + 8i, p_ready + 8i, pv_done + 8i; per V stage s: v_full + 8s, v_empty + 8s
     const uint32_t q_ready = bars, s_full = bars + 16, p_ready = bars + 32, pv_done = bars + 48;
     const uint32_t k_full = bars + 64, k_empty = bars + 72, v_full = bars + 80, v_empty = bars + 96;
     const uint32_t s_free = bars + 112;              // + 8i: tile i's scores have been read out of TMEM
-    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen + 7 * U_TILE + 128);
+    volatile uint32_t *tmem_slot = (volatile uint32_t *)(gen + U_BARS + 128);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -151,16 +155,16 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                     for (int kv = 0; kv < 2 && ok; kv++) {
                         const uint32_t st = gs & 1;                                   // V's stage
                         const uint32_t full = kv ? v_full + 8 * st : k_full, empty = kv ? v_empty + 8 * st : k_empty;
-                        const uint32_t dst = kv ? sV + st * U_TILE : sK;
+                        const uint32_t dst = kv ? sV + st * HT : sK;
                         if (lane == 0) {
                             ok = mbar_wait(empty, kv ? (((gs >> 1) & 1) ^ 1) : ((gs & 1) ^ 1), abort_flag, err);
-                            if (ok) mbar_arrive_expect_tx(full, U_TILE);
+                            if (ok) mbar_arrive_expect_tx(full, HT);
                         }
                         ok = __shfl_sync(0xffffffffu, ok, 0);
-                        const int pg = lane >> 1, half = lane & 1;
+                        const int pg = D == 128 ? lane >> 1 : lane, half = D == 128 ? lane & 1 : 0;
                         const int row = __shfl_sync(0xffffffffu, my_row, t * pages + min(pg, pages - 1));
                         if (ok && pg < pages)
-                            tma_load_2d(dst + (uint32_t)pg * bs * 128u + half * U_SUB, kv ? &map_v : &map_k, it.g * U_D + half * 64, row, full);
+                            tma_load_2d(dst + (uint32_t)pg * bs * 128u + half * U_SUB, kv ? &map_v : &map_k, it.g * D + half * 64, row, full);
                     }
                 }
             }
@@ -168,32 +172,33 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     } else if (warp == 1) {
         // ---- tensor-core issue ------------------------------------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_s = bf16_idesc(U_ROWS, U_KEYS, false), idesc_pv = bf16_idesc(U_ROWS, U_D, true);
+            constexpr uint32_t idesc_s = bf16_idesc(U_ROWS, U_KEYS, false), idesc_pv = bf16_idesc(U_ROWS, D, true);
             // Every operand sits at a fixed place, so all descriptors are made once: a single thread issues 32
             // products per step, and what it computes between two of them is time the tensor core waits.
-            uint64_t dq[2][U_D / 16], dk[U_D / 16], dp[2][U_KEYS / 16], dv[U_KEYS / 16];
+            uint64_t dq[2][D / 16], dk[D / 16], dp[2][U_KEYS / 16], dv[U_KEYS / 16];
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
                 const uint32_t o = (uint32_t)(kk >> 2) * U_SUB + (uint32_t)(kk & 3) * 32u;
-                dk[kk] = sw128_desc(sK + o);
 #pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    dq[i][kk] = sw128_desc(sQ + i * U_TILE + o);
-                    dp[i][kk] = sw128_desc(sP + i * U_TILE + o);
+                for (int i = 0; i < 2; i++) dp[i][kk] = sw128_desc(sP + i * U_TILE + o);
+                if (kk < D / 16) {
+                    dk[kk] = sw128_desc(sK + o);
+#pragma unroll
+                    for (int i = 0; i < 2; i++) dq[i][kk] = sw128_desc(sQ + i * HT + o);
                 }
-                dv[kk] = sw128_desc_mn(sV + (uint32_t)kk * 2048u, U_SUB);                // 16 keys further; both halves of the head
+                dv[kk] = sw128_desc_mn(sV + (uint32_t)kk * 2048u, U_SUB);                // 16 keys further; every 64-wide piece of the head
             }
             const uint32_t tS0 = tmem_base, tO0 = tmem_base + 256;
             auto issue_s = [&](int i) {
 #pragma unroll
-                for (int kk = 0; kk < U_D / 16; kk++)
+                for (int kk = 0; kk < D / 16; kk++)
                     tc_mma_bf16(tS0 + i * 128, i ? dq[1][kk] : dq[0][kk], dk[kk], idesc_s, kk > 0 ? 1u : 0u);
                 tc_commit(s_full + 8 * i);
             };
             auto issue_pv = [&](int i, bool accumulate, uint64_t v_stage) {      // v_stage: 0 or the second V buffer
 #pragma unroll
                 for (int kk = 0; kk < U_KEYS / 16; kk++)
-                    tc_mma_bf16(tO0 + i * 128, i ? dp[1][kk] : dp[0][kk], dv[kk] + v_stage, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+                    tc_mma_bf16(tO0 + i * D, i ? dp[1][kk] : dp[0][kk], dv[kk] + v_stage, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
                 tc_commit(pv_done + 8 * i);
             };
             bool ok = true;
@@ -215,7 +220,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 }
                 for (int j = 0; j < it.n_kt && ok; j++, gs++) {
                     const uint32_t st = gs & 1;
-                    const uint64_t v_stage = st ? (uint64_t)(U_TILE >> 4) : 0;      // added to a descriptor's address field
+                    const uint64_t v_stage = st ? (uint64_t)(HT >> 4) : 0;          // added to a descriptor's address field
                     // The scores of step j + 1 are queued as soon as those of step j have left TMEM for the softmax
                     // threads' registers, long before their exponentials are done: a tile's softmax warps then go
                     // from one step to the next without waiting for the tensor core.
@@ -251,7 +256,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
         const int row = (warp & 3) * 32 + lane;                          // TMEM lane = row; a warp reads its own quarter
         const int tl = row / r, hl = row % r;
         const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-        const uint32_t tS = lane_base + i * 128, tO = lane_base + 256 + i * 128;
+        const uint32_t tS = lane_base + i * 128, tO = lane_base + 256 + i * D;
         uint32_t g_mine = 0;                                             // this tile's steps so far
         bool ok = true;
         for (int round = 0; round < n_rounds && ok; round++) {
@@ -260,14 +265,14 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
             const int n_mine = i ? it.n_kt1 : it.n_kt0, nt_mine = i ? it.nt1 : it.nt0, t_first = it.t0 + i * p.per;
             if (n_mine <= 0) continue;
             const bool valid = tl < nt_mine;
-            const size_t th = ((size_t)(t_first + (valid ? tl : 0)) * p.H + it.g * r + hl) * U_D;
+            const size_t th = ((size_t)(t_first + (valid ? tl : 0)) * p.H + it.g * r + hl) * D;
             {
                 // the tile's products of the item before are done (their scores have all been waited for)
                 const uint4 *src = (const uint4 *)(p.q + th);
 #pragma unroll
-                for (int c = 0; c < 16; c++) {
+                for (int c = 0; c < D / 8; c++) {
                     uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + i * U_TILE + u_sw_off(row, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(sQ + i * HT + u_sw_off(row, c)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
@@ -333,7 +338,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                     tc_fence_after();
                     if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-                        for (int c = 0; c < 8; c++) {
+                        for (int c = 0; c < D / 16; c++) {
                             uint32_t ov[16];
                             tmem_ld16(tO + 16 * c, ov);
                             tmem_wait_ld();
@@ -360,7 +365,7 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
                 uint4 *dst = (uint4 *)(p.out + th);
 #pragma unroll 1
-                for (int c = 0; c < 8; c += 4) {                      // four reads of 16 columns under way together
+                for (int c = 0; c < D / 16; c += 4) {                 // four reads of 16 columns under way together
                     uint32_t ov[64];
 #pragma unroll
                     for (int u = 0; u < 4; u++) tmem_ld16(tO + 16 * (c + u), ov + 16 * u);   // all lanes take part, valid row or not
@@ -395,11 +400,26 @@ attention_tc2_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
     }
 }
 
+template <int D>
+static int launch_tc2(const CUtensorMap &mk, const CUtensorMap &mv, const AttnTc2Params &p, int grid, cudaStream_t st)
+{
+    constexpr uint32_t smem = 1024 + 2 * U_TILE + 5 * (D / 64) * U_SUB + 160;
+    static_assert(smem <= 227 * 1024, "the tiles do not fit");
+    static bool configured[64] = {false};                 // (the opt-in is a property of the function on one device)
+    if (!configured[current_device()]) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_tc2: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured[current_device()] = true;
+    }
+    g_launch_err = launch_pdl(attention_tc2_kernel<D>, dim3(grid), dim3(U_THREADS), smem, st, mk, mv, p, error_word());
+    return check_pdl_launch(g_launch_err, "attention_tc2");
+}
+
 }  // namespace hfb
 
 using namespace hfb;
 
-// Attention of long prompt portions with two query tiles per CTA: bfloat16, head_dim 128, block sizes 8..128 that
+// Attention of long prompt portions with two query tiles per CTA: bfloat16, head_dim 64 or 128, block sizes 8..128 that
 // divide 128, at most 128 query heads per key/value head.  Tiles (tile_seq, tile_t0, tile_nt) hold at most
 // 2 * (128 / (H/G)) consecutive tokens of one request each.
 extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
@@ -408,7 +428,7 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
                                  float scale, void *out, int T, int H, int G, int d, hfb_stream s)
 {
     if (n_tiles <= 0) return HFB_OK;
-    if (d != U_D) return fail(HFB_ENOTSUP, "attention_tc2: head_dim %d (128 only)", d);
+    if (d != 64 && d != 128) return fail(HFB_ENOTSUP, "attention_tc2: head_dim %d (64 and 128 only)", d);
     if (G <= 0 || H % G || H / G > U_ROWS) return fail(HFB_ENOTSUP, "attention_tc2: %d heads over %d key/value heads", H, G);
     if (block_size < 8 || block_size > U_KEYS || U_KEYS % block_size) return fail(HFB_ENOTSUP, "attention_tc2: block size %d (8..128, dividing 128)", block_size);
     if (num_pages * block_size >= (1ll << 31) - U_KEYS) return fail(HFB_ENOTSUP, "attention_tc2: cache too large for 32-bit coordinates");
@@ -428,18 +448,10 @@ extern "C" int hfb_attention_tc2(const void *q, const void *k_cache, const void 
     p.per = U_ROWS / (H / G);
     p.n_tiles = n_tiles;
     p.scale_log2 = scale * 1.4426950408889634f;
-    constexpr uint32_t smem = 1024 + 7 * U_TILE + 160;
-    static bool configured[64] = {false};                 // (the opt-in is a property of the function on one device)
-    if (!configured[current_device()]) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return fail(HFB_ECUDA, "attention_tc2: cannot opt in to %u bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        configured[current_device()] = true;
-    }
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long items = (long long)n_tiles * G;
     const int grid = (int)(items < sms ? items : (sms > 0 ? sms : 1));      // one CTA per SM walks its share of the items
-    g_launch_err = launch_pdl(attention_tc2_kernel, dim3(grid), dim3(U_THREADS), smem, (cudaStream_t)s, mk, mv, p, error_word());
-    return check_pdl_launch(g_launch_err, "attention_tc2");
+    return d == 128 ? launch_tc2<128>(mk, mv, p, grid, (cudaStream_t)s) : launch_tc2<64>(mk, mv, p, grid, (cudaStream_t)s);
 }

@@ -156,12 +156,14 @@ class NativeBackend:
                 if seq is None:
                     return None
                 return seq, tile_arrays[h + ".t0"], tile_arrays[h + ".nt"], seq.shape[0]
-            if (not decode and self.attention_tc and d == 128 and meta.block_size >= 8 and 128 % meta.block_size == 0
+            if (not decode and self.attention_tc and meta.block_size >= 8 and 128 % meta.block_size == 0
                     and H // G <= 128):
                 # two 128-row tiles per CTA once there is an item for every SM: it does more per key fetched and overlaps
-                # softmax and products, but has half as many items to spread
+                # softmax and products, but has half as many items to spread.  Head size 64 has this form only, and
+                # takes it from half as many items on (what it falls back to is the mma.sync kernel, three times slower)
                 tiling = tiles(H // G, 16) if self.attention_tc2 else None
-                if tiling is not None and (tiling[3] * G >= self.tc2_min_rounds * self.sm_count):
+                enough = self.tc2_min_rounds * self.sm_count * (1.0 if d == 128 else 0.5)
+                if tiling is not None and tiling[3] * G >= enough:
                     tile_seq, tile_t0, tile_nt, n_tiles = tiling
                     self._check(self.lib.hfb_attention_tc2(
                         _p(q), _p(k_cache), _p(v_cache), _p(meta.block_table), c_int(meta.max_blocks), _p(ctx.positions),
@@ -169,7 +171,7 @@ class NativeBackend:
                         c_int64(k_cache.shape[0]), c_int(window), c_float(scale), _p(out), c_int(T), c_int(H), c_int(G),
                         c_int(d), self._stream()), "attention_tc2")
                     return
-                tiling = tiles(H // G, 8)                    # tiles of 128 rows, as the 8-warp kernel's
+                tiling = tiles(H // G, 8) if d == 128 else None      # tiles of 128 rows, as the 8-warp kernel's
                 if tiling is not None:
                     tile_seq, tile_t0, tile_nt, n_tiles = tiling
                     self._check(self.lib.hfb_attention_tc(

@@ -441,10 +441,12 @@ def test_linear_rope_kv_fused(geom):
     kernels.check_device_errors()
 
 
-@pytest.mark.parametrize("geom", [(28, 4, 128, 16), (4, 4, 128, 8), (16, 1, 128, 128), (5, 5, 128, 32)])
+@pytest.mark.parametrize("geom", [(28, 4, 128, 16), (4, 4, 128, 8), (16, 1, 128, 128), (5, 5, 128, 32),
+                                  (14, 2, 64, 16), (6, 3, 64, 8), (8, 8, 64, 64), (3, 1, 64, 128)])
 def test_attention_tensor_core_prompt_portions(geom, both_tc_forms):
-    """The tcgen05 attention kernel (head_dim 128): long portions over long histories, several requests, windows,
-    in both forms (two query tiles per CTA, one), against the torch reference and against the mma.sync kernel."""
+    """The tcgen05 attention kernels (head_dim 128 in both forms, two query tiles per CTA and one; head_dim 64 in the
+    first): long portions over long histories, several requests, windows, against the torch reference and against
+    the mma.sync kernel."""
     from hfcpu_b200 import kernels
     H, G, d, bs = geom
     b = kernels.backend()
@@ -472,11 +474,12 @@ def test_attention_tensor_core_prompt_portions(geom, both_tc_forms):
     kernels.check_device_errors()
 
 
+@pytest.mark.parametrize("geom", [(28, 4, 128, 16), (14, 2, 64, 16)])
 @pytest.mark.parametrize("lens_q", [[1, 1], [1, 300]])
-def test_attention_long_context_far_keys(lens_q, both_tc_forms):
+def test_attention_long_context_far_keys(lens_q, geom, both_tc_forms):
     """33,000 cached keys: a decode token (the keys split over many CTAs) and a 300-token portion (hundreds of
     tiles per query tile), with one key made to stand out near the start, in the middle and at the very end."""
-    H, G, d, bs = 28, 4, 128, 16
+    H, G, d, bs = geom
     lens_kv = [700, 33000]
     for key_pos in (3, 16384, 32999 - (lens_q[1] - 1)):
         q_off = 0 if key_pos > 30000 else lens_q[1] - 1
