@@ -129,7 +129,7 @@ int hfb_attention_tc(const void *q, const void *k_cache, const void *v_cache, co
                      float scale, void *out, int T, int H, int G, int d, hfb_stream s);
 
 /* The same with two 128-row tiles per CTA (tiles hold at most 2 * (128 / (H/G)) tokens): the softmax of one tile
- * runs while the tensor core works on the other; the running output stays in TMEM. */
+ * runs while the tensor core works on the other; the running output stays in TMEM.  head_dim 64 or 128. */
 int hfb_attention_tc2(const void *q, const void *k_cache, const void *v_cache, const int32_t *block_table,
                       int max_blocks, const int32_t *positions, const int32_t *tile_seq, const int32_t *tile_t0,
                       const int32_t *tile_nt, int n_tiles, int block_size, int64_t num_pages, int window, float scale,
