@@ -60,7 +60,7 @@ class NativeBackend:
         self.attention_tc = os.environ.get("HFB_ATTN_TC", "1") != "0"     # tcgen05 attention for prompt portions
         self.attention_tc2 = os.environ.get("HFB_ATTN_TC2", "1") != "0"   # its form with two query tiles per CTA
         # the two-tile form takes over once there is a work item for every SM this many times over (tests set 0)
-        self.tc2_min_rounds = 1.0
+        self.tc2_min_rounds = 0.55                # items per SM from which head size 128 takes the two-tile attention kernel
         self.decode_ctas_per_sm = 2               # CTAs of the decode attention kernel per SM, over all requests' splits
         self.decode_stages = 3                    # tiles of 64 keys in flight per CTA (measured again: 1 or 3 CTAs, 2 or 4 stages lose 0.4-7 %)
         self.sm_count = torch.cuda.get_device_properties(0).multi_processor_count
@@ -158,11 +158,12 @@ class NativeBackend:
                 return seq, tile_arrays[h + ".t0"], tile_arrays[h + ".nt"], seq.shape[0]
             if (not decode and self.attention_tc and meta.block_size >= 8 and 128 % meta.block_size == 0
                     and H // G <= 128):
-                # two 128-row tiles per CTA once there is an item for every SM: it does more per key fetched and overlaps
-                # softmax and products, but has half as many items to spread.  Head size 64 has this form only, and
-                # takes it from half as many items on (what it falls back to is the mma.sync kernel, three times slower)
+                # two 128-row tiles per CTA once there are items for more than half of the SMs: it does more per key
+                # fetched and overlaps softmax and products, but has half as many items to spread (28 heads over 4: 60
+                # items 22.7 against 17.9 us, 116 items 32.3 against 37.9 us; 40 over 8: 88 items 23.0 against 26.7 us).
+                # Head size 64 has this form only and always takes it (16 items: 14.6 us against 17.7 us of mma.sync)
                 tiling = tiles(H // G, 16) if self.attention_tc2 else None
-                enough = self.tc2_min_rounds * self.sm_count * (1.0 if d == 128 else 0.5)
+                enough = self.tc2_min_rounds * self.sm_count if d == 128 else 0
                 if tiling is not None and tiling[3] * G >= enough:
                     tile_seq, tile_t0, tile_nt, n_tiles = tiling
                     self._check(self.lib.hfb_attention_tc2(
