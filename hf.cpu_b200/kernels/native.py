@@ -205,7 +205,7 @@ class NativeBackend:
                 scratch = ctx.buf("attn_scratch", (need,), torch.uint8) if need else None
                 if decode_tma:
                     # the keys and values come by TMA, a warp of their own keeps them coming; the CTA that stores a
-                    # tile's last split merges the splits (HFB_FUSE_TAILS=0: a second kernel does)
+                    # tile's last split merges the splits (merge_in_kernel off: a second kernel does)
                     counters = None
                     if self.merge_in_kernel and splits > 1 and n_tiles * G <= 4096:
                         if self._counters is None or self._counters.device != q.device:
