@@ -43,20 +43,30 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._bufs: Dict[tuple, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}  # (name, dtype, shape) -> the view handed out (asked for at every call of every step)
         self._retired: List[torch.Tensor] = []      # outgrown buffers stay alive: captured graphs may point at them
 
     def get(self, name, shape, dtype) -> torch.Tensor:
+        shape = tuple(int(s) for s in shape)
+        vkey = (name, dtype, shape)
+        v = self._views.get(vkey)
+        if v is not None:
+            return v
         n = 1
         for s in shape:
-            n *= int(s)
+            n *= s
         key = (name, dtype)
         b = self._bufs.get(key)
         if b is None or b.numel() < n:
             if b is not None:
                 self._retired.append(b)
+                self._views = {k: w for k, w in self._views.items() if k[:2] != key}      # they showed the old buffer
             b = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[key] = b
-        return b[:n].view(*shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        v = self._views[vkey] = b[:n].view(*shape)
+        return v
 
 
 @dataclass
