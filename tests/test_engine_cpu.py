@@ -70,3 +70,22 @@ def test_step_rejects_bad_entries(tiny_folders, emu):
     assert eng.length("a") == 0 and eng.cache.pages_in_use() == 0
     eng.step([StepEntry("a", [1] * 64, [])])
     assert eng.length("a") == 64
+
+
+def test_scratch_buffers_keep_and_drop_their_views():
+    """A named scratch buffer hands out the same view for the same shape, a buffer that grew hands out views of the
+    new storage only, and different shapes of one name share the storage."""
+    import torch
+    from hfcpu_b200.engine.step import Workspace
+    ws = Workspace(torch.device("cpu"))
+    a = ws.get("x", (4, 8), torch.float32)
+    assert ws.get("x", (4, 8), torch.float32) is a and a.shape == (4, 8)
+    b = ws.get("x", (2, 8), torch.float32)
+    assert b.data_ptr() == a.data_ptr() and b.shape == (2, 8)
+    big = ws.get("x", (16, 8), torch.float32)
+    assert big.data_ptr() != a.data_ptr()
+    again = ws.get("x", (4, 8), torch.float32)
+    assert again.data_ptr() == big.data_ptr() and again is not a
+    other = ws.get("x", (4, 8), torch.bfloat16)
+    assert other.dtype == torch.bfloat16 and other.data_ptr() != again.data_ptr()
+    assert a.shape == (4, 8)                                # the outgrown buffer stays alive for graphs that point at it
