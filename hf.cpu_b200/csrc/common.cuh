@@ -57,8 +57,7 @@ __device__ __forceinline__ float warp_max(float v)
 // Programmatic dependent launch.  Every kernel of the forward pass is launched so that it may start while the
 // kernel before it is still running; it does what needs none of that kernel's results (set-up, and in the
 // products the first loads of the weights), then waits for the predecessor to finish, then lets its own
-// successor start, so that never more than one kernel runs ahead.  (Letting the successor start on entry, so
-// that the chain runs further ahead, was measured: no faster.)
+// successor start, so that one kernel runs ahead (two behind a short kernel: see pdl_entry below).
 //
 // A build with -DHFB_TRACE (developers only) logs, from thread 0 of block 0 of each kernel, the time the block
 // started and the time its wait for the predecessor returned; `hfb_trace_take` reads the log.
@@ -123,6 +122,14 @@ namespace { struct TraceRegistration { TraceRegistration() { trace_register(trac
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); HFB_TRACE_READY(); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_sync() { pdl_wait(); pdl_trigger(); }
+// The short kernels between the products (norms, sums of split-K partials, rotation, embedding, arg-max) release their
+// successor when they start, not when their own wait returns: the product behind a short kernel is then resident a
+// few microseconds earlier and its weight tiles are on their way while the short kernel still waits and works (a
+// successor's blocks are placed only when all of this kernel's have started, so they never take their place; what a
+// kernel does before its wait depends on nothing the kernels in front write).  Batch 8: 3.098 -> 3.055 ms a step.  The
+// products and the attention kernels release at their wait: released at entry too, the step was slower.
+__device__ __forceinline__ void pdl_entry() { pdl_trigger(); }
+__device__ __forceinline__ void pdl_sync_small() { pdl_wait(); }
 
 // One rotation pair (src/model.c:587-601): products and sums each rounded to float32 on their own, so that every kernel
 // that rotates gives the same bits (the compiler is free to contract a * c - b * s into a fused multiply-add in one

@@ -10,7 +10,8 @@ int *error_word();
 __global__ void embed_kernel(const int32_t *ids, const void *table, int dt, float *out, int V, int E, int *err)
 {
     HFB_TRACE_ENTRY(7);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= V) {
@@ -40,7 +41,8 @@ __global__ void rmsnorm_kernel(const float *x, const void *w, int w_dt, float ep
                                const int32_t *rows, int E)
 {
     HFB_TRACE_ENTRY(15);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     int m = blockIdx.x;
     const float *xr = x + (size_t)(rows ? rows[m] : m) * E;
     float ss = 0.f;
@@ -66,7 +68,8 @@ template <typename TW, typename TO>
 __global__ void rmsnorm_vec_kernel(const float *x, const TW *w, float eps, TO *out, const int32_t *rows, int E)
 {
     HFB_TRACE_ENTRY(6);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     int m = blockIdx.x;
     const float4 *xr = (const float4 *)(x + (size_t)(rows ? rows[m] : m) * E);
     const int E4 = E >> 2;
@@ -103,7 +106,8 @@ template <typename TW, typename TO, int PER>
 __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(const float *x, const TW *w, float eps, TO *out, const int32_t *rows, int E)
 {
     HFB_TRACE_ENTRY(6);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     const int m = blockIdx.x;
     const float4 *xr = (const float4 *)(x + (size_t)(rows ? rows[m] : m) * E);
     const int E4 = E >> 2;
@@ -149,7 +153,8 @@ __global__ void rope_kv_write_kernel(const T *qkv, const float *cos_sin, int n_r
                                      T *v_cache, long long cache_slots, int H, int G, int d, int *err)
 {
     HFB_TRACE_ENTRY(16);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     int t = blockIdx.x, head = blockIdx.y;
     const T *src = qkv + (size_t)t * (H + 2 * G) * d + (size_t)head * d;
     T *dst;
@@ -191,7 +196,8 @@ __global__ void rope_kv_write_vec_kernel(const T *qkv, const float *cos_sin, int
                                          T *v_cache, long long cache_slots, int H, int G, int d, int *err)
 {
     HFB_TRACE_ENTRY(16);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     constexpr int VEC = 16 / sizeof(T);
     struct alignas(16) Pack { T e[VEC]; };
     const int t = blockIdx.x;
@@ -239,7 +245,8 @@ template <typename T>
 __global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total, int interleaved)
 {
     HFB_TRACE_ENTRY(14);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     size_t t = i / F;
@@ -252,7 +259,7 @@ __global__ void swiglu_kernel(const T *gu, T *out, int F, size_t total, int inte
 // ---- arg-max, the lowest index wins ties (src/sample.c:72-77) ---------------------------------
 __global__ void argmax_kernel(const float *logits, int32_t *out, int V)
 {
-    pdl_sync();
+    pdl_sync_small();
     const float *row = logits + (size_t)blockIdx.x * V;
     float best = 0.f;
     int bi = -1;

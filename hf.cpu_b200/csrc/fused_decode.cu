@@ -17,7 +17,8 @@ __global__ void reduce_residual_norm_kernel(const float *partial, int splits, in
                                             float *residual, const void *w, int w_dt, float eps, void *xn, int xn_dt)
 {
     HFB_TRACE_ENTRY(11);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     const int m = blockIdx.x;
     const size_t MN = (size_t)M * N;
     float *res = residual + (size_t)m * N;
@@ -57,6 +58,7 @@ reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, 
                                 float *residual, const TW *w, float eps, TO *xn)
 {
     HFB_TRACE_ENTRY(5);
+    pdl_entry();
     const int m = blockIdx.x, N4 = N >> 2;
     // the norm's weights and the bias do not come from the kernel in front: fetch them while it finishes
     float4 wv[RRN_VEC], bv[RRN_VEC];
@@ -70,7 +72,7 @@ reduce_residual_norm_vec_kernel(const float *partial, int splits, int M, int N, 
                                           load_any(bias, bias_dt, 4 * i + 2), load_any(bias, bias_dt, 4 * i + 3));
         }
     }
-    pdl_sync();
+    pdl_sync_small();
     const size_t MN4 = ((size_t)M * N) >> 2;
     const float4 *part = (const float4 *)partial + (size_t)m * N4;
     float4 *res = (float4 *)(residual + (size_t)m * N);
@@ -135,6 +137,7 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
                                       int H, int G, int d, int *err)
 {
     HFB_TRACE_ENTRY(2);
+    pdl_entry();
     // The slot, the position, the rotation's cosines and sines and the bias are inputs of the step or constants:
     // they are fetched before the wait for the product in front, whose partial sums are read after it.
     const int t = blockIdx.x, head = blockIdx.y;
@@ -164,7 +167,7 @@ __global__ void reduce_rope_kv_kernel(const float *partial, int splits, int Tn, 
     }
     const float b0 = (bias && (int)threadIdx.x < d) ? load_any(bias, bias_dt, (size_t)head * d + threadIdx.x) : 0.f;
     const float b1 = (bias && (int)threadIdx.x + half < d) ? load_any(bias, bias_dt, (size_t)head * d + threadIdx.x + half) : 0.f;
-    pdl_sync();
+    pdl_sync_small();
     if (!live) return;
     auto value = [&](int i) {
         float v = 0.f;
@@ -209,7 +212,8 @@ __device__ __forceinline__ void argmax_take(float &best, int &bi, float v, int i
 __global__ void __launch_bounds__(256) argmax_chunks_kernel(const float *logits, int V, int chunk, float *best_v, int32_t *best_i)
 {
     HFB_TRACE_ENTRY(9);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     const int row = blockIdx.y, c = blockIdx.x;
     const float *p = logits + (size_t)row * V;
     const int lo = c * chunk, hi = min(V, lo + chunk);
@@ -253,7 +257,8 @@ __global__ void __launch_bounds__(256) argmax_chunks_kernel(const float *logits,
 __global__ void argmax_final_kernel(const float *best_v, const int32_t *best_i, int chunks, int32_t *out)
 {
     HFB_TRACE_ENTRY(10);
-    pdl_sync();
+    pdl_entry();
+    pdl_sync_small();
     const int row = blockIdx.x;
     float best = 0.f;
     int bi = -1;
